@@ -1,0 +1,204 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm, rotary encoding fused
+// with the paged cache write, SwiGLU.  All arithmetic is float32; storage is float32
+// or bfloat16.  Formulas follow the reference's scalar kernels
+// (crates/kernels/src/scalar.rs:143-156 rms, :167-189 rope; crates/kernels/src/math.rs:8-10 silu).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :] as float32 (the residual stream is float32 in every mode).
+// An id outside [0, V) writes zeros and raises the error flag: never a wild read.
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int E, int V, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < V;
+  if (!ok && threadIdx.x == 0) atomicExch(err, 1);
+  const T* row = table + (size_t)(ok ? id : 0) * E;
+  float* o = out + (size_t)t * E;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = ok ? to_f32<T>(row[i]) : 0.f;
+}
+
+FERRUM_API int ferrum_embedding(const void* table, int dtype, const int* ids, float* out, int n_tokens,
+                                int E, int V, int* err_flag, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_tokens >= 0 && E > 0 && V > 0, "embedding: bad sizes T=%d E=%d V=%d", n_tokens, E, V);
+  if (n_tokens == 0) return 0;
+  const int threads = E >= 1024 ? 256 : 128;
+  if (dtype == FERRUM_F32)
+    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, E, V, err_flag);
+  else if (dtype == FERRUM_BF16)
+    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, E, V, err_flag);
+  else
+    FERRUM_CHECK_ARG(false, "embedding: unknown dtype code %d", dtype);
+  FERRUM_CHECK_LAUNCH("embedding");
+  return 0;
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// out[r, i] = x[src(r), i] * rsqrt(mean(x^2) + eps) * w[i]; src(r) = rows ? rows[r] : r.
+// One block per row, the same reduction tree for every row.
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               TOut* __restrict__ out, const int* __restrict__ rows, int E, float eps) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * E;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)E + eps);
+  TOut* o = out + (size_t)r * E;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * inv * w[i]);
+}
+
+FERRUM_API int ferrum_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows,
+                              int n_rows, int E, float eps, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_rows >= 0 && E > 0, "rmsnorm: bad sizes rows=%d E=%d", n_rows, E);
+  FERRUM_CHECK_ARG(eps > 0.f, "rmsnorm: eps must be positive");
+  if (n_rows == 0) return 0;
+  const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
+  if (out_dtype == FERRUM_F32)
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, (float*)out, rows, E, eps);
+  else if (out_dtype == FERRUM_BF16)
+    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, E, eps);
+  else
+    FERRUM_CHECK_ARG(false, "rmsnorm: unknown dtype code %d", out_dtype);
+  FERRUM_CHECK_LAUNCH("rmsnorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------- rotary + cache write
+// qkv: [T, ld] rows of (q: Hq*D | k: Hkv*D | v: Hkv*D).  q is rotated in place; k is
+// rotated and stored, v is stored, both at page block_table[req][pos / ps], row pos % ps.
+// A page holds K[Hkv][ps][D] then V[Hkv][ps][D].  cos_sin: [n_pos, R/2, 2] float32.
+// pairing 0: (2i, 2i+1); pairing 1: (i, i + R/2).  Dimensions R..D are copied unchanged.
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
+                                  const int* __restrict__ req_of_token, const int* __restrict__ block_table,
+                                  int table_width, const float* __restrict__ cos_sin, int n_pos,
+                                  T* __restrict__ kv_plane, long long page_stride, int page_size, int Hq,
+                                  int Hkv, int D, int R, int pairing, int write_kv, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = R >> 1;
+  T* row = qkv + (size_t)t * ld;
+  const bool pos_ok = pos >= 0 && (half == 0 || pos < n_pos);
+  if (!pos_ok) {
+    if (threadIdx.x == 0) atomicExch(err, 2);
+    return;
+  }
+  const float* cs = cos_sin + (size_t)pos * half * 2;
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (write_kv) {
+    const int lp = pos / page_size;
+    if (lp >= table_width) {
+      if (threadIdx.x == 0) atomicExch(err, 3);
+      return;
+    }
+    const int page = block_table[(size_t)req_of_token[t] * table_width + lp];
+    if (page < 0) {
+      if (threadIdx.x == 0) atomicExch(err, 4);
+      return;
+    }
+    kdst = kv_plane + (size_t)page * page_stride + (size_t)(pos % page_size) * D;
+    vdst = kdst + (size_t)Hkv * page_size * D;
+  }
+  const int hd2 = D >> 1;  // work items per head: D/2 "pairs" (rotated below `half`, copied above)
+  // q heads then k heads
+  for (int w = threadIdx.x; w < (Hq + Hkv) * hd2; w += blockDim.x) {
+    const int h = w / hd2, i = w % hd2;
+    T* src = row + (size_t)h * D;
+    int ia, ib;
+    float a, b;
+    if (i < half) {
+      ia = pairing == 0 ? 2 * i : i;
+      ib = pairing == 0 ? 2 * i + 1 : i + half;
+      const float x0 = to_f32<T>(src[ia]), x1 = to_f32<T>(src[ib]);
+      const float c = cs[2 * i], s = cs[2 * i + 1];
+      a = x0 * c - x1 * s;
+      b = x0 * s + x1 * c;
+    } else {  // the unrotated tail, two elements per item
+      ia = R + 2 * (i - half);
+      ib = ia + 1;
+      a = to_f32<T>(src[ia]);
+      b = to_f32<T>(src[ib]);
+    }
+    if (h < Hq) {
+      if (i < half) {
+        src[ia] = from_f32<T>(a);
+        src[ib] = from_f32<T>(b);
+      }
+    } else if (write_kv) {
+      T* dst = kdst + (size_t)(h - Hq) * page_size * D;
+      dst[ia] = from_f32<T>(a);
+      dst[ib] = from_f32<T>(b);
+    }
+  }
+  if (write_kv) {
+    const T* v = row + (size_t)(Hq + Hkv) * D;
+    for (int w = threadIdx.x; w < Hkv * D; w += blockDim.x) {
+      const int h = w / D, d = w % D;
+      vdst[(size_t)h * page_size * D + d] = v[w];
+    }
+  }
+}
+
+FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int ld, const int* positions,
+                                       const int* req_of_token, const int* block_table, int table_width,
+                                       const float* cos_sin, int n_pos, void* kv_plane, long long page_stride,
+                                       int page_size, int Hq, int Hkv, int D, int R, int pairing, int write_kv,
+                                       int* err_flag, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_tokens >= 0 && Hq > 0 && Hkv > 0 && D > 0 && D % 2 == 0, "rope: bad sizes T=%d Hq=%d Hkv=%d D=%d",
+                   n_tokens, Hq, Hkv, D);
+  FERRUM_CHECK_ARG(R >= 0 && R % 2 == 0 && R <= D, "rope: rope_dim %d must be even and at most head_dim %d", R, D);
+  FERRUM_CHECK_ARG(ld >= (Hq + 2 * Hkv) * D, "rope: row stride %d shorter than (Hq+2Hkv)*D", ld);
+  FERRUM_CHECK_ARG(pairing == 0 || pairing == 1, "rope: pairing code %d", pairing);
+  FERRUM_CHECK_ARG(!write_kv || (page_size > 0 && table_width > 0 && kv_plane), "rope: cache arguments missing");
+  if (n_tokens == 0) return 0;
+  const int threads = 256;
+  if (dtype == FERRUM_F32)
+    rope_cache_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, ld, positions, req_of_token, block_table,
+        table_width, cos_sin, n_pos, (float*)kv_plane, page_stride, page_size, Hq, Hkv, D, R, pairing, write_kv, err_flag);
+  else if (dtype == FERRUM_BF16)
+    rope_cache_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((__nv_bfloat16*)qkv, ld, positions, req_of_token,
+        block_table, table_width, cos_sin, n_pos, (__nv_bfloat16*)kv_plane, page_stride, page_size, Hq, Hkv, D, R,
+        pairing, write_kv, err_flag);
+  else
+    FERRUM_CHECK_ARG(false, "rope: unknown dtype code %d", dtype);
+  FERRUM_CHECK_LAUNCH("rope_cache_write");
+  return 0;
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// act[t, f] = silu(gu[t, f]) * gu[t, F + f], silu(g) = g / (1 + exp(-g)), in float32.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int F, int ld_in, int ld_out) {
+  const int t = blockIdx.y;
+  const T* g = gu + (size_t)t * ld_in;
+  const T* u = g + F;
+  T* o = act + (size_t)t * ld_out;
+  for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F; f += gridDim.x * blockDim.x) {
+    const float gv = to_f32<T>(g[f]);
+    o[f] = from_f32<T>(gv / (1.0f + expf(-gv)) * to_f32<T>(u[f]));
+  }
+}
+
+FERRUM_API int ferrum_swiglu(const void* gu, void* act, int dtype, int n_tokens, int F, int ld_in, int ld_out,
+                             cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_tokens >= 0 && F > 0 && ld_in >= 2 * F && ld_out >= F, "swiglu: bad sizes T=%d F=%d", n_tokens, F);
+  if (n_tokens == 0) return 0;
+  FERRUM_CHECK_ARG(n_tokens <= 65535, "swiglu: more than 65535 tokens in one call");
+  dim3 grid((F + 255) / 256 > 64 ? 64 : (F + 255) / 256, n_tokens);
+  if (dtype == FERRUM_F32)
+    swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)act, F, ld_in, ld_out);
+  else if (dtype == FERRUM_BF16)
+    swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, F, ld_in, ld_out);
+  else
+    FERRUM_CHECK_ARG(false, "swiglu: unknown dtype code %d", dtype);
+  FERRUM_CHECK_LAUNCH("swiglu");
+  return 0;
+}

@@ -1,0 +1,90 @@
+// Next-token choice on the GPU: argmax, or the Gumbel-max draw from softmax(logits / T).
+//
+// Greedy follows the reference's argmax (crates/core-types/src/model.rs:44-62): the lowest
+// index wins ties, NaN entries are skipped, a row of NaN only is an error (id -1 and the
+// error flag).  With a temperature the kernel returns argmax_i(logit_i / T + g_i) where
+// g_i = -log(-log(u_i)) and u_i is a pure function of (seed, counter, i), so a request's
+// draw does not depend on the batch it is in.  The reference samples greedily only.
+#include "common.cuh"
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7FEB352Du;
+  x ^= x >> 15;
+  x *= 0x846CA68Bu;
+  x ^= x >> 16;
+  return x;
+}
+
+struct Best {
+  float v;
+  int i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  // an index of -1 marks "nothing seen"
+  if (b.i < 0) return a;
+  if (a.i < 0) return b;
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ inv_temperature,
+              const unsigned long long* __restrict__ seeds, const int* __restrict__ counters,
+              int* __restrict__ out_ids, int* __restrict__ err) {
+  __shared__ Best red[32];
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const float inv_t = inv_temperature ? inv_temperature[r] : 0.f;
+  uint32_t key = 0;
+  if (inv_t != 0.f) {
+    const unsigned long long seed = seeds[r];
+    key = mix32((uint32_t)seed ^ mix32((uint32_t)(seed >> 32) ^ mix32((uint32_t)counters[r])));
+  }
+  Best best{0.f, -1};
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float z = row[i];
+    if (z != z) continue;
+    if (inv_t != 0.f) {
+      const uint32_t bits = mix32(key ^ mix32((uint32_t)i)) >> 9;
+      const float u = __fmul_rn(__fadd_rn((float)bits, 0.5f), 1.0f / 8388608.0f);
+      const float g = -logf(-logf(u));
+      z = __fadd_rn(__fmul_rn(z, inv_t), g);
+    }
+    best = better(best, Best{z, i});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best = lane < nw ? red[lane] : Best{0.f, -1};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+      best = better(best, other);
+    }
+    if (lane == 0) {
+      out_ids[r] = best.i;
+      if (best.i < 0) atomicExch(err, 6);
+    }
+  }
+}
+
+// inv_temperature[r] == 0 (or a null array) means greedy for row r.
+FERRUM_API int ferrum_sample(const float* logits, int ld, int n_rows, int V, const float* inv_temperature,
+                             const unsigned long long* seeds, const int* counters, int* out_ids, int* err_flag,
+                             cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_rows >= 0 && V > 0 && ld >= V, "sample: bad sizes rows=%d V=%d ld=%d", n_rows, V, ld);
+  FERRUM_CHECK_ARG(!inv_temperature || (seeds && counters), "sample: temperature given without seeds and counters");
+  if (n_rows == 0) return 0;
+  const int threads = V >= 8192 ? 1024 : 256;
+  sample_kernel<<<n_rows, threads, 0, stream>>>(logits, ld, V, inv_temperature, seeds, counters, out_ids, err_flag);
+  FERRUM_CHECK_LAUNCH("sample");
+  return 0;
+}

@@ -1,0 +1,202 @@
+"""The Python entry point: load a model, submit requests, step, generate.
+
+`Engine` is the composition root, as the reference's CLI is for its crates
+(docs/ARCHITECTURE.md:15-26): registry -> model -> cache -> runner -> scheduler -> sampler.
+Request fields and their meanings follow the reference's `SubmitRequest` and
+`SamplingParams` (crates/core-types/src/schedule.rs:16-49): prompt_tokens, max_new_tokens,
+temperature (0 = greedy), top_p (kept for the interface, must be 1), seed, stop_tokens.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import host
+from ..cache import CacheStorage
+from ..config import registry
+from ..errors import ConfigError, InvalidRequest
+from ..ops import lib as ops
+from ..weights import init_random, load_weights
+from .batch import StepEntry
+from .runner import ModelRunner
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          "f32": torch.float32}
+FINISH_REASONS = {0: "stop", 1: "length", 2: "cancelled"}
+
+
+def parse_dtype(name):
+    try:
+        return DTYPES[str(name).lower()]
+    except KeyError:
+        raise ConfigError(f"unsupported dtype {name!r}; choose bfloat16 or float32") from None
+
+
+def load_model(path, dtype="bfloat16", device="cuda", max_positions=None, random_seed=None):
+    """(model, torch dtype) from a model folder.  With random_seed the folder needs only
+    config.json and the weights are drawn on the device."""
+    ops.require_cuda()
+    td = parse_dtype(dtype)
+    arch, cfg = registry.read_config(path)
+    model = arch.build(cfg, td, device, max_positions=max_positions)
+    if random_seed is not None:
+        init_random(model, random_seed, device)
+    else:
+        load_weights(model, path, arch.hf_names(cfg) if arch.hf_names else None, device)
+    return model, td
+
+
+@dataclass
+class SamplingParams:
+    """crates/core-types/src/schedule.rs:16-29."""
+    temperature: float = 0.0
+    top_p: float = 1.0
+    seed: int = 0
+
+    @staticmethod
+    def greedy():
+        return SamplingParams()
+
+
+@dataclass
+class StepEvent:
+    """`token` events carry a token id; `finished` events a reason (stop, length, cancelled)."""
+    kind: str
+    id: int
+    token: Optional[int] = None
+    reason: Optional[str] = None
+
+
+class Engine:
+    def __init__(self, model_path=None, dtype="bfloat16", random_weights=False, seed=0, page_size=16,
+                 num_pages=None, max_batch_tokens=2048, max_batch_seqs=64, chunk_size=0, max_model_len=None,
+                 gpu_memory_fraction=0.85, device="cuda", model=None):
+        ops.require_cuda()
+        if model is None:
+            model, td = load_model(model_path, dtype, device, max_positions=max_model_len,
+                                   random_seed=seed if random_weights else None)
+        else:
+            td = model.dtype
+        self.model, self.dtype, self.device = model, td, device
+        cfg = model.config
+        self.max_model_len = int(max_model_len or getattr(cfg, "n_ctx_train", 4096))
+        if num_pages is None:
+            layout_bytes = CacheStorage.bytes_per_token_of(model, td)
+            free, _total = torch.cuda.mem_get_info()
+            budget = int(free * gpu_memory_fraction) - 2 * (1 << 30)
+            num_pages = max(16, min(budget // max(layout_bytes * page_size, 1),
+                                    (self.max_model_len * max_batch_seqs + page_size - 1) // page_size))
+        self.cache = CacheStorage(model, td, device, page_size=page_size, num_pages=num_pages,
+                                  max_requests=max_batch_seqs, max_model_len=self.max_model_len)
+        self.runner = ModelRunner(model, self.cache, max_batch_tokens=max_batch_tokens,
+                                  max_batch_requests=max_batch_seqs)
+        sc = host.module().SchedulerConfig()
+        sc.max_batch_tokens, sc.max_batch_seqs, sc.chunk_size = int(max_batch_tokens), int(max_batch_seqs), int(chunk_size)
+        sc.max_model_len, sc.n_vocab = self.max_model_len, model.n_vocab
+        eos = getattr(cfg, "eos_token_id", None)
+        sc.eos_token_id = -1 if eos is None else int(eos)
+        self.scheduler = host.module().Scheduler(self.cache.manager, sc)
+        self._next_id = 0
+        n = int(max_batch_seqs)
+        pin = lambda dt: torch.empty(n + 1, dtype=dt).pin_memory()
+        dev = lambda dt: torch.empty(n + 1, dtype=dt, device=device)
+        self._inv_t = (pin(torch.float32), dev(torch.float32))
+        self._seeds = (pin(torch.int64), dev(torch.int64))
+        self._counters = (pin(torch.int32), dev(torch.int32))
+        self._ids = (pin(torch.int32), dev(torch.int32))
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, prompt_tokens: Sequence[int], max_new_tokens: int, sampling: SamplingParams = None,
+               stop_tokens: Sequence[int] = (), request_id: Optional[int] = None, temperature=None, seed=None) -> int:
+        sp = sampling or SamplingParams()
+        if temperature is not None:
+            sp = SamplingParams(float(temperature), sp.top_p, sp.seed)
+        if seed is not None:
+            sp = SamplingParams(sp.temperature, sp.top_p, int(seed))
+        rid = self._next_id if request_id is None else int(request_id)
+        self._next_id = max(self._next_id, rid) + 1
+        self.scheduler.submit(rid, [int(t) for t in prompt_tokens], int(max_new_tokens), float(sp.temperature),
+                              float(sp.top_p), int(sp.seed) & 0xFFFFFFFFFFFFFFFF, [int(t) for t in stop_tokens])
+        return rid
+
+    def cancel(self, request_id: int) -> None:
+        self.scheduler.cancel(int(request_id))
+
+    # ------------------------------------------------------------------ one step
+    def step(self) -> List[StepEvent]:
+        """Plan a batch, run it, sample on the device, read the ids back, commit."""
+        plan = self.scheduler.plan()
+        if not plan:
+            return self._events(self.scheduler.commit([]))
+        try:
+            entries, rows = [], []
+            for p in plan:
+                n = len(p.tokens)
+                entries.append(StepEntry(p.slot, p.pos0, p.tokens, [n - 1] if p.sample else []))
+                if p.sample:
+                    rows.append(p)
+            logits = self.runner.step(entries, commit=False, check=False)
+            ids = self._sample(logits, rows) if rows else []
+        except Exception:
+            self.scheduler.abandon()
+            raise
+        return self._events(self.scheduler.commit(ids))
+
+    def _sample(self, logits, rows):
+        """One id per wanted row, chosen on the device; the ids and the device error flag
+        come back to the host in one copy."""
+        n = len(rows)
+        ids_h, ids_d = self._ids
+        if any(p.temperature > 0 for p in rows):
+            (it_h, it_d), (sd_h, sd_d), (ct_h, ct_d) = self._inv_t, self._seeds, self._counters
+            for i, p in enumerate(rows):
+                it_h[i] = float(np.float32(1.0 / p.temperature)) if p.temperature > 0 else 0.0
+                sd_h[i] = int(np.uint64(p.seed).astype(np.int64))
+                ct_h[i] = p.counter
+            for h, d in (self._inv_t, self._seeds, self._counters):
+                d[:n].copy_(h[:n], non_blocking=True)
+            ops.sample(logits, n, ids_d, self.runner.ctx.err, it_d[:n], sd_d[:n], ct_d[:n])
+        else:
+            ops.sample(logits, n, ids_d, self.runner.ctx.err)
+        ids_d[n:n + 1].copy_(self.runner.ctx.err)
+        ids_h[:n + 1].copy_(ids_d[:n + 1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        out = ids_h[:n + 1].tolist()
+        if out[n]:
+            self.runner.check_device_errors()
+        return out[:n]
+
+    @staticmethod
+    def _events(raw):
+        return [StepEvent("token", e.id, token=e.token) if e.kind == 0 else
+                StepEvent("finished", e.id, reason=FINISH_REASONS[e.reason]) for e in raw]
+
+    # ------------------------------------------------------------------ whole generations
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens=16, temperature=0.0, seed=0,
+                 stop_tokens: Sequence[int] = ()) -> List[List[int]]:
+        """Generates for every prompt (token ids in, token ids out), batching them continuously."""
+        ids = [self.submit(p, max_new_tokens, SamplingParams(temperature, 1.0, seed), stop_tokens) for p in prompts]
+        out: Dict[int, List[int]] = {i: [] for i in ids}
+        live = set(ids)
+        while live:
+            for ev in self.step():
+                if ev.id not in out:
+                    continue
+                if ev.kind == "token":
+                    out[ev.id].append(ev.token)
+                else:
+                    live.discard(ev.id)
+        return [out[i] for i in ids]
+
+    def stats(self) -> dict:
+        s = self.scheduler.stats()
+        m = self.cache.manager
+        return {"steps": s.steps, "prompt_tokens": s.prompt_tokens, "decode_tokens": s.decode_tokens,
+                "preemptions": s.preemptions, "finished": s.finished, "queued": self.scheduler.queued(),
+                "active": self.scheduler.active(),
+                "pages_used": [m.used_pages(g) for g in range(m.n_groups)],
+                "pages_free": [m.free_pages(g) for g in range(m.n_groups)]}

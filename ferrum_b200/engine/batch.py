@@ -1,0 +1,127 @@
+"""The description of one step's batch, on the device, and the scratch memory of a step.
+
+A step is a list of entries (request slot, first position, its next tokens, which of them
+want logits).  The reference's step takes one sequence per call
+(`forward(token_ids, position0, slot, logits_out)`, crates/core-types/src/model.rs:200-206);
+here all entries are flattened into one batch: per token its id, its position and its
+request's index; per request its first token's index, the number of cached positions, its
+slot id and one block-table row per cache group.  Everything travels in one pinned buffer
+and one host-to-device copy per step (plus one per cache group for the block tables).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    pos0: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()       # indices into `tokens` whose logits are wanted
+
+
+class Scratch:
+    """Named device buffers that live across steps and only ever grow, so that a buffer
+    keeps its address from step to step."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+
+    def get(self, name, shape, dtype):
+        n = 1
+        for s in shape:
+            n *= int(s)
+        t = self._bufs.get(name)
+        if t is None or t.dtype != dtype or t.numel() < n:
+            t = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = t
+        return t[:n].view(*shape)
+
+    def bytes(self):
+        return sum(t.numel() * t.element_size() for t in self._bufs.values())
+
+
+class StepContext:
+    """Built once per runner; `fill` rewrites it for each step."""
+
+    def __init__(self, device, max_tokens, max_requests, table_widths: List[int]):
+        self.device = device
+        self.max_tokens, self.max_requests = int(max_tokens), int(max_requests)
+        self.table_widths = list(table_widths)
+        self.scratch = Scratch(device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        n_small = 4 * self.max_tokens + 3 * self.max_requests + 1
+        self._host = torch.empty(n_small, dtype=torch.int32).pin_memory() if device != "cpu" else torch.empty(n_small, dtype=torch.int32)
+        self._dev = torch.empty(n_small, dtype=torch.int32, device=device)
+        self._bt_host = [torch.empty((self.max_requests, w), dtype=torch.int32) for w in self.table_widths]
+        if device != "cpu":
+            self._bt_host = [t.pin_memory() for t in self._bt_host]
+        self._bt_dev = [torch.empty((self.max_requests, w), dtype=torch.int32, device=device) for w in self.table_widths]
+        self._splitk_counters = torch.zeros(4096, dtype=torch.int32, device=device)
+        self.n_tokens = self.n_reqs = self.n_want = 0
+        self.token_capacity = self.want_capacity = 0
+
+    # ------------------------------------------------------------------ per step
+    def fill(self, entries: List[StepEntry], tables: List[List[Sequence[int]]], token_capacity=None):
+        """tables[g][r] is the block-table row of entry r in group g."""
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        if R > self.max_requests or T > self.max_tokens:
+            raise ValueError(f"batch of {T} tokens / {R} requests exceeds the runner's limits "
+                             f"({self.max_tokens} / {self.max_requests})")
+        W = sum(len(e.want) for e in entries)
+        h = self._host.numpy()
+        tok, pos, req, want = h[0:T], h[T:2 * T], h[2 * T:3 * T], h[3 * T:3 * T + W]
+        o = 3 * T + W
+        qstart, pos0, slots = h[o:o + R + 1], h[o + R + 1:o + 2 * R + 1], h[o + 2 * R + 1:o + 3 * R + 1]
+        t = w = 0
+        self.h_q_start, self.h_q_len, self.h_pos0, self.h_slots = [], [], [], []
+        for r, e in enumerate(entries):
+            n = len(e.tokens)
+            tok[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
+            pos[t:t + n] = np.arange(e.pos0, e.pos0 + n, dtype=np.int32)
+            req[t:t + n] = r
+            for i in e.want:
+                if not 0 <= i < n:
+                    raise ValueError(f"wanted index {i} is outside the entry's {n} tokens")
+                want[w] = t + i
+                w += 1
+            qstart[r], pos0[r], slots[r] = t, e.pos0, e.slot
+            self.h_q_start.append(t); self.h_q_len.append(n); self.h_pos0.append(e.pos0); self.h_slots.append(e.slot)
+            t += n
+        qstart[R] = T
+        total = o + 3 * R + 1
+        self._dev[:total].copy_(self._host[:total], non_blocking=True)
+        d = self._dev
+        self.token_ids, self.positions, self.req_of_token = d[0:T], d[T:2 * T], d[2 * T:3 * T]
+        self.want_rows = d[3 * T:3 * T + W]
+        self.q_start, self.pos0, self.slots = d[o:o + R + 1], d[o + R + 1:o + 2 * R + 1], d[o + 2 * R + 1:o + 3 * R + 1]
+        self.block_tables = []
+        for g, rows in enumerate(tables):
+            bh = self._bt_host[g].numpy()
+            for r, row in enumerate(rows):
+                bh[r, :len(row)] = row
+            self._bt_dev[g][:R].copy_(self._bt_host[g][:R], non_blocking=True)
+            self.block_tables.append(self._bt_dev[g][:R])
+        self.n_tokens, self.n_reqs, self.n_want = T, R, W
+        self.token_capacity = int(token_capacity or T)
+        self.want_capacity = max(W, 1)
+        self.max_q_len = max(self.h_q_len) if R else 0
+        self.max_kv_len = max((p + n for p, n in zip(self.h_pos0, self.h_q_len)), default=0)
+
+    # ------------------------------------------------------------------ scratch
+    def buf(self, name, shape, dtype):
+        return self.scratch.get(name, shape, dtype)
+
+    def splitk_scratch(self, M, N, dual, splits):
+        from ..ops import lib as ops
+        floats, tiles = ops.gemm_tc_workspace(M, N, dual, splits)
+        if tiles > self._splitk_counters.numel():
+            self._splitk_counters = torch.zeros(tiles, dtype=torch.int32, device=self.device)
+        return self.scratch.get("splitk", (floats,), torch.float32), self._splitk_counters

@@ -1,0 +1,76 @@
+"""The step function: runs one batch of (request, its next tokens) through the model.
+
+It runs only the tokens it is given, as one batch, against the cache that earlier steps
+left, and returns the logits at the wanted places.  The reference's contract is kept per
+entry: the first position must equal the number of positions the request already holds
+(crates/model/src/llama.rs:353-361), and a step that fails leaves the lengths untouched
+(:368-377; here the cache manager's lengths only advance in `commit`).
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..cache import CacheStorage
+from ..errors import CacheError, FerrumError, InvalidRequest, KernelError
+from ..ops import lib as ops
+from .batch import StepContext, StepEntry
+
+_DEVICE_ERRORS = {
+    1: "a token id is outside the vocabulary", 2: "a position is outside the rotary table",
+    3: "a position is beyond the block table", 4: "a token's page is missing from the block table",
+    5: "attention reached a position whose page is missing", 6: "a row of logits is all NaN",
+    10: "tensor-core product: the producer timed out", 11: "tensor-core product: the matrix unit timed out",
+    12: "tensor-core product: the epilogue timed out",
+}
+
+
+class ModelRunner:
+    def __init__(self, model, cache: CacheStorage, max_batch_tokens=2048, max_batch_requests=None):
+        ops.require_cuda()
+        self.model, self.cache = model, cache
+        self.device = cache.device
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.max_batch_requests = int(max_batch_requests or cache.max_requests)
+        widths = [cache.table_width] * cache.n_groups
+        self.ctx = StepContext(self.device, self.max_batch_tokens, self.max_batch_requests, widths)
+        self.ctx.cache = cache
+
+    def step(self, entries: List[StepEntry], commit=True, check=True):
+        """Returns float32 logits [n_wanted, V] on the device (a view that the next step
+        overwrites), in the order of the entries and of their `want` lists; None when no
+        logits are wanted.  With commit=False the caller advances the cache lengths itself."""
+        mgr = self.cache.manager
+        if not entries:
+            return None
+        seen = set()
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise InvalidRequest("a step entry has no tokens")
+            if e.slot in seen:
+                raise InvalidRequest("a request appears twice in one step")
+            seen.add(e.slot)
+            have = mgr.seq_len(e.slot)
+            if e.pos0 != have:
+                raise CacheError(f"position0 {e.pos0} does not match sequence length {have}")
+            mgr.grow(e.slot, e.pos0 + len(e.tokens))      # no-op when the scheduler already reserved
+            if e.pos0 == 0:
+                for s in self.cache.states:
+                    s[e.slot].zero_()                      # a request starts from an all-zero state
+        tables = [[mgr.table(g, e.slot) for e in entries] for g in range(self.cache.n_groups)]
+        self.ctx.fill(entries, tables)
+        logits = self.model.forward(self.ctx, self.cache)
+        if commit:
+            for e in entries:
+                mgr.commit(e.slot, e.pos0 + len(e.tokens))
+        if check:
+            self.check_device_errors()
+        return logits[:self.ctx.n_want] if logits is not None else None
+
+    def check_device_errors(self):
+        """Synchronises and raises if a kernel raised the error flag."""
+        code = int(self.ctx.err.item())
+        if code:
+            self.ctx.err.zero_()
+            raise KernelError(f"device error {code}: {_DEVICE_ERRORS.get(code, 'unknown')}")

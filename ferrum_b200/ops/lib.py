@@ -1,0 +1,220 @@
+"""The kernel library, loaded once, and thin checked wrappers around its C entry points.
+
+There is no fallback: if the library cannot be built or loaded, or there is no CUDA
+device, every op raises `KernelError`.  Wrappers take torch tensors only as typed
+memory (pointer, shape, stride); no torch operator runs on the product path.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..errors import KernelError
+from . import build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL = 0, 1, 2                       # generic product
+TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05 product
+
+_lib = None
+_lock = threading.Lock()
+ABI = 1
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = build.build_kernels()
+                try:
+                    handle = ctypes.CDLL(path)
+                except OSError as e:
+                    raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+                handle.ferrum_last_error.restype = ctypes.c_char_p
+                handle.ferrum_gemm_tc_workspace.restype = c_longlong
+                if handle.ferrum_kernels_abi() != ABI:
+                    raise KernelError(f"{path} is a stale build; delete it and call again")
+                _lib = handle
+    return _lib
+
+
+def require_cuda(device=None):
+    if not torch.cuda.is_available():
+        raise KernelError("ferrum_b200 runs on a CUDA device only (sm_100a); none is visible")
+    lib()
+
+
+def _check(rc, name):
+    if rc != 0:
+        raise KernelError(f"{name}: {lib().ferrum_last_error().decode()}")
+
+
+def _ptr(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t, dtype, name, ndim=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, found {t.dim()}")
+    if t.dim() and t.stride(-1) != 1 and t.shape[-1] > 1:
+        raise KernelError(f"{name} must be contiguous in its last dimension")
+
+
+def dtype_code(dtype):
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise KernelError(f"unsupported compute dtype {dtype}") from None
+
+
+# ----------------------------------------------------------------------------- ops
+def embedding(table, ids, out, err):
+    """out[t] = table[ids[t]] as float32."""
+    _need(table, None, "table", 2); _need(ids, torch.int32, "ids", 1); _need(out, torch.float32, "out", 2)
+    V, E = table.shape
+    T = ids.shape[0]
+    if out.shape[0] < T or out.shape[1] != E or not table.is_contiguous() or not out.is_contiguous():
+        raise KernelError("embedding: out must be contiguous [>=T, E] and table contiguous")
+    _check(lib().ferrum_embedding(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), c_int(T), c_int(E),
+                                  c_int(V), _ptr(err), _stream()), "embedding")
+
+
+def rmsnorm(x, weight, out, eps, rows=None, n_rows=None):
+    """out[r] = rmsnorm(x[rows[r] if rows else r]) * weight; x float32, out float32 or bfloat16."""
+    _need(x, torch.float32, "x", 2); _need(weight, torch.float32, "weight", 1); _need(out, None, "out", 2)
+    E = x.shape[1]
+    if n_rows is None:
+        n_rows = rows.shape[0] if rows is not None else x.shape[0]
+    if weight.shape[0] != E or out.shape[1] != E or out.shape[0] < n_rows or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("rmsnorm: shapes do not agree")
+    if rows is not None:
+        _need(rows, torch.int32, "rows", 1)
+    _check(lib().ferrum_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), _ptr(rows), c_int(n_rows),
+                                c_int(E), c_float(eps), _stream()), "rmsnorm")
+
+
+def gemm_generic(x, w, out, epilogue, M=None):
+    """out[t, n] (=, or += for EPI_RESIDUAL) sum_k x[t, k] w[n, k]; CUDA cores, float32 accumulate."""
+    _need(x, None, "x", 2); _need(w, x.dtype, "w", 2); _need(out, None, "out", 2)
+    M = x.shape[0] if M is None else M
+    N, K = w.shape
+    if x.shape[1] != K or out.shape[1] < N or out.shape[0] < M or x.shape[0] < M:
+        raise KernelError(f"gemm: shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    want = x.dtype if epilogue == EPI_STORE else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm: out must be {want} for epilogue {epilogue}")
+    _check(lib().ferrum_gemm_generic(_ptr(x), _ptr(w), _ptr(out), dtype_code(x.dtype), c_int(M), c_int(N), c_int(K),
+                                     c_int(x.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue),
+                                     _stream()), "gemm_generic")
+
+
+def gemm_tc_supported(x, w):
+    """True when the tcgen05 kernel takes these operands (bfloat16, 16-byte rows)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc_token_tile(M, dual):
+    return lib().ferrum_gemm_tc_token_tile(c_int(M), c_int(1 if dual else 0))
+
+
+def gemm_tc_workspace(M, N, dual, splits):
+    """(workspace floats, tile counters) that a split-K launch needs."""
+    tiles = c_int(0)
+    bt = gemm_tc_token_tile(M, dual)
+    need = lib().ferrum_gemm_tc_workspace(c_int(M), c_int(N), c_int(bt), c_int(1 if dual else 0), c_int(splits),
+                                          ctypes.byref(tiles))
+    return int(need), tiles.value
+
+
+def gemm_tc(x, w, out, epilogue, err, M=None, N=None, dual_offset=0, splits=1, workspace=None, counters=None):
+    """bfloat16 tensor-core product; see csrc/kernels/gemm_tc.cu.  `N` is the number of
+    output features (rows of w used per accumulator); with dual_offset > 0 rows
+    dual_offset + n feed the second accumulator of the SwiGLU epilogue."""
+    _need(x, torch.bfloat16, "x", 2); _need(w, torch.bfloat16, "w", 2); _need(out, None, "out", 2)
+    M = x.shape[0] if M is None else M
+    K = w.shape[1]
+    N = (w.shape[0] - dual_offset) if N is None else N
+    if x.shape[1] != K or out.shape[1] < N or out.shape[0] < M or x.shape[0] < M:
+        raise KernelError(f"gemm_tc: shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    want = torch.bfloat16 if epilogue in (TC_STORE_BF16, TC_SWIGLU) else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm_tc: out must be {want} for epilogue {epilogue}")
+    ws_n = workspace.numel() if workspace is not None else 0
+    if workspace is not None:
+        _need(workspace, torch.float32, "workspace")
+        _need(counters, torch.int32, "counters")
+    _check(lib().ferrum_gemm_tc(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
+                                c_int(w.stride(0)), c_int(out.stride(0)), c_int(w.shape[0]), c_int(epilogue),
+                                c_int(dual_offset), c_int(splits), _ptr(workspace), c_longlong(ws_n), _ptr(counters),
+                                c_int(counters.numel() if counters is not None else 0), _ptr(err), _stream()),
+           "gemm_tc")
+
+
+def rope_cache_write(qkv, n_tokens, positions, req_of_token, block_table, cos_sin, kv_plane, page_stride, page_size,
+                     Hq, Hkv, D, R, pairing, write_kv, err):
+    """Rotate q (in place) and k, store k and v into the paged cache plane."""
+    _need(qkv, None, "qkv", 2); _need(positions, torch.int32, "positions", 1)
+    _need(req_of_token, torch.int32, "req_of_token", 1); _need(block_table, torch.int32, "block_table", 2)
+    if R:
+        _need(cos_sin, torch.float32, "cos_sin", 3)
+        if cos_sin.shape[1] != R // 2 or cos_sin.shape[2] != 2 or not cos_sin.is_contiguous():
+            raise KernelError("rope: cos_sin must be contiguous [positions, rope_dim/2, 2]")
+    if write_kv:
+        _need(kv_plane, qkv.dtype, "kv_plane")
+    if not block_table.is_contiguous():
+        raise KernelError("rope: block_table must be contiguous")
+    _check(lib().ferrum_rope_cache_write(_ptr(qkv), dtype_code(qkv.dtype), c_int(n_tokens), c_int(qkv.stride(0)),
+                                         _ptr(positions), _ptr(req_of_token), _ptr(block_table),
+                                         c_int(block_table.shape[1]), _ptr(cos_sin if R else None),
+                                         c_int(cos_sin.shape[0] if R else 0), _ptr(kv_plane if write_kv else None),
+                                         c_longlong(page_stride), c_int(page_size), c_int(Hq), c_int(Hkv), c_int(D),
+                                         c_int(R), c_int(pairing), c_int(1 if write_kv else 0), _ptr(err), _stream()),
+           "rope_cache_write")
+
+
+def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv_plane, page_stride, page_size, Hq,
+                      Hkv, D, scale, window, err):
+    """Causal GQA attention of every token over its request's pages (one warp per token and head)."""
+    _need(q, None, "q", 2); _need(out, q.dtype, "out", 2); _need(kv_plane, q.dtype, "kv_plane")
+    _need(positions, torch.int32, "positions", 1); _need(req_of_token, torch.int32, "req_of_token", 1)
+    _need(block_table, torch.int32, "block_table", 2)
+    if not block_table.is_contiguous():
+        raise KernelError("attention: block_table must be contiguous")
+    _check(lib().ferrum_attention_generic(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)),
+                                          dtype_code(q.dtype), c_int(n_tokens), _ptr(positions), _ptr(req_of_token),
+                                          _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_plane),
+                                          c_longlong(page_stride), c_int(page_size), c_int(Hq), c_int(Hkv), c_int(D),
+                                          c_float(scale), c_int(window), _ptr(err), _stream()), "attention_generic")
+
+
+def swiglu(gu, act, n_tokens, F):
+    """act[t, f] = silu(gu[t, f]) * gu[t, F + f]."""
+    _need(gu, None, "gu", 2); _need(act, gu.dtype, "act", 2)
+    _check(lib().ferrum_swiglu(_ptr(gu), _ptr(act), dtype_code(gu.dtype), c_int(n_tokens), c_int(F),
+                               c_int(gu.stride(0)), c_int(act.stride(0)), _stream()), "swiglu")
+
+
+def sample(logits, n_rows, out_ids, err, inv_temperature=None, seeds=None, counters=None):
+    """out_ids[r] = argmax, or the Gumbel-max draw where inv_temperature[r] != 0."""
+    _need(logits, torch.float32, "logits", 2); _need(out_ids, torch.int32, "out_ids", 1)
+    if inv_temperature is not None:
+        _need(inv_temperature, torch.float32, "inv_temperature", 1)
+        _need(seeds, torch.int64, "seeds", 1); _need(counters, torch.int32, "counters", 1)
+    _check(lib().ferrum_sample(_ptr(logits), c_int(logits.stride(0)), c_int(n_rows), c_int(logits.shape[1]),
+                               _ptr(inv_temperature), _ptr(seeds), _ptr(counters), _ptr(out_ids), _ptr(err),
+                               _stream()), "sample")

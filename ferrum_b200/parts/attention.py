@@ -1,0 +1,59 @@
+"""Causal grouped-query attention over the paged cache.
+
+q, k, v projections (one fused matrix), rotary encoding of q and k fused with the cache
+write, attention of every token over its request's pages, output projection added to the
+residual stream (crates/model/src/llama.rs:185-257).  Query head h reads KV head
+h / (Hq/Hkv); the score scale is 1/sqrt(head_dim) unless given.  `window` > 0 keeps the last
+`window` keys only; the reference has no window.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..ops import lib as ops
+from .base import CacheNeed, Mixer, PagedKVNeed, ParamSpec
+from .linear import RESIDUAL, STORE, linear
+
+
+class PagedAttention(Mixer):
+    def __init__(self, width, n_head, n_head_kv, head_dim, position, dtype, window=0, scale=None):
+        if n_head % n_head_kv:
+            raise ValueError("head count is not divisible by kv head count")
+        self.width, self.Hq, self.Hkv, self.D = width, n_head, n_head_kv, head_dim
+        self.position, self.dtype, self.window = position, dtype, int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.w_q_weight = self.w_k_weight = self.w_v_weight = self.w_output_weight = None
+        self.w_qkv = None
+
+    def param_specs(self):
+        q, kv = self.Hq * self.D, self.Hkv * self.D
+        return {"q.weight": ParamSpec((q, self.width)), "k.weight": ParamSpec((kv, self.width)),
+                "v.weight": ParamSpec((kv, self.width)), "output.weight": ParamSpec((self.width, q))}
+
+    def finalize(self):
+        self.w_qkv = torch.cat([self.w_q_weight, self.w_k_weight, self.w_v_weight], dim=0).contiguous()
+        self.w_q_weight = self.w_k_weight = self.w_v_weight = None
+
+    def cache_need(self):
+        return CacheNeed(paged=PagedKVNeed(self.Hkv, self.D, self.window))
+
+    def forward(self, x, ctx, cache, residual):
+        T, Hq, Hkv, D = ctx.n_tokens, self.Hq, self.Hkv, self.D
+        qw = Hq * D
+        qkv = ctx.buf("attn_qkv", (ctx.token_capacity, (Hq + 2 * Hkv) * D), self.dtype)
+        if cache.writes:
+            linear(x, self.w_qkv, qkv, STORE, ctx, M=T)
+        else:  # this run of the layer reads another run's keys and values
+            linear(x, self.w_qkv[:qw], qkv, STORE, ctx, M=T)
+        rot = self.position.rotary() if self.position is not None else None
+        table = ctx.block_tables[cache.group]
+        ops.rope_cache_write(qkv, T, ctx.positions, ctx.req_of_token, table,
+                             rot.cos_sin if rot is not None else None, cache.plane, cache.page_stride,
+                             cache.page_size, Hq, Hkv, D, rot.rope_dim if rot is not None else 0,
+                             rot.pairing if rot is not None else 0, cache.writes, ctx.err)
+        out = ctx.buf("attn_out", (ctx.token_capacity, qw), self.dtype)
+        ops.attention_generic(qkv, out, T, ctx.positions, ctx.req_of_token, table, cache.plane, cache.page_stride,
+                              cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err)
+        linear(out, self.w_output_weight, residual, RESIDUAL, ctx, M=T)

@@ -1,0 +1,65 @@
+"""Random-weights mode: fills a model, or writes a model folder, from a config and a seed.
+
+Every tensor has its own generator keyed by (seed, name), so values do not depend on the
+order or the set of tensors: matrices are N(0, 0.02), norm weights 1 + N(0, 0.02).  The
+reference has no such mode (its tests fill every weight with 0.01,
+crates/model/src/tests.rs:25-34).
+"""
+from __future__ import annotations
+
+import json
+import os
+import zlib
+
+import torch
+
+from ..config import registry
+from .loader import convert
+from .safetensors_io import write_safetensors
+
+_DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+
+
+def _tensor(name, spec, seed, device, std):
+    g = torch.Generator(device=device)
+    g.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (2 ** 63))
+    if spec.kind == "table":
+        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+    t = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32) * std
+    if spec.init == "ones_normal":
+        t += 1.0
+    return t
+
+
+def init_random(model, seed, device="cuda", std=0.02):
+    """Assign random values to every parameter of `model` on `device` and finalize it."""
+    for name, (spec, part, local) in model.weight_specs().items():
+        if spec.optional:
+            continue          # e.g. an output matrix the model can share with the embedding
+        part.assign(local, convert(_tensor(name, spec, seed, device, std), spec.kind, model.dtype).contiguous())
+    model.finalize()
+    return model
+
+
+def write_random_model(config_dict, folder, seed, dtype="float32", std=0.02, tie=None):
+    """Write `folder/config.json` and `folder/model.safetensors` for the architecture that
+    config_dict names; tensor names are the checkpoint's (HF) names."""
+    arch = registry.lookup(str(config_dict["architectures"][0]))
+    cfg = arch.read_config(config_dict)
+    model = arch.build(cfg, _DT[dtype], "cpu", max_positions=1)
+    back = {v: k for k, v in (arch.hf_names(cfg) if arch.hf_names else {}).items()}
+    tied = getattr(cfg, "tie_word_embeddings", False) if tie is None else tie
+    tensors = {}
+    for name, (spec, _, _) in model.weight_specs().items():
+        if spec.optional and tied:
+            continue
+        t = _tensor(name, spec, seed, "cpu", std)
+        store = _DT[dtype] if spec.kind == "matrix" else (torch.int32 if spec.kind == "table" else torch.float32)
+        tensors[back.get(name, name)] = t.to(store)
+    os.makedirs(folder, exist_ok=True)
+    out = dict(config_dict)
+    out["torch_dtype"] = dtype
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(out, f, indent=1)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors, {"format": "pt"})
+    return folder

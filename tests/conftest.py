@@ -1,0 +1,54 @@
+"""Shared fixtures: tiny configurations, model folders in a temporary directory, markers."""
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+# Two tiny Llamas that differ in every size and option, and a third whose widths share
+# no factor with the others (query width != hidden size, head size 48).
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 172, "vocab_size": 256, "rope_theta": 10000.0,
+    "rope_scaling": None, "max_position_embeddings": 128, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 96, "num_hidden_layers": 3, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 256, "vocab_size": 512, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "max_position_embeddings": 256, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+}
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 80, "num_hidden_layers": 1, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 48, "intermediate_size": 200, "vocab_size": 301, "rope_theta": 2500.0,
+    "rope_scaling": None, "max_position_embeddings": 512, "rms_norm_eps": 3e-6, "tie_word_embeddings": False,
+}
+TINY = {"A": (TINY_A, 0, "float32"), "B": (TINY_B, 1, "bfloat16"), "C": (TINY_C, 2, "float32")}
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def model_dirs(tmp_path_factory):
+    """name -> folder with config.json + model.safetensors, written by the random-weights mode."""
+    from ferrum_b200.weights import write_random_model
+    out = {}
+    for name, (cfg, seed, dtype) in TINY.items():
+        d = tmp_path_factory.mktemp("tiny_" + name)
+        write_random_model(cfg, str(d), seed, dtype=dtype)
+        out[name] = str(d)
+    return out
+
+
+@pytest.fixture(scope="session")
+def cuda():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda")

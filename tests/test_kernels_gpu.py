@@ -1,0 +1,352 @@
+"""Each CUDA kernel alone against a plain float64 reference of the same op, at sizes the
+engine's own models do not use (odd widths, tails, several tile shapes)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(cuda):
+    from ferrum_b200.ops import lib
+    lib.require_cuda()
+    return lib
+
+
+def err_flag():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+def lim(ref, rel):
+    return torch.clamp(rel * torch.clamp(ref.abs(), min=1.0), min=1e-6)
+
+
+# ---------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,E,T", [(301, 80, 7), (1000, 1537, 33)])
+def test_embedding(ops, dtype, V, E, T):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    table = torch.randn(V, E, device="cuda", generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32)
+    out = torch.empty(T, E, device="cuda")
+    e = err_flag()
+    ops.embedding(table, ids, out, e)
+    assert torch.equal(out, table[ids.long()].float()) and e.item() == 0
+    ids[2] = V
+    ops.embedding(table, ids, out, e)
+    assert e.item() == 1 and out[2].abs().sum().item() == 0      # refused, not read
+
+
+# ---------------------------------------------------------------- rmsnorm
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,T,eps", [(80, 5, 3e-6), (1537, 9, 1e-5), (4096, 3, 1e-5)])
+def test_rmsnorm(ops, out_dtype, E, T, eps):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(T, E, device="cuda", generator=g) * 3
+    w = 1 + 0.1 * torch.randn(E, device="cuda", generator=g)
+    out = torch.empty(T, E, device="cuda", dtype=out_dtype)
+    ops.rmsnorm(x, w, out, eps)
+    ref = torch.from_numpy(P.rms_norm(x.double().cpu().numpy(), w.double().cpu().numpy(), eps)).cuda()
+    tol = 1e-4 if out_dtype == torch.float32 else 8e-3
+    assert ((out.double() - ref).abs() <= lim(ref, tol)).all()
+    rows = torch.tensor([4, 0, 2], dtype=torch.int32, device="cuda")
+    out2 = torch.empty(3, E, device="cuda", dtype=out_dtype)
+    ops.rmsnorm(x, w, out2, eps, rows=rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+def test_rmsnorm_anchor(ops):
+    """crates/kernels/src/tests.rs:170-176: rms of [3,4] with weights [2,0.5]."""
+    x = torch.tensor([[3.0, 4.0]], device="cuda")
+    w = torch.tensor([2.0, 0.5], device="cuda")
+    out = torch.empty(1, 2, device="cuda")
+    ops.rmsnorm(x, w, out, 1e-12)
+    inv = 1 / math.sqrt(12.5)
+    assert torch.allclose(out.cpu(), torch.tensor([[3 * inv * 2, 4 * inv * 0.5]]), rtol=1e-6)
+
+
+# ---------------------------------------------------------------- generic product
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 6, 3), (7, 172, 64), (65, 129, 173), (130, 64, 300)])
+def test_gemm_generic(ops, dtype, M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    w = torch.randn(N, K, device="cuda", generator=g).to(dtype)
+    ref = x.double() @ w.double().T
+    out = torch.empty(M, N, device="cuda", dtype=dtype)
+    ops.gemm_generic(x, w, out, ops.EPI_STORE)
+    tol = 1e-4 if dtype == torch.float32 else 8e-3
+    assert ((out.double() - ref).abs() <= lim(ref, tol) * math.sqrt(K)).all()
+    out32 = torch.empty(M, N, device="cuda")
+    ops.gemm_generic(x, w, out32, ops.EPI_STORE_F32)
+    assert ((out32.double() - ref).abs() <= lim(ref, 1e-4) * math.sqrt(K) * (1 if dtype == torch.float32 else 1)).all()
+    res = torch.randn(M, N, device="cuda", generator=g)
+    acc = res.clone()
+    ops.gemm_generic(x, w, acc, ops.EPI_RESIDUAL)
+    assert ((acc.double() - (res.double() + ref)).abs() <= lim(ref, 1e-4) * math.sqrt(K)).all()
+
+
+def test_gemm_generic_anchor(ops):
+    """crates/kernels/src/tests.rs:247-268: [[1,2,3],[4,5,6]] . [1,1,1] = [6,15]."""
+    w = torch.tensor([[1.0, 2, 3], [4, 5, 6]], device="cuda")
+    x = torch.tensor([[1.0, 1, 1], [1, 0, 0]], device="cuda")
+    out = torch.empty(2, 2, device="cuda")
+    ops.gemm_generic(x, w, out, ops.EPI_STORE)
+    assert out.cpu().tolist() == [[6.0, 15.0], [1.0, 4.0]]
+
+
+def test_gemm_generic_row_independent_of_batch(ops):
+    """A token's product is bit-identical whether it is alone or among others."""
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(70, 333, device="cuda", generator=g)
+    w = torch.randn(90, 333, device="cuda", generator=g)
+    full = torch.empty(70, 90, device="cuda")
+    ops.gemm_generic(x, w, full, ops.EPI_STORE)
+    one = torch.empty(1, 90, device="cuda")
+    ops.gemm_generic(x[37:38].contiguous(), w, one, ops.EPI_STORE)
+    assert torch.equal(one[0], full[37])
+
+
+# ---------------------------------------------------------------- tensor-core product
+TC_SHAPES = [(1, 128, 64), (5, 200, 136), (16, 384, 512), (33, 1000, 264), (64, 256, 1024), (100, 130, 4096),
+             (200, 640, 320), (300, 256, 192), (515, 384, 128)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+@pytest.mark.parametrize("splits", [1, 3])
+def test_gemm_tc(ops, M, N, K, splits):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = (torch.randn(M, K, device="cuda", generator=g)).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g)).bfloat16()
+    ref = x.double() @ w.double().T
+    e = err_flag()
+    nkb = (K + 63) // 64
+    if splits > nkb:
+        pytest.skip("fewer k-blocks than splits")
+    ws = cnt = None
+    if splits > 1:
+        floats, tiles = ops.gemm_tc_workspace(M, N, False, splits)
+        ws = torch.empty(floats, device="cuda")
+        cnt = torch.zeros(tiles, dtype=torch.int32, device="cuda")
+    out = torch.full((M, N), float("nan"), device="cuda")
+    ops.gemm_tc(x, w, out, ops.TC_STORE_F32, e, splits=splits, workspace=ws, counters=cnt)
+    assert e.item() == 0
+    assert ((out.double() - ref).abs() <= lim(ref, 2e-5) * math.sqrt(K)).all(), (out.double() - ref).abs().max()
+    outb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tc(x, w, outb, ops.TC_STORE_BF16, e, splits=splits, workspace=ws, counters=cnt)
+    assert ((outb.double() - ref).abs() <= lim(ref, 8e-3)).all()
+    res = torch.randn(M, N, device="cuda", generator=g)
+    acc = res.clone()
+    ops.gemm_tc(x, w, acc, ops.TC_RESIDUAL, e, splits=splits, workspace=ws, counters=cnt)
+    assert ((acc.double() - (res.double() + ref)).abs() <= lim(ref, 2e-5) * math.sqrt(K)).all()
+    if cnt is not None:
+        assert cnt.sum().item() == 0          # the counters are left ready for the next launch
+    assert e.item() == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(3, 172 * 2, 64), (16, 256, 96), (40, 200, 320), (130, 384, 256), (300, 128, 128)])
+@pytest.mark.parametrize("splits", [1, 2])
+def test_gemm_tc_swiglu(ops, M, F, K, splits):
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * F, K, device="cuda", generator=g) * 0.2).bfloat16()
+    gate, up = x.double() @ w[:F].double().T, x.double() @ w[F:].double().T
+    ref = gate / (1 + torch.exp(-gate)) * up
+    e = err_flag()
+    ws = cnt = None
+    if splits > 1:
+        if (K + 63) // 64 < splits:
+            pytest.skip("fewer k-blocks than splits")
+        floats, tiles = ops.gemm_tc_workspace(M, F, True, splits)
+        ws = torch.empty(floats, device="cuda")
+        cnt = torch.zeros(tiles, dtype=torch.int32, device="cuda")
+    act = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tc(x, w, act, ops.TC_SWIGLU, e, N=F, dual_offset=F, splits=splits, workspace=ws, counters=cnt)
+    assert e.item() == 0
+    assert ((act.double() - ref).abs() <= lim(ref, 1e-2)).all(), (act.double() - ref).abs().max()
+
+
+def test_gemm_tc_refuses_unaligned(ops):
+    from ferrum_b200.errors import KernelError
+    x = torch.zeros(4, 172, device="cuda", dtype=torch.bfloat16)
+    w = torch.zeros(8, 172, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(4, 8, device="cuda")
+    assert not ops.gemm_tc_supported(x, w)
+    with pytest.raises(KernelError):
+        ops.gemm_tc(x, w, out, ops.TC_STORE_F32, err_flag())
+
+
+# ---------------------------------------------------------------- rope + cache write, attention
+def paged_setup(lens, Hkv, D, page_size, dtype, seed, extra_pages=3):
+    """Random K/V for requests of the given lengths, scattered over shuffled pages."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    n_pages = sum((n + page_size - 1) // page_size for n in lens) + extra_pages
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max((n + page_size - 1) // page_size for n in lens) + 1
+    table = torch.full((len(lens), width), -1, dtype=torch.int32)
+    plane = torch.full((n_pages, 2, Hkv, page_size, D), float("nan"), device="cuda").to(dtype)
+    ks, vs, p = [], [], 0
+    for r, n in enumerate(lens):
+        k = torch.randn(n, Hkv, D, device="cuda", generator=g).to(dtype)
+        v = torch.randn(n, Hkv, D, device="cuda", generator=g).to(dtype)
+        for lp in range((n + page_size - 1) // page_size):
+            page = perm[p]; p += 1
+            table[r, lp] = page
+            lo, hi = lp * page_size, min(n, (lp + 1) * page_size)
+            plane[page, 0, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            plane[page, 1, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+        ks.append(k); vs.append(v)
+    return plane, table.cuda(), ks, vs
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(4, 2, 16, 16, 0), (6, 3, 48, 8, 0), (8, 1, 128, 16, 0),
+                                                (3, 3, 80, 32, 0), (4, 2, 32, 16, 21), (2, 1, 256, 16, 0)])
+def test_attention_generic(ops, dtype, Hq, Hkv, D, ps, window):
+    """Mixed batch: a whole prompt, a late portion, two single decoded tokens."""
+    lens = [37, 130, 65, 1]
+    qlens = [37, 9, 1, 1]
+    plane, table, ks, vs = paged_setup(lens, Hkv, D, ps, dtype, 7)
+    g = torch.Generator(device="cuda").manual_seed(8)
+    T = sum(qlens)
+    q = torch.randn(T, Hq * D, device="cuda", generator=g).to(dtype)
+    pos, req = [], []
+    for r, (n, ql) in enumerate(zip(lens, qlens)):
+        pos += list(range(n - ql, n)); req += [r] * ql
+    out = torch.empty(T, Hq * D, device="cuda", dtype=dtype)
+    e = err_flag()
+    ops.attention_generic(q, out, T, torch.tensor(pos, dtype=torch.int32, device="cuda"),
+                          torch.tensor(req, dtype=torch.int32, device="cuda"), table, plane, plane.stride(0), ps,
+                          Hq, Hkv, D, 1.0 / math.sqrt(D), window, e)
+    assert e.item() == 0
+    t0 = 0
+    for r, (n, ql) in enumerate(zip(lens, qlens)):
+        qfull = np.zeros((n, Hq, D))
+        qfull[n - ql:] = q[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
+        ref = P.attention(qfull, ks[r].double().cpu().numpy(), vs[r].double().cpu().numpy(), window)[n - ql:]
+        got = out[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
+        tol = 1e-4 if dtype == torch.float32 else 1.5e-2
+        assert np.abs(got - ref).max() <= tol, (r, np.abs(got - ref).max())
+        t0 += ql
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("far_key", [0, 15, 16, 17, 255, 256, 499])
+def test_attention_finds_one_far_key(ops, dtype, far_key):
+    """One key among 500 matches the query strongly; its value must come through.  A kernel
+    that skips a page edge or the first or last key shows at once."""
+    Hq = Hkv = 2; D = 32; ps = 16; n = 500
+    plane, table, ks, vs = paged_setup([n], Hkv, D, ps, dtype, 9)
+    kq = ks[0][far_key].float()                       # [Hkv, D]; Hq == Hkv here
+    # score of the far key = 40, of every other key ~ N(0, 7)
+    q = (kq * (40.0 * math.sqrt(D) / kq.pow(2).sum(-1, keepdim=True))).reshape(1, Hq * D)
+    q = q.to(dtype)
+    out = torch.empty(1, Hq * D, device="cuda", dtype=dtype)
+    e = err_flag()
+    ops.attention_generic(q, out, 1, torch.tensor([n - 1], dtype=torch.int32, device="cuda"),
+                          torch.zeros(1, dtype=torch.int32, device="cuda"), table, plane, plane.stride(0), ps, Hq, Hkv,
+                          D, 1.0 / math.sqrt(D), 0, e)
+    qfull = np.zeros((n, Hq, D)); qfull[-1] = q.double().cpu().numpy().reshape(Hq, D)
+    ref = P.attention(qfull, ks[0].double().cpu().numpy(), vs[0].double().cpu().numpy())[-1]
+    got = out.double().cpu().numpy().reshape(Hq, D)
+    assert np.abs(ref - vs[0][far_key].double().cpu().numpy()).max() < 0.05      # the construction works
+    assert np.abs(got - ref).max() <= (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairing", ["adjacent", "half"])
+@pytest.mark.parametrize("Hq,Hkv,D,R", [(4, 2, 16, 16), (3, 1, 48, 32), (2, 2, 128, 128)])
+def test_rope_cache_write(ops, dtype, pairing, Hq, Hkv, D, R):
+    from ferrum_b200.parts.rope import RotaryEmbedding
+    ps, n_pos = 8, 300
+    rot = RotaryEmbedding(D, R, 10000.0, None, pairing, n_pos, "cuda")
+    positions = [0, 1, 7, 8, 9, 250, 299, 64]
+    req = [0, 0, 0, 0, 0, 1, 1, 1]
+    T = len(positions)
+    g = torch.Generator(device="cuda").manual_seed(10)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", generator=g).to(dtype)
+    orig = qkv.clone()
+    width = (n_pos + ps - 1) // ps
+    # the two requests share no page; logical pages map to shuffled page ids
+    table = torch.stack([torch.arange(width), torch.arange(width) + width]).to(torch.int32)
+    table = table[:, torch.randperm(width, generator=torch.Generator().manual_seed(3))].contiguous().cuda()
+    plane = torch.zeros(2 * width, 2, Hkv, ps, D, device="cuda", dtype=dtype)
+    e = err_flag()
+    ops.rope_cache_write(qkv, T, torch.tensor(positions, dtype=torch.int32, device="cuda"),
+                         torch.tensor(req, dtype=torch.int32, device="cuda"), table, rot.cos_sin, plane,
+                         plane.stride(0), ps, Hq, Hkv, D, R, rot.pairing, True, e)
+    assert e.item() == 0
+    inv = np.array([10000.0 ** (-2.0 * i / R) for i in range(R // 2)])
+    o = orig.double().cpu().numpy()
+    qref = o[:, :Hq * D].reshape(T, Hq, D).copy()
+    kref = o[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D).copy()
+    qref[..., :R] = P.rope(qref[..., :R], np.array(positions), inv, pairing)
+    kref[..., :R] = P.rope(kref[..., :R], np.array(positions), inv, pairing)
+    vref = o[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert np.abs(qkv[:, :Hq * D].double().cpu().numpy().reshape(T, Hq, D) - qref).max() <= tol
+    for t, (p, r) in enumerate(zip(positions, req)):
+        page = table[r, p // ps].item()
+        assert np.abs(plane[page, 0, :, p % ps].double().cpu().numpy() - kref[t]).max() <= tol
+        assert np.abs(plane[page, 1, :, p % ps].double().cpu().numpy() - vref[t]).max() == 0
+    # position 0 is the identity (crates/kernels/src/tests.rs:197-238)
+    assert torch.equal(qkv[0, :Hq * D], orig[0, :Hq * D])
+
+
+# ---------------------------------------------------------------- swiglu, sampling
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,F", [(3, 172), (17, 1000)])
+def test_swiglu(ops, dtype, T, F):
+    g = torch.Generator(device="cuda").manual_seed(11)
+    gu = (torch.randn(T, 2 * F, device="cuda", generator=g) * 3).to(dtype)
+    act = torch.empty(T, F, device="cuda", dtype=dtype)
+    ops.swiglu(gu, act, T, F)
+    a = gu.double()
+    ref = torch.from_numpy(P.silu(a[:, :F].cpu().numpy())).cuda() * a[:, F:]
+    assert ((act.double() - ref).abs() <= lim(ref, 1e-5 if dtype == torch.float32 else 8e-3)).all()
+
+
+def test_argmax_rules(ops):
+    """crates/core-types/src/model.rs:304-309: [1,3,3,NaN] -> 1; all NaN is an error."""
+    logits = torch.tensor([[1.0, 3.0, 3.0, float("nan")], [float("nan")] * 4, [-5.0, -7.0, -5.0, -9.0]], device="cuda")
+    ids = torch.empty(3, dtype=torch.int32, device="cuda")
+    e = err_flag()
+    ops.sample(logits, 3, ids, e)
+    assert ids.cpu().tolist() == [1, -1, 0] and e.item() == 6
+
+
+@pytest.mark.parametrize("V", [301, 128256])
+def test_sampling_matches_plain(ops, V):
+    g = torch.Generator(device="cuda").manual_seed(12)
+    R = 6
+    logits = torch.randn(R, V, device="cuda", generator=g) * 2
+    temps = [0.0, 0.8, 0.8, 1.5, 0.3, 0.8]
+    seeds = [0, 1, 2 ** 40 + 7, 5, 5, 1]
+    counters = [0, 0, 3, 9, 9, 1]
+    inv_t = torch.tensor([np.float32(1.0 / t) if t else 0.0 for t in temps], dtype=torch.float32, device="cuda")
+    ids = torch.empty(R, dtype=torch.int32, device="cuda")
+    e = err_flag()
+    ops.sample(logits, R, ids, e, inv_t, torch.tensor(seeds, dtype=torch.int64, device="cuda"),
+               torch.tensor(counters, dtype=torch.int32, device="cuda"))
+    host = logits.cpu().numpy()
+    for r in range(R):
+        want = P.sample(host[r], temps[r], seeds[r], counters[r])
+        got = ids[r].item()
+        if got != want:      # only a near-tie of the perturbed logits may differ (logf rounding)
+            u = P.gumbel_uniform(seeds[r], counters[r], V)
+            z = host[r].astype(np.float64) / temps[r] - np.log(-np.log(u))
+            assert abs(z[got] - z[want]) < 1e-4, (r, got, want)
+    # the draw follows softmax(logits / T): frequencies over many seeds, small vocabulary
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]], device="cuda").repeat(4000, 1)
+    n = small.shape[0]
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample(small, n, out, e, torch.full((n,), 1.0, device="cuda"),
+               torch.arange(n, dtype=torch.int64, device="cuda"), torch.zeros(n, dtype=torch.int32, device="cuda"))
+    freq = np.bincount(out.cpu().numpy(), minlength=4) / n
+    p = np.exp([2.0, 1, 0, -1]); p /= p.sum()
+    assert np.abs(freq - p).max() < 0.03, (freq, p)
