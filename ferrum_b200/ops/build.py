@@ -104,7 +104,7 @@ def build_kernels(force=False, verbose_ptxas=False):
     if cmds:
         _run_all(cmds, f"{len(cmds)} CUDA source(s) for sm_100a")
     tmp = KERNEL_LIB + f".tmp{os.getpid()}"
-    link = [nvcc, *NVCC_ARCH, "-shared", "-o", tmp, *objs, "-cudart", "shared"]
+    link = [nvcc, *NVCC_ARCH, "-shared", "-o", tmp, *objs]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise KernelError(f"link failed: {' '.join(link)}\n{r.stdout}")

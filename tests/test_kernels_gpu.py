@@ -54,7 +54,7 @@ def test_rmsnorm(ops, out_dtype, E, T, eps):
     ref = torch.from_numpy(P.rms_norm(x.double().cpu().numpy(), w.double().cpu().numpy(), eps)).cuda()
     tol = 1e-4 if out_dtype == torch.float32 else 8e-3
     assert ((out.double() - ref).abs() <= lim(ref, tol)).all()
-    rows = torch.tensor([4, 0, 2], dtype=torch.int32, device="cuda")
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device="cuda")
     out2 = torch.empty(3, E, device="cuda", dtype=out_dtype)
     ops.rmsnorm(x, w, out2, eps, rows=rows)
     assert torch.equal(out2, out[rows.long()])
