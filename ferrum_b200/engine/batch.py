@@ -65,6 +65,7 @@ class StepContext:
         self._bt_dev = [torch.empty((self.max_requests, w), dtype=torch.int32, device=device) for w in self.table_widths]
         self._splitk_counters = torch.zeros(4096, dtype=torch.int32, device=device)
         self.n_tokens = self.n_reqs = self.n_want = 0
+        self.h2d_bytes = 0            # bytes copied to the device by the last fill
         self.token_capacity = self.want_capacity = 0
 
     # ------------------------------------------------------------------ per step
@@ -98,6 +99,7 @@ class StepContext:
         qstart[R] = T
         total = o + 3 * R + 1
         self._dev[:total].copy_(self._host[:total], non_blocking=True)
+        self.h2d_bytes = total * 4
         d = self._dev
         self.token_ids, self.positions, self.req_of_token = d[0:T], d[T:2 * T], d[2 * T:3 * T]
         self.want_rows = d[3 * T:3 * T + W]
@@ -108,6 +110,7 @@ class StepContext:
             for r, row in enumerate(rows):
                 bh[r, :len(row)] = row
             self._bt_dev[g][:R].copy_(self._bt_host[g][:R], non_blocking=True)
+            self.h2d_bytes += R * self.table_widths[g] * 4
             self.block_tables.append(self._bt_dev[g][:R])
         self.n_tokens, self.n_reqs, self.n_want = T, R, W
         self.token_capacity = int(token_capacity or T)

@@ -50,9 +50,14 @@ def require_cuda(device=None):
     lib()
 
 
+launches = 0          # kernel launches made through this module (every entry point launches one kernel)
+
+
 def _check(rc, name):
+    global launches
     if rc != 0:
         raise KernelError(f"{name}: {lib().ferrum_last_error().decode()}")
+    launches += 1
 
 
 def _ptr(t):
