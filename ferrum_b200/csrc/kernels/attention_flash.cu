@@ -1,0 +1,409 @@
+// Paged causal GQA attention on the tensor cores (bfloat16), for prompt portions and for
+// decoded tokens, with an optional split of the key range across CTAs.
+//
+// One CTA handles one work item x one KV head.  A work item is a tile of BM "packed rows"
+// of one request and a key range [kv_begin, kv_end).  Packed row r of a request stands for
+// token r / G, query head (kv_head * G + r % G), G = Hq / Hkv: all query heads that share a
+// KV head sit in the same tile, so a K/V tile loaded once serves G heads.  A decoded token
+// is a tile of G rows (BM = 16, four warps split every 64-key tile between them); a prompt
+// portion is a run of BM = 64 row tiles (four warps own 16 rows each).
+//
+// Per 64-key tile: K and V rows are gathered page by page with cp.async into swizzled
+// shared memory (double buffered), S = Q K^T and O += P V run on mma.sync m16n8k16 with
+// float32 accumulators, and the softmax is the online one in float32 (scores scaled by
+// log2(e)/sqrt(D), exp2).  A work item that covers its rows' whole key range writes the
+// output; otherwise it writes (m, l, O) partials and `attention_combine` merges the
+// splits in a fixed order.  Same formulas as the float32 kernel (attention_generic.cu);
+// the reference computes them one head and one position at a time
+// (crates/model/src/llama.rs:220-247).
+#include "common.cuh"
+
+namespace {
+
+struct FlashParams {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  const __nv_bfloat16* kv_plane;
+  const int* block_table;
+  const int* q_start;   // [R + 1] first token of each request in this batch
+  const int* pos0;      // [R] cached positions before this step
+  const int* work;      // [n_work][8]: req, row0, kv_begin, kv_end, n_splits, part_slot, -, -
+  float* part_o;        // [slot][Hkv][BM][D]
+  float* part_ml;       // [slot][Hkv][BM][2]
+  long long page_stride;
+  int ldq, ldo, page_size, table_width;
+  int Hq, Hkv, G, window;
+  float scale_log2;
+};
+
+constexpr int BN = 64;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// element (row, col) of a [rows][D] bfloat16 tile whose 16-byte chunks are XOR-swizzled by row
+template <int D>
+__device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row, int col) {
+  const int chunk = (col >> 3) ^ (row & 7);
+  return base + row * D + (chunk << 3) + (col & 7);
+}
+
+template <int D, int WM, int WN>
+__global__ void __launch_bounds__(WM * WN * 32)
+flash_kernel(const FlashParams p) {
+  constexpr int BM = 16 * WM;
+  constexpr int NT = WM * WN * 32;
+  constexpr int KW = BN / WN;   // keys of a tile that one warp handles
+  constexpr int CH = D / 8;     // 16-byte chunks per row
+  static_assert(KW % 16 == 0, "a warp needs at least 16 keys per tile");
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BM][D]
+  __nv_bfloat16* sK = sQ + BM * D;                                  // [2][BN][D]
+  __nv_bfloat16* sV = sK + 2 * BN * D;                              // [2][BN][D]
+
+  const int* wk = p.work + (size_t)blockIdx.x * 8;
+  const int req = wk[0], row0 = wk[1], kv_begin = wk[2], kv_end = wk[3], n_splits = wk[4], part = wk[5];
+  const int kvh = blockIdx.y;
+  const int G = p.G;
+  const int qs = p.q_start[req];
+  const int n_rows = (p.q_start[req + 1] - qs) * G;
+  const int pos0 = p.pos0[req];
+  const int* bt = p.block_table + (size_t)req * p.table_width;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp % WM, wn = warp / WM;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int ps = p.page_size;
+  const size_t v_off = (size_t)p.Hkv * ps * D;
+
+  // ---- Q tile -> shared memory
+  for (int idx = tid; idx < BM * CH; idx += NT) {
+    const int r = idx / CH, c = idx % CH;
+    const int pr = row0 + r;
+    __nv_bfloat16* dst = sQ + r * D + ((c ^ (r & 7)) << 3);
+    if (pr < n_rows) {
+      const __nv_bfloat16* src = p.q + (size_t)(qs + pr / G) * p.ldq + (size_t)(kvh * G + pr % G) * D + c * 8;
+      cp_async16(dst, src, 16);
+    } else {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  auto load_tile = [&](int buf, int key0) {
+    __nv_bfloat16* dk = sK + buf * BN * D;
+    __nv_bfloat16* dv = sV + buf * BN * D;
+    for (int idx = tid; idx < BN * CH; idx += NT) {
+      const int r = idx / CH, c = idx % CH;
+      const int key = key0 + r;
+      const bool valid = key < kv_end;
+      const __nv_bfloat16* src = p.kv_plane;
+      if (valid) {
+        const int page = bt[key / ps];
+        src += (size_t)page * p.page_stride + ((size_t)kvh * ps + key % ps) * D + c * 8;
+      }
+      const int off = r * D + ((c ^ (r & 7)) << 3);
+      cp_async16(dk + off, src, valid ? 16 : 0);
+      cp_async16(dv + off, valid ? src + v_off : src, valid ? 16 : 0);
+    }
+  };
+  const int n_tiles = (kv_end - kv_begin + BN - 1) / BN;
+  if (n_tiles > 0) load_tile(0, kv_begin);
+  cp_async_commit();
+
+  // per-thread row bookkeeping: this thread owns rows gid and gid + 8 of its warp's 16
+  int row_pos[2], row_lo[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int pr = row0 + wm * 16 + gid + h * 8;
+    row_ok[h] = pr < n_rows;
+    row_pos[h] = pos0 + pr / G;
+    row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  unsigned qf[D / 16][4];
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    if (it + 1 < n_tiles) load_tile(buf ^ 1, kv_begin + (it + 1) * BN);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int r = wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(qf[kk], tile_ptr<D>(sQ, r, kk * 16 + (lane >> 4) * 8));
+      }
+    }
+    __nv_bfloat16* tK = sK + buf * BN * D;
+    __nv_bfloat16* tV = sV + buf * BN * D;
+    const int key0 = kv_begin + it * BN + wn * KW;
+
+    // ---- S = Q K^T for this warp's 16 rows x KW keys
+    float s[KW / 8][4];
+#pragma unroll
+    for (int j = 0; j < KW / 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int nb = 0; nb < KW / 16; ++nb) {
+        unsigned b[4];
+        const int r = wn * KW + nb * 16 + (lane & 7) + (lane >> 4) * 8;
+        ldmatrix_x4(b, tile_ptr<D>(tK, r, kk * 16 + ((lane >> 3) & 1) * 8));
+        mma_bf16(s[2 * nb], qf[kk], b[0], b[1]);
+        mma_bf16(s[2 * nb + 1], qf[kk], b[2], b[3]);
+      }
+    }
+    // ---- mask, scale, online softmax
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < KW / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + j * 8 + tig * 2 + (e & 1);
+        const int h = e >> 1;
+        const bool keep = row_ok[h] && key <= row_pos[h] && key >= row_lo[h] && key < kv_end;
+        s[j][e] = keep ? s[j][e] * p.scale_log2 : -INFINITY;
+        mx[h] = fmaxf(mx[h], s[j][e]);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+      corr[h] = exp2f(m_run[h] - m_use[h]);   // 0 when nothing was seen before
+      m_run[h] = m_new;
+      l_run[h] *= corr[h];
+    }
+#pragma unroll
+    for (int j = 0; j < KW / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = exp2f(s[j][e] - m_use[e >> 1]);
+        s[j][e] = pv;
+        l_run[e >> 1] += pv;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      o[j][0] *= corr[0];
+      o[j][1] *= corr[0];
+      o[j][2] *= corr[1];
+      o[j][3] *= corr[1];
+    }
+    // ---- O += P V
+#pragma unroll
+    for (int ks = 0; ks < KW / 16; ++ks) {
+      unsigned a[4];
+      a[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+      a[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+      a[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+      a[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+      for (int db = 0; db < D / 16; ++db) {
+        unsigned b[4];
+        const int r = wn * KW + ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4_trans(b, tile_ptr<D>(tV, r, db * 16 + (lane >> 4) * 8));
+        mma_bf16(o[2 * db], a, b[0], b[1]);
+        mma_bf16(o[2 * db + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();  // everyone is done with this buffer before the next load overwrites it
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- each warp leaves (m, l, O) in shared memory; the WN partial results are merged
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  float* sO = reinterpret_cast<float*>(smem_raw);        // [WN][BM][D]
+  float* sML = sO + WN * BM * D;                          // [WN][BM][2]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = wm * 16 + gid + h * 8;
+    if (tig == 0) {
+      sML[(wn * BM + r) * 2] = m_run[h];
+      sML[(wn * BM + r) * 2 + 1] = l_run[h];
+    }
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      float2 v = make_float2(o[j][2 * h], o[j][2 * h + 1]);
+      *reinterpret_cast<float2*>(sO + ((size_t)(wn * BM + r)) * D + j * 8 + tig * 2) = v;
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < BM * (D / 4); idx += NT) {
+    const int r = idx / (D / 4), d = (idx % (D / 4)) * 4;
+    const int pr = row0 + r;
+    if (pr >= n_rows) continue;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WN; ++w) M = fmaxf(M, sML[(w * BM + r) * 2]);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < WN; ++w) {
+      const float mw = sML[(w * BM + r) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      L += sML[(w * BM + r) * 2 + 1] * f;
+      const float4 v = *reinterpret_cast<const float4*>(sO + ((size_t)(w * BM + r)) * D + d);
+      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+    }
+    if (n_splits == 1) {
+      const float inv = L > 0.f ? 1.0f / L : 0.f;
+      __nv_bfloat16* dst = p.out + (size_t)(qs + pr / G) * p.ldo + (size_t)(kvh * G + pr % G) * D + d;
+      uint2 packed;
+      packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+      packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(dst) = packed;
+    } else {
+      const size_t slot = ((size_t)part * p.Hkv + kvh) * BM + r;
+      *reinterpret_cast<float4*>(p.part_o + slot * D + d) = acc;
+      if (d == 0) {
+        p.part_ml[slot * 2] = M;
+        p.part_ml[slot * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Merges the splits of every (token, head) whose tile was split.  tile_info: per tile
+// [first part slot, n_splits]; req_tile0[r]: index of request r's first tile; token_list:
+// the tokens to visit (null: all n_tokens).
+template <int D>
+__global__ void __launch_bounds__(D / 4 < 32 ? 32 : D / 4)
+combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* part_ml, const int* q_start,
+               const int* req_of_token, const int* req_tile0, const int* tile_info, const int* token_list, int G,
+               int Hkv, int BM) {
+  const int t = token_list ? token_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
+  const int req = req_of_token[t];
+  const int kvh = head / G;
+  const int pr = (t - q_start[req]) * G + head % G;
+  const int* info = tile_info + 2 * (req_tile0[req] + pr / BM);
+  const int first = info[0], n = info[1];
+  if (n <= 1) return;
+  const int r = pr % BM;
+  const int d = threadIdx.x * 4;
+  if (d >= D) return;
+  float M = -INFINITY;
+  for (int s = 0; s < n; ++s) M = fmaxf(M, part_ml[(((size_t)(first + s) * Hkv + kvh) * BM + r) * 2]);
+  float L = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < n; ++s) {
+    const size_t slot = ((size_t)(first + s) * Hkv + kvh) * BM + r;
+    const float ms = part_ml[slot * 2];
+    const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+    L += part_ml[slot * 2 + 1] * f;
+    const float4 v = *reinterpret_cast<const float4*>(part_o + slot * D + d);
+    acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  uint2 packed;
+  packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+  packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(out + (size_t)t * ldo + (size_t)head * D + d) = packed;
+}
+
+template <int D, int WM, int WN>
+int launch_flash(const FlashParams& p, int n_work, cudaStream_t stream) {
+  constexpr int BM = 16 * WM;
+  constexpr int kv_bytes = 4 * BN * D * 2 + BM * D * 2;
+  constexpr int merge_bytes = WN * BM * (D + 2) * 4;
+  constexpr int smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_kernel<D, WM, WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    FERRUM_CHECK_ARG(e == cudaSuccess, "attention_flash: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid(n_work, p.Hkv);
+  flash_kernel<D, WM, WN><<<grid, WM * WN * 32, smem, stream>>>(p);
+  FERRUM_CHECK_LAUNCH("attention_flash");
+  return 0;
+}
+
+}  // namespace
+
+FERRUM_API int ferrum_attention_flash_supported(int D, int bm) { return (D == 64 || D == 128) && (bm == 16 || bm == 64); }
+
+// work: [n_work][8] int32 on the device (see FlashParams).  bm: 16 (a few rows per request,
+// key range split between four warps) or 64.
+FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo, const void* kv_plane,
+                                      long long page_stride, int page_size, const int* block_table, int table_width,
+                                      const int* q_start, const int* pos0, const int* work, int n_work, float* part_o,
+                                      float* part_ml, int Hq, int Hkv, int D, float scale, int window, int bm,
+                                      cudaStream_t stream) {
+  FERRUM_CHECK_ARG(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_flash: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
+  FERRUM_CHECK_ARG(ferrum_attention_flash_supported(D, bm), "attention_flash: head size %d with row tile %d is not built; "
+                   "use the generic kernel", D, bm);
+  FERRUM_CHECK_ARG(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                   ((uintptr_t)kv_plane & 15) == 0, "attention_flash: operands must be 16-byte aligned");
+  FERRUM_CHECK_ARG(page_size > 0 && table_width > 0 && window >= 0 && n_work >= 0, "attention_flash: bad arguments");
+  if (n_work == 0) return 0;
+  FlashParams p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.kv_plane = (const __nv_bfloat16*)kv_plane;
+  p.block_table = block_table; p.q_start = q_start; p.pos0 = pos0; p.work = work;
+  p.part_o = part_o; p.part_ml = part_ml; p.page_stride = page_stride;
+  p.ldq = ldq; p.ldo = ldo; p.page_size = page_size; p.table_width = table_width;
+  p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  if (D == 64 && bm == 16) return launch_flash<64, 1, 4>(p, n_work, stream);
+  if (D == 64 && bm == 64) return launch_flash<64, 4, 1>(p, n_work, stream);
+  if (D == 128 && bm == 16) return launch_flash<128, 1, 4>(p, n_work, stream);
+  return launch_flash<128, 4, 1>(p, n_work, stream);
+}
+
+FERRUM_API int ferrum_attention_combine(void* out, int ldo, const float* part_o, const float* part_ml,
+                                        const int* q_start, const int* req_of_token, const int* req_tile0,
+                                        const int* tile_info, const int* token_list, int n_tokens, int Hq, int Hkv,
+                                        int D, int bm, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(D == 64 || D == 128, "attention_combine: head size %d is not built", D);
+  if (n_tokens == 0) return 0;
+  dim3 grid(n_tokens, Hq);
+  FERRUM_CHECK_ARG(grid.y <= 65535, "attention_combine: too many heads");
+  if (D == 64)
+    combine_kernel<64><<<grid, 32, 0, stream>>>((__nv_bfloat16*)out, ldo, part_o, part_ml, q_start, req_of_token,
+                                               req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
+  else
+    combine_kernel<128><<<grid, 32, 0, stream>>>((__nv_bfloat16*)out, ldo, part_o, part_ml, q_start, req_of_token,
+                                                req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
+  FERRUM_CHECK_LAUNCH("attention_combine");
+  return 0;
+}

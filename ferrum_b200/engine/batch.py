@@ -64,6 +64,8 @@ class StepContext:
             self._bt_host = [t.pin_memory() for t in self._bt_host]
         self._bt_dev = [torch.empty((self.max_requests, w), dtype=torch.int32, device=device) for w in self.table_widths]
         self._splitk_counters = torch.zeros(4096, dtype=torch.int32, device=device)
+        from .attn_plan import AttentionPlans
+        self._attn_plans = AttentionPlans(device)
         self.n_tokens = self.n_reqs = self.n_want = 0
         self.h2d_bytes = 0            # bytes copied to the device by the last fill
         self.token_capacity = self.want_capacity = 0
@@ -117,6 +119,11 @@ class StepContext:
         self.want_capacity = max(W, 1)
         self.max_q_len = max(self.h_q_len) if R else 0
         self.max_kv_len = max((p + n for p, n in zip(self.h_pos0, self.h_q_len)), default=0)
+        self._attn_plans.reset()
+
+    def attention_plans(self, G, window, Hkv):
+        """The step's work lists for the tensor-core attention kernel (built on first use)."""
+        return self._attn_plans.get(self, G, window, Hkv)
 
     # ------------------------------------------------------------------ scratch
     def buf(self, name, shape, dtype):

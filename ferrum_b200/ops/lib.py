@@ -207,6 +207,32 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
                                           c_float(scale), c_int(window), _ptr(err), _stream()), "attention_generic")
 
 
+def attention_flash_supported(dtype, D, page_stride=0):
+    """True when the tensor-core attention kernel is built for this dtype and head size."""
+    return dtype == torch.bfloat16 and bool(lib().ferrum_attention_flash_supported(c_int(D), c_int(16)))
+
+
+def attention_flash(q, out, kv_plane, page_stride, page_size, block_table, q_start, pos0, work, n_work, part_o,
+                    part_ml, Hq, Hkv, D, scale, window, bm):
+    """Tensor-core attention over the work items of one row-tile class (bm 16 or 64)."""
+    _need(q, torch.bfloat16, "q", 2); _need(out, torch.bfloat16, "out", 2); _need(kv_plane, torch.bfloat16, "kv_plane")
+    _need(block_table, torch.int32, "block_table", 2); _need(work, torch.int32, "work", 1)
+    _check(lib().ferrum_attention_flash(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(kv_plane),
+                                        c_longlong(page_stride), c_int(page_size), _ptr(block_table),
+                                        c_int(block_table.shape[1]), _ptr(q_start), _ptr(pos0), _ptr(work),
+                                        c_int(n_work), _ptr(part_o), _ptr(part_ml), c_int(Hq), c_int(Hkv), c_int(D),
+                                        c_float(scale), c_int(window), c_int(bm), _stream()), "attention_flash")
+
+
+def attention_combine(out, part_o, part_ml, q_start, req_of_token, req_tile0, tile_info, token_list, n_tokens, Hq, Hkv,
+                      D, bm):
+    """Merges the key-range splits written by attention_flash into `out`."""
+    _check(lib().ferrum_attention_combine(_ptr(out), c_int(out.stride(0)), _ptr(part_o), _ptr(part_ml), _ptr(q_start),
+                                          _ptr(req_of_token), _ptr(req_tile0), _ptr(tile_info), _ptr(token_list),
+                                          c_int(n_tokens), c_int(Hq), c_int(Hkv), c_int(D), c_int(bm), _stream()),
+           "attention_combine")
+
+
 def swiglu(gu, act, n_tokens, F):
     """act[t, f] = silu(gu[t, f]) * gu[t, F + f]."""
     _need(gu, None, "gu", 2); _need(act, gu.dtype, "act", 2)

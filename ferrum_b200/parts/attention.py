@@ -54,6 +54,27 @@ class PagedAttention(Mixer):
                              cache.page_size, Hq, Hkv, D, rot.rope_dim if rot is not None else 0,
                              rot.pairing if rot is not None else 0, cache.writes, ctx.err)
         out = ctx.buf("attn_out", (ctx.token_capacity, qw), self.dtype)
-        ops.attention_generic(qkv, out, T, ctx.positions, ctx.req_of_token, table, cache.plane, cache.page_stride,
-                              cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err)
+        if ops.attention_flash_supported(self.dtype, D):
+            self._flash(qkv, out, ctx, cache, table)
+        else:
+            ops.attention_generic(qkv, out, T, ctx.positions, ctx.req_of_token, table, cache.plane, cache.page_stride,
+                                  cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err)
         linear(out, self.w_output_weight, residual, RESIDUAL, ctx, M=T)
+
+    def _flash(self, qkv, out, ctx, cache, table):
+        """Tensor-core path: one launch per row-tile class of the step's plan, plus a merge
+        launch where key ranges were split."""
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        for plan in ctx.attention_plans(Hq // Hkv, self.window, Hkv):
+            if plan is None:
+                continue
+            part_o = part_ml = None
+            if plan.n_slots:
+                part_o = ctx.buf("attn_part_o", (plan.n_slots * Hkv * plan.bm * D,), torch.float32)
+                part_ml = ctx.buf("attn_part_ml", (plan.n_slots * Hkv * plan.bm * 2,), torch.float32)
+            ops.attention_flash(qkv, out, cache.plane, cache.page_stride, cache.page_size, table, ctx.q_start,
+                                ctx.pos0, plan.work, plan.n_work, part_o, part_ml, Hq, Hkv, D, self.scale,
+                                self.window, plan.bm)
+            if plan.n_comb:
+                ops.attention_combine(out, part_o, part_ml, ctx.q_start, ctx.req_of_token, plan.req_tile0,
+                                      plan.tile_info, plan.comb_tokens, plan.n_comb, Hq, Hkv, D, plan.bm)

@@ -27,7 +27,17 @@ TINY_C = {
     "num_key_value_heads": 3, "head_dim": 48, "intermediate_size": 200, "vocab_size": 301, "rope_theta": 2500.0,
     "rope_scaling": None, "max_position_embeddings": 512, "rms_norm_eps": 3e-6, "tie_word_embeddings": False,
 }
-TINY = {"A": (TINY_A, 0, "float32"), "B": (TINY_B, 1, "bfloat16"), "C": (TINY_C, 2, "float32")}
+# head size 64 and 16-byte rows everywhere: the tensor-core kernels (tcgen05 products, flash
+# attention) run on this one; A, B and C mostly take the generic kernels.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 192, "num_hidden_layers": 2, "num_attention_heads": 6,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 328, "vocab_size": 424, "rope_theta": 100000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 2.0,
+                     "original_max_position_embeddings": 32},
+    "max_position_embeddings": 1024, "rms_norm_eps": 2e-5, "tie_word_embeddings": True,
+}
+TINY = {"A": (TINY_A, 0, "float32"), "B": (TINY_B, 1, "bfloat16"), "C": (TINY_C, 2, "float32"),
+        "D": (TINY_D, 3, "bfloat16")}
 
 
 def pytest_configure(config):

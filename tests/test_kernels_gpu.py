@@ -258,6 +258,73 @@ def test_attention_finds_one_far_key(ops, dtype, far_key):
     assert np.abs(got - ref).max() <= (1e-4 if dtype == torch.float32 else 2e-2)
 
 
+def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window):
+    """Drive the tensor-core attention the way the attention part does: plan, launch per
+    row-tile class, merge splits."""
+    from ferrum_b200.engine.attn_plan import build_host
+    T = sum(qlens)
+    out = torch.full((T, Hq * D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    pos0 = [n - ql for n, ql in zip(lens, qlens)]
+    qs = np.concatenate([[0], np.cumsum(qlens)]).astype(np.int32)
+    req = np.repeat(np.arange(len(lens)), qlens).astype(np.int32)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.int32).cuda()
+    n_split_items = 0
+    for h in build_host(qlens, pos0, Hq // Hkv, window, Hkv):
+        if h is None:
+            continue
+        part_o = torch.empty(max(1, h["n_slots"] * Hkv * h["bm"] * D), device="cuda")
+        part_ml = torch.empty(max(1, h["n_slots"] * Hkv * h["bm"] * 2), device="cuda")
+        ops.attention_flash(q, out, plane, plane.stride(0), ps, table, dev(qs), dev(pos0), dev(h["work"]), h["n_work"],
+                            part_o, part_ml, Hq, Hkv, D, 1.0 / math.sqrt(D), window, h["bm"])
+        if h["comb"].size:
+            ops.attention_combine(out, part_o, part_ml, dev(qs), dev(req), dev(h["req_tile0"]), dev(h["tile_info"]),
+                                  dev(h["comb"]), int(h["comb"].size), Hq, Hkv, D, h["bm"])
+        n_split_items += h["n_slots"]
+    return out, n_split_items
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(4, 2, 64, 16, 0), (6, 2, 64, 8, 0), (8, 1, 128, 16, 0), (32, 8, 128, 16, 0),
+                                                (3, 3, 128, 32, 0), (4, 2, 64, 16, 21), (8, 2, 128, 16, 300),
+                                                (40, 2, 64, 16, 0)])
+def test_attention_flash(ops, Hq, Hkv, D, ps, window):
+    """Mixed batch on the tensor-core kernel: a whole prompt, a late portion of a long
+    request, decoded tokens at short and long contexts (the long ones are split)."""
+    lens = [137, 1500, 65, 1, 2300, 700]
+    qlens = [137, 70, 1, 1, 1, 2]
+    plane, table, ks, vs = paged_setup(lens, Hkv, D, ps, torch.bfloat16, 17)
+    g = torch.Generator(device="cuda").manual_seed(18)
+    T = sum(qlens)
+    q = torch.randn(T, Hq * D, device="cuda", generator=g).bfloat16()
+    out, n_split = run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window)
+    assert n_split > 0 or window > 0
+    t0 = 0
+    for r, (n, ql) in enumerate(zip(lens, qlens)):
+        qfull = np.zeros((n, Hq, D))
+        qfull[n - ql:] = q[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
+        ref = P.attention(qfull, ks[r].double().cpu().numpy(), vs[r].double().cpu().numpy(), window)[n - ql:]
+        got = out[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
+        assert np.abs(got - ref).max() <= 1.5e-2, (r, np.abs(got - ref).max())
+        t0 += ql
+
+
+@pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 1023, 1024, 2999])
+@pytest.mark.parametrize("qlen", [1, 40])
+def test_attention_flash_finds_one_far_key(ops, far_key, qlen):
+    """As for the generic kernel: one strongly matching key among 3000, at tile, page and
+    split edges, for a decoded token (split key range) and for a prompt portion."""
+    Hq = Hkv = 2; D = 64; ps = 16; n = 3000
+    plane, table, ks, vs = paged_setup([n], Hkv, D, ps, torch.bfloat16, 19)
+    kq = ks[0][far_key].float()
+    qrow = (kq * (40.0 * math.sqrt(D) / kq.pow(2).sum(-1, keepdim=True))).reshape(1, Hq * D)
+    q = qrow.repeat(qlen, 1).bfloat16()
+    out, _ = run_flash(ops, q, [n], [qlen], table, plane, ps, Hq, Hkv, D, 0)
+    qfull = np.zeros((n, Hq, D)); qfull[n - qlen:] = q.double().cpu().numpy().reshape(qlen, Hq, D)
+    ref = P.attention(qfull, ks[0].double().cpu().numpy(), vs[0].double().cpu().numpy())[n - qlen:]
+    got = out.double().cpu().numpy().reshape(qlen, Hq, D)
+    assert np.abs(ref[-1] - vs[0][far_key].double().cpu().numpy()).max() < 0.05
+    assert np.abs(got - ref).max() <= 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("pairing", ["adjacent", "half"])
 @pytest.mark.parametrize("Hq,Hkv,D,R", [(4, 2, 16, 16), (3, 1, 48, 32), (2, 2, 128, 128)])

@@ -7,7 +7,7 @@ from conftest import TINY
 
 pytestmark = pytest.mark.gpu
 
-CASES = [(m, d) for m in ("A", "B", "C") for d in ("float32", "bfloat16")]
+CASES = [(m, d) for m in ("A", "B", "C", "D") for d in ("float32", "bfloat16")]
 
 
 def session(model_dirs, name, dtype, max_tokens, **kw):
