@@ -147,7 +147,7 @@ def main():
     arch = registry.lookup(cfgd["architectures"][0])
     cfg = arch.read_config(cfgd)
     ctx_len, B = args.context, args.batch
-    max_len = ctx_len + W + K + 64
+    max_len = ctx_len + W + K + 128 + 4 * args.batch
     page = 16
     torch.manual_seed(0)
     model = arch.build(cfg, torch.bfloat16, "cuda", max_positions=max_len)
@@ -247,10 +247,10 @@ def main():
         eng = Engine(model=model, page_size=page, num_pages=(B * (max_len + page)) // page, max_batch_tokens=8192,
                      max_batch_seqs=B, max_model_len=max_len)
         for _ in range(B):
-            eng.submit(tokens(ctx_len - 1), W + K + 8)
-        n_tok = 0
-        while n_tok < B:                               # prompts, untimed; ends with every request decoding
-            n_tok += sum(1 for ev in eng.step() if ev.kind == "token")
+            eng.submit(tokens(ctx_len - 1), W + K + 64 + 4 * B)
+        started = set()
+        while len(started) < B:                        # prompts, untimed; ends with every request decoding
+            started.update(ev.id for ev in eng.step() if ev.kind == "token")
         for _ in range(W):
             eng.step()
         torch.cuda.synchronize()
