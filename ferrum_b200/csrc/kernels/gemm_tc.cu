@@ -1,22 +1,27 @@
 // bfloat16 matrix product on the tcgen05 tensor cores: out[t, n] = sum_k x[t, k] * w[n, k].
 //
-// Orientation: the weight rows are the M side of the instruction (128 rows of W per CTA,
+// Orientation: the weight rows are the M side of the instruction (128 rows of W per tile,
 // one row per TMEM lane) and the tokens are the N side (BT columns, 16..256).  The same
 // kernel therefore serves a 2048-token prompt (BT = 256) and a single decoded token
-// (BT = 16): in decode the tensor cores idle and the CTA is a TMA streaming engine for its
-// slice of the weights.  Both operands are K-major tiles of 64 bfloat16 per row, brought in
-// by TMA with the 128-byte swizzle into a ring of stages; one thread issues the MMAs, the
-// accumulator lives in tensor memory, four warps read it back for the epilogue.
+// (BT = 16): in decode the tensor cores idle and every CTA is a TMA streaming engine for
+// its share of the weights.  Both operands are K-major tiles of 64 bfloat16 per row, brought
+// in by TMA with the 128-byte swizzle into a ring of stages; one thread issues the MMAs, the
+// accumulators live in tensor memory, four warps read them back for the epilogue.
 //
-// Roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA issuer,
-// warps 2..5 = epilogue.  DUAL computes two accumulators from two weight tiles (rows n and
-// dual_offset + n) against the same tokens; the SwiGLU epilogue combines them, so gate and
-// up need no interleaving in memory.
+// Persistent, stream-K: the work is the line of all (tile, k-block) units, tile-major.  The
+// grid is one CTA per SM and CTA c owns the contiguous units [c*U/P, (c+1)*U/P), so every SM
+// streams the same number of bytes whatever the shape.  A CTA's range is a sequence of
+// segments, one per tile it touches.  A segment that covers the whole K of its tile ends in
+// the epilogue proper; a partial one writes its float32 accumulator to the workspace and
+// bumps the tile's counter, and the CTA that arrives last adds the partials in K order (so
+// the sum does not depend on arrival order) and runs the epilogue.  Nobody waits for anybody.
+// Counters are left at zero for the next launch.
 //
-// Split-K: grid.z CTAs share a tile's K range.  Each writes its float32 partial tile to the
-// workspace; the CTA that arrives last at the tile's counter adds the partials in split
-// order (so the sum does not depend on arrival order) and runs the epilogue.  Nobody waits
-// for anybody.  The counter is left at zero for the next launch.
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA issuer, warps
+// 2..5 = epilogue.  Two accumulators in tensor memory let segment i+1 be computed while
+// segment i is read back.  DUAL computes two products per segment, from weight rows n and
+// dual_offset + n against the same tokens; the SwiGLU epilogue combines them, so gate and up
+// need no interleaving in memory.
 //
 // Every mbarrier wait is bounded; on a timeout the kernel raises the error flag, lets the
 // copies in flight land, frees its tensor memory and returns.
@@ -42,10 +47,10 @@ struct TcParams {
   int* err;
   int M, N, K, ldo;
   int epilogue;
-  int dual_offset;  // row of the second weight tile relative to the first (DUAL)
+  int dual_offset;   // row of the second weight tile relative to the first (DUAL)
 };
 
-constexpr int TILE_N = 128;  // weight rows per CTA (the instruction's M)
+constexpr int TILE_N = 128;  // weight rows per tile (the instruction's M)
 constexpr int TILE_K = 64;   // bfloat16 per row of a stage: 128 bytes, one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = TILE_N * TILE_K * 2;
@@ -55,21 +60,61 @@ struct TcConfig {
   static constexpr int B_BYTES = BT * TILE_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
   static constexpr int BUDGET = 196 * 1024;
-  static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
+  static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 10 ? 10 : (BUDGET / STAGE_BYTES);
   static constexpr int ACC_COLS = BT * (DUAL ? 2 : 1);
-  static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
+  static constexpr int ALL_COLS = 2 * ACC_COLS;  // two accumulators
+  static constexpr int TMEM_COLS = ALL_COLS <= 32 ? 32 : (ALL_COLS <= 64 ? 64 : (ALL_COLS <= 128 ? 128 : (ALL_COLS <= 256 ? 256 : 512)));
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static_assert(STAGES >= 2, "tile too large for the shared memory budget");
+  static_assert(ALL_COLS <= 512, "accumulators do not fit tensor memory");
 };
 
-__device__ __forceinline__ void tc_apply(const TcParams& p, int t, int n, float a0, float a1) {
-  const size_t o = (size_t)t * p.ldo + n;
+// Epilogue of 16 token columns t_base..t_base+15 of feature n.  Loads come first and
+// stores last, so that the 16 read-modify-writes of the residual overlap instead of
+// queueing behind each other.
+__device__ __forceinline__ void tc_apply16(const TcParams& p, int t_base, int n, const float (&a0)[16], const float (&a1)[16]) {
+  const int valid = p.M - t_base;  // columns j < valid exist
+  if (valid <= 0) return;
+  const size_t o = (size_t)t_base * p.ldo + n;
+  const size_t ld = (size_t)p.ldo;
   switch (p.epilogue) {
-    case TC_STORE_BF16: ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(a0); break;
-    case TC_STORE_F32: ((float*)p.out)[o] = a0; break;
-    case TC_RESIDUAL: ((float*)p.out)[o] += a0; break;
-    case TC_SWIGLU: ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(a0 / (1.0f + __expf(-a0)) * a1); break;
+    case TC_STORE_BF16: {
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + o;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (j < valid) out[j * ld] = __float2bfloat16_rn(a0[j]);
+      break;
+    }
+    case TC_STORE_F32: {
+      float* out = (float*)p.out + o;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (j < valid) out[j * ld] = a0[j];
+      break;
+    }
+    case TC_RESIDUAL: {
+      float* out = (float*)p.out + o;
+      float r[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) r[j] = j < valid ? out[j * ld] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (j < valid) out[j * ld] = r[j] + a0[j];
+      break;
+    }
+    case TC_SWIGLU: {
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + o;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (j < valid) out[j * ld] = __float2bfloat16_rn(a0[j] / (1.0f + __expf(-a0[j])) * a1[j]);
+      break;
+    }
   }
+}
+
+// The CTA that owns unit u when CTA c owns [c*U/P, (c+1)*U/P).
+__device__ __forceinline__ int unit_owner(long long u, long long U, int P) {
+  return (int)(((u + 1) * P + U - 1) / U) - 1;
 }
 
 template <int BT, bool DUAL>
@@ -79,22 +124,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE_BYTES);  // full[S], empty[S], acc_full
+  uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE_BYTES);  // full[S], empty[S], acc_full[2], acc_empty[2]
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int is_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TILE_N, t0 = blockIdx.y * BT;
-  const int splits = gridDim.z, split = blockIdx.z;
+  const int P = gridDim.x, cta = blockIdx.x;
   const int nkb = (p.K + TILE_K - 1) / TILE_K;
-  const int kb_begin = (int)((long long)nkb * split / splits), kb_end = (int)((long long)nkb * (split + 1) / splits);
+  const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
+  const int tiles_t = (p.M + BT - 1) / BT;
+  const long long U = (long long)tiles_n * tiles_t * nkb;
+  const long long u_begin = U * cta / P, u_end = U * (cta + 1) / P;
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_u32(bars);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  const uint32_t acc_bar = bar_base + 8u * (2 * STAGES);
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -105,7 +153,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+    }
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -123,12 +174,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      long long tile = u_begin / nkb;
+      int kb = (int)(u_begin % nkb);
+      for (long long u = u_begin; u < u_end; ++u) {
         if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p)) {
           abort_flag = 1;
           atomicExch(p.err, 10);
           break;
         }
+        const int n0 = (int)(tile % tiles_n) * TILE_N, t0 = (int)(tile / tiles_n) * BT;
         const uint32_t a = smem_base + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
         tma_load_2d(a, &tmap_w, full_bar(s), kb * TILE_K, n0);
@@ -138,6 +192,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           s = 0;
           phase ^= 1;
         }
+        if (++kb == nkb) {
+          kb = 0;
+          ++tile;
+        }
       }
     }
   } else if (warp == 1) {
@@ -146,101 +204,136 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       const uint32_t idesc = umma_idesc_bf16(TILE_N, BT);
       int s = 0;
       uint32_t phase = 0;
+      int seg = 0;
+      long long u = u_begin;
       bool ok = true;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
-        if (!mbar_wait(full_bar(s), phase, abort_p)) {
+      while (ok && u < u_end) {
+        const long long tile = u / nkb;
+        const long long seg_end = min(u_end, (tile + 1) * (long long)nkb);
+        const int buf = seg & 1, use = seg >> 1;
+        if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, abort_p)) {
           abort_flag = 1;
-          atomicExch(p.err, 11);
-          ok = false;
+          atomicExch(p.err, 13);
           break;
         }
         tc_fence_after();
-        const uint32_t a = smem_base + s * Cfg::STAGE_BYTES;
-        const uint64_t a_desc = umma_desc_k_sw128(a);
-        const uint64_t a2_desc = umma_desc_k_sw128(a + A_BYTES);
-        const uint64_t b_desc = umma_desc_k_sw128(a + A_BYTES * (DUAL ? 2 : 1));
+        const uint32_t d0 = tmem_base + buf * Cfg::ACC_COLS;
+        bool first = true;
+        for (; u < seg_end; ++u) {
+          if (!mbar_wait(full_bar(s), phase, abort_p)) {
+            abort_flag = 1;
+            atomicExch(p.err, 11);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a = smem_base + s * Cfg::STAGE_BYTES;
+          const uint64_t a_desc = umma_desc_k_sw128(a);
+          const uint64_t a2_desc = umma_desc_k_sw128(a + A_BYTES);
+          const uint64_t b_desc = umma_desc_k_sw128(a + A_BYTES * (DUAL ? 2 : 1));
 #pragma unroll
-        for (int kk = 0; kk < TILE_K / UMMA_K; ++kk) {
-          const bool acc = (kb > kb_begin) || (kk > 0);
-          const uint64_t adv = (uint64_t)(kk * UMMA_K * 2 >> 4);  // 32 bytes per step, in 16-byte units
-          umma_bf16(tmem_base, a_desc + adv, b_desc + adv, idesc, acc);
-          if (DUAL) umma_bf16(tmem_base + BT, a2_desc + adv, b_desc + adv, idesc, acc);
+          for (int kk = 0; kk < TILE_K / UMMA_K; ++kk) {
+            const bool acc = !first || kk > 0;
+            const uint64_t adv = (uint64_t)(kk * UMMA_K * 2 >> 4);  // 32 bytes per step, in 16-byte units
+            umma_bf16(d0, a_desc + adv, b_desc + adv, idesc, acc);
+            if (DUAL) umma_bf16(d0 + BT, a2_desc + adv, b_desc + adv, idesc, acc);
+          }
+          first = false;
+          umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
         }
-        umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
-        if (++s == STAGES) {
-          s = 0;
-          phase ^= 1;
-        }
+        if (ok) umma_commit(acc_full_bar(buf));
+        ++seg;
       }
-      if (ok) umma_commit(acc_bar);
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
     const int n_local = quarter * 32 + lane;
-    const int n = n0 + n_local;
     const int ep_tid = threadIdx.x - 64;
-    bool ok = mbar_wait(acc_bar, 0, abort_p);
-    ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
-    if (!ok && lane == 0) {
-      abort_flag = 1;
-      atomicExch(p.err, 12);
-    }
-    tc_fence_after();
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    if (ok && splits == 1) {
+    const size_t tile_floats = (size_t)Cfg::ACC_COLS * TILE_N;
+    int seg = 0;
+    long long u = u_begin;
+    while (u < u_end) {
+      const long long tile = u / nkb;
+      const int kb0 = (int)(u % nkb);
+      const long long seg_end = min(u_end, (tile + 1) * (long long)nkb);
+      const bool whole = kb0 == 0 && seg_end == (tile + 1) * (long long)nkb;
+      const int buf = seg & 1, use = seg >> 1;
+      bool ok = mbar_wait(acc_full_bar(buf), use & 1, abort_p);
+      if (!ok) abort_flag = 1;
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps agree on going on
+      if (abort_flag) {
+        if (ep_tid == 0) atomicExch(p.err, 12);
+        break;
+      }
+      tc_fence_after();
+      const int n0 = (int)(tile % tiles_n) * TILE_N, t0 = (int)(tile / tiles_n) * BT;
+      const int n = n0 + n_local;
+      const uint32_t acc_addr = lane_addr + buf * Cfg::ACC_COLS;
+      if (whole) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BT; c0 += 16) {
-        float v0[16], v1[16];
-        tmem_ld16(lane_addr + c0, v0);
-        if (DUAL) tmem_ld16(lane_addr + BT + c0, v1);
-        if (n < p.N) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c0 + j;
-            if (t < p.M) tc_apply(p, t, n, v0[j], DUAL ? v1[j] : 0.f);
-          }
+        for (int c0 = 0; c0 < BT; c0 += 16) {
+          float v0[16], v1[16];
+          tmem_ld16(acc_addr + c0, v0);
+          if (DUAL) tmem_ld16(acc_addr + BT + c0, v1);
+          if (n < p.N) tc_apply16(p, t0 + c0, n, v0, DUAL ? v1 : v0);
         }
-      }
-    } else if (ok) {
-      // partial tile -> workspace [tile][split][column][lane]
-      const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
-      float* ws = p.workspace + (tile * splits + split) * (size_t)(Cfg::ACC_COLS * TILE_N);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+      } else {
+        // partial tile -> workspace [cta][slot][column][lane]; a CTA has at most two partial
+        // segments: slot 0 if the segment lies in the tile where its range begins, else slot 1
+        const int c_first = unit_owner(tile * nkb, U, P), c_last = unit_owner(tile * nkb + nkb - 1, U, P);
+        const int n_contrib = c_last - c_first + 1;
+        float* ws = p.workspace + ((size_t)cta * 2 + (u_begin / nkb == tile ? 0 : 1)) * tile_floats;
 #pragma unroll 1
-      for (int c0 = 0; c0 < Cfg::ACC_COLS; c0 += 16) {
-        float v[16];
-        tmem_ld16(lane_addr + c0, v);
+        for (int c0 = 0; c0 < Cfg::ACC_COLS; c0 += 16) {
+          float v[16];
+          tmem_ld16(acc_addr + c0, v);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) ws[(size_t)(c0 + j) * TILE_N + n_local] = v[j];
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ep_tid == 0) {
-        const int old = atomicAdd(p.counters + tile, 1);
-        if (old == splits - 1) {
-          is_last = 1;
-          p.counters[tile] = 0;
+          for (int j = 0; j < 16; ++j) ws[(size_t)(c0 + j) * TILE_N + n_local] = v[j];
         }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (is_last) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
         __threadfence();
-        const float* base = p.workspace + tile * splits * (size_t)(Cfg::ACC_COLS * TILE_N);
-        if (n < p.N) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ep_tid == 0) {
+          const int old = atomicAdd(p.counters + tile, 1);
+          is_last = old == n_contrib - 1;
+          if (is_last) p.counters[tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (is_last) {
+          __threadfence();
+          if (n < p.N) {
 #pragma unroll 1
-          for (int c = 0; c < BT; ++c) {
-            const int t = t0 + c;
-            if (t >= p.M) break;
-            float a0 = 0.f, a1 = 0.f;
-            for (int s = 0; s < splits; ++s) {
-              const float* wsp = base + (size_t)s * (Cfg::ACC_COLS * TILE_N);
-              a0 += __ldcg(wsp + (size_t)c * TILE_N + n_local);
-              if (DUAL) a1 += __ldcg(wsp + (size_t)(BT + c) * TILE_N + n_local);
+            for (int c0 = 0; c0 < BT && t0 + c0 < p.M; c0 += 16) {
+              float a0[16], a1[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) a0[j] = a1[j] = 0.f;
+              for (int cc = c_first; cc <= c_last; ++cc) {  // K order; 16 (or 32) loads in flight per thread
+                const float* wsp = p.workspace + ((size_t)cc * 2 + ((U * cc / P) / nkb == tile ? 0 : 1)) * tile_floats +
+                                   (size_t)c0 * TILE_N + n_local;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  a0[j] += __ldcg(wsp + (size_t)j * TILE_N);
+                  if (DUAL) a1[j] += __ldcg(wsp + (size_t)(BT + j) * TILE_N);
+                }
+              }
+              tc_apply16(p, t0 + c0, n, a0, a1);
             }
-            tc_apply(p, t, n, a0, a1);
           }
         }
       }
+      u = seg_end;
+      ++seg;
     }
     tc_fence_before();
   }
@@ -329,7 +422,7 @@ static int get_tensor_map(const void* ptr, long long rows, long long cols, long 
 }
 
 template <int BT, bool DUAL>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int splits, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int n_ctas, cudaStream_t stream) {
   using Cfg = TcConfig<BT, DUAL>;
   static bool configured = false;
   if (!configured) {
@@ -337,19 +430,20 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((p.N + TILE_N - 1) / TILE_N, (p.M + BT - 1) / BT, splits);
-  FERRUM_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
-  gemm_tc_kernel<BT, DUAL><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(mw, mx, p);
+  gemm_tc_kernel<BT, DUAL><<<n_ctas, 192, Cfg::SMEM_BYTES, stream>>>(mw, mx, p);
   FERRUM_CHECK_LAUNCH("gemm_tc");
   return 0;
 }
 
-// Workspace floats one launch needs (0 without split-K); also the number of tile counters.
-FERRUM_API long long ferrum_gemm_tc_workspace(int M, int N, int bt, int dual, int splits, int* n_tiles) {
-  const long long tiles = (long long)((N + TILE_N - 1) / TILE_N) * ((M + bt - 1) / bt);
-  if (n_tiles) *n_tiles = (int)tiles;
-  if (splits <= 1) return 0;
-  return tiles * splits * (long long)(bt * (dual ? 2 : 1)) * TILE_N;
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaDeviceProp prop;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaGetDeviceProperties(&prop, dev) == cudaSuccess) n = prop.multiProcessorCount;
+    if (n <= 0) n = 148;
+  }
+  return n;
 }
 
 // The token-tile width the kernel uses for M tokens.
@@ -361,11 +455,24 @@ FERRUM_API int ferrum_gemm_tc_token_tile(int M, int dual) {
   return 256;
 }
 
-// x [M, K] bf16 (row stride ldx), w [N (+dual_offset) rows, K] bf16 (row stride ldw).
-// dual_offset > 0 selects the two-accumulator kernel with the SwiGLU epilogue: the second
-// weight tile starts at row dual_offset + n.  w_rows is the number of rows of w in memory.
+// The grid the kernel runs with when the caller passes n_ctas = 0: one CTA per SM.
+FERRUM_API int ferrum_gemm_tc_default_ctas() { return sm_count(); }
+
+// Workspace floats and tile counters a launch needs.  Partial tiles arise where a CTA's
+// range of units begins or ends inside a tile, so every CTA has two partial slots.
+FERRUM_API long long ferrum_gemm_tc_workspace(int M, int N, int K, int dual, int n_ctas, int* n_tiles) {
+  const int bt = ferrum_gemm_tc_token_tile(M, dual);
+  if (n_ctas <= 0) n_ctas = sm_count();
+  const long long tiles = (long long)((N + TILE_N - 1) / TILE_N) * ((M + bt - 1) / bt);
+  if (n_tiles) *n_tiles = (int)tiles;
+  return 2LL * n_ctas * (long long)(bt * (dual ? 2 : 1)) * TILE_N;
+}
+
+// x [M, K] bf16 (row stride ldx), w [w_rows, K] bf16 (row stride ldw), N output features.
+// dual_offset > 0 selects the two-product kernel with the SwiGLU epilogue: the second weight
+// tile starts at row dual_offset + n.  n_ctas = 0 means one CTA per SM.
 FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo,
-                              int w_rows, int epilogue, int dual_offset, int splits, float* workspace,
+                              int w_rows, int epilogue, int dual_offset, int n_ctas, float* workspace,
                               long long workspace_floats, int* counters, int n_counters, int* err_flag,
                               cudaStream_t stream) {
   FERRUM_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
@@ -379,15 +486,16 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
   FERRUM_CHECK_ARG(dual == (epilogue == TC_SWIGLU), "gemm_tc: the SwiGLU epilogue needs dual_offset, and only it does");
   FERRUM_CHECK_ARG(epilogue >= 0 && epilogue <= 3, "gemm_tc: unknown epilogue %d", epilogue);
   FERRUM_CHECK_ARG(w_rows >= N + dual_offset, "gemm_tc: w has %d rows, needs %d", w_rows, N + dual_offset);
-  const int nkb = (K + TILE_K - 1) / TILE_K;
-  FERRUM_CHECK_ARG(splits >= 1 && splits <= nkb, "gemm_tc: splits=%d must be in [1, %d]", splits, nkb);
+  if (n_ctas <= 0) n_ctas = sm_count();
   const int bt = ferrum_gemm_tc_token_tile(M, dual);
   int tiles = 0;
-  const long long need = ferrum_gemm_tc_workspace(M, N, bt, dual, splits, &tiles);
-  if (splits > 1) {
-    FERRUM_CHECK_ARG(workspace && workspace_floats >= need, "gemm_tc: split-K needs %lld workspace floats, got %lld", need,
-                     workspace_floats);
-    FERRUM_CHECK_ARG(counters && n_counters >= tiles, "gemm_tc: split-K needs %d tile counters, got %d", tiles, n_counters);
+  const long long need = ferrum_gemm_tc_workspace(M, N, K, dual, n_ctas, &tiles);
+  FERRUM_CHECK_ARG(workspace && workspace_floats >= need, "gemm_tc: needs %lld workspace floats, got %lld", need, workspace_floats);
+  FERRUM_CHECK_ARG(counters && n_counters >= tiles, "gemm_tc: needs %d tile counters, got %d", tiles, n_counters);
+  {
+    // every CTA must own at least one unit, or the CTAs that share a tile are not consecutive
+    const long long units = (long long)tiles * ((K + TILE_K - 1) / TILE_K);
+    if (n_ctas > units) n_ctas = (int)units;
   }
   CUtensorMap mw, mx;
   if (int r = get_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
@@ -395,14 +503,14 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
   TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset};
 #define TC_CASE(BT_)                                                         \
   case BT_:                                                                  \
-    return dual ? launch_tc<BT_, true>(mw, mx, p, splits, stream) : launch_tc<BT_, false>(mw, mx, p, splits, stream);
+    return dual ? launch_tc<BT_, true>(mw, mx, p, n_ctas, stream) : launch_tc<BT_, false>(mw, mx, p, n_ctas, stream);
   switch (bt) {
     TC_CASE(16)
     TC_CASE(32)
     TC_CASE(64)
     TC_CASE(128)
     case 256:
-      return launch_tc<256, false>(mw, mx, p, splits, stream);
+      return launch_tc<256, false>(mw, mx, p, n_ctas, stream);
   }
 #undef TC_CASE
   FERRUM_CHECK_ARG(false, "gemm_tc: no kernel for token tile %d", bt);

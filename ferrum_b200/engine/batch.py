@@ -129,9 +129,10 @@ class StepContext:
     def buf(self, name, shape, dtype):
         return self.scratch.get(name, shape, dtype)
 
-    def splitk_scratch(self, M, N, dual, splits):
+    def gemm_scratch(self, M, N, K, dual):
+        """(float32 workspace, zeroed int32 tile counters) for the tensor-core product."""
         from ..ops import lib as ops
-        floats, tiles = ops.gemm_tc_workspace(M, N, dual, splits)
+        floats, tiles = ops.gemm_tc_workspace(M, N, K, dual)
         if tiles > self._splitk_counters.numel():
-            self._splitk_counters = torch.zeros(tiles, dtype=torch.int32, device=self.device)
-        return self.scratch.get("splitk", (floats,), torch.float32), self._splitk_counters
+            self._splitk_counters = torch.zeros(2 * tiles, dtype=torch.int32, device=self.device)
+        return self.scratch.get("gemm_partials", (floats,), torch.float32), self._splitk_counters

@@ -137,19 +137,20 @@ def gemm_tc_token_tile(M, dual):
     return lib().ferrum_gemm_tc_token_tile(c_int(M), c_int(1 if dual else 0))
 
 
-def gemm_tc_workspace(M, N, dual, splits):
-    """(workspace floats, tile counters) that a split-K launch needs."""
+def gemm_tc_workspace(M, N, K, dual, n_ctas=0):
+    """(workspace floats, tile counters) that a launch needs."""
     tiles = c_int(0)
-    bt = gemm_tc_token_tile(M, dual)
-    need = lib().ferrum_gemm_tc_workspace(c_int(M), c_int(N), c_int(bt), c_int(1 if dual else 0), c_int(splits),
+    need = lib().ferrum_gemm_tc_workspace(c_int(M), c_int(N), c_int(K), c_int(1 if dual else 0), c_int(n_ctas),
                                           ctypes.byref(tiles))
     return int(need), tiles.value
 
 
-def gemm_tc(x, w, out, epilogue, err, M=None, N=None, dual_offset=0, splits=1, workspace=None, counters=None):
+def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_offset=0, n_ctas=0):
     """bfloat16 tensor-core product; see csrc/kernels/gemm_tc.cu.  `N` is the number of
-    output features (rows of w used per accumulator); with dual_offset > 0 rows
-    dual_offset + n feed the second accumulator of the SwiGLU epilogue."""
+    output features (rows of w used per product); with dual_offset > 0 rows dual_offset + n
+    feed the second product of the SwiGLU epilogue.  `workspace` (float32) and `counters`
+    (int32, all zero) are scratch for tiles that several CTAs share; n_ctas = 0 means one CTA
+    per SM."""
     _need(x, torch.bfloat16, "x", 2); _need(w, torch.bfloat16, "w", 2); _need(out, None, "out", 2)
     M = x.shape[0] if M is None else M
     K = w.shape[1]
@@ -159,15 +160,12 @@ def gemm_tc(x, w, out, epilogue, err, M=None, N=None, dual_offset=0, splits=1, w
     want = torch.bfloat16 if epilogue in (TC_STORE_BF16, TC_SWIGLU) else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm_tc: out must be {want} for epilogue {epilogue}")
-    ws_n = workspace.numel() if workspace is not None else 0
-    if workspace is not None:
-        _need(workspace, torch.float32, "workspace")
-        _need(counters, torch.int32, "counters")
+    _need(workspace, torch.float32, "workspace")
+    _need(counters, torch.int32, "counters")
     _check(lib().ferrum_gemm_tc(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
                                 c_int(w.stride(0)), c_int(out.stride(0)), c_int(w.shape[0]), c_int(epilogue),
-                                c_int(dual_offset), c_int(splits), _ptr(workspace), c_longlong(ws_n), _ptr(counters),
-                                c_int(counters.numel() if counters is not None else 0), _ptr(err), _stream()),
-           "gemm_tc")
+                                c_int(dual_offset), c_int(n_ctas), _ptr(workspace), c_longlong(workspace.numel()),
+                                _ptr(counters), c_int(counters.numel()), _ptr(err), _stream()), "gemm_tc")
 
 
 def rope_cache_write(qkv, n_tokens, positions, req_of_token, block_table, cos_sin, kv_plane, page_stride, page_size,

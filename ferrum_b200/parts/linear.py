@@ -14,22 +14,6 @@ STORE, STORE_F32, RESIDUAL = "store", "store_f32", "residual"
 _GENERIC = {STORE: ops.EPI_STORE, STORE_F32: ops.EPI_STORE_F32, RESIDUAL: ops.EPI_RESIDUAL}
 _TC = {STORE: ops.TC_STORE_BF16, STORE_F32: ops.TC_STORE_F32, RESIDUAL: ops.TC_RESIDUAL}
 
-N_SMS = 148          # B200; only steers the split-K choice, never correctness
-MAX_SPLITS = 16
-
-
-def choose_splits(M, N, K, dual=False):
-    """Split-K factor of the tensor-core kernel: a function of the shape only, so the
-    same call always reduces in the same order."""
-    bt = ops.gemm_tc_token_tile(M, dual)
-    tiles = ((N + 127) // 128) * ((M + bt - 1) // bt)
-    nkb = (K + 63) // 64
-    if tiles >= N_SMS or M > 256:
-        return 1
-    want = (N_SMS + tiles - 1) // tiles
-    return max(1, min(want, nkb // 4 if nkb >= 8 else 1, MAX_SPLITS))
-
-
 def linear(x, w, out, mode, ctx, M=None):
     """out (=, or += when mode is RESIDUAL) x[:M] @ w.T."""
     M = x.shape[0] if M is None else M
@@ -37,11 +21,8 @@ def linear(x, w, out, mode, ctx, M=None):
         return
     if ops.gemm_tc_supported(x, w):
         N, K = w.shape
-        splits = choose_splits(M, N, K)
-        ws = cnt = None
-        if splits > 1:
-            ws, cnt = ctx.splitk_scratch(M, N, False, splits)
-        ops.gemm_tc(x, w, out, _TC[mode], ctx.err, M=M, splits=splits, workspace=ws, counters=cnt)
+        ws, cnt = ctx.gemm_scratch(M, N, K, False)
+        ops.gemm_tc(x, w, out, _TC[mode], ctx.err, ws, cnt, M=M)
     else:
         ops.gemm_generic(x, w, out, _GENERIC[mode], M=M)
 
@@ -53,9 +34,5 @@ def linear_swiglu(x, w_gate_up, act, F, ctx, M=None):
     if M == 0:
         return
     K = w_gate_up.shape[1]
-    splits = choose_splits(M, F, K, dual=True)
-    ws = cnt = None
-    if splits > 1:
-        ws, cnt = ctx.splitk_scratch(M, F, True, splits)
-    ops.gemm_tc(x, w_gate_up, act, ops.TC_SWIGLU, ctx.err, M=M, N=F, dual_offset=F, splits=splits, workspace=ws,
-                counters=cnt)
+    ws, cnt = ctx.gemm_scratch(M, F, K, True)
+    ops.gemm_tc(x, w_gate_up, act, ops.TC_SWIGLU, ctx.err, ws, cnt, M=M, N=F, dual_offset=F)

@@ -117,56 +117,52 @@ TC_SHAPES = [(1, 128, 64), (5, 200, 136), (16, 384, 512), (33, 1000, 264), (64, 
              (200, 640, 320), (300, 256, 192), (515, 384, 128)]
 
 
+def tc_scratch(ops, M, N, K, dual, n_ctas):
+    floats, tiles = ops.gemm_tc_workspace(M, N, K, dual, n_ctas)
+    return torch.empty(floats, device="cuda"), torch.zeros(tiles, dtype=torch.int32, device="cuda")
+
+
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
-@pytest.mark.parametrize("splits", [1, 3])
-def test_gemm_tc(ops, M, N, K, splits):
+@pytest.mark.parametrize("n_ctas", [0, 1, 3, 7])
+def test_gemm_tc(ops, M, N, K, n_ctas):
+    """n_ctas 0 is the production grid (one CTA per SM, ranges end inside tiles); small
+    grids make every CTA walk several tiles and share some with its neighbours."""
     g = torch.Generator(device="cuda").manual_seed(5)
     x = (torch.randn(M, K, device="cuda", generator=g)).bfloat16()
     w = (torch.randn(N, K, device="cuda", generator=g)).bfloat16()
     ref = x.double() @ w.double().T
     e = err_flag()
-    nkb = (K + 63) // 64
-    if splits > nkb:
-        pytest.skip("fewer k-blocks than splits")
-    ws = cnt = None
-    if splits > 1:
-        floats, tiles = ops.gemm_tc_workspace(M, N, False, splits)
-        ws = torch.empty(floats, device="cuda")
-        cnt = torch.zeros(tiles, dtype=torch.int32, device="cuda")
+    ws, cnt = tc_scratch(ops, M, N, K, False, n_ctas)
     out = torch.full((M, N), float("nan"), device="cuda")
-    ops.gemm_tc(x, w, out, ops.TC_STORE_F32, e, splits=splits, workspace=ws, counters=cnt)
+    ops.gemm_tc(x, w, out, ops.TC_STORE_F32, e, ws, cnt, n_ctas=n_ctas)
     assert e.item() == 0
     assert ((out.double() - ref).abs() <= lim(ref, 2e-5) * math.sqrt(K)).all(), (out.double() - ref).abs().max()
     outb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    ops.gemm_tc(x, w, outb, ops.TC_STORE_BF16, e, splits=splits, workspace=ws, counters=cnt)
+    ops.gemm_tc(x, w, outb, ops.TC_STORE_BF16, e, ws, cnt, n_ctas=n_ctas)
     assert ((outb.double() - ref).abs() <= lim(ref, 8e-3)).all()
     res = torch.randn(M, N, device="cuda", generator=g)
     acc = res.clone()
-    ops.gemm_tc(x, w, acc, ops.TC_RESIDUAL, e, splits=splits, workspace=ws, counters=cnt)
+    ops.gemm_tc(x, w, acc, ops.TC_RESIDUAL, e, ws, cnt, n_ctas=n_ctas)
     assert ((acc.double() - (res.double() + ref)).abs() <= lim(ref, 2e-5) * math.sqrt(K)).all()
-    if cnt is not None:
-        assert cnt.sum().item() == 0          # the counters are left ready for the next launch
+    assert cnt.sum().item() == 0          # the counters are left ready for the next launch
     assert e.item() == 0
+    again = torch.empty(M, N, device="cuda")
+    ops.gemm_tc(x, w, again, ops.TC_STORE_F32, e, ws, cnt, n_ctas=n_ctas)
+    assert torch.equal(again, out)        # shared tiles are summed in K order: run-to-run identical
 
 
 @pytest.mark.parametrize("M,F,K", [(3, 172 * 2, 64), (16, 256, 96), (40, 200, 320), (130, 384, 256), (300, 128, 128)])
-@pytest.mark.parametrize("splits", [1, 2])
-def test_gemm_tc_swiglu(ops, M, F, K, splits):
+@pytest.mark.parametrize("n_ctas", [0, 2, 5])
+def test_gemm_tc_swiglu(ops, M, F, K, n_ctas):
     g = torch.Generator(device="cuda").manual_seed(6)
     x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
     w = (torch.randn(2 * F, K, device="cuda", generator=g) * 0.2).bfloat16()
     gate, up = x.double() @ w[:F].double().T, x.double() @ w[F:].double().T
     ref = gate / (1 + torch.exp(-gate)) * up
     e = err_flag()
-    ws = cnt = None
-    if splits > 1:
-        if (K + 63) // 64 < splits:
-            pytest.skip("fewer k-blocks than splits")
-        floats, tiles = ops.gemm_tc_workspace(M, F, True, splits)
-        ws = torch.empty(floats, device="cuda")
-        cnt = torch.zeros(tiles, dtype=torch.int32, device="cuda")
+    ws, cnt = tc_scratch(ops, M, F, K, True, n_ctas)
     act = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
-    ops.gemm_tc(x, w, act, ops.TC_SWIGLU, e, N=F, dual_offset=F, splits=splits, workspace=ws, counters=cnt)
+    ops.gemm_tc(x, w, act, ops.TC_SWIGLU, e, ws, cnt, N=F, dual_offset=F, n_ctas=n_ctas)
     assert e.item() == 0
     assert ((act.double() - ref).abs() <= lim(ref, 1e-2)).all(), (act.double() - ref).abs().max()
 
@@ -178,7 +174,8 @@ def test_gemm_tc_refuses_unaligned(ops):
     out = torch.zeros(4, 8, device="cuda")
     assert not ops.gemm_tc_supported(x, w)
     with pytest.raises(KernelError):
-        ops.gemm_tc(x, w, out, ops.TC_STORE_F32, err_flag())
+        ops.gemm_tc(x, w, out, ops.TC_STORE_F32, err_flag(), torch.empty(1 << 20, device="cuda"),
+                    torch.zeros(16, dtype=torch.int32, device="cuda"))
 
 
 # ---------------------------------------------------------------- rope + cache write, attention
