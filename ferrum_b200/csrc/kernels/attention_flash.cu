@@ -88,6 +88,7 @@ flash_kernel(const FlashParams p) {
 
   const int* wk = p.work + (size_t)blockIdx.x * 8;
   const int req = wk[0], row0 = wk[1], kv_begin = wk[2], kv_end = wk[3], n_splits = wk[4], part = wk[5];
+  if (n_splits == 0) return;  // padding of a fixed-size work list
   const int kvh = blockIdx.y;
   const int G = p.G;
   const int qs = p.q_start[req];

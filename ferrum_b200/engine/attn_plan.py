@@ -8,10 +8,14 @@ every layer with the same (G, window).
 
 Requests with at most 16 rows (decoded tokens) go to the 16-row kernel, the others to the
 64-row kernel; each class has its own work list.  A work item is
-[request, first row, key begin, key end, number of splits, partial slot, 0, 0].
-Split boundaries are multiples of 64 keys counted from the tile's first key, and the splits
-are merged in order, so a row's result does not depend on the other requests in the batch
-beyond the choice of the split length.
+[request, first row, key begin, key end, number of splits, partial slot, 0, 0]; an item with
+zero splits is padding.  Split boundaries are multiples of 64 keys counted from the tile's
+first key, and the splits are merged in order, so a row's result does not depend on the
+other requests in the batch beyond the choice of the split length.
+
+The lists live in device buffers that keep their address from step to step, and a plan can
+be padded to a fixed number of items, so that a captured CUDA graph can be replayed with the
+next step's lists.
 """
 from __future__ import annotations
 
@@ -26,20 +30,18 @@ CLASSES = (16, 64)
 MIN_SPLIT_KEYS = {16: 256, 64: 1024}
 
 
-@dataclass
-class ClassPlan:
-    bm: int
-    n_work: int = 0
-    work: Optional[torch.Tensor] = None        # int32 [n_work * 8]
-    n_slots: int = 0                            # partial slots (work items that are splits)
-    req_tile0: Optional[torch.Tensor] = None
-    tile_info: Optional[torch.Tensor] = None
-    comb_tokens: Optional[torch.Tensor] = None
-    n_comb: int = 0
+def target_items(Hkv):
+    """Work items per class that fill the GPU once at two CTAs per SM."""
+    return max(1, (2 * N_SMS) // Hkv)
+
+
+def item_capacity(n_requests, Hkv):
+    """Upper bound of the 16-row class's work items for n_requests decoded tokens."""
+    return target_items(Hkv) + 2 * n_requests
 
 
 def build_host(q_len, pos0, G, window, Hkv):
-    """numpy description of both classes: list of dicts with int32 arrays."""
+    """numpy description of both classes: None or a dict of int32 arrays per class."""
     q_len = np.asarray(q_len, dtype=np.int64)
     pos0 = np.asarray(pos0, dtype=np.int64)
     R = len(q_len)
@@ -60,9 +62,8 @@ def build_host(q_len, pos0, G, window, Hkv):
         hi = pos0[req_of_tile] + last_tok + 1
         lo = np.maximum(0, pos0[req_of_tile] + first_tok - window + 1) if window > 0 else np.zeros_like(hi)
         length = hi - lo
-        # enough work items to fill the GPU about twice over, never splits shorter than the minimum
-        target = max(1, (2 * N_SMS + Hkv - 1) // Hkv)
-        chunk = int(max(MIN_SPLIT_KEYS[bm], -(-int(length.sum()) // target)))
+        # about one item per CTA slot of the GPU, never splits shorter than the minimum
+        chunk = int(max(MIN_SPLIT_KEYS[bm], -(-int(length.sum()) // target_items(Hkv))))
         chunk = (chunk + 63) // 64 * 64
         n_splits = np.maximum(1, (length + chunk - 1) // chunk)
         T = int(n_splits.sum())
@@ -78,7 +79,8 @@ def build_host(q_len, pos0, G, window, Hkv):
         work[:, 4], work[:, 5] = ns, slot
         order = np.argsort(-(ke - kb), kind="stable")          # long items first
         # per tile: first partial slot and number of splits (slots of a tile are consecutive)
-        first_slot = np.where(n_splits > 1, np.cumsum(np.where(n_splits > 1, n_splits, 0)) - np.where(n_splits > 1, n_splits, 0), 0)
+        split_sizes = np.where(n_splits > 1, n_splits, 0)
+        first_slot = np.where(n_splits > 1, np.cumsum(split_sizes) - split_sizes, 0)
         tile_info = np.stack([first_slot, n_splits], axis=1).astype(np.int32)
         req_tile0 = np.zeros(R, dtype=np.int32)
         req_tile0[sel] = (np.cumsum(n_tiles) - n_tiles).astype(np.int32)
@@ -90,49 +92,89 @@ def build_host(q_len, pos0, G, window, Hkv):
     return out
 
 
+@dataclass
+class ClassPlan:
+    bm: int
+    n_work: int = 0                             # grid size (includes padding items)
+    work: Optional[torch.Tensor] = None        # int32 [n_work * 8]
+    n_slots: int = 0                            # partial slots to provide
+    req_tile0: Optional[torch.Tensor] = None
+    tile_info: Optional[torch.Tensor] = None
+    comb_tokens: Optional[torch.Tensor] = None  # None: every token of the batch
+    n_comb: int = 0
+
+
 class AttentionPlans:
     """Per-step cache of plans, keyed by (G, window, Hkv); owns the device copies."""
 
     def __init__(self, device):
         self.device = device
         self._plans = {}
-        self._host = None
-        self._dev = None
+        self._bufs = {}          # key -> (pinned, device) int32 buffers, grow-only
+        self.generation = 0      # bumped whenever a device buffer moves
 
     def reset(self):
         self._plans = {}
 
-    def get(self, ctx, G, window, Hkv) -> List[Optional[ClassPlan]]:
+    def keys_built(self):
+        return list(self._plans)
+
+    def _buffers(self, key, n):
+        from .batch import PinnedRing
+        b = self._bufs.get(key)
+        if b is None or b[1].numel() < n:
+            cap = max(1024, 2 * n)
+            b = (PinnedRing(cap, torch.int32, self.device), torch.empty(cap, dtype=torch.int32, device=self.device))
+            self._bufs[key] = b
+            self.generation += 1
+        return b
+
+    def get(self, ctx, G, window, Hkv, fixed=False) -> List[Optional[ClassPlan]]:
+        """fixed=True (a decode-only batch under a CUDA graph): the 16-row list is padded to
+        `item_capacity` items and the merge visits every token, so that the launch shapes
+        depend on the number of requests only."""
         key = (G, window, Hkv)
         if key in self._plans:
             return self._plans[key]
         host = build_host(ctx.h_q_len, ctx.h_pos0, G, window, Hkv)
+        R = len(ctx.h_q_len)
+        if fixed:
+            h = host[0]
+            if h is None or host[1] is not None:
+                raise ValueError("a fixed-shape plan needs a batch of decoded tokens only")
+            cap = item_capacity(R, Hkv)
+            if h["n_work"] > cap:
+                raise ValueError("attention plan exceeds its fixed capacity")
+            padded = np.zeros(cap * 8, dtype=np.int32)
+            padded[:h["work"].size] = h["work"]
+            h["work"], h["n_work"], h["n_slots"] = padded, cap, cap
         arrays = []
         for h in host:
             if h is not None:
                 arrays += [h["work"], h["tile_info"], h["req_tile0"], h["comb"]]
         total = sum(a.size for a in arrays)
-        pinned = torch.empty(max(total, 1), dtype=torch.int32).pin_memory()
-        dev = torch.empty(max(total, 1), dtype=torch.int32, device=self.device)
-        np.concatenate(arrays, out=pinned.numpy()[:total]) if arrays else None
+        ring, dev = self._buffers(key, total)
+        pinned = ring.next()
+        if arrays:
+            np.concatenate(arrays, out=pinned.numpy()[:total])
         dev[:total].copy_(pinned[:total], non_blocking=True)
+        ring.sent()
         ctx.h2d_bytes += total * 4
-        self._keep = getattr(self, "_keep", []) + [pinned]      # alive until the copy has run
-        if len(self._keep) > 8:
-            self._keep = self._keep[-8:]
         plans, o = [], 0
         for h in host:
             if h is None:
                 plans.append(None)
                 continue
-            def take(a):
-                nonlocal o
-                v = dev[o:o + a.size]
-                o += a.size
-                return v
-            cp = ClassPlan(h["bm"], h["n_work"], take(h["work"]), h["n_slots"])
-            cp.tile_info, cp.req_tile0, cp.comb_tokens = take(h["tile_info"]), take(h["req_tile0"]), take(h["comb"])
-            cp.n_comb = int(h["comb"].size)
+            views = []
+            for name in ("work", "tile_info", "req_tile0", "comb"):
+                views.append(dev[o:o + h[name].size])
+                o += h[name].size
+            cp = ClassPlan(h["bm"], h["n_work"], views[0], h["n_slots"])
+            cp.tile_info, cp.req_tile0 = views[1], views[2]
+            if fixed:
+                cp.comb_tokens, cp.n_comb = None, ctx.n_tokens
+            else:
+                cp.comb_tokens, cp.n_comb = views[3], int(h["comb"].size)
             plans.append(cp)
         self._plans[key] = plans
         return plans

@@ -32,6 +32,7 @@ class Scratch:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
+        self.generation = 0      # bumped whenever a buffer is (re)allocated and so may have moved
 
     def get(self, name, shape, dtype):
         n = 1
@@ -41,10 +42,37 @@ class Scratch:
         if t is None or t.dtype != dtype or t.numel() < n:
             t = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[name] = t
+            self.generation += 1
         return t[:n].view(*shape)
 
     def bytes(self):
         return sum(t.numel() * t.element_size() for t in self._bufs.values())
+
+
+class PinnedRing:
+    """A few pinned host buffers used in turn for host-to-device copies.  A buffer is
+    rewritten only after the copy that last read it has run, so the host may run several
+    steps ahead of the GPU without tearing a step's inputs."""
+
+    def __init__(self, numel, dtype, device, depth=4):
+        self.cuda = str(device) != "cpu"
+        mk = (lambda: torch.empty(numel, dtype=dtype).pin_memory()) if self.cuda else (lambda: torch.empty(numel, dtype=dtype))
+        self.bufs = [mk() for _ in range(depth)]
+        self.events = [None] * depth
+        self.i = 0
+
+    def next(self):
+        self.i = (self.i + 1) % len(self.bufs)
+        if self.events[self.i] is not None:
+            self.events[self.i].synchronize()
+        return self.bufs[self.i]
+
+    def sent(self):
+        """Call right after enqueueing the copy out of the current buffer."""
+        if self.cuda:
+            if self.events[self.i] is None:
+                self.events[self.i] = torch.cuda.Event()
+            self.events[self.i].record()
 
 
 class StepContext:
@@ -57,16 +85,15 @@ class StepContext:
         self.scratch = Scratch(device)
         self.err = torch.zeros(1, dtype=torch.int32, device=device)
         n_small = 4 * self.max_tokens + 3 * self.max_requests + 1
-        self._host = torch.empty(n_small, dtype=torch.int32).pin_memory() if device != "cpu" else torch.empty(n_small, dtype=torch.int32)
+        self._host = PinnedRing(n_small, torch.int32, device)
         self._dev = torch.empty(n_small, dtype=torch.int32, device=device)
-        self._bt_host = [torch.empty((self.max_requests, w), dtype=torch.int32) for w in self.table_widths]
-        if device != "cpu":
-            self._bt_host = [t.pin_memory() for t in self._bt_host]
+        self._bt_host = [PinnedRing(self.max_requests * w, torch.int32, device) for w in self.table_widths]
         self._bt_dev = [torch.empty((self.max_requests, w), dtype=torch.int32, device=device) for w in self.table_widths]
         self._splitk_counters = torch.zeros(4096, dtype=torch.int32, device=device)
         from .attn_plan import AttentionPlans
         self._attn_plans = AttentionPlans(device)
         self.n_tokens = self.n_reqs = self.n_want = 0
+        self.fixed_shapes = False     # True while a decode-only batch runs under a CUDA graph
         self.h2d_bytes = 0            # bytes copied to the device by the last fill
         self.token_capacity = self.want_capacity = 0
 
@@ -79,7 +106,8 @@ class StepContext:
             raise ValueError(f"batch of {T} tokens / {R} requests exceeds the runner's limits "
                              f"({self.max_tokens} / {self.max_requests})")
         W = sum(len(e.want) for e in entries)
-        h = self._host.numpy()
+        host = self._host.next()
+        h = host.numpy()
         tok, pos, req, want = h[0:T], h[T:2 * T], h[2 * T:3 * T], h[3 * T:3 * T + W]
         o = 3 * T + W
         qstart, pos0, slots = h[o:o + R + 1], h[o + R + 1:o + 2 * R + 1], h[o + 2 * R + 1:o + 3 * R + 1]
@@ -100,7 +128,8 @@ class StepContext:
             t += n
         qstart[R] = T
         total = o + 3 * R + 1
-        self._dev[:total].copy_(self._host[:total], non_blocking=True)
+        self._dev[:total].copy_(host[:total], non_blocking=True)
+        self._host.sent()
         self.h2d_bytes = total * 4
         d = self._dev
         self.token_ids, self.positions, self.req_of_token = d[0:T], d[T:2 * T], d[2 * T:3 * T]
@@ -108,10 +137,13 @@ class StepContext:
         self.q_start, self.pos0, self.slots = d[o:o + R + 1], d[o + R + 1:o + 2 * R + 1], d[o + 2 * R + 1:o + 3 * R + 1]
         self.block_tables = []
         for g, rows in enumerate(tables):
-            bh = self._bt_host[g].numpy()
+            w = self.table_widths[g]
+            bhost = self._bt_host[g].next()
+            bh = bhost.numpy().reshape(self.max_requests, w)
             for r, row in enumerate(rows):
                 bh[r, :len(row)] = row
-            self._bt_dev[g][:R].copy_(self._bt_host[g][:R], non_blocking=True)
+            self._bt_dev[g][:R].copy_(bhost[:R * w].view(R, w), non_blocking=True)
+            self._bt_host[g].sent()
             self.h2d_bytes += R * self.table_widths[g] * 4
             self.block_tables.append(self._bt_dev[g][:R])
         self.n_tokens, self.n_reqs, self.n_want = T, R, W
@@ -123,7 +155,7 @@ class StepContext:
 
     def attention_plans(self, G, window, Hkv):
         """The step's work lists for the tensor-core attention kernel (built on first use)."""
-        return self._attn_plans.get(self, G, window, Hkv)
+        return self._attn_plans.get(self, G, window, Hkv, fixed=self.fixed_shapes)
 
     # ------------------------------------------------------------------ scratch
     def buf(self, name, shape, dtype):

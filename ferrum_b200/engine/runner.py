@@ -26,8 +26,17 @@ _DEVICE_ERRORS = {
 }
 
 
+class _CapturedStep:
+    def __init__(self, graph, logits, plan_keys, generation, n_launches):
+        self.graph, self.logits, self.plan_keys, self.generation = graph, logits, plan_keys, generation
+        self.n_launches = n_launches      # kernels one replay launches
+
+
 class ModelRunner:
-    def __init__(self, model, cache: CacheStorage, max_batch_tokens=2048, max_batch_requests=None):
+    def __init__(self, model, cache: CacheStorage, max_batch_tokens=2048, max_batch_requests=None, use_graphs=True):
+        """use_graphs: steps that bring one token per request (decoding) are captured in a
+        CUDA graph per (requests, wanted rows) the second time that shape is seen, and
+        replayed afterwards; every other step is launched kernel by kernel."""
         ops.require_cuda()
         self.model, self.cache = model, cache
         self.device = cache.device
@@ -36,6 +45,10 @@ class ModelRunner:
         widths = [cache.table_width] * cache.n_groups
         self.ctx = StepContext(self.device, self.max_batch_tokens, self.max_batch_requests, widths)
         self.ctx.cache = cache
+        self.use_graphs = bool(use_graphs)
+        self._graphs = {}
+        self._seen = {}
+        self.graph_replays = 0
 
     def step(self, entries: List[StepEntry], commit=True, check=True):
         """Returns float32 logits [n_wanted, V] on the device (a view that the next step
@@ -59,14 +72,48 @@ class ModelRunner:
                 for s in self.cache.states:
                     s[e.slot].zero_()                      # a request starts from an all-zero state
         tables = [[mgr.table(g, e.slot) for e in entries] for g in range(self.cache.n_groups)]
+        decode_only = self.use_graphs and all(len(e.tokens) == 1 for e in entries)
+        self.ctx.fixed_shapes = decode_only
         self.ctx.fill(entries, tables)
-        logits = self.model.forward(self.ctx, self.cache)
+        logits = self._run_decode() if decode_only else self.model.forward(self.ctx, self.cache)
         if commit:
             for e in entries:
                 mgr.commit(e.slot, e.pos0 + len(e.tokens))
         if check:
             self.check_device_errors()
         return logits[:self.ctx.n_want] if logits is not None else None
+
+    def _generation(self):
+        return (self.ctx.scratch.generation, self.ctx._attn_plans.generation)
+
+    def _run_decode(self):
+        """A decode-only batch: replay its graph, or run it kernel by kernel and capture."""
+        ctx = self.ctx
+        key = (ctx.n_reqs, ctx.n_want)
+        cap = self._graphs.get(key)
+        if cap is not None and cap.generation == self._generation():
+            for k in cap.plan_keys:
+                ctx.attention_plans(*k)          # this step's work lists, into the buffers the graph reads
+            if cap.generation == self._generation():
+                cap.graph.replay()
+                self.graph_replays += 1
+                ops.launches += cap.n_launches
+                return cap.logits
+        logits = self.model.forward(ctx, self.cache)
+        self._seen[key] = self._seen.get(key, 0) + 1
+        if self._seen[key] >= 2:
+            # every buffer exists now and the plans of this step are cached: capturing
+            # launches nothing and allocates nothing
+            plan_keys = ctx._attn_plans.keys_built()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                captured = self.model.forward(ctx, self.cache)
+            n_launches, ops.launches = ops.launches - before, before      # captured, not launched
+            self._graphs[key] = _CapturedStep(graph, captured, plan_keys, self._generation(), n_launches)
+            if len(self._graphs) > 96:
+                self._graphs.pop(next(iter(self._graphs)))
+        return logits
 
     def check_device_errors(self):
         """Synchronises and raises if a kernel raised the error flag."""

@@ -157,3 +157,28 @@ def test_trace_run_program(cuda, model_dirs, tmp_path):
     ref = plain_logits(model_dirs["A"], "float32", toks[:30])
     assert_close(got, ref[[0, 29]], "float32", "trace_run")
     assert not (out / "1.f32").exists()
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_decode_graph_replay_matches_kernel_launches(cuda, model_dirs, name):
+    """Decode steps replayed from a captured CUDA graph give the logits that the same steps
+    give when launched kernel by kernel, while requests grow across page and split edges."""
+    vocab = TINY[name][0]["vocab_size"]
+    toks = {k: random_tokens(170, vocab, 30 + i) for i, k in enumerate("abc")}
+    outs = []
+    for graphs in (False, True):
+        s = session(model_dirs, name, "bfloat16", 3 * 192)
+        s.runner.use_graphs = graphs
+        r = Replay(s)
+        r.step([(k, toks[k][:40 + 7 * i], []) for i, k in enumerate("abc")])
+        cur = {k: 40 + 7 * i for i, k in enumerate("abc")}
+        for _ in range(100):
+            r.step([(k, [toks[k][cur[k]]], "all") for k in "abc"])
+            for k in "abc":
+                cur[k] += 1
+        assert (s.runner.graph_replays > 90) == graphs
+        outs.append(np.stack([r.rows[(k, p)] for k in "abc" for p in range(40 + 7 * "abc".index(k), 140)]))
+    assert np.abs(outs[0] - outs[1]).max() <= 1e-6
+    ref = plain_logits(model_dirs[name], "bfloat16", toks["a"][:140])
+    got = np.stack([r.rows[("a", p)] for p in range(40, 140)])
+    assert_close(got, ref[40:140], "bfloat16", "graph decode")
