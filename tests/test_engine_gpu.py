@@ -1,0 +1,123 @@
+"""Generation through the Python entry point against the plain implementation."""
+import numpy as np
+import pytest
+
+import plain_llama as P
+from conftest import TINY
+from helpers import random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def engine(model_dirs, name, dtype, **kw):
+    from ferrum_b200 import Engine
+    args = dict(dtype=dtype, num_pages=64, max_batch_tokens=64, max_batch_seqs=4, max_model_len=256)
+    args.update(kw)
+    return Engine(model_dirs[name], **args)
+
+
+def check_against_plain(folder, dtype, prompt, got, temperature=0.0, seed=0):
+    """Token by token; under bfloat16 a near-tie may flip a token, after which the two
+    continuations differ legitimately, so the comparison stops there."""
+    cfg, w = P.read_model(folder, weights_as="bfloat16" if dtype == "bfloat16" else "stored")
+    toks = list(prompt)
+    for n, t in enumerate(got):
+        logits = P.forward(cfg, w, toks)[-1]
+        want = P.sample(logits, temperature, seed, n)
+        if t != want:
+            assert dtype == "bfloat16", (n, t, want)
+            z = np.sort(logits)[::-1]
+            assert temperature > 0 or z[0] - logits[t] < 0.05, (n, t, want, z[0] - logits[t])
+            return n
+        toks.append(t)
+    return len(got)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation(cuda, model_dirs, name, dtype):
+    vocab = TINY[name][0]["vocab_size"]
+    prompt = random_tokens(16, vocab, 40)
+    eng = engine(model_dirs, name, dtype)
+    got = eng.generate([prompt], max_new_tokens=16)[0]
+    assert len(got) == 16
+    agreed = check_against_plain(model_dirs[name], dtype, prompt, got)
+    assert agreed == 16 or dtype == "bfloat16"
+    assert agreed >= 4
+
+
+def test_temperature_generation_float32(cuda, model_dirs):
+    vocab = TINY["B"][0]["vocab_size"]
+    prompt = random_tokens(7, vocab, 41)
+    eng = engine(model_dirs, "B", "float32")
+    got = eng.generate([prompt], max_new_tokens=12, temperature=0.8, seed=1)[0]
+    assert check_against_plain(model_dirs["B"], "float32", prompt, got, 0.8, 1) == 12
+    again = engine(model_dirs, "B", "float32").generate([prompt], max_new_tokens=12, temperature=0.8, seed=1)[0]
+    other = engine(model_dirs, "B", "float32").generate([prompt], max_new_tokens=12, temperature=0.8, seed=2)[0]
+    assert again == got and other != got
+
+
+def test_continuous_batching_gives_each_request_what_it_gets_alone(cuda, model_dirs):
+    """The mixed workload of the second tiny configuration: prompts of 7, 33 and 1 tokens,
+    portions of 8, greedy and temperature 0.8 with seed 1 side by side."""
+    vocab = TINY["B"][0]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 50 + n) for n in (7, 33, 1)]
+    alone = []
+    for i, p in enumerate(prompts):
+        t = 0.8 if i == 1 else 0.0
+        alone.append(engine(model_dirs, "B", "float32").generate([p], max_new_tokens=10, temperature=t, seed=1)[0])
+    from ferrum_b200 import SamplingParams
+    eng = engine(model_dirs, "B", "float32", chunk_size=8, max_batch_tokens=12)
+    ids = [eng.submit(p, 10, SamplingParams(0.8 if i == 1 else 0.0, 1.0, 1)) for i, p in enumerate(prompts)]
+    out = {i: [] for i in ids}
+    reasons = {}
+    while len(reasons) < 3:
+        for ev in eng.step():
+            if ev.kind == "token":
+                out[ev.id].append(ev.token)
+            else:
+                reasons[ev.id] = ev.reason
+    assert [out[i] for i in ids] == alone
+    assert set(reasons.values()) == {"length"}
+    st = eng.stats()
+    assert st["pages_used"] == [0] and st["finished"] == 3 and st["prompt_tokens"] == 41
+
+
+def test_preemption_in_the_engine_keeps_outputs(cuda, model_dirs):
+    """So few pages that two decoding requests cannot both stay: one is preempted and
+    recomputed, and both still produce what they produce alone."""
+    vocab = TINY["A"][0]["vocab_size"]
+    prompts = [random_tokens(20, vocab, 60), random_tokens(20, vocab, 61)]
+    alone = [engine(model_dirs, "A", "float32").generate([p], max_new_tokens=40)[0] for p in prompts]
+    eng = engine(model_dirs, "A", "float32", num_pages=6, max_model_len=64)      # 96 tokens of cache, 120 needed
+    assert eng.generate(prompts, max_new_tokens=40) == alone
+    assert eng.stats()["preemptions"] >= 1 and eng.stats()["pages_used"] == [0]
+
+
+def test_stop_tokens_cancel_and_errors(cuda, model_dirs):
+    from ferrum_b200 import InvalidRequest, NotFound
+    vocab = TINY["A"][0]["vocab_size"]
+    prompt = random_tokens(9, vocab, 62)
+    eng = engine(model_dirs, "A", "float32")
+    free = eng.generate([prompt], max_new_tokens=8)[0]
+    stopped = eng.generate([prompt], max_new_tokens=8, stop_tokens=[free[3]])[0]
+    assert stopped == free[:free.index(free[3]) + 1]                 # the stopping token is emitted
+    with pytest.raises(InvalidRequest):
+        eng.submit([], 4)
+    with pytest.raises(InvalidRequest):
+        eng.submit([vocab], 4)
+    rid = eng.submit(prompt, 50)
+    eng.step()
+    eng.cancel(rid)
+    with pytest.raises(NotFound):
+        eng.cancel(rid)
+    assert eng.step() == [] and eng.stats()["pages_used"] == [0]
+
+
+def test_missing_extension_or_device_fails_loudly(cuda, monkeypatch):
+    import torch
+    from ferrum_b200 import KernelError
+    from ferrum_b200.ops import lib
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    with pytest.raises(KernelError, match="CUDA device only"):
+        lib.require_cuda()
