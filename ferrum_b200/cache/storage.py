@@ -91,8 +91,8 @@ class CacheStorage:
         self.table_width = (max_model_len + self.page_size - 1) // self.page_size
         specs = [host.module().GroupSpec(self.page_size, key[2], pages[g], self.table_width)
                  for g, key in enumerate(self.layout.group_keys)]
-        if not specs:   # a model without paged layers still needs slots for its state
-            specs = [host.module().GroupSpec(self.page_size, 0, 1, self.table_width)]
+        if not specs:   # a model without paged layers still needs slots and lengths: pages without memory
+            specs = [host.module().GroupSpec(self.page_size, 0, int(max_requests) * self.table_width, self.table_width)]
             self._dummy_group = True
         else:
             self._dummy_group = False

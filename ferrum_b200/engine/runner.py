@@ -45,7 +45,7 @@ class ModelRunner:
         widths = [cache.table_width] * cache.n_groups
         self.ctx = StepContext(self.device, self.max_batch_tokens, self.max_batch_requests, widths)
         self.ctx.cache = cache
-        self.use_graphs = bool(use_graphs)
+        self.use_graphs = bool(use_graphs) and model.all_graph_safe()
         self._graphs = {}
         self._seen = {}
         self.graph_replays = 0

@@ -21,6 +21,8 @@ class Run:
 
 
 class DecoderModel(Part):
+    graph_safe = True
+
     def __init__(self, config, dtype, embedding, position, blocks, final_norm, head, schedule=None,
                  block_prefix="blk.{}.", names=("token_embd.", "output_norm.", "output.")):
         self.config, self.dtype = config, dtype

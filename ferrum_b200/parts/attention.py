@@ -18,6 +18,8 @@ from .linear import RESIDUAL, STORE, linear
 
 
 class PagedAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, width, n_head, n_head_kv, head_dim, position, dtype, window=0, scale=None):
         if n_head % n_head_kv:
             raise ValueError("head count is not divisible by kv head count")

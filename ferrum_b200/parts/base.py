@@ -61,6 +61,14 @@ class CacheNeed:
 class Part:
     """Base of every part: a tree of named parameters."""
 
+    # True when `forward` only enqueues work on the current stream with launch shapes that
+    # depend on the batch's sizes alone (no host synchronisation, no data-dependent
+    # allocation): such a part may be captured in a CUDA graph.  Parts say so themselves.
+    graph_safe = False
+
+    def all_graph_safe(self) -> bool:
+        return self.graph_safe and all(c.all_graph_safe() for _, c in self.children())
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}
 

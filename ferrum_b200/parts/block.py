@@ -9,6 +9,8 @@ from .base import FeedForward, Mixer, Norm, Part
 
 
 class PreNormBlock(Part):
+    graph_safe = True
+
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward,
                  names=("attn_norm.", "attn_", "ffn_norm.", "ffn_")):
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn

@@ -15,6 +15,8 @@ from .linear import STORE_F32, linear
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, n_vocab, width):
         self.n_vocab, self.width = n_vocab, width
         self.w_weight = None
@@ -29,6 +31,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    graph_safe = True
+
     def __init__(self, n_vocab, width, tied_to: TokenEmbedding = None, tied="auto"):
         """tied: True (no matrix of its own), False (must have one), "auto" (use the file's
         matrix when present, else the embedding: the reference's rule)."""

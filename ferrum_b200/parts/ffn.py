@@ -14,6 +14,8 @@ from .linear import RESIDUAL, STORE, linear, linear_swiglu
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, width, hidden, dtype):
         self.width, self.hidden, self.dtype = width, hidden, dtype
         self.w_gate_weight = self.w_up_weight = self.w_down_weight = None

@@ -6,6 +6,8 @@ from .base import Norm, ParamSpec
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, width: int, eps: float, out_dtype):
         self.width, self.eps, self.out_dtype = width, float(eps), out_dtype
         self.w_weight = None

@@ -40,6 +40,8 @@ def inverse_frequencies(rope_dim, theta, scaling=None):
 
 
 class RotaryEmbedding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim, rope_dim, theta, scaling, pairing, max_positions, device):
         if rope_dim % 2 or rope_dim > head_dim:
             raise ValueError("invalid rope dimension")
