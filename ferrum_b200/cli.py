@@ -1,0 +1,215 @@
+"""`ferrum` command line.
+
+In the manner of the reference's CLI (crates/ferrum-cli/src/main.rs): a hand-written
+argument parser, `--flag VALUE` and `--flag=VALUE`, unknown commands and arguments are
+errors, exit code 2 for usage errors and 1 for runtime errors, messages prefixed
+`ferrum: `.  The reference's only command, `serve`, is answered as it answers it without
+`--mock`: this engine has no server.  Request options carry the names of the reference's
+`SubmitRequest` and `SamplingParams` (crates/core-types/src/schedule.rs:16-49).
+
+    ferrum generate --model DIR|FILE.gguf --prompt-tokens 1,2,3 [--prompt-tokens ...]
+                    [--dtype bfloat16|float32] [--max-new-tokens N] [--temperature T] [--top-p 1]
+                    [--seed S] [--stop-tokens a,b] [--max-batch-tokens N] [--max-batch-seqs N]
+                    [--chunk-size N] [--page-size N] [--num-pages N] [--max-model-len N]
+                    [--random-weights] [--weights-seed S] [--stats]
+    ferrum random-weights --config CONFIG.json --out DIR [--seed S] [--dtype float32|bfloat16|float16] [--gguf]
+    ferrum replay --model DIR --dtype D --out DIR --max-tokens N        (steps on standard input)
+    ferrum dump FILE.gguf|FILE.safetensors|DIR
+    ferrum serve                                                          (not part of this engine)
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+USAGE = "usage: ferrum generate|random-weights|replay|dump|serve [options]  (ferrum --help lists them)"
+
+# option -> (kind, repeatable)
+OPTIONS = {
+    "generate": {"--model": "str", "--prompt-tokens": "tokens+", "--prompt-file": "str", "--dtype": "str",
+                 "--max-new-tokens": "int", "--temperature": "float", "--top-p": "float", "--seed": "int",
+                 "--stop-tokens": "tokens", "--max-batch-tokens": "int", "--max-batch-seqs": "int",
+                 "--chunk-size": "int", "--page-size": "int", "--num-pages": "int", "--max-model-len": "int",
+                 "--random-weights": "flag", "--weights-seed": "int", "--stats": "flag"},
+    "random-weights": {"--config": "str", "--out": "str", "--seed": "int", "--dtype": "str", "--gguf": "flag"},
+    "replay": {"--model": "str", "--dtype": "str", "--out": "str", "--max-tokens": "int", "--page-size": "int",
+               "--max-requests": "int"},
+    "dump": {},
+    "serve": {"--mock": "flag", "--bind": "str"},
+}
+
+
+class CliError(Exception):
+    pass
+
+
+def _convert(kind, flag, text):
+    try:
+        if kind == "int":
+            return int(text)
+        if kind == "float":
+            return float(text)
+        if kind.startswith("tokens"):
+            return [int(t) for t in text.replace(" ", "").split(",") if t != ""]
+    except ValueError:
+        raise CliError(f"{flag}: cannot read {text!r}") from None
+    return text
+
+
+def parse_args(argv):
+    """(command, options dict, positional list).  Errors follow the reference's wording."""
+    args = list(argv)
+    if not args:
+        raise CliError(USAGE)
+    command = args.pop(0)
+    if command in ("-h", "--help", "help"):
+        return "help", {}, []
+    if command not in OPTIONS:
+        raise CliError(f"unknown command: {command}")
+    spec, opts, positional = OPTIONS[command], {}, []
+    while args:
+        arg = args.pop(0)
+        flag, eq, inline = arg.partition("=")
+        if not arg.startswith("--"):
+            if command == "dump":
+                positional.append(arg)
+                continue
+            raise CliError(f"unknown argument: {arg}")
+        if flag not in spec:
+            raise CliError(f"unknown argument: {arg}")
+        kind = spec[flag]
+        if kind == "flag":
+            if eq:
+                raise CliError(f"{flag} takes no value")
+            opts[flag] = True
+            continue
+        if eq:
+            value = inline
+        else:
+            if not args or (args[0].startswith("--") and not kind.startswith("tokens")):
+                raise CliError(f"{flag} requires a value")
+            value = args.pop(0)
+        if value == "":
+            raise CliError(f"{flag} requires a value")
+        value = _convert(kind, flag, value)
+        if kind.endswith("+"):
+            opts.setdefault(flag, []).append(value)
+        elif flag in opts:
+            raise CliError(f"{flag} specified more than once")
+        else:
+            opts[flag] = value
+    return command, opts, positional
+
+
+def _need(opts, flag):
+    if flag not in opts:
+        raise CliError(f"{flag} is required")
+    return opts[flag]
+
+
+def cmd_generate(opts):
+    from .engine.api import Engine, SamplingParams
+    model = _need(opts, "--model")
+    prompts = list(opts.get("--prompt-tokens", []))
+    if "--prompt-file" in opts:
+        with open(opts["--prompt-file"]) as f:
+            for line in f:
+                if line.strip():
+                    prompts.append(_convert("tokens", "--prompt-file", line.strip()))
+    if not prompts:
+        raise CliError("--prompt-tokens is required")
+    kw = {}
+    for flag, name in (("--page-size", "page_size"), ("--num-pages", "num_pages"), ("--max-batch-tokens", "max_batch_tokens"),
+                       ("--max-batch-seqs", "max_batch_seqs"), ("--chunk-size", "chunk_size"),
+                       ("--max-model-len", "max_model_len")):
+        if flag in opts:
+            kw[name] = opts[flag]
+    eng = Engine(model, dtype=opts.get("--dtype", "bfloat16"), random_weights=bool(opts.get("--random-weights")),
+                 seed=opts.get("--weights-seed", 0), **kw)
+    sp = SamplingParams(opts.get("--temperature", 0.0), opts.get("--top-p", 1.0), opts.get("--seed", 0))
+    ids = [eng.submit(p, opts.get("--max-new-tokens", 16), sp, opts.get("--stop-tokens", [])) for p in prompts]
+    out, reasons = {i: [] for i in ids}, {}
+    while len(reasons) < len(ids):
+        for ev in eng.step():
+            if ev.kind == "token":
+                out[ev.id].append(ev.token)
+            else:
+                reasons[ev.id] = ev.reason
+    for i in ids:
+        print(json.dumps({"id": i, "tokens": out[i], "finish_reason": reasons[i]}))
+    if opts.get("--stats"):
+        print(json.dumps(eng.stats()), file=sys.stderr)
+    return 0
+
+
+def cmd_random_weights(opts):
+    from .weights import write_random_gguf, write_random_model
+    with open(_need(opts, "--config")) as f:
+        cfg = json.load(f)
+    out = _need(opts, "--out")
+    if opts.get("--gguf"):
+        write_random_gguf(cfg, out, opts.get("--seed", 0), opts.get("--dtype", "float16"))
+    else:
+        write_random_model(cfg, out, opts.get("--seed", 0), opts.get("--dtype", "float32"))
+    print(out)
+    return 0
+
+
+def cmd_replay(opts):
+    from .engine.trace import TraceSession
+    s = TraceSession(_need(opts, "--model"), _need(opts, "--dtype"), _need(opts, "--max-tokens"),
+                     opts.get("--page-size", 16), opts.get("--max-requests", 8))
+    s.run_stream(sys.stdin, _need(opts, "--out"), sys.stdout)
+    return 0
+
+
+def cmd_dump(positional):
+    if len(positional) != 1:
+        raise CliError("usage: ferrum dump FILE.gguf|FILE.safetensors|DIR")
+    path = positional[0]
+    if path.endswith(".gguf"):
+        from .weights.gguf_io import GGUFFile
+        sys.stdout.write(GGUFFile(path).dump())
+        return 0
+    from .weights.loader import open_source
+    src = open_source(path)
+    print(f"ferrum-safetensors tensors={len(src.entries)}")
+    for name, (shape, dtype, _) in src.entries.items():
+        print(f"{name} [{', '.join(str(d) for d in shape)}] {str(dtype).replace('torch.', '')}")
+    return 0
+
+
+def main(argv=None):
+    argv = sys.argv[1:] if argv is None else argv
+    try:
+        command, opts, positional = parse_args(argv)
+    except CliError as e:
+        print(f"ferrum: {e}", file=sys.stderr)
+        return 2
+    try:
+        if command == "help":
+            print(__doc__)
+            return 0
+        if command == "serve":
+            # crates/ferrum-cli/src/main.rs:17-20 answers `serve` without --mock the same way
+            print("ferrum: the HTTP server is not part of this engine; use `ferrum generate` or the Python API",
+                  file=sys.stderr)
+            return 1
+        if command == "generate":
+            return cmd_generate(opts)
+        if command == "random-weights":
+            return cmd_random_weights(opts)
+        if command == "replay":
+            return cmd_replay(opts)
+        return cmd_dump(positional)
+    except CliError as e:
+        print(f"ferrum: {e}", file=sys.stderr)
+        return 2
+    except Exception as e:                      # runtime errors: exit 1, one line
+        print(f"ferrum: {e}", file=sys.stderr)
+        return 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

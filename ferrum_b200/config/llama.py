@@ -253,6 +253,28 @@ class LlamaConfig:
             d["eos_token_id"] = self.eos_token_id
         return d
 
+    def to_gguf_metadata(self) -> dict:
+        """GGUF keys, the inverse of `from_gguf_metadata` (crates/core-types/src/model.rs:64-128)."""
+        m = {"general.architecture": "llama", "general.name": self.name or "ferrum_b200",
+             "llama.context_length": self.n_ctx_train, "llama.embedding_length": self.n_embd,
+             "llama.block_count": self.n_layer, "llama.attention.head_count": self.n_head,
+             "llama.attention.head_count_kv": self.n_head_kv, "llama.feed_forward_length": self.n_ff,
+             "llama.attention.layer_norm_rms_epsilon": float(self.rms_norm_eps),
+             "llama.rope.freq_base": float(self.rope_freq_base), "llama.attention.key_length": self.head_dim,
+             "llama.attention.value_length": self.head_dim, "llama.rope.dimension_count": self.rope_dim,
+             "llama.vocab_size": self.n_vocab}
+        if self.rope_scaling is not None:
+            rs = self.rope_scaling
+            m.update({"llama.rope.scaling.type": rs.rope_type, "llama.rope.scaling.factor": float(rs.factor),
+                      "llama.rope.scaling.low_freq_factor": float(rs.low_freq_factor),
+                      "llama.rope.scaling.high_freq_factor": float(rs.high_freq_factor),
+                      "llama.rope.scaling.original_context_length": rs.original_max_position_embeddings})
+        if self.bos_token_id is not None:
+            m["tokenizer.ggml.bos_token_id"] = self.bos_token_id
+        if self.eos_token_id is not None:
+            m["tokenizer.ggml.eos_token_id"] = self.eos_token_id
+        return m
+
     @property
     def q_width(self) -> int:
         return self.n_head * self.head_dim

@@ -46,7 +46,8 @@ def load_model(path, dtype="bfloat16", device="cuda", max_positions=None, random
     if random_seed is not None:
         init_random(model, random_seed, device)
     else:
-        load_weights(model, path, arch.hf_names(cfg) if arch.hf_names else None, device)
+        rename = arch.hf_names(cfg) if arch.hf_names and not str(path).endswith(".gguf") else None
+        load_weights(model, path, rename, device)
     return model, td
 
 

@@ -55,4 +55,5 @@ def hf_names(config: LlamaConfig):
     return out
 
 
-register(Architecture("LlamaForCausalLM", LlamaConfig.from_dict, build_llama, hf_names), "llama")
+register(Architecture("LlamaForCausalLM", LlamaConfig.from_dict, build_llama, hf_names,
+                      LlamaConfig.from_gguf_metadata), "llama")

@@ -63,3 +63,24 @@ def write_random_model(config_dict, folder, seed, dtype="float32", std=0.02, tie
         json.dump(out, f, indent=1)
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors, {"format": "pt"})
     return folder
+
+
+def write_random_gguf(config_dict, path, seed, dtype="float16", std=0.02):
+    """Write a GGUF file (canonical tensor names, metadata keys of the reference) with the same
+    random values that `write_random_model` draws for this config and seed.  Rows of the q and
+    k matrices are stored as drawn, so the file means "adjacent-pair rotation" as every GGUF
+    Llama file does."""
+    from .gguf_io import write_gguf
+    store = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}[dtype]
+    arch = registry.lookup(str(config_dict["architectures"][0]))
+    cfg = arch.read_config(config_dict)
+    model = arch.build(cfg, torch.float32, "cpu", max_positions=1)
+    tied = getattr(cfg, "tie_word_embeddings", False)
+    tensors = {}
+    for name, (spec, _, _) in model.weight_specs().items():
+        if spec.optional and tied:
+            continue
+        t = _tensor(name, spec, seed, "cpu", std)
+        tensors[name] = t.to(store if spec.kind == "matrix" else torch.float32)
+    write_gguf(path, cfg.to_gguf_metadata(), tensors)
+    return path
