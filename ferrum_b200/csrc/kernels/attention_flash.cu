@@ -13,7 +13,13 @@
 // float32 accumulators, and the softmax is the online one in float32 (scores scaled by
 // log2(e)/sqrt(D), exp2).  A work item that covers its rows' whole key range writes the
 // output; otherwise it writes (m, l, O) partials and `attention_combine` merges the
-// splits in a fixed order.  Same formulas as the float32 kernel (attention_generic.cu);
+// splits in a fixed order.
+//
+// Two ways to hand out work.  Grid (items, Hkv): one item per CTA and KV head (prompt
+// portions).  Or a balanced list: the host cuts the line of all (request, KV head, 64-key
+// tile) units into one equal share per CTA slot of the GPU; a share is a few items, each
+// naming its KV head, and the CTA walks them (decoded tokens: the whole GPU reads the cache
+// at the same rate whatever the mix of context lengths).  Same formulas as the float32 kernel (attention_generic.cu);
 // the reference computes them one head and one position at a time
 // (crates/model/src/llama.rs:220-247).
 #include "common.cuh"
@@ -27,9 +33,10 @@ struct FlashParams {
   const int* block_table;
   const int* q_start;   // [R + 1] first token of each request in this batch
   const int* pos0;      // [R] cached positions before this step
-  const int* work;      // [n_work][8]: req, row0, kv_begin, kv_end, n_splits, part_slot, -, -
-  float* part_o;        // [slot][Hkv][BM][D]
-  float* part_ml;       // [slot][Hkv][BM][2]
+  const int* work;      // [n_work][8]: req, row0, kv_begin, kv_end, n_splits, part_slot, kv_head, -
+  const int* cta_items; // null: CTA (x, y) runs item x for KV head y; else CTA x runs items [cta_items[x], cta_items[x+1])
+  float* part_o;        // [slot][BM][D]
+  float* part_ml;       // [slot][BM][2]
   long long page_stride;
   int ldq, ldo, page_size, table_width;
   int Hq, Hkv, G, window;
@@ -74,22 +81,18 @@ __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row,
 }
 
 template <int D, int WM, int WN>
-__global__ void __launch_bounds__(WM * WN * 32)
-flash_kernel(const FlashParams p) {
+__device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, int kvh, uint8_t* smem_raw) {
   constexpr int BM = 16 * WM;
   constexpr int NT = WM * WN * 32;
   constexpr int KW = BN / WN;   // keys of a tile that one warp handles
   constexpr int CH = D / 8;     // 16-byte chunks per row
   static_assert(KW % 16 == 0, "a warp needs at least 16 keys per tile");
-  extern __shared__ __align__(128) uint8_t smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BM][D]
   __nv_bfloat16* sK = sQ + BM * D;                                  // [2][BN][D]
   __nv_bfloat16* sV = sK + 2 * BN * D;                              // [2][BN][D]
 
-  const int* wk = p.work + (size_t)blockIdx.x * 8;
   const int req = wk[0], row0 = wk[1], kv_begin = wk[2], kv_end = wk[3], n_splits = wk[4], part = wk[5];
   if (n_splits == 0) return;  // padding of a fixed-size work list
-  const int kvh = blockIdx.y;
   const int G = p.G;
   const int qs = p.q_start[req];
   const int n_rows = (p.q_start[req + 1] - qs) * G;
@@ -295,7 +298,7 @@ flash_kernel(const FlashParams p) {
       packed.y = pack_bf16(acc.z * inv, acc.w * inv);
       *reinterpret_cast<uint2*>(dst) = packed;
     } else {
-      const size_t slot = ((size_t)part * p.Hkv + kvh) * BM + r;
+      const size_t slot = (size_t)part * BM + r;
       *reinterpret_cast<float4*>(p.part_o + slot * D + d) = acc;
       if (d == 0) {
         p.part_ml[slot * 2] = M;
@@ -305,9 +308,32 @@ flash_kernel(const FlashParams p) {
   }
 }
 
-// Merges the splits of every (token, head) whose tile was split.  tile_info: per tile
-// [first part slot, n_splits]; req_tile0[r]: index of request r's first tile; token_list:
-// the tokens to visit (null: all n_tokens).
+template <int D, int WM, int WN>
+__global__ void __launch_bounds__(WM * WN * 32)
+flash_kernel(const FlashParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  if (p.cta_items == nullptr) {
+    const int* wk = p.work + (size_t)blockIdx.x * 8;
+    // with one item per (CTA, head) the item's partial slot is per head
+    int item[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) item[i] = wk[i];
+    item[5] = item[5] * p.Hkv + blockIdx.y;
+    flash_item<D, WM, WN>(p, item, blockIdx.y, smem_raw);
+    return;
+  }
+  const int begin = p.cta_items[blockIdx.x], end = p.cta_items[blockIdx.x + 1];
+  for (int w = begin; w < end; ++w) {
+    const int* wk = p.work + (size_t)w * 8;
+    flash_item<D, WM, WN>(p, wk, wk[6], smem_raw);
+    __syncthreads();  // the next item's loads reuse the shared memory the merge just read
+  }
+}
+
+
+// Merges the splits of every (token, head) whose tile was split.  tile_info: per (tile, KV
+// head) [first part slot, n_splits, slot stride, 0]; req_tile0[r]: index of request r's first
+// tile; token_list: the tokens to visit (null: all n_tokens).
 template <int D>
 __global__ void __launch_bounds__(D / 4 < 32 ? 32 : D / 4)
 combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* part_ml, const int* q_start,
@@ -317,18 +343,18 @@ combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* pa
   const int req = req_of_token[t];
   const int kvh = head / G;
   const int pr = (t - q_start[req]) * G + head % G;
-  const int* info = tile_info + 2 * (req_tile0[req] + pr / BM);
-  const int first = info[0], n = info[1];
+  const int* info = tile_info + 4 * ((size_t)(req_tile0[req] + pr / BM) * Hkv + kvh);
+  const int first = info[0], n = info[1], stride = info[2];
   if (n <= 1) return;
   const int r = pr % BM;
   const int d = threadIdx.x * 4;
   if (d >= D) return;
   float M = -INFINITY;
-  for (int s = 0; s < n; ++s) M = fmaxf(M, part_ml[(((size_t)(first + s) * Hkv + kvh) * BM + r) * 2]);
+  for (int s = 0; s < n; ++s) M = fmaxf(M, part_ml[((size_t)(first + s * stride) * BM + r) * 2]);
   float L = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s = 0; s < n; ++s) {
-    const size_t slot = ((size_t)(first + s) * Hkv + kvh) * BM + r;
+    const size_t slot = (size_t)(first + s * stride) * BM + r;
     const float ms = part_ml[slot * 2];
     const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
     L += part_ml[slot * 2 + 1] * f;
@@ -343,7 +369,7 @@ combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* pa
 }
 
 template <int D, int WM, int WN>
-int launch_flash(const FlashParams& p, int n_work, cudaStream_t stream) {
+int launch_flash(const FlashParams& p, int n_work, int n_ctas, cudaStream_t stream) {
   constexpr int BM = 16 * WM;
   constexpr int kv_bytes = 4 * BN * D * 2 + BM * D * 2;
   constexpr int merge_bytes = WN * BM * (D + 2) * 4;
@@ -354,7 +380,7 @@ int launch_flash(const FlashParams& p, int n_work, cudaStream_t stream) {
     FERRUM_CHECK_ARG(e == cudaSuccess, "attention_flash: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid(n_work, p.Hkv);
+  dim3 grid = p.cta_items ? dim3(n_ctas, 1) : dim3(n_work, p.Hkv);
   flash_kernel<D, WM, WN><<<grid, WM * WN * 32, smem, stream>>>(p);
   FERRUM_CHECK_LAUNCH("attention_flash");
   return 0;
@@ -365,12 +391,13 @@ int launch_flash(const FlashParams& p, int n_work, cudaStream_t stream) {
 FERRUM_API int ferrum_attention_flash_supported(int D, int bm) { return (D == 64 || D == 128) && (bm == 16 || bm == 64); }
 
 // work: [n_work][8] int32 on the device (see FlashParams).  bm: 16 (a few rows per request,
-// key range split between four warps) or 64.
+// key range split between four warps) or 64.  cta_items (n_ctas + 1 ints) selects the
+// balanced-list mode; null runs a grid of (n_work, Hkv).
 FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo, const void* kv_plane,
                                       long long page_stride, int page_size, const int* block_table, int table_width,
-                                      const int* q_start, const int* pos0, const int* work, int n_work, float* part_o,
-                                      float* part_ml, int Hq, int Hkv, int D, float scale, int window, int bm,
-                                      cudaStream_t stream) {
+                                      const int* q_start, const int* pos0, const int* work, int n_work,
+                                      const int* cta_items, int n_ctas, float* part_o, float* part_ml, int Hq, int Hkv,
+                                      int D, float scale, int window, int bm, cudaStream_t stream) {
   FERRUM_CHECK_ARG(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_flash: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
   FERRUM_CHECK_ARG(ferrum_attention_flash_supported(D, bm), "attention_flash: head size %d with row tile %d is not built; "
                    "use the generic kernel", D, bm);
@@ -378,17 +405,19 @@ FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo
                    ((uintptr_t)kv_plane & 15) == 0, "attention_flash: operands must be 16-byte aligned");
   FERRUM_CHECK_ARG(page_size > 0 && table_width > 0 && window >= 0 && n_work >= 0, "attention_flash: bad arguments");
   if (n_work == 0) return 0;
+  FERRUM_CHECK_ARG(cta_items == nullptr || n_ctas > 0, "attention_flash: an item list needs a CTA count");
   FlashParams p;
+  p.cta_items = cta_items;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.kv_plane = (const __nv_bfloat16*)kv_plane;
   p.block_table = block_table; p.q_start = q_start; p.pos0 = pos0; p.work = work;
   p.part_o = part_o; p.part_ml = part_ml; p.page_stride = page_stride;
   p.ldq = ldq; p.ldo = ldo; p.page_size = page_size; p.table_width = table_width;
   p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
-  if (D == 64 && bm == 16) return launch_flash<64, 1, 4>(p, n_work, stream);
-  if (D == 64 && bm == 64) return launch_flash<64, 4, 1>(p, n_work, stream);
-  if (D == 128 && bm == 16) return launch_flash<128, 1, 4>(p, n_work, stream);
-  return launch_flash<128, 4, 1>(p, n_work, stream);
+  if (D == 64 && bm == 16) return launch_flash<64, 1, 4>(p, n_work, n_ctas, stream);
+  if (D == 64 && bm == 64) return launch_flash<64, 4, 1>(p, n_work, n_ctas, stream);
+  if (D == 128 && bm == 16) return launch_flash<128, 1, 4>(p, n_work, n_ctas, stream);
+  return launch_flash<128, 4, 1>(p, n_work, n_ctas, stream);
 }
 
 FERRUM_API int ferrum_attention_combine(void* out, int ldo, const float* part_o, const float* part_ml,

@@ -8,10 +8,12 @@ every layer with the same (G, window).
 
 Requests with at most 16 rows (decoded tokens) go to the 16-row kernel, the others to the
 64-row kernel; each class has its own work list.  A work item is
-[request, first row, key begin, key end, number of splits, partial slot, 0, 0]; an item with
-zero splits is padding.  Split boundaries are multiples of 64 keys counted from the tile's
-first key, and the splits are merged in order, so a row's result does not depend on the
-other requests in the batch beyond the choice of the split length.
+[request, first row, key begin, key end, number of splits, partial slot, KV head, 0]; an item
+with zero splits is padding.  The 64-row class runs a grid of (items, KV heads).  The 16-row
+class runs a balanced list: every CTA slot of the GPU gets an equal share of all (request,
+head, 64-key tile) units.  Split boundaries are multiples of 64 keys counted from the tile's
+first key and the splits are merged in key order; where they fall depends on the batch, so a
+row's bfloat16 result may differ between batches by rounding, never by more.
 
 The lists live in device buffers that keep their address from step to step, and a plan can
 be padded to a fixed number of items, so that a captured CUDA graph can be replayed with the
@@ -30,14 +32,108 @@ CLASSES = (16, 64)
 MIN_SPLIT_KEYS = {16: 256, 64: 1024}
 
 
-def target_items(Hkv):
-    """Work items per class that fill the GPU once at two CTAs per SM."""
-    return max(1, (2 * N_SMS) // Hkv)
+CTA_SLOTS = 2 * N_SMS      # the 16-row kernel keeps two CTAs on an SM
+MIN_TILES_PER_CTA = 4
 
 
 def item_capacity(n_requests, Hkv):
-    """Upper bound of the 16-row class's work items for n_requests decoded tokens."""
-    return target_items(Hkv) + 2 * n_requests
+    """Upper bound of the balanced list's items: one per CTA slot plus one per (request, head)."""
+    return CTA_SLOTS + n_requests * Hkv
+
+
+def _tiles(q_len, pos0, G, window, bm, sel):
+    """Row tiles of the selected requests: (request, first row, first key, end key) per tile."""
+    rows = q_len * G
+    n_tiles = (rows[sel] + bm - 1) // bm
+    req_of_tile = np.repeat(sel, n_tiles)
+    tile_in_req = np.arange(n_tiles.sum()) - np.repeat(np.cumsum(n_tiles) - n_tiles, n_tiles)
+    row0 = tile_in_req * bm
+    first_tok = row0 // G
+    last_tok = np.minimum(q_len[req_of_tile] - 1, (row0 + bm - 1) // G)
+    hi = pos0[req_of_tile] + last_tok + 1
+    lo = np.maximum(0, pos0[req_of_tile] + first_tok - window + 1) if window > 0 else np.zeros_like(hi)
+    return n_tiles, req_of_tile, row0, lo, hi
+
+
+def _grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start):
+    """One item per (tile, key split); the kernel runs it once per KV head."""
+    n_tiles, req_of_tile, row0, lo, hi = _tiles(q_len, pos0, G, window, bm, sel)
+    length = hi - lo
+    # about one item per CTA slot of the GPU, never splits shorter than the minimum
+    chunk = int(max(MIN_SPLIT_KEYS[bm], -(-int(length.sum()) // max(1, CTA_SLOTS // Hkv))))
+    chunk = (chunk + 63) // 64 * 64
+    n_splits = np.maximum(1, (length + chunk - 1) // chunk)
+    T = int(n_splits.sum())
+    tile_of_work = np.repeat(np.arange(len(req_of_tile)), n_splits)
+    split_idx = np.arange(T) - np.repeat(np.cumsum(n_splits) - n_splits, n_splits)
+    kb = lo[tile_of_work] + split_idx * chunk
+    ke = np.minimum(hi[tile_of_work], kb + chunk)
+    ns = n_splits[tile_of_work]
+    is_split = ns > 1
+    slot = np.where(is_split, np.cumsum(is_split) - 1, -1)
+    work = np.zeros((T, 8), dtype=np.int32)
+    work[:, 0], work[:, 1], work[:, 2], work[:, 3] = req_of_tile[tile_of_work], row0[tile_of_work], kb, ke
+    work[:, 4], work[:, 5] = ns, slot
+    order = np.argsort(-(ke - kb), kind="stable")          # long items first
+    # per (tile, head): first partial slot, number of splits, slot stride.  The kernel gives
+    # item s of head h the slot (first item slot + s) * Hkv + h.
+    split_sizes = np.where(n_splits > 1, n_splits, 0)
+    first_slot = np.cumsum(split_sizes) - split_sizes
+    info = np.zeros((len(req_of_tile), Hkv, 4), dtype=np.int32)
+    info[:, :, 0] = first_slot[:, None] * Hkv + np.arange(Hkv)[None, :]
+    info[:, :, 1] = n_splits[:, None]
+    info[:, :, 2] = Hkv
+    req_tile0 = np.zeros(R, dtype=np.int32)
+    req_tile0[sel] = (np.cumsum(n_tiles) - n_tiles).astype(np.int32)
+    split_reqs = np.unique(req_of_tile[n_splits > 1])
+    comb = np.concatenate([np.arange(q_start[r], q_start[r + 1]) for r in split_reqs]).astype(np.int32) \
+        if len(split_reqs) else np.zeros(0, dtype=np.int32)
+    return {"bm": bm, "work": work[order].reshape(-1), "n_work": T, "n_slots": int(is_split.sum()) * Hkv,
+            "tile_info": info.reshape(-1), "req_tile0": req_tile0, "comb": comb,
+            "cta_items": np.zeros(0, dtype=np.int32), "n_ctas": 0}
+
+
+def _balanced_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start):
+    """Requests with one row tile each (decoded tokens).  All (request, head, 64-key tile)
+    units form one line; CTA slot c owns units [c*U/P, (c+1)*U/P); a share is cut into items
+    at (request, head) borders."""
+    n_tiles, req_of_tile, row0, lo, hi = _tiles(q_len, pos0, G, window, bm, sel)
+    assert (n_tiles == 1).all()
+    n_req = len(sel)
+    kt = np.maximum(1, (hi - lo + 63) // 64)                       # key tiles per request
+    pair_tiles = np.repeat(kt, Hkv)                                 # pairs in (request, head) order
+    pair_start = np.concatenate([[0], np.cumsum(pair_tiles)])
+    U = int(pair_start[-1])
+    P = int(min(CTA_SLOTS, max(1, U // MIN_TILES_PER_CTA)))     # no share shorter than a few tiles
+    bounds = (np.arange(P + 1, dtype=np.int64) * U) // P
+    cuts = np.unique(np.concatenate([pair_start, bounds]))
+    seg_b, seg_e = cuts[:-1], cuts[1:]
+    pair = np.searchsorted(pair_start, seg_b, side="right") - 1
+    r_idx, head = pair // Hkv, pair % Hkv
+    t0, t1 = seg_b - pair_start[pair], seg_e - pair_start[pair]
+    kb = lo[r_idx] + t0 * 64
+    ke = np.minimum(hi[r_idx], lo[r_idx] + t1 * 64)
+    per_pair = np.bincount(pair, minlength=n_req * Hkv)
+    ns = per_pair[pair]
+    is_split = ns > 1
+    slot = np.where(is_split, np.cumsum(is_split) - 1, -1)
+    n_seg = len(seg_b)
+    work = np.zeros((n_seg, 8), dtype=np.int32)
+    work[:, 0], work[:, 1], work[:, 2], work[:, 3] = sel[r_idx], 0, kb, ke
+    work[:, 4], work[:, 5], work[:, 6] = ns, slot, head
+    cta_items = np.searchsorted(seg_b, bounds[:-1], side="left").astype(np.int32)
+    cta_items = np.concatenate([cta_items, [n_seg]]).astype(np.int32)
+    split_sizes = np.where(per_pair > 1, per_pair, 0)
+    first_slot = np.cumsum(split_sizes) - split_sizes              # a pair's items are consecutive
+    info = np.zeros((n_req * Hkv, 4), dtype=np.int32)
+    info[:, 0], info[:, 1], info[:, 2] = first_slot, per_pair, 1
+    req_tile0 = np.zeros(R, dtype=np.int32)
+    req_tile0[sel] = np.arange(n_req, dtype=np.int32)
+    split_reqs = np.unique(r_idx[is_split])
+    comb = np.concatenate([np.arange(q_start[sel[r]], q_start[sel[r] + 1]) for r in split_reqs]).astype(np.int32) \
+        if len(split_reqs) else np.zeros(0, dtype=np.int32)
+    return {"bm": bm, "work": work.reshape(-1), "n_work": n_seg, "n_slots": int(is_split.sum()),
+            "tile_info": info.reshape(-1), "req_tile0": req_tile0, "comb": comb, "cta_items": cta_items, "n_ctas": P}
 
 
 def build_host(q_len, pos0, G, window, Hkv):
@@ -52,43 +148,10 @@ def build_host(q_len, pos0, G, window, Hkv):
         sel = np.nonzero((rows <= 16) if bm == 16 else (rows > 16))[0]
         if len(sel) == 0:
             out.append(None)
-            continue
-        n_tiles = (rows[sel] + bm - 1) // bm
-        req_of_tile = np.repeat(sel, n_tiles)
-        tile_in_req = np.arange(n_tiles.sum()) - np.repeat(np.cumsum(n_tiles) - n_tiles, n_tiles)
-        row0 = tile_in_req * bm
-        first_tok = row0 // G
-        last_tok = np.minimum(q_len[req_of_tile] - 1, (row0 + bm - 1) // G)
-        hi = pos0[req_of_tile] + last_tok + 1
-        lo = np.maximum(0, pos0[req_of_tile] + first_tok - window + 1) if window > 0 else np.zeros_like(hi)
-        length = hi - lo
-        # about one item per CTA slot of the GPU, never splits shorter than the minimum
-        chunk = int(max(MIN_SPLIT_KEYS[bm], -(-int(length.sum()) // target_items(Hkv))))
-        chunk = (chunk + 63) // 64 * 64
-        n_splits = np.maximum(1, (length + chunk - 1) // chunk)
-        T = int(n_splits.sum())
-        tile_of_work = np.repeat(np.arange(len(req_of_tile)), n_splits)
-        split_idx = np.arange(T) - np.repeat(np.cumsum(n_splits) - n_splits, n_splits)
-        kb = lo[tile_of_work] + split_idx * chunk
-        ke = np.minimum(hi[tile_of_work], kb + chunk)
-        ns = n_splits[tile_of_work]
-        is_split = ns > 1
-        slot = np.where(is_split, np.cumsum(is_split) - 1, -1)
-        work = np.zeros((T, 8), dtype=np.int32)
-        work[:, 0], work[:, 1], work[:, 2], work[:, 3] = req_of_tile[tile_of_work], row0[tile_of_work], kb, ke
-        work[:, 4], work[:, 5] = ns, slot
-        order = np.argsort(-(ke - kb), kind="stable")          # long items first
-        # per tile: first partial slot and number of splits (slots of a tile are consecutive)
-        split_sizes = np.where(n_splits > 1, n_splits, 0)
-        first_slot = np.where(n_splits > 1, np.cumsum(split_sizes) - split_sizes, 0)
-        tile_info = np.stack([first_slot, n_splits], axis=1).astype(np.int32)
-        req_tile0 = np.zeros(R, dtype=np.int32)
-        req_tile0[sel] = (np.cumsum(n_tiles) - n_tiles).astype(np.int32)
-        split_reqs = np.unique(req_of_tile[n_splits > 1])
-        comb = np.concatenate([np.arange(q_start[r], q_start[r + 1]) for r in split_reqs]).astype(np.int32) \
-            if len(split_reqs) else np.zeros(0, dtype=np.int32)
-        out.append({"bm": bm, "work": work[order].reshape(-1), "n_work": T, "n_slots": int(is_split.sum()),
-                    "tile_info": tile_info.reshape(-1), "req_tile0": req_tile0, "comb": comb})
+        elif bm == 16:
+            out.append(_balanced_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start))
+        else:
+            out.append(_grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start))
     return out
 
 
@@ -102,6 +165,8 @@ class ClassPlan:
     tile_info: Optional[torch.Tensor] = None
     comb_tokens: Optional[torch.Tensor] = None  # None: every token of the batch
     n_comb: int = 0
+    cta_items: Optional[torch.Tensor] = None    # balanced list: first item of every CTA (+ end)
+    n_ctas: int = 0
 
 
 class AttentionPlans:
@@ -143,15 +208,18 @@ class AttentionPlans:
             if h is None or host[1] is not None:
                 raise ValueError("a fixed-shape plan needs a batch of decoded tokens only")
             cap = item_capacity(R, Hkv)
-            if h["n_work"] > cap:
+            if h["n_work"] > cap or h["n_ctas"] > CTA_SLOTS:
                 raise ValueError("attention plan exceeds its fixed capacity")
             padded = np.zeros(cap * 8, dtype=np.int32)
             padded[:h["work"].size] = h["work"]
-            h["work"], h["n_work"], h["n_slots"] = padded, cap, cap
+            # the grid is always CTA_SLOTS wide; CTAs beyond the plan's get an empty range
+            items = np.full(CTA_SLOTS + 1, h["n_work"], dtype=np.int32)
+            items[:h["cta_items"].size] = h["cta_items"]
+            h["work"], h["n_slots"], h["cta_items"], h["n_ctas"] = padded, cap, items, CTA_SLOTS
         arrays = []
         for h in host:
             if h is not None:
-                arrays += [h["work"], h["tile_info"], h["req_tile0"], h["comb"]]
+                arrays += [h["work"], h["tile_info"], h["req_tile0"], h["comb"], h["cta_items"]]
         total = sum(a.size for a in arrays)
         ring, dev = self._buffers(key, total)
         pinned = ring.next()
@@ -166,11 +234,13 @@ class AttentionPlans:
                 plans.append(None)
                 continue
             views = []
-            for name in ("work", "tile_info", "req_tile0", "comb"):
+            for name in ("work", "tile_info", "req_tile0", "comb", "cta_items"):
                 views.append(dev[o:o + h[name].size])
                 o += h[name].size
             cp = ClassPlan(h["bm"], h["n_work"], views[0], h["n_slots"])
             cp.tile_info, cp.req_tile0 = views[1], views[2]
+            if h["n_ctas"]:
+                cp.cta_items, cp.n_ctas = views[4], h["n_ctas"]
             if fixed:
                 cp.comb_tokens, cp.n_comb = None, ctx.n_tokens
             else:

@@ -72,11 +72,11 @@ class PagedAttention(Mixer):
                 continue
             part_o = part_ml = None
             if plan.n_slots:
-                part_o = ctx.buf("attn_part_o", (plan.n_slots * Hkv * plan.bm * D,), torch.float32)
-                part_ml = ctx.buf("attn_part_ml", (plan.n_slots * Hkv * plan.bm * 2,), torch.float32)
+                part_o = ctx.buf("attn_part_o", (plan.n_slots * plan.bm * D,), torch.float32)
+                part_ml = ctx.buf("attn_part_ml", (plan.n_slots * plan.bm * 2,), torch.float32)
             ops.attention_flash(qkv, out, cache.plane, cache.page_stride, cache.page_size, table, ctx.q_start,
                                 ctx.pos0, plan.work, plan.n_work, part_o, part_ml, Hq, Hkv, D, self.scale,
-                                self.window, plan.bm)
+                                self.window, plan.bm, plan.cta_items, plan.n_ctas)
             if plan.n_comb:
                 ops.attention_combine(out, part_o, part_ml, ctx.q_start, ctx.req_of_token, plan.req_tile0,
                                       plan.tile_info, plan.comb_tokens, plan.n_comb, Hq, Hkv, D, plan.bm)

@@ -269,10 +269,11 @@ def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window):
     for h in build_host(qlens, pos0, Hq // Hkv, window, Hkv):
         if h is None:
             continue
-        part_o = torch.empty(max(1, h["n_slots"] * Hkv * h["bm"] * D), device="cuda")
-        part_ml = torch.empty(max(1, h["n_slots"] * Hkv * h["bm"] * 2), device="cuda")
+        part_o = torch.empty(max(1, h["n_slots"] * h["bm"] * D), device="cuda")
+        part_ml = torch.empty(max(1, h["n_slots"] * h["bm"] * 2), device="cuda")
         ops.attention_flash(q, out, plane, plane.stride(0), ps, table, dev(qs), dev(pos0), dev(h["work"]), h["n_work"],
-                            part_o, part_ml, Hq, Hkv, D, 1.0 / math.sqrt(D), window, h["bm"])
+                            part_o, part_ml, Hq, Hkv, D, 1.0 / math.sqrt(D), window, h["bm"],
+                            dev(h["cta_items"]) if h["n_ctas"] else None, h["n_ctas"])
         if h["comb"].size:
             ops.attention_combine(out, part_o, part_ml, dev(qs), dev(req), dev(h["req_tile0"]), dev(h["tile_info"]),
                                   dev(h["comb"]), int(h["comb"].size), Hq, Hkv, D, h["bm"])
