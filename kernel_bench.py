@@ -1,0 +1,157 @@
+#!/usr/bin/env python3
+"""Times one kernel of the engine in isolation (CUDA events, warm-up, inputs larger than L2)
+and prints one JSON line with its achieved bandwidth or throughput against the measured
+peaks.  This is the small case that `ncu` captures are taken on.
+
+    python kernel_bench.py attn_decode [--batch 8] [--context 8192] [--layers 4]
+    python kernel_bench.py attn_prefill [--tokens 2048]
+    python kernel_bench.py gemm --tokens 8 --n 6144 --k 4096 [--epilogue store|residual|swiglu] [--copies 8]
+    python kernel_bench.py rmsnorm|rope --tokens 8
+Shapes default to Llama-3.1-8B (32 query heads, 8 KV heads, head size 128, width 4096).
+"""
+import argparse
+import json
+import math
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemm", "rmsnorm", "rope"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--tokens", type=int, default=8)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--epilogue", default="store", choices=["store", "residual", "swiglu"])
+    ap.add_argument("--copies", type=int, default=8, help="distinct weight/cache copies cycled through, to defeat L2")
+    ap.add_argument("--layers", type=int, default=4, help="cache planes cycled through (attention)")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
+    args = ap.parse_args()
+
+    import torch
+    from bench import peaks
+    from ferrum_b200.engine.batch import StepContext, StepEntry
+    from ferrum_b200.ops import lib as ops
+    ops.require_cuda()
+    pk = peaks()
+    dev = "cuda"
+    Hq, Hkv, D, ps = args.hq, args.hkv, args.head_dim, args.page_size
+    gen = torch.Generator(device=dev).manual_seed(0)
+    runs = []
+
+    if args.kernel in ("attn_decode", "attn_prefill"):
+        from ferrum_b200.parts import PagedAttention
+        decode = args.kernel == "attn_decode"
+        R = args.batch if decode else 1
+        qlen = 1 if decode else args.tokens
+        ctx_len = args.context if decode else args.tokens
+        n_pages = R * ((ctx_len + ps - 1) // ps)
+        width = (ctx_len + ps - 1) // ps
+        planes = [torch.randn(n_pages, 2, Hkv, ps, D, device=dev, generator=gen).mul_(0.5).bfloat16() for _ in range(args.layers)]
+        perm = torch.randperm(n_pages).view(R, width).tolist()
+        ctx = StepContext(dev, max(16, R * qlen), R, [width])
+        ctx.fixed_shapes = False
+        ctx.fill([StepEntry(r, ctx_len - qlen, [1] * qlen) for r in range(R)], [perm])
+        T = R * qlen
+        q = torch.randn(T, Hq * D, device=dev, generator=gen).bfloat16()
+        out = torch.empty(T, Hq * D, device=dev, dtype=torch.bfloat16)
+        att = PagedAttention(Hq * D, Hq, Hkv, D, None, torch.bfloat16)
+
+        class Cache:
+            pass
+        caches = []
+        for pl in planes:
+            c = Cache()
+            c.plane, c.page_stride, c.page_size, c.group, c.writes = pl, pl.stride(0), ps, 0, True
+            caches.append(c)
+        table = ctx.block_tables[0]
+        runs = [lambda c=c: att._flash(q, out, ctx, c, table) for c in caches]
+        kv_bytes = R * ctx_len * 2 * Hkv * D * 2
+        flops = 4.0 * Hq * D * (ctx_len * qlen if decode else qlen * qlen / 2) * R
+        work = {"bytes": kv_bytes + 2 * T * Hq * D * 2, "flops": flops, "bound": "hbm" if decode else "tensor"}
+    elif args.kernel == "gemm":
+        M, N, K = args.tokens, args.n, args.k
+        dual = args.epilogue == "swiglu"
+        ws_f, tiles = ops.gemm_tc_workspace(M, N, K, dual)
+        ws = torch.empty(ws_f, device=dev)
+        cnt = torch.zeros(max(tiles, 1), dtype=torch.int32, device=dev)
+        err = torch.zeros(1, dtype=torch.int32, device=dev)
+        x = torch.randn(M, K, device=dev, generator=gen).bfloat16()
+        weights = [torch.randn(N * (2 if dual else 1), K, device=dev, generator=gen).mul_(0.02).bfloat16() for _ in range(args.copies)]
+        if args.epilogue == "residual":
+            o = torch.zeros(M, N, device=dev)
+            epi = ops.TC_RESIDUAL
+        else:
+            o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            epi = ops.TC_SWIGLU if dual else ops.TC_STORE_BF16
+        runs = [lambda w=w: ops.gemm_tc(x, w, o, epi, err, ws, cnt, N=N, dual_offset=N if dual else 0) for w in weights]
+        wb = N * K * 2 * (2 if dual else 1)
+        work = {"bytes": wb + M * K * 2 + M * N * (4 if args.epilogue == "residual" else 2),
+                "flops": 2.0 * M * N * K * (2 if dual else 1), "bound": "hbm" if M <= 128 else "tensor"}
+    elif args.kernel == "rmsnorm":
+        T, E = args.tokens, args.k
+        x = torch.randn(T, E, device=dev, generator=gen)
+        w = torch.ones(E, device=dev)
+        o = torch.empty(T, E, device=dev, dtype=torch.bfloat16)
+        runs = [lambda: ops.rmsnorm(x, w, o, 1e-5)]
+        work = {"bytes": T * E * 6, "flops": 3.0 * T * E, "bound": "hbm"}
+    else:
+        from ferrum_b200.parts.rope import RotaryEmbedding
+        T = args.tokens
+        rot = RotaryEmbedding(D, D, 500000.0, None, "half", args.context + 8, dev)
+        width = (args.context + ps) // ps
+        plane = torch.zeros(T * width, 2, Hkv, ps, D, device=dev, dtype=torch.bfloat16)
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev, generator=gen).bfloat16()
+        pos = torch.full((T,), args.context - 1, dtype=torch.int32, device=dev)
+        req = torch.arange(T, dtype=torch.int32, device=dev)
+        table = torch.arange(T * width, dtype=torch.int32, device=dev).view(T, width)
+        err = torch.zeros(1, dtype=torch.int32, device=dev)
+        runs = [lambda: ops.rope_cache_write(qkv, T, pos, req, table, rot.cos_sin, plane, plane.stride(0), ps, Hq, Hkv, D, D,
+                                             rot.pairing, True, err)]
+        work = {"bytes": T * (Hq + 2 * Hkv) * D * 2 * 2, "flops": 0.0, "bound": "hbm"}
+
+    for i in range(args.warmup):
+        runs[i % len(runs)]()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.no_graph:
+        ev0.record()
+        for i in range(args.iters):
+            runs[i % len(runs)]()
+        ev1.record()
+    else:
+        # the launches go into one CUDA graph so that the host's launch rate does not bound
+        # the measurement of kernels that take a few microseconds
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(args.iters):
+                runs[i % len(runs)]()
+        graph.replay()
+        torch.cuda.synchronize()
+        ev0.record()
+        graph.replay()
+        ev1.record()
+    torch.cuda.synchronize()
+    us = ev0.elapsed_time(ev1) / args.iters * 1e3
+    gbs = work["bytes"] / (us * 1e-6) / 1e9
+    tf = work["flops"] / (us * 1e-6) / 1e12
+    frac = gbs / pk["hbm_gbs"] if work["bound"] == "hbm" else tf / pk["bf16_tflops"]
+    print(json.dumps({"kernel": args.kernel, "us": round(us, 2), "GBps": round(gbs, 1), "TFLOPs": round(tf, 2),
+                      "bound": work["bound"], "frac_of_peak": round(frac, 4), "peaks": pk["source"],
+                      "args": {k: v for k, v in vars(args).items() if k != "kernel"}}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
