@@ -515,3 +515,96 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
 #undef TC_CASE
   FERRUM_CHECK_ARG(false, "gemm_tc: no kernel for token tile %d", bt);
 }
+
+// ------------------------------------------------------------------ no-allocation entry point
+// See ferrum_noalloc.h for who needs this and for the rules of use.
+#include "ferrum_noalloc.h"
+
+// Scratch of ferrum_gemm_tc_noalloc: float32 partial tiles, then the tile counters.  It is
+// part of the library's device image: every GPU that loads the library holds it until exit.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[FERRUM_NOALLOC_SCRATCH_BYTES + FERRUM_NOALLOC_MAX_TILES * sizeof(int)];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel
+// can use; the device address is looked up once per device, with that device current.
+static int noalloc_scratch_address(unsigned char** out) {
+  constexpr int kMaxDevices = 64;
+  static unsigned char* addr[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  FERRUM_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "gemm_tc_noalloc: device ordinal %d is not supported", dev);
+  std::lock_guard<std::mutex> g(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    FERRUM_CHECK_ARG(e == cudaSuccess && p != nullptr, "gemm_tc_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    addr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = addr[dev];
+  return 0;
+}
+
+// A tensor map built on the stack (the cached variant keeps maps in a host container).
+static int encode_tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+  EncodeTiledFn fn = get_encode_fn();
+  FERRUM_CHECK_ARG(fn != nullptr, "gemm_tc_noalloc: the driver does not export cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FERRUM_CHECK_ARG(r == CUDA_SUCCESS, "gemm_tc_noalloc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+FERRUM_API int ferrum_gemm_tc_noalloc(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw,
+                                      int ldo, int w_rows, int epilogue, int dual_offset, int* err_flag,
+                                      cudaStream_t stream) {
+  FERRUM_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm_tc_noalloc: bad sizes M=%d N=%d K=%d", M, N, K);
+  FERRUM_CHECK_ARG(err_flag != nullptr, "gemm_tc_noalloc: the error flag is required");
+  if (M == 0) return 0;
+  FERRUM_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tc_noalloc: K=%d and the row strides (%d, %d) must be "
+                   "multiples of 8 (16-byte rows for TMA)", K, ldx, ldw);
+  FERRUM_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc_noalloc: operands must be 16-byte aligned");
+  FERRUM_CHECK_ARG(ldx >= K && ldw >= K && ldo >= N, "gemm_tc_noalloc: a row stride is shorter than its row");
+  const bool dual = dual_offset > 0;
+  FERRUM_CHECK_ARG(epilogue >= 0 && epilogue <= 3, "gemm_tc_noalloc: unknown epilogue %d", epilogue);
+  FERRUM_CHECK_ARG(dual == (epilogue == TC_SWIGLU), "gemm_tc_noalloc: the SwiGLU epilogue needs dual_offset, and only it does");
+  FERRUM_CHECK_ARG(w_rows >= N + dual_offset, "gemm_tc_noalloc: w has %d rows, needs %d", w_rows, N + dual_offset);
+  int n_ctas = sm_count();
+  const int bt = ferrum_gemm_tc_token_tile(M, dual);
+  int tiles = 0;
+  const long long need_floats = ferrum_gemm_tc_workspace(M, N, K, dual, n_ctas, &tiles);
+  FERRUM_CHECK_ARG(need_floats * (long long)sizeof(float) <= (long long)FERRUM_NOALLOC_SCRATCH_BYTES,
+                   "gemm_tc_noalloc: %d tokens%s need %lld bytes of scratch, the built-in array holds %u; use ferrum_gemm_tc "
+                   "with a caller-provided workspace", M, dual ? " with the SwiGLU epilogue" : "",
+                   need_floats * (long long)sizeof(float), FERRUM_NOALLOC_SCRATCH_BYTES);
+  FERRUM_CHECK_ARG(tiles <= FERRUM_NOALLOC_MAX_TILES, "gemm_tc_noalloc: %d output tiles exceed the built-in %d counters", tiles,
+                   FERRUM_NOALLOC_MAX_TILES);
+  unsigned char* scratch = nullptr;
+  if (int r = noalloc_scratch_address(&scratch)) return r;
+  float* workspace = reinterpret_cast<float*>(scratch);
+  int* counters = reinterpret_cast<int*>(scratch + FERRUM_NOALLOC_SCRATCH_BYTES);
+  // the counters are the only part of the shared array that must start at zero
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)tiles * sizeof(int), stream);
+  FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
+  {
+    const long long units = (long long)tiles * ((K + TILE_K - 1) / TILE_K);
+    if (n_ctas > units) n_ctas = (int)units;
+  }
+  CUtensorMap mw, mx;
+  if (int r = encode_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
+  if (int r = encode_tensor_map(x, M, K, ldx, bt, &mx)) return r;
+  TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset};
+  switch (bt) {
+    case 16: return dual ? launch_tc<16, true>(mw, mx, p, n_ctas, stream) : launch_tc<16, false>(mw, mx, p, n_ctas, stream);
+    case 32: return dual ? launch_tc<32, true>(mw, mx, p, n_ctas, stream) : launch_tc<32, false>(mw, mx, p, n_ctas, stream);
+    case 64: return dual ? launch_tc<64, true>(mw, mx, p, n_ctas, stream) : launch_tc<64, false>(mw, mx, p, n_ctas, stream);
+    case 128: return dual ? launch_tc<128, true>(mw, mx, p, n_ctas, stream) : launch_tc<128, false>(mw, mx, p, n_ctas, stream);
+    case 256: return launch_tc<256, false>(mw, mx, p, n_ctas, stream);
+  }
+  FERRUM_CHECK_ARG(false, "gemm_tc_noalloc: no kernel for token tile %d", bt);
+}
