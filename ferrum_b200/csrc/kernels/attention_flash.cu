@@ -38,7 +38,7 @@ struct FlashParams {
   float* part_o;        // [slot][BM][D]
   float* part_ml;       // [slot][BM][2]
   long long page_stride;
-  int ldq, ldo, page_size, table_width;
+  int ldq, ldo, page_size, page_shift, table_width;
   int Hq, Hkv, G, window;
   float scale_log2;
 };
@@ -116,21 +116,30 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
       *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
   }
+  // Every thread copies the same 16-byte column c of rows r_base, r_base + RPP, ... of a tile;
+  // the swizzle term (row & 7) is the same for all of them because RPP is a multiple of 8.
+  constexpr int RPP = NT / CH;       // rows covered by one pass of the CTA
+  constexpr int PASSES = BN / RPP;
+  static_assert(NT % CH == 0 && RPP % 8 == 0 && BN % RPP == 0, "load pattern");
+  const int ld_c = tid % CH, ld_r = tid / CH;
+  const int ld_off = ld_r * D + ((ld_c ^ (ld_r & 7)) << 3);
+  const __nv_bfloat16* kv_head = p.kv_plane + (size_t)kvh * ps * D + ld_c * 8;
+  const int ps_shift = p.page_shift;  // log2(page_size), or -1 when it is no power of two
   auto load_tile = [&](int buf, int key0) {
-    __nv_bfloat16* dk = sK + buf * BN * D;
-    __nv_bfloat16* dv = sV + buf * BN * D;
-    for (int idx = tid; idx < BN * CH; idx += NT) {
-      const int r = idx / CH, c = idx % CH;
-      const int key = key0 + r;
+    __nv_bfloat16* dk = sK + buf * BN * D + ld_off;
+    __nv_bfloat16* dv = sV + buf * BN * D + ld_off;
+#pragma unroll
+    for (int i = 0; i < PASSES; ++i) {
+      const int key = key0 + ld_r + i * RPP;
       const bool valid = key < kv_end;
       const __nv_bfloat16* src = p.kv_plane;
       if (valid) {
-        const int page = bt[key / ps];
-        src += (size_t)page * p.page_stride + ((size_t)kvh * ps + key % ps) * D + c * 8;
+        const int lp = ps_shift >= 0 ? key >> ps_shift : key / ps;
+        const int in_page = ps_shift >= 0 ? key & (ps - 1) : key - lp * ps;
+        src = kv_head + (size_t)bt[lp] * p.page_stride + in_page * D;
       }
-      const int off = r * D + ((c ^ (r & 7)) << 3);
-      cp_async16(dk + off, src, valid ? 16 : 0);
-      cp_async16(dv + off, valid ? src + v_off : src, valid ? 16 : 0);
+      cp_async16(dk + i * RPP * D, src, valid ? 16 : 0);
+      cp_async16(dv + i * RPP * D, valid ? src + v_off : src, valid ? 16 : 0);
     }
   };
   const int n_tiles = (kv_end - kv_begin + BN - 1) / BN;
@@ -147,6 +156,11 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
     row_pos[h] = pos0 + pr / G;
     row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
   }
+  // the earliest position and the latest window start among the warp's rows that exist
+  const int warp_row0 = row0 + wm * 16;
+  const int warp_last = min(warp_row0 + 15, n_rows - 1);
+  const int warp_min_pos = pos0 + warp_row0 / G;
+  const int warp_max_lo = p.window > 0 && warp_last >= warp_row0 ? max(0, pos0 + warp_last / G - p.window + 1) : 0;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[D / 8][4];
 #pragma unroll
@@ -189,17 +203,29 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
         mma_bf16(s[2 * nb + 1], qf[kk], b[2], b[3]);
       }
     }
-    // ---- mask, scale, online softmax
+    // ---- mask, scale, online softmax.  A tile that every row of the warp sees in full
+    // needs no mask (rows past the request's last row compute on zeros and are dropped).
     float mx[2] = {-INFINITY, -INFINITY};
+    if (key0 + KW - 1 <= warp_min_pos && key0 >= warp_max_lo && key0 + KW <= kv_end) {
 #pragma unroll
-    for (int j = 0; j < KW / 8; ++j) {
+      for (int j = 0; j < KW / 8; ++j) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key0 + j * 8 + tig * 2 + (e & 1);
-        const int h = e >> 1;
-        const bool keep = row_ok[h] && key <= row_pos[h] && key >= row_lo[h] && key < kv_end;
-        s[j][e] = keep ? s[j][e] * p.scale_log2 : -INFINITY;
-        mx[h] = fmaxf(mx[h], s[j][e]);
+        for (int e = 0; e < 4; ++e) {
+          s[j][e] *= p.scale_log2;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < KW / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key0 + j * 8 + tig * 2 + (e & 1);
+          const int h = e >> 1;
+          const bool keep = row_ok[h] && key <= row_pos[h] && key >= row_lo[h] && key < kv_end;
+          s[j][e] = keep ? s[j][e] * p.scale_log2 : -INFINITY;
+          mx[h] = fmaxf(mx[h], s[j][e]);
+        }
       }
     }
     float corr[2], m_use[2];
@@ -412,6 +438,9 @@ FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo
   p.block_table = block_table; p.q_start = q_start; p.pos0 = pos0; p.work = work;
   p.part_o = part_o; p.part_ml = part_ml; p.page_stride = page_stride;
   p.ldq = ldq; p.ldo = ldo; p.page_size = page_size; p.table_width = table_width;
+  p.page_shift = -1;
+  for (int b = 0; b < 30; ++b)
+    if ((1 << b) == page_size) p.page_shift = b;
   p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   if (D == 64 && bm == 16) return launch_flash<64, 1, 4>(p, n_work, n_ctas, stream);

@@ -32,7 +32,7 @@ CLASSES = (16, 64)
 MIN_SPLIT_KEYS = {16: 256, 64: 1024}
 
 
-CTA_SLOTS = 2 * N_SMS      # the 16-row kernel keeps two CTAs on an SM
+CTA_SLOTS = 3 * N_SMS      # the 16-row kernel keeps three CTAs on an SM (registers and shared memory)
 MIN_TILES_PER_CTA = 4
 
 
