@@ -338,6 +338,8 @@ template <int D, int WM, int WN>
 __global__ void __launch_bounds__(WM * WN * 32)
 flash_kernel(const FlashParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
+  pdl_wait();
+  pdl_launch();
   if (p.cta_items == nullptr) {
     const int* wk = p.work + (size_t)blockIdx.x * 8;
     // with one item per (CTA, head) the item's partial slot is per head
@@ -365,6 +367,8 @@ __global__ void __launch_bounds__(D / 4 < 32 ? 32 : D / 4)
 combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* part_ml, const int* q_start,
                const int* req_of_token, const int* req_tile0, const int* tile_info, const int* token_list, int G,
                int Hkv, int BM) {
+  pdl_wait();
+  pdl_launch();
   const int t = token_list ? token_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int req = req_of_token[t];
   const int kvh = head / G;
@@ -407,7 +411,7 @@ int launch_flash(const FlashParams& p, int n_work, int n_ctas, cudaStream_t stre
     configured = true;
   }
   dim3 grid = p.cta_items ? dim3(n_ctas, 1) : dim3(n_work, p.Hkv);
-  flash_kernel<D, WM, WN><<<grid, WM * WN * 32, smem, stream>>>(p);
+  launch_kernel(flash_kernel<D, WM, WN>, grid, dim3(WM * WN * 32), smem, stream, p);
   FERRUM_CHECK_LAUNCH("attention_flash");
   return 0;
 }
@@ -458,11 +462,11 @@ FERRUM_API int ferrum_attention_combine(void* out, int ldo, const float* part_o,
   dim3 grid(n_tokens, Hq);
   FERRUM_CHECK_ARG(grid.y <= 65535, "attention_combine: too many heads");
   if (D == 64)
-    combine_kernel<64><<<grid, 32, 0, stream>>>((__nv_bfloat16*)out, ldo, part_o, part_ml, q_start, req_of_token,
-                                               req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
+    launch_kernel(combine_kernel<64>, grid, dim3(32), 0, stream, (__nv_bfloat16*)out, ldo, part_o, part_ml, q_start,
+                  req_of_token, req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
   else
-    combine_kernel<128><<<grid, 32, 0, stream>>>((__nv_bfloat16*)out, ldo, part_o, part_ml, q_start, req_of_token,
-                                                req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
+    launch_kernel(combine_kernel<128>, grid, dim3(32), 0, stream, (__nv_bfloat16*)out, ldo, part_o, part_ml, q_start,
+                  req_of_token, req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
   FERRUM_CHECK_LAUNCH("attention_combine");
   return 0;
 }

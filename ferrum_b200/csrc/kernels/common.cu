@@ -19,3 +19,8 @@ FERRUM_API const char* ferrum_last_error() { return g_error; }
 
 // Version of the kernel library's C interface; the Python side refuses a stale build.
 FERRUM_API int ferrum_kernels_abi() { return 1; }
+
+// Dependent launch (see common.cuh) can be switched off, e.g. to compare timings.
+static bool g_dependent_launch = true;
+bool ferrum_dependent_launch_enabled() { return g_dependent_launch; }
+FERRUM_API void ferrum_set_dependent_launch(int on) { g_dependent_launch = on != 0; }

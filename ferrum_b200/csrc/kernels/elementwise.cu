@@ -10,6 +10,8 @@
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int E, int V, int* __restrict__ err) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;
@@ -25,9 +27,9 @@ FERRUM_API int ferrum_embedding(const void* table, int dtype, const int* ids, fl
   if (n_tokens == 0) return 0;
   const int threads = E >= 1024 ? 256 : 128;
   if (dtype == FERRUM_F32)
-    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, E, V, err_flag);
+    launch_kernel(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, E, V, err_flag);
   else if (dtype == FERRUM_BF16)
-    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, E, V, err_flag);
+    launch_kernel(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, E, V, err_flag);
   else
     FERRUM_CHECK_ARG(false, "embedding: unknown dtype code %d", dtype);
   FERRUM_CHECK_LAUNCH("embedding");
@@ -41,6 +43,8 @@ template <typename TOut>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TOut* __restrict__ out, const int* __restrict__ rows, int E, float eps) {
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * E;
   float ss = 0.f;
@@ -61,9 +65,9 @@ FERRUM_API int ferrum_rmsnorm(const float* x, const float* w, void* out, int out
   if (n_rows == 0) return 0;
   const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
   if (out_dtype == FERRUM_F32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, (float*)out, rows, E, eps);
+    launch_kernel(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)out, rows, E, eps);
   else if (out_dtype == FERRUM_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)out, rows, E, eps);
+    launch_kernel(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, (__nv_bfloat16*)out, rows, E, eps);
   else
     FERRUM_CHECK_ARG(false, "rmsnorm: unknown dtype code %d", out_dtype);
   FERRUM_CHECK_LAUNCH("rmsnorm");
@@ -81,6 +85,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
                                   int table_width, const float* __restrict__ cos_sin, int n_pos,
                                   T* __restrict__ kv_plane, long long page_stride, int page_size, int Hq,
                                   int Hkv, int D, int R, int pairing, int write_kv, int* __restrict__ err) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = R >> 1;
@@ -161,10 +167,10 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
   if (n_tokens == 0) return 0;
   const int threads = 256;
   if (dtype == FERRUM_F32)
-    rope_cache_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, ld, positions, req_of_token, block_table,
+    launch_kernel(rope_cache_kernel<float>, n_tokens, threads, 0, stream, (float*)qkv, ld, positions, req_of_token, block_table,
         table_width, cos_sin, n_pos, (float*)kv_plane, page_stride, page_size, Hq, Hkv, D, R, pairing, write_kv, err_flag);
   else if (dtype == FERRUM_BF16)
-    rope_cache_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((__nv_bfloat16*)qkv, ld, positions, req_of_token,
+    launch_kernel(rope_cache_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions, req_of_token,
         block_table, table_width, cos_sin, n_pos, (__nv_bfloat16*)kv_plane, page_stride, page_size, Hq, Hkv, D, R,
         pairing, write_kv, err_flag);
   else
@@ -177,6 +183,8 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
 // act[t, f] = silu(gu[t, f]) * gu[t, F + f], silu(g) = g / (1 + exp(-g)), in float32.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int F, int ld_in, int ld_out) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.y;
   const T* g = gu + (size_t)t * ld_in;
   const T* u = g + F;
@@ -194,9 +202,9 @@ FERRUM_API int ferrum_swiglu(const void* gu, void* act, int dtype, int n_tokens,
   FERRUM_CHECK_ARG(n_tokens <= 65535, "swiglu: more than 65535 tokens in one call");
   dim3 grid((F + 255) / 256 > 64 ? 64 : (F + 255) / 256, n_tokens);
   if (dtype == FERRUM_F32)
-    swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)act, F, ld_in, ld_out);
+    launch_kernel(swiglu_kernel<float>, grid, 256, 0, stream, (const float*)gu, (float*)act, F, ld_in, ld_out);
   else if (dtype == FERRUM_BF16)
-    swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, F, ld_in, ld_out);
+    launch_kernel(swiglu_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, F, ld_in, ld_out);
   else
     FERRUM_CHECK_ARG(false, "swiglu: unknown dtype code %d", dtype);
   FERRUM_CHECK_LAUNCH("swiglu");

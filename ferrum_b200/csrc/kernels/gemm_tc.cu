@@ -59,7 +59,9 @@ template <int BT, bool DUAL>
 struct TcConfig {
   static constexpr int B_BYTES = BT * TILE_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
-  static constexpr int BUDGET = 196 * 1024;
+  // few tokens: the CTA is a streaming engine and half the shared memory leaves room for a
+  // second CTA on the SM (the next launch's, see the dependent-launch prologue)
+  static constexpr int BUDGET = (BT <= 64 && !DUAL ? 100 : 196) * 1024;
   static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 10 ? 10 : (BUDGET / STAGE_BYTES);
   static constexpr int ACC_COLS = BT * (DUAL ? 2 : 1);
   static constexpr int ALL_COLS = 2 * ACC_COLS;  // two accumulators
@@ -176,7 +178,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       uint32_t phase = 0;
       long long tile = u_begin / nkb;
       int kb = (int)(u_begin % nkb);
-      for (long long u = u_begin; u < u_end; ++u) {
+      // The weights never change, so the first ring of weight tiles is requested before the
+      // kernel ahead of this one in the stream has finished; the activations it writes are
+      // requested after the dependency wait.
+      const int pre = (int)min((long long)STAGES, u_end - u_begin);
+      {
+        long long tl = tile;
+        int k = kb;
+        for (int i = 0; i < pre; ++i) {
+          const uint32_t a = smem_base + i * Cfg::STAGE_BYTES;
+          mbar_expect_tx(full_bar(i), Cfg::STAGE_BYTES);
+          tma_load_2d(a, &tmap_w, full_bar(i), k * TILE_K, (int)(tl % tiles_n) * TILE_N);
+          if (DUAL) tma_load_2d(a + A_BYTES, &tmap_w, full_bar(i), k * TILE_K, p.dual_offset + (int)(tl % tiles_n) * TILE_N);
+          if (++k == nkb) {
+            k = 0;
+            ++tl;
+          }
+        }
+      }
+      pdl_wait();
+      pdl_launch();
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t a = smem_base + i * Cfg::STAGE_BYTES;
+        tma_load_2d(a + A_BYTES * (DUAL ? 2 : 1), &tmap_x, full_bar(i), kb * TILE_K, (int)(tile / tiles_n) * BT);
+        if (++kb == nkb) {
+          kb = 0;
+          ++tile;
+        }
+      }
+      s = pre % STAGES;
+      phase = pre == STAGES ? 1 : 0;
+      for (long long u = u_begin + pre; u < u_end; ++u) {
         if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p)) {
           abort_flag = 1;
           atomicExch(p.err, 10);
@@ -258,6 +290,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const size_t tile_floats = (size_t)Cfg::ACC_COLS * TILE_N;
     int seg = 0;
     long long u = u_begin;
+    pdl_wait();  // the epilogue reads and writes what earlier kernels of the stream wrote
     while (u < u_end) {
       const long long tile = u / nkb;
       const int kb0 = (int)(u % nkb);
@@ -430,7 +463,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  gemm_tc_kernel<BT, DUAL><<<n_ctas, 192, Cfg::SMEM_BYTES, stream>>>(mw, mx, p);
+  launch_kernel(gemm_tc_kernel<BT, DUAL>, dim3(n_ctas), dim3(192), Cfg::SMEM_BYTES, stream, mw, mx, p);
   FERRUM_CHECK_LAUNCH("gemm_tc");
   return 0;
 }

@@ -50,6 +50,12 @@ def require_cuda(device=None):
     lib()
 
 
+def set_dependent_launch(on: bool):
+    """Programmatic dependent launch between the kernels of a step (on by default): a kernel's
+    prologue may overlap the tail of the kernel before it.  Off: plain stream order."""
+    lib().ferrum_set_dependent_launch(c_int(1 if on else 0))
+
+
 launches = 0          # kernel launches made through this module (every entry point launches one kernel)
 
 

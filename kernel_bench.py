@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--no-dependent-launch", action="store_true", help="plain stream order between the launches")
     args = ap.parse_args()
 
     import torch
@@ -44,6 +45,7 @@ def main():
     from ferrum_b200.engine.batch import StepContext, StepEntry
     from ferrum_b200.ops import lib as ops
     ops.require_cuda()
+    ops.set_dependent_launch(not args.no_dependent_launch)
     pk = peaks()
     dev = "cuda"
     Hq, Hkv, D, ps = args.hq, args.hkv, args.head_dim, args.page_size
