@@ -5,6 +5,7 @@
 
 #include "cache_manager.hpp"
 #include "scheduler.hpp"
+#include "step_plan.hpp"
 
 namespace py = pybind11;
 using namespace ferrum;
@@ -16,7 +17,7 @@ static void raise_as(const char* cls, const char* what) {
 
 PYBIND11_MODULE(_host, m) {
   m.doc() = "native cache manager and scheduler of ferrum_b200";
-  m.attr("ABI") = 1;
+  m.attr("ABI") = 2;
 
   py::register_exception_translator([](std::exception_ptr p) {
     try {
@@ -116,6 +117,17 @@ PYBIND11_MODULE(_host, m) {
       .def("active", &Scheduler::active)
       .def("idle", &Scheduler::idle)
       .def("stats", &Scheduler::stats);
+
+  py::class_<DecodePlan>(m, "DecodePlan")
+      .def_readonly("n_items", &DecodePlan::n_items)
+      .def_readonly("n_ctas", &DecodePlan::n_ctas)
+      .def_readonly("n_slots", &DecodePlan::n_slots)
+      .def_readonly("n_split_requests", &DecodePlan::n_split_requests);
+  m.def("copy_tables", &copy_tables, py::arg("cache"), py::arg("group"), py::arg("slots"), py::arg("dst"),
+        py::arg("row_stride"));
+  m.def("build_decode_plan", &build_decode_plan, py::arg("kv_lo"), py::arg("kv_hi"), py::arg("n_kv_heads"),
+        py::arg("cta_slots"), py::arg("min_tiles_per_cta"), py::arg("item_cap"), py::arg("cta_cap"), py::arg("pad"),
+        py::arg("dst"));
 
   m.attr("FINISH_STOP") = (int)FINISH_STOP;
   m.attr("FINISH_LENGTH") = (int)FINISH_LENGTH;

@@ -194,6 +194,32 @@ class AttentionPlans:
             self.generation += 1
         return b
 
+    def _decode_plans(self, ctx, key, G, window, Hkv, fixed):
+        """Every request brings one row tile: the balanced list, built by the native module
+        straight into the pinned staging buffer."""
+        from .. import host as host_module
+        R = len(ctx.h_q_len)
+        cap = item_capacity(R, Hkv)
+        total = cap * 8 + R * Hkv * 4 + R + CTA_SLOTS + 1
+        ring, dev = self._buffers(key, total)
+        pinned = ring.next()
+        hi = [p + n for p, n in zip(ctx.h_pos0, ctx.h_q_len)]
+        lo = [max(0, p - window + 1) for p in ctx.h_pos0] if window > 0 else [0] * R
+        d = host_module.module().build_decode_plan(lo, hi, Hkv, CTA_SLOTS, MIN_TILES_PER_CTA, cap, CTA_SLOTS, bool(fixed),
+                                                   pinned.data_ptr())
+        dev[:total].copy_(pinned[:total], non_blocking=True)
+        ring.sent()
+        ctx.h2d_bytes += total * 4
+        o1 = cap * 8
+        o2 = o1 + R * Hkv * 4
+        o3 = o2 + R
+        cp = ClassPlan(16, cap if fixed else d.n_items, dev[:o1], cap if fixed else d.n_slots)
+        cp.tile_info, cp.req_tile0 = dev[o1:o2], dev[o2:o3]
+        cp.cta_items, cp.n_ctas = dev[o3:total], CTA_SLOTS if fixed else d.n_ctas
+        # the merge visits every token; those whose keys were not split return at once
+        cp.comb_tokens, cp.n_comb = None, (ctx.n_tokens if (fixed or d.n_slots) else 0)
+        return [cp, None]
+
     def get(self, ctx, G, window, Hkv, fixed=False) -> List[Optional[ClassPlan]]:
         """fixed=True (a decode-only batch under a CUDA graph): the 16-row list is padded to
         `item_capacity` items and the merge visits every token, so that the launch shapes
@@ -201,6 +227,10 @@ class AttentionPlans:
         key = (G, window, Hkv)
         if key in self._plans:
             return self._plans[key]
+        if max(ctx.h_q_len) * G <= 16:
+            plans = self._decode_plans(ctx, key, G, window, Hkv, fixed)     # native fast path
+            self._plans[key] = plans
+            return plans
         host = build_host(ctx.h_q_len, ctx.h_pos0, G, window, Hkv)
         R = len(ctx.h_q_len)
         if fixed:

@@ -98,8 +98,9 @@ class StepContext:
         self.token_capacity = self.want_capacity = 0
 
     # ------------------------------------------------------------------ per step
-    def fill(self, entries: List[StepEntry], tables: List[List[Sequence[int]]], token_capacity=None):
-        """tables[g][r] is the block-table row of entry r in group g."""
+    def fill(self, entries: List[StepEntry], tables, token_capacity=None):
+        """tables: the native CacheManager whose block tables the entries' slots index, or
+        explicit rows, tables[g][r] being the row of entry r in group g."""
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         if R > self.max_requests or T > self.max_tokens:
@@ -111,21 +112,35 @@ class StepContext:
         tok, pos, req, want = h[0:T], h[T:2 * T], h[2 * T:3 * T], h[3 * T:3 * T + W]
         o = 3 * T + W
         qstart, pos0, slots = h[o:o + R + 1], h[o + R + 1:o + 2 * R + 1], h[o + 2 * R + 1:o + 3 * R + 1]
-        t = w = 0
-        self.h_q_start, self.h_q_len, self.h_pos0, self.h_slots = [], [], [], []
-        for r, e in enumerate(entries):
-            n = len(e.tokens)
-            tok[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
-            pos[t:t + n] = np.arange(e.pos0, e.pos0 + n, dtype=np.int32)
-            req[t:t + n] = r
-            for i in e.want:
-                if not 0 <= i < n:
-                    raise ValueError(f"wanted index {i} is outside the entry's {n} tokens")
-                want[w] = t + i
-                w += 1
-            qstart[r], pos0[r], slots[r] = t, e.pos0, e.slot
-            self.h_q_start.append(t); self.h_q_len.append(n); self.h_pos0.append(e.pos0); self.h_slots.append(e.slot)
-            t += n
+        if T == R and W in (0, R):
+            # one token per request (decoding): whole-array assignments
+            self.h_q_start, self.h_q_len = list(range(R)), [1] * R
+            self.h_pos0, self.h_slots = [e.pos0 for e in entries], [e.slot for e in entries]
+            tok[:] = [e.tokens[0] for e in entries]
+            pos[:] = self.h_pos0
+            req[:] = qstart[:R] = self.h_q_start
+            pos0[:] = self.h_pos0
+            slots[:] = self.h_slots
+            if W:
+                if any(tuple(e.want) != (0,) for e in entries):
+                    raise ValueError("wanted index is outside the entry's 1 tokens")
+                want[:] = self.h_q_start
+        else:
+            t = w = 0
+            self.h_q_start, self.h_q_len, self.h_pos0, self.h_slots = [], [], [], []
+            for r, e in enumerate(entries):
+                n = len(e.tokens)
+                tok[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
+                pos[t:t + n] = np.arange(e.pos0, e.pos0 + n, dtype=np.int32)
+                req[t:t + n] = r
+                for i in e.want:
+                    if not 0 <= i < n:
+                        raise ValueError(f"wanted index {i} is outside the entry's {n} tokens")
+                    want[w] = t + i
+                    w += 1
+                qstart[r], pos0[r], slots[r] = t, e.pos0, e.slot
+                self.h_q_start.append(t); self.h_q_len.append(n); self.h_pos0.append(e.pos0); self.h_slots.append(e.slot)
+                t += n
         qstart[R] = T
         total = o + 3 * R + 1
         self._dev[:total].copy_(host[:total], non_blocking=True)
@@ -136,12 +151,17 @@ class StepContext:
         self.want_rows = d[3 * T:3 * T + W]
         self.q_start, self.pos0, self.slots = d[o:o + R + 1], d[o + R + 1:o + 2 * R + 1], d[o + 2 * R + 1:o + 3 * R + 1]
         self.block_tables = []
-        for g, rows in enumerate(tables):
+        explicit = isinstance(tables, (list, tuple))
+        for g in range(len(self.table_widths)):
             w = self.table_widths[g]
             bhost = self._bt_host[g].next()
-            bh = bhost.numpy().reshape(self.max_requests, w)
-            for r, row in enumerate(rows):
-                bh[r, :len(row)] = row
+            if explicit:
+                bh = bhost.numpy().reshape(self.max_requests, w)
+                for r, row in enumerate(tables[g]):
+                    bh[r, :len(row)] = row
+            else:
+                from .. import host as host_module
+                host_module.module().copy_tables(tables, g, self.h_slots, bhost.data_ptr(), w)
             self._bt_dev[g][:R].copy_(bhost[:R * w].view(R, w), non_blocking=True)
             self._bt_host[g].sent()
             self.h2d_bytes += R * self.table_widths[g] * 4

@@ -71,10 +71,9 @@ class ModelRunner:
             if e.pos0 == 0:
                 for s in self.cache.states:
                     s[e.slot].zero_()                      # a request starts from an all-zero state
-        tables = [[mgr.table(g, e.slot) for e in entries] for g in range(self.cache.n_groups)]
         decode_only = self.use_graphs and all(len(e.tokens) == 1 for e in entries)
         self.ctx.fixed_shapes = decode_only
-        self.ctx.fill(entries, tables)
+        self.ctx.fill(entries, mgr if self.cache.n_groups else [])
         logits = self._run_decode() if decode_only else self.model.forward(self.ctx, self.cache)
         if commit:
             for e in entries:
