@@ -385,6 +385,256 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------ the CTA-pair kernel
+// For many tokens the single-CTA tile (128 weight rows x 256 tokens) asks the L2 for 48 KB
+// per 4.2 MFLOP and the tensor cores wait for operands half of the time.  Here two CTAs of a
+// cluster compute a 256 x 256 tile with one tcgen05.mma.cta_group::2 per K step: each CTA
+// loads its own 128 weight rows and its own 128 tokens (32 KB per stage instead of 48 KB for
+// the same flops), the leader issues the MMAs, and each CTA's tensor memory receives its 128
+// rows of the product, which its own epilogue warps read back.  The stream-K bookkeeping is
+// that of the single-CTA kernel with the cluster in the role of the CTA and the 128-row half
+// tile in the role of the tile.  No multicast loads are used.
+constexpr int PAIR_BT = 256;                              // tokens per tile pair
+constexpr int PAIR_B_BYTES = (PAIR_BT / 2) * TILE_K * 2;  // each CTA stages half of the tokens
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
+  constexpr int STAGES = PAIR_STAGES;
+  constexpr int ACC_COLS = PAIR_BT;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * PAIR_STAGE_BYTES);  // full[S], empty[S], acc_full[2], acc_empty[2]
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ int is_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader of the pair
+  const int P = gridDim.x / 2, cluster = blockIdx.x / 2;
+  const int nkb = (p.K + TILE_K - 1) / TILE_K;
+  const int tiles_n = (p.N + 2 * TILE_N - 1) / (2 * TILE_N);  // 256-row tiles
+  const int tiles_t = (p.M + PAIR_BT - 1) / PAIR_BT;
+  const long long U = (long long)tiles_n * tiles_t * nkb;
+  const long long u_begin = U * cluster / P, u_end = U * (cluster + 1) / P;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    is_last = 0;
+    prefetch_tensormap(&tmap_w);
+    prefetch_tensormap(&tmap_x);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);   // the leader's: its producer's expect_tx; bytes arrive from both CTAs
+      mbar_init(empty_bar(s), 1);  // one multicast commit of the leader's MMA thread
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 8);  // the leader's: four epilogue warps of each CTA
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&tmem_slot), 2 * ACC_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_p = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      long long tile = u_begin / nkb;
+      int kb = (int)(u_begin % nkb);
+      pdl_wait();
+      pdl_launch();
+      for (long long u = u_begin; u < u_end; ++u) {
+        if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p)) {
+          abort_flag = 1;
+          atomicExch(p.err, 10);
+          break;
+        }
+        const int n0 = (int)(tile % tiles_n) * 2 * TILE_N + (int)rank * TILE_N;
+        const int t0 = (int)(tile / tiles_n) * PAIR_BT + (int)rank * (PAIR_BT / 2);
+        const uint32_t a = smem_base + s * PAIR_STAGE_BYTES;
+        const uint32_t leader_full = map_to_cta(full_bar(s), 0);
+        if (rank == 0) mbar_expect_tx(full_bar(s), 2 * PAIR_STAGE_BYTES);
+        tma_load_2d_pair(a, &tmap_w, leader_full, kb * TILE_K, n0);
+        tma_load_2d_pair(a + A_BYTES, &tmap_x, leader_full, kb * TILE_K, t0);
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+        if (++kb == nkb) {
+          kb = 0;
+          ++tile;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc_bf16(2 * TILE_N, PAIR_BT);
+      int s = 0;
+      uint32_t phase = 0;
+      int seg = 0;
+      long long u = u_begin;
+      bool ok = true;
+      while (ok && u < u_end) {
+        const long long tile = u / nkb;
+        const long long seg_end = min(u_end, (tile + 1) * (long long)nkb);
+        const int buf = seg & 1, use = seg >> 1;
+        if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, abort_p)) {
+          abort_flag = 1;
+          atomicExch(p.err, 13);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + buf * ACC_COLS;
+        bool first = true;
+        for (; u < seg_end; ++u) {
+          if (!mbar_wait(full_bar(s), phase, abort_p)) {
+            abort_flag = 1;
+            atomicExch(p.err, 11);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a = smem_base + s * PAIR_STAGE_BYTES;
+          const uint64_t a_desc = umma_desc_k_sw128(a);
+          const uint64_t b_desc = umma_desc_k_sw128(a + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < TILE_K / UMMA_K; ++kk) {
+            const uint64_t adv = (uint64_t)(kk * UMMA_K * 2 >> 4);
+            umma_bf16_pair(d0, a_desc + adv, b_desc + adv, idesc, !first || kk > 0);
+          }
+          first = false;
+          umma_commit_pair(empty_bar(s), 3);  // both CTAs may refill the stage
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit_pair(acc_full_bar(buf), 3);
+        ++seg;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    const int n_local = quarter * 32 + lane;
+    const int ep_tid = threadIdx.x - 64;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const size_t tile_floats = (size_t)ACC_COLS * TILE_N;
+    int seg = 0;
+    long long u = u_begin;
+    pdl_wait();
+    while (u < u_end) {
+      const long long tile = u / nkb;
+      const int kb0 = (int)(u % nkb);
+      const long long seg_end = min(u_end, (tile + 1) * (long long)nkb);
+      const bool whole = kb0 == 0 && seg_end == (tile + 1) * (long long)nkb;
+      const int buf = seg & 1, use = seg >> 1;
+      bool ok = mbar_wait(acc_full_bar(buf), use & 1, abort_p);
+      if (!ok) abort_flag = 1;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (abort_flag) {
+        if (ep_tid == 0) atomicExch(p.err, 12);
+        break;
+      }
+      tc_fence_after();
+      const int n0 = (int)(tile % tiles_n) * 2 * TILE_N + (int)rank * TILE_N, t0 = (int)(tile / tiles_n) * PAIR_BT;
+      const int n = n0 + n_local;
+      const uint32_t acc_addr = lane_addr + buf * ACC_COLS;
+      const uint32_t leader_acc_empty = map_to_cta(acc_empty_bar(buf), 0);
+      if (whole) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < PAIR_BT; c0 += 16) {
+          float v0[16];
+          tmem_ld16(acc_addr + c0, v0);
+          if (n < p.N) tc_apply16(p, t0 + c0, n, v0, v0);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+      } else {
+        // half-tile partial -> workspace [cluster][end][rank][column][lane]
+        const int c_first = unit_owner(tile * nkb, U, P), c_last = unit_owner(tile * nkb + nkb - 1, U, P);
+        const int n_contrib = c_last - c_first + 1;
+        float* ws = p.workspace + (((size_t)cluster * 2 + (u_begin / nkb == tile ? 0 : 1)) * 2 + rank) * tile_floats;
+#pragma unroll 1
+        for (int c0 = 0; c0 < ACC_COLS; c0 += 16) {
+          float v[16];
+          tmem_ld16(acc_addr + c0, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ws[(size_t)(c0 + j) * TILE_N + n_local] = v[j];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ep_tid == 0) {
+          int* counter = p.counters + tile * 2 + rank;
+          const int old = atomicAdd(counter, 1);
+          is_last = old == n_contrib - 1;
+          if (is_last) *counter = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (is_last) {
+          __threadfence();
+          if (n < p.N) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 16) {
+              float a0[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) a0[j] = 0.f;
+              for (int cc = c_first; cc <= c_last; ++cc) {  // K order
+                const float* wsp = p.workspace + (((size_t)cc * 2 + ((U * cc / P) / nkb == tile ? 0 : 1)) * 2 + rank) * tile_floats +
+                                   (size_t)c0 * TILE_N + n_local;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) a0[j] += __ldcg(wsp + (size_t)j * TILE_N);
+              }
+              tc_apply16(p, t0 + c0, n, a0, a0);
+            }
+          }
+        }
+      }
+      u = seg_end;
+      ++seg;
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) {
+    const long long t0c = clock64();
+    while (clock64() - t0c < 2000000LL) {
+    }
+  }
+  // neither CTA may leave while the other can still read its shared memory or signal its barriers
+  tc_fence_before();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * ACC_COLS);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -468,6 +718,37 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
   return 0;
 }
 
+static bool g_pair_kernel = true;
+// The CTA-pair kernel can be switched off (every shape then runs on the single-CTA kernel).
+FERRUM_API void ferrum_set_gemm_pair_kernel(int on) { g_pair_kernel = on != 0; }
+
+static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int n_ctas, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
+    FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc: cannot reserve %d bytes of shared memory: %s", PAIR_SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_ctas);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ferrum_dependent_launch_enabled() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, p);
+  FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc: pair kernel launch failed: %s", cudaGetErrorString(e));
+  FERRUM_CHECK_LAUNCH("gemm_tc_pair");
+  return 0;
+}
+
 static int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -496,7 +777,8 @@ FERRUM_API int ferrum_gemm_tc_default_ctas() { return sm_count(); }
 FERRUM_API long long ferrum_gemm_tc_workspace(int M, int N, int K, int dual, int n_ctas, int* n_tiles) {
   const int bt = ferrum_gemm_tc_token_tile(M, dual);
   if (n_ctas <= 0) n_ctas = sm_count();
-  const long long tiles = (long long)((N + TILE_N - 1) / TILE_N) * ((M + bt - 1) / bt);
+  // counters: one per 128-row tile; the pair kernel numbers them by 256-row tile and half
+  const long long tiles = 2LL * ((N + 2 * TILE_N - 1) / (2 * TILE_N)) * ((M + bt - 1) / bt);
   if (n_tiles) *n_tiles = (int)tiles;
   return 2LL * n_ctas * (long long)(bt * (dual ? 2 : 1)) * TILE_N;
 }
@@ -527,13 +809,21 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
   FERRUM_CHECK_ARG(counters && n_counters >= tiles, "gemm_tc: needs %d tile counters, got %d", tiles, n_counters);
   {
     // every CTA must own at least one unit, or the CTAs that share a tile are not consecutive
-    const long long units = (long long)tiles * ((K + TILE_K - 1) / TILE_K);
+    const long long units = (long long)((N + TILE_N - 1) / TILE_N) * ((M + bt - 1) / bt) * ((K + TILE_K - 1) / TILE_K);
     if (n_ctas > units) n_ctas = (int)units;
   }
+  TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset};
   CUtensorMap mw, mx;
   if (int r = get_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
+  if (bt == PAIR_BT && !dual && g_pair_kernel && n_ctas >= 2) {
+    // many tokens: pairs of CTAs on 256 x 256 tiles; each CTA stages 128 tokens
+    const long long units = (long long)((N + 2 * TILE_N - 1) / (2 * TILE_N)) * ((M + PAIR_BT - 1) / PAIR_BT) * ((K + TILE_K - 1) / TILE_K);
+    int pairs = n_ctas / 2;
+    if (pairs > units) pairs = (int)units;
+    if (int r = get_tensor_map(x, M, K, ldx, PAIR_BT / 2, &mx)) return r;
+    return launch_tc_pair(mw, mx, p, 2 * pairs, stream);
+  }
   if (int r = get_tensor_map(x, M, K, ldx, bt, &mx)) return r;
-  TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset};
 #define TC_CASE(BT_)                                                         \
   case BT_:                                                                  \
     return dual ? launch_tc<BT_, true>(mw, mx, p, n_ctas, stream) : launch_tc<BT_, false>(mw, mx, p, n_ctas, stream);
@@ -625,7 +915,7 @@ FERRUM_API int ferrum_gemm_tc_noalloc(const void* x, const void* w, void* out, i
   cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)tiles * sizeof(int), stream);
   FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
   {
-    const long long units = (long long)tiles * ((K + TILE_K - 1) / TILE_K);
+    const long long units = (long long)((N + TILE_N - 1) / TILE_N) * ((M + bt - 1) / bt) * ((K + TILE_K - 1) / TILE_K);
     if (n_ctas > units) n_ctas = (int)units;
   }
   CUtensorMap mw, mx;
