@@ -561,7 +561,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const int n = n0 + n_local;
       const uint32_t acc_addr = lane_addr + buf * ACC_COLS;
       const uint32_t leader_acc_empty = map_to_cta(acc_empty_bar(buf), 0);
-      if (whole) {
+      if (whole && p.epilogue == TC_RESIDUAL) {
+        // 32 columns per round: the residual loads are issued before the accumulator is read,
+        // so that a round costs one memory latency, not two
+        float* out = (float*)p.out + (size_t)t0 * p.ldo + n;
+        const size_t ld = (size_t)p.ldo;
+#pragma unroll 1
+        for (int c0 = 0; c0 < PAIR_BT; c0 += 32) {
+          const int valid = n < p.N ? p.M - t0 - c0 : 0;
+          float r[32], v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = j < valid ? out[(c0 + j) * ld] : 0.f;
+          tmem_ld16(acc_addr + c0, &v[0]);
+          tmem_ld16(acc_addr + c0 + 16, &v[16]);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) out[(c0 + j) * ld] = r[j] + v[j];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+      } else if (whole) {
 #pragma unroll 1
         for (int c0 = 0; c0 < PAIR_BT; c0 += 16) {
           float v0[16];
