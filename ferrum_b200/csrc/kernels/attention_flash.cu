@@ -338,8 +338,9 @@ template <int D, int WM, int WN>
 __global__ void __launch_bounds__(WM * WN * 32)
 flash_kernel(const FlashParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
+  // No early pdl_launch() here: blocks of the next kernels that sit on the SMs waiting for
+  // this one to finish slow a large attention grid down by a third (measured at 64 requests).
   pdl_wait();
-  pdl_launch();
   if (p.cta_items == nullptr) {
     const int* wk = p.work + (size_t)blockIdx.x * 8;
     // with one item per (CTA, head) the item's partial slot is per head

@@ -3,6 +3,7 @@
 // or bfloat16.  Formulas follow the reference's scalar kernels
 // (crates/kernels/src/scalar.rs:143-156 rms, :167-189 rope; crates/kernels/src/math.rs:8-10 silu).
 #include "common.cuh"
+#include "partials.cuh"
 
 // ---------------------------------------------------------------- embedding
 // out[t, :] = table[ids[t], :] as float32 (the residual stream is float32 in every mode).
@@ -74,6 +75,88 @@ FERRUM_API int ferrum_rmsnorm(const float* x, const float* w, void* out, int out
   return 0;
 }
 
+// The same norm for a residual stream whose last product is still in partials: first
+// h[r, :] += sum of the partials (the deferred residual sum, float32), then the norm.
+template <typename TOut>
+__global__ void rmsnorm_reduce_kernel(float* __restrict__ h, const float* __restrict__ w, TOut* __restrict__ out,
+                                      const int* __restrict__ rows, int E, float eps, const PartialLayout L) {
+  __shared__ float red[32];
+  __shared__ PartialTable tab;
+  build_partial_table(L, tab);   // shapes only: may run before the dependency wait
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* hr = h + (size_t)src * E;
+  float ss = 0.f;
+#pragma unroll 4
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    const float v = hr[i] + partial_sum(L, tab, src, i);
+    hr[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);  // also orders the writes above before the reads below
+  const float inv = 1.0f / sqrtf(ss / (float)E + eps);
+  TOut* o = out + (size_t)r * E;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = from_f32<TOut>(hr[i] * inv * w[i]);
+}
+
+// h[r, :] += partials, nothing else (for a consumer that does not know about partials).
+__global__ void residual_reduce_kernel(float* __restrict__ h, int E, const PartialLayout L) {
+  __shared__ PartialTable tab;
+  build_partial_table(L, tab);
+  pdl_wait();
+  pdl_launch();
+  float* hr = h + (size_t)blockIdx.x * E;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) hr[i] += partial_sum(L, tab, blockIdx.x, i);
+}
+
+static int make_layout(const float* ws, const int* layout, PartialLayout* L) {
+  FERRUM_CHECK_ARG(ws && layout && layout[0] > 0 && layout[1] > 0 && layout[2] > 0 && layout[3] > 0, "partials: bad layout");
+  FERRUM_CHECK_ARG(layout[1] <= PARTIAL_MAX_TILES && layout[2] < 65536, "partials: more than %d tiles", PARTIAL_MAX_TILES);
+  {
+    // a tile's contributors must fit the 32 slot bits: ranges are at least U/P units long
+    const long long per = (long long)layout[0] * layout[1] / layout[2];
+    FERRUM_CHECK_ARG(per > 0 && layout[0] / per + 2 <= PARTIAL_MAX_CONTRIB, "partials: too many CTAs share a tile");
+  }
+  L->ws = ws;
+  L->nkb = layout[0];
+  L->tiles = layout[1];
+  L->n_ctas = layout[2];
+  L->acc_cols = layout[3];
+  return 0;
+}
+
+FERRUM_API int ferrum_rmsnorm_reduce(float* h, const float* w, void* out, int out_dtype, const int* rows, int n_rows,
+                                     int E, float eps, const float* partials, const int* layout, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_rows >= 0 && E > 0 && eps > 0.f, "rmsnorm_reduce: bad arguments");
+  if (n_rows == 0) return 0;
+  PartialLayout L;
+  if (int r = make_layout(partials, layout, &L)) return r;
+  FERRUM_CHECK_ARG(E <= L.tiles * 128, "rmsnorm_reduce: the partials cover %d features, the rows have %d", L.tiles * 128, E);
+  const int threads = E >= 2048 ? 1024 : (E >= 512 ? 256 : 128);  // many loads per element: many threads
+  if (out_dtype == FERRUM_F32)
+    launch_kernel(rmsnorm_reduce_kernel<float>, n_rows, threads, 0, stream, h, w, (float*)out, rows, E, eps, L);
+  else if (out_dtype == FERRUM_BF16)
+    launch_kernel(rmsnorm_reduce_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, h, w, (__nv_bfloat16*)out, rows, E, eps, L);
+  else
+    FERRUM_CHECK_ARG(false, "rmsnorm_reduce: unknown dtype code %d", out_dtype);
+  FERRUM_CHECK_LAUNCH("rmsnorm_reduce");
+  return 0;
+}
+
+FERRUM_API int ferrum_residual_reduce(float* h, int n_rows, int E, const float* partials, const int* layout,
+                                      cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_rows >= 0 && E > 0, "residual_reduce: bad arguments");
+  if (n_rows == 0) return 0;
+  PartialLayout L;
+  if (int r = make_layout(partials, layout, &L)) return r;
+  FERRUM_CHECK_ARG(E <= L.tiles * 128 && n_rows <= L.acc_cols, "residual_reduce: the partials do not cover the rows");
+  launch_kernel(residual_reduce_kernel, n_rows, 256, 0, stream, h, E, L);
+  FERRUM_CHECK_LAUNCH("residual_reduce");
+  return 0;
+}
+
 // ---------------------------------------------------------------- rotary + cache write
 // qkv: [T, ld] rows of (q: Hq*D | k: Hkv*D | v: Hkv*D).  q is rotated in place; k is
 // rotated and stored, v is stored, both at page block_table[req][pos / ps], row pos % ps.
@@ -84,13 +167,30 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
                                   const int* __restrict__ req_of_token, const int* __restrict__ block_table,
                                   int table_width, const float* __restrict__ cos_sin, int n_pos,
                                   T* __restrict__ kv_plane, long long page_stride, int page_size, int Hq,
-                                  int Hkv, int D, int R, int pairing, int write_kv, int* __restrict__ err) {
+                                  int Hkv, int D, int R, int pairing, int write_kv, int* __restrict__ err,
+                                  const PartialLayout L) {
+  __shared__ PartialTable tab;
+  if (L.ws != nullptr) build_partial_table(L, tab);
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = R >> 1;
   T* row = qkv + (size_t)t * ld;
+  // The row's head slots (Hq query heads, Hkv key heads, Hkv value heads) are shared out
+  // between the gridDim.y blocks of this token.
+  const int slots = Hq + 2 * Hkv;
+  const int per_block = (slots + gridDim.y - 1) / gridDim.y;
+  const int s_lo = blockIdx.y * per_block, s_hi = min(slots, s_lo + per_block);
+  if (s_lo >= s_hi) return;
+  if (L.ws != nullptr) {
+    // the q, k, v product is still in partials: sum this block's part of the row first
+    // (rounded to the storage type, as the product's own epilogue would have done)
+    const int e_hi = min(s_hi, write_kv ? slots : Hq) * D;
+#pragma unroll 2
+    for (int i = s_lo * D + threadIdx.x; i < e_hi; i += blockDim.x) row[i] = from_f32<T>(partial_sum(L, tab, t, i));
+    __syncthreads();
+  }
   const bool pos_ok = pos >= 0 && (half == 0 || pos < n_pos);
   if (!pos_ok) {
     if (threadIdx.x == 0) atomicExch(err, 2);
@@ -114,8 +214,9 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
     vdst = kdst + (size_t)Hkv * page_size * D;
   }
   const int hd2 = D >> 1;  // work items per head: D/2 "pairs" (rotated below `half`, copied above)
-  // q heads then k heads
-  for (int w = threadIdx.x; w < (Hq + Hkv) * hd2; w += blockDim.x) {
+  // query and key heads of this block
+  const int qk_hi = min(s_hi, Hq + Hkv);
+  for (int w = s_lo * hd2 + threadIdx.x; w < qk_hi * hd2; w += blockDim.x) {
     const int h = w / hd2, i = w % hd2;
     T* src = row + (size_t)h * D;
     int ia, ib;
@@ -144,9 +245,11 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
       dst[ib] = from_f32<T>(b);
     }
   }
+  // value heads of this block
   if (write_kv) {
+    const int v_lo = max(s_lo, Hq + Hkv) - (Hq + Hkv), v_hi = s_hi - (Hq + Hkv);
     const T* v = row + (size_t)(Hq + Hkv) * D;
-    for (int w = threadIdx.x; w < Hkv * D; w += blockDim.x) {
+    for (int w = v_lo * D + threadIdx.x; w < v_hi * D; w += blockDim.x) {
       const int h = w / D, d = w % D;
       vdst[(size_t)h * page_size * D + d] = v[w];
     }
@@ -157,7 +260,7 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
                                        const int* req_of_token, const int* block_table, int table_width,
                                        const float* cos_sin, int n_pos, void* kv_plane, long long page_stride,
                                        int page_size, int Hq, int Hkv, int D, int R, int pairing, int write_kv,
-                                       int* err_flag, cudaStream_t stream) {
+                                       int* err_flag, const float* partials, const int* layout, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && Hq > 0 && Hkv > 0 && D > 0 && D % 2 == 0, "rope: bad sizes T=%d Hq=%d Hkv=%d D=%d",
                    n_tokens, Hq, Hkv, D);
   FERRUM_CHECK_ARG(R >= 0 && R % 2 == 0 && R <= D, "rope: rope_dim %d must be even and at most head_dim %d", R, D);
@@ -165,14 +268,23 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
   FERRUM_CHECK_ARG(pairing == 0 || pairing == 1, "rope: pairing code %d", pairing);
   FERRUM_CHECK_ARG(!write_kv || (page_size > 0 && table_width > 0 && kv_plane), "rope: cache arguments missing");
   if (n_tokens == 0) return 0;
+  PartialLayout L{nullptr, 0, 0, 0, 0};
+  if (partials != nullptr) {
+    if (int r = make_layout(partials, layout, &L)) return r;
+    FERRUM_CHECK_ARG((write_kv ? Hq + 2 * Hkv : Hq) * D <= L.tiles * 128 && n_tokens <= L.acc_cols,
+                     "rope: the partials do not cover the rows");
+  }
   const int threads = 256;
+  // few tokens: several blocks per token, four head slots each, so that the row (and the
+  // partials behind it) is read by many SMs at once
+  const dim3 grid(n_tokens, n_tokens <= 64 ? (Hq + 2 * Hkv + 3) / 4 : 1);
   if (dtype == FERRUM_F32)
-    launch_kernel(rope_cache_kernel<float>, n_tokens, threads, 0, stream, (float*)qkv, ld, positions, req_of_token, block_table,
-        table_width, cos_sin, n_pos, (float*)kv_plane, page_stride, page_size, Hq, Hkv, D, R, pairing, write_kv, err_flag);
+    launch_kernel(rope_cache_kernel<float>, grid, threads, 0, stream, (float*)qkv, ld, positions, req_of_token, block_table,
+        table_width, cos_sin, n_pos, (float*)kv_plane, page_stride, page_size, Hq, Hkv, D, R, pairing, write_kv, err_flag, L);
   else if (dtype == FERRUM_BF16)
-    launch_kernel(rope_cache_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions, req_of_token,
+    launch_kernel(rope_cache_kernel<__nv_bfloat16>, grid, threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions, req_of_token,
         block_table, table_width, cos_sin, n_pos, (__nv_bfloat16*)kv_plane, page_stride, page_size, Hq, Hkv, D, R,
-        pairing, write_kv, err_flag);
+        pairing, write_kv, err_flag, L);
   else
     FERRUM_CHECK_ARG(false, "rope: unknown dtype code %d", dtype);
   FERRUM_CHECK_LAUNCH("rope_cache_write");
@@ -193,6 +305,34 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
     const float gv = to_f32<T>(g[f]);
     o[f] = from_f32<T>(gv / (1.0f + expf(-gv)) * to_f32<T>(u[f]));
   }
+}
+
+// act[t, f] = silu(gate) * up where gate and up are still partials of a two-product launch
+// (columns t and acc_cols / 2 + t of the partial tiles).
+__global__ void swiglu_reduce_kernel(__nv_bfloat16* __restrict__ act, int F, int ld_out, const PartialLayout L) {
+  __shared__ PartialTable tab;
+  build_partial_table(L, tab);
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.y;
+  __nv_bfloat16* o = act + (size_t)t * ld_out;
+  for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F; f += gridDim.x * blockDim.x) {
+    const float g = partial_sum(L, tab, t, f), u = partial_sum(L, tab, L.acc_cols / 2 + t, f);
+    o[f] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+  }
+}
+
+FERRUM_API int ferrum_swiglu_reduce(void* act, int n_tokens, int F, int ld_out, const float* partials, const int* layout,
+                                    cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_tokens >= 0 && F > 0 && ld_out >= F, "swiglu_reduce: bad sizes");
+  if (n_tokens == 0) return 0;
+  PartialLayout L;
+  if (int r = make_layout(partials, layout, &L)) return r;
+  FERRUM_CHECK_ARG(F <= L.tiles * 128 && n_tokens <= L.acc_cols / 2, "swiglu_reduce: the partials do not cover the rows");
+  dim3 grid((F + 255) / 256 > 32 ? 32 : (F + 255) / 256, n_tokens);
+  launch_kernel(swiglu_reduce_kernel, grid, dim3(256), 0, stream, (__nv_bfloat16*)act, F, ld_out, L);
+  FERRUM_CHECK_LAUNCH("swiglu_reduce");
+  return 0;
 }
 
 FERRUM_API int ferrum_swiglu(const void* gu, void* act, int dtype, int n_tokens, int F, int ld_in, int ld_out,

@@ -48,6 +48,7 @@ struct TcParams {
   int M, N, K, ldo;
   int epilogue;
   int dual_offset;   // row of the second weight tile relative to the first (DUAL)
+  int defer;         // 1: leave every segment's float32 partial in the workspace; the next kernel sums them
 };
 
 constexpr int TILE_N = 128;  // weight rows per tile (the instruction's M)
@@ -308,7 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       const int n0 = (int)(tile % tiles_n) * TILE_N, t0 = (int)(tile / tiles_n) * BT;
       const int n = n0 + n_local;
       const uint32_t acc_addr = lane_addr + buf * Cfg::ACC_COLS;
-      if (whole) {
+      if (whole && !p.defer) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BT; c0 += 16) {
           float v0[16], v1[16];
@@ -335,6 +336,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+        if (p.defer) {  // the kernel that reads this product adds the partials itself
+          u = seg_end;
+          ++seg;
+          continue;
+        }
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ep_tid == 0) {
@@ -832,7 +838,7 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
     const long long units = (long long)((N + TILE_N - 1) / TILE_N) * ((M + bt - 1) / bt) * ((K + TILE_K - 1) / TILE_K);
     if (n_ctas > units) n_ctas = (int)units;
   }
-  TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset};
+  TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset, 0};
   CUtensorMap mw, mx;
   if (int r = get_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
   if (bt == PAIR_BT && !dual && g_pair_kernel && n_ctas >= 2) {
@@ -857,6 +863,60 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
   }
 #undef TC_CASE
   FERRUM_CHECK_ARG(false, "gemm_tc: no kernel for token tile %d", bt);
+}
+
+// ------------------------------------------------------------------ deferred reduction
+// With few tokens every output tile is shared by several CTAs and the in-kernel reduction
+// (fence, counter, reload) is a serial tail of several microseconds per launch.  In deferred
+// mode the kernel stops after writing its float32 partials; the kernel that consumes the
+// product (RMSNorm, the rotary kernel, ...) adds them while it reads, in K order, with
+// partial_sum() of partials.cuh.  Requirements: one token tile (M <= 64) and at most one
+// output tile per CTA, so that a CTA writes at most two partials.
+FERRUM_API int ferrum_gemm_tc_can_defer(int M, int N, int K, int dual, int n_ctas) {
+  if (n_ctas <= 0) n_ctas = sm_count();
+  const int bt = ferrum_gemm_tc_token_tile(M, dual);
+  const long long tiles = (N + TILE_N - 1) / TILE_N;
+  const long long units = tiles * ((K + TILE_K - 1) / TILE_K);
+  if (n_ctas > units) n_ctas = (int)units;
+  // at most 8 CTAs may share a tile (the consumers keep that many loads in flight per element)
+  const long long per = units / n_ctas;
+  return M > 0 && bt <= 64 && tiles <= n_ctas && per > 0 && ((K + TILE_K - 1) / TILE_K) / per + 2 <= 8;
+}
+
+// layout[0..3] = k-blocks per tile, tiles, CTAs, columns per partial: what partial_sum() needs.
+FERRUM_API int ferrum_gemm_tc_deferred(const void* x, const void* w, int M, int N, int K, int ldx, int ldw, int w_rows,
+                                       int dual_offset, int n_ctas, float* workspace, long long workspace_floats,
+                                       int* layout, int* err_flag, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(M > 0 && N > 0 && K > 0 && err_flag && layout, "gemm_tc_deferred: bad arguments");
+  FERRUM_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0,
+                   "gemm_tc_deferred: operands must have 16-byte rows and alignment");
+  FERRUM_CHECK_ARG(ldx >= K && ldw >= K, "gemm_tc_deferred: a row stride is shorter than its row");
+  const bool dual = dual_offset > 0;
+  FERRUM_CHECK_ARG(w_rows >= N + dual_offset, "gemm_tc_deferred: w has %d rows, needs %d", w_rows, N + dual_offset);
+  FERRUM_CHECK_ARG(ferrum_gemm_tc_can_defer(M, N, K, dual, n_ctas), "gemm_tc_deferred: shape M=%d N=%d K=%d cannot defer its "
+                   "reduction (more than 64 tokens, or more output tiles than CTAs)", M, N, K);
+  if (n_ctas <= 0) n_ctas = sm_count();
+  const int bt = ferrum_gemm_tc_token_tile(M, dual);
+  const int nkb = (K + TILE_K - 1) / TILE_K, tiles = (N + TILE_N - 1) / TILE_N;
+  if (n_ctas > (long long)tiles * nkb) n_ctas = tiles * nkb;
+  const int acc_cols = bt * (dual ? 2 : 1);
+  const long long need = 2LL * n_ctas * acc_cols * TILE_N;
+  FERRUM_CHECK_ARG(workspace && workspace_floats >= need, "gemm_tc_deferred: needs %lld workspace floats, got %lld", need,
+                   workspace_floats);
+  layout[0] = nkb;
+  layout[1] = tiles;
+  layout[2] = n_ctas;
+  layout[3] = acc_cols;
+  CUtensorMap mw, mx;
+  if (int r = get_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
+  if (int r = get_tensor_map(x, M, K, ldx, bt, &mx)) return r;
+  TcParams p{nullptr, workspace, nullptr, err_flag, M, N, K, 0, dual ? TC_SWIGLU : TC_STORE_F32, dual_offset, 1};
+  switch (bt) {
+    case 16: return dual ? launch_tc<16, true>(mw, mx, p, n_ctas, stream) : launch_tc<16, false>(mw, mx, p, n_ctas, stream);
+    case 32: return dual ? launch_tc<32, true>(mw, mx, p, n_ctas, stream) : launch_tc<32, false>(mw, mx, p, n_ctas, stream);
+    case 64: return dual ? launch_tc<64, true>(mw, mx, p, n_ctas, stream) : launch_tc<64, false>(mw, mx, p, n_ctas, stream);
+  }
+  FERRUM_CHECK_ARG(false, "gemm_tc_deferred: no kernel for token tile %d", bt);
 }
 
 // ------------------------------------------------------------------ no-allocation entry point
@@ -941,7 +1001,7 @@ FERRUM_API int ferrum_gemm_tc_noalloc(const void* x, const void* w, void* out, i
   CUtensorMap mw, mx;
   if (int r = encode_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
   if (int r = encode_tensor_map(x, M, K, ldx, bt, &mx)) return r;
-  TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset};
+  TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset, 0};
   switch (bt) {
     case 16: return dual ? launch_tc<16, true>(mw, mx, p, n_ctas, stream) : launch_tc<16, false>(mw, mx, p, n_ctas, stream);
     case 32: return dual ? launch_tc<32, true>(mw, mx, p, n_ctas, stream) : launch_tc<32, false>(mw, mx, p, n_ctas, stream);

@@ -94,6 +94,11 @@ class StepContext:
         self._attn_plans = AttentionPlans(device)
         self.n_tokens = self.n_reqs = self.n_want = 0
         self.fixed_shapes = False     # True while a decode-only batch runs under a CUDA graph
+        # A residual product of a few tokens may stay in partials until the next norm adds it
+        # (one kernel less on the critical path): (residual tensor, ops.Partials) or None.
+        self.pending_residual = None
+        self.defer_residuals = True
+        self.defer_swiglu = True
         self.h2d_bytes = 0            # bytes copied to the device by the last fill
         self.token_capacity = self.want_capacity = 0
 
@@ -172,10 +177,33 @@ class StepContext:
         self.max_q_len = max(self.h_q_len) if R else 0
         self.max_kv_len = max((p + n for p, n in zip(self.h_pos0, self.h_q_len)), default=0)
         self._attn_plans.reset()
+        self.pending_residual = None
 
     def attention_plans(self, G, window, Hkv):
         """The step's work lists for the tensor-core attention kernel (built on first use)."""
         return self._attn_plans.get(self, G, window, Hkv, fixed=self.fixed_shapes)
+
+    # ------------------------------------------------------------------ pending residual sum
+    def take_pending_residual(self, h):
+        """For a norm about to read `h`: the partials it must add first, or None.  Partials
+        pending for another tensor are added to that tensor now."""
+        p = self.pending_residual
+        if p is None:
+            return None
+        if p[0].data_ptr() == h.data_ptr():
+            self.pending_residual = None
+            return p[1]
+        self.flush_residual()
+        return None
+
+    def flush_residual(self):
+        """Adds a pending residual product to its tensor (for consumers that do not know
+        about partials, and before the product workspace is used again)."""
+        p = self.pending_residual
+        if p is not None:
+            from ..ops import lib as ops
+            self.pending_residual = None
+            ops.residual_reduce(p[0], self.n_tokens, p[1])
 
     # ------------------------------------------------------------------ scratch
     def buf(self, name, shape, dtype):

@@ -67,6 +67,8 @@ class DecoderModel(Part):
         for k, run in enumerate(self.schedule):
             self.blocks[run.block].forward(h, ctx, cache.layer_cache(k))
         if ctx.n_want == 0:
+            ctx.pending_residual = None      # nobody reads the residual stream any more
             return None
         x = self.final_norm.forward(h, ctx, rows=ctx.want_rows, n_rows=ctx.n_want, tag="final_norm")
+        ctx.flush_residual()
         return self.head.forward(x, ctx, ctx.n_want)

@@ -7,6 +7,7 @@ memory (pointer, shape, stride); no torch operator runs on the product path.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
@@ -40,6 +41,8 @@ def lib():
                 handle.ferrum_gemm_tc_workspace.restype = c_longlong
                 if handle.ferrum_kernels_abi() != ABI:
                     raise KernelError(f"{path} is a stale build; delete it and call again")
+                if os.environ.get("FERRUM_DEPENDENT_LAUNCH", "1") == "0":
+                    handle.ferrum_set_dependent_launch(c_int(0))
                 _lib = handle
     return _lib
 
@@ -104,8 +107,19 @@ def embedding(table, ids, out, err):
                                   c_int(V), _ptr(err), _stream()), "embedding")
 
 
-def rmsnorm(x, weight, out, eps, rows=None, n_rows=None):
-    """out[r] = rmsnorm(x[rows[r] if rows else r]) * weight; x float32, out float32 or bfloat16."""
+class Partials:
+    """A product that the tensor-core kernel left as float32 partials (see gemm_tc_deferred):
+    the workspace that holds them and the four numbers a consumer needs to sum them."""
+
+    def __init__(self, workspace, layout):
+        self.workspace, self.layout = workspace, layout
+        self._c = (c_int * 4)(*layout)
+
+
+def rmsnorm(x, weight, out, eps, rows=None, n_rows=None, partials=None):
+    """out[r] = rmsnorm(x[rows[r] if rows else r]) * weight; x float32, out float32 or bfloat16.
+    With `partials` (a deferred residual product) the rows of x first get the partials added,
+    in place."""
     _need(x, torch.float32, "x", 2); _need(weight, torch.float32, "weight", 1); _need(out, None, "out", 2)
     E = x.shape[1]
     if n_rows is None:
@@ -114,8 +128,48 @@ def rmsnorm(x, weight, out, eps, rows=None, n_rows=None):
         raise KernelError("rmsnorm: shapes do not agree")
     if rows is not None:
         _need(rows, torch.int32, "rows", 1)
+    if partials is not None:
+        _check(lib().ferrum_rmsnorm_reduce(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), _ptr(rows),
+                                           c_int(n_rows), c_int(E), c_float(eps), _ptr(partials.workspace), partials._c,
+                                           _stream()), "rmsnorm_reduce")
+        return
     _check(lib().ferrum_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), _ptr(rows), c_int(n_rows),
                                 c_int(E), c_float(eps), _stream()), "rmsnorm")
+
+
+def residual_reduce(h, n_rows, partials):
+    """h[:n_rows] += the deferred product."""
+    _need(h, torch.float32, "h", 2)
+    _check(lib().ferrum_residual_reduce(_ptr(h), c_int(n_rows), c_int(h.shape[1]), _ptr(partials.workspace), partials._c,
+                                        _stream()), "residual_reduce")
+
+
+def swiglu_reduce(act, n_tokens, F, partials):
+    """act[t, f] = silu(gate) * up from a deferred two-product launch."""
+    _need(act, torch.bfloat16, "act", 2)
+    _check(lib().ferrum_swiglu_reduce(_ptr(act), c_int(n_tokens), c_int(F), c_int(act.stride(0)), _ptr(partials.workspace),
+                                      partials._c, _stream()), "swiglu_reduce")
+
+
+def gemm_tc_can_defer(M, N, K, dual):
+    return bool(lib().ferrum_gemm_tc_can_defer(c_int(M), c_int(N), c_int(K), c_int(1 if dual else 0), c_int(0)))
+
+
+def gemm_tc_deferred(x, w, err, workspace, M=None, N=None, dual_offset=0, n_ctas=0):
+    """The tensor-core product without its final reduction: returns `Partials` for the kernel
+    that consumes the product.  Only for shapes that `gemm_tc_can_defer` accepts."""
+    _need(x, torch.bfloat16, "x", 2); _need(w, torch.bfloat16, "w", 2); _need(workspace, torch.float32, "workspace")
+    M = x.shape[0] if M is None else M
+    K = w.shape[1]
+    N = (w.shape[0] - dual_offset) if N is None else N
+    if x.shape[1] != K or x.shape[0] < M:
+        raise KernelError(f"gemm_tc_deferred: shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)}")
+    layout = (c_int * 4)()
+    _check(lib().ferrum_gemm_tc_deferred(_ptr(x), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
+                                         c_int(w.stride(0)), c_int(w.shape[0]), c_int(dual_offset), c_int(n_ctas),
+                                         _ptr(workspace), c_longlong(workspace.numel()), layout, _ptr(err), _stream()),
+           "gemm_tc_deferred")
+    return Partials(workspace, tuple(layout))
 
 
 def gemm_generic(x, w, out, epilogue, M=None):
@@ -175,8 +229,9 @@ def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_
 
 
 def rope_cache_write(qkv, n_tokens, positions, req_of_token, block_table, cos_sin, kv_plane, page_stride, page_size,
-                     Hq, Hkv, D, R, pairing, write_kv, err):
-    """Rotate q (in place) and k, store k and v into the paged cache plane."""
+                     Hq, Hkv, D, R, pairing, write_kv, err, partials=None):
+    """Rotate q (in place) and k, store k and v into the paged cache plane.  With `partials`
+    the q, k, v rows are first summed from a deferred product into `qkv`."""
     _need(qkv, None, "qkv", 2); _need(positions, torch.int32, "positions", 1)
     _need(req_of_token, torch.int32, "req_of_token", 1); _need(block_table, torch.int32, "block_table", 2)
     if R:
@@ -192,7 +247,9 @@ def rope_cache_write(qkv, n_tokens, positions, req_of_token, block_table, cos_si
                                          c_int(block_table.shape[1]), _ptr(cos_sin if R else None),
                                          c_int(cos_sin.shape[0] if R else 0), _ptr(kv_plane if write_kv else None),
                                          c_longlong(page_stride), c_int(page_size), c_int(Hq), c_int(Hkv), c_int(D),
-                                         c_int(R), c_int(pairing), c_int(1 if write_kv else 0), _ptr(err), _stream()),
+                                         c_int(R), c_int(pairing), c_int(1 if write_kv else 0), _ptr(err),
+                                         _ptr(partials.workspace if partials is not None else None),
+                                         partials._c if partials is not None else None, _stream()),
            "rope_cache_write")
 
 

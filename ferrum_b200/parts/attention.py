@@ -14,7 +14,7 @@ import torch
 
 from ..ops import lib as ops
 from .base import CacheNeed, Mixer, PagedKVNeed, ParamSpec
-from .linear import RESIDUAL, STORE, linear
+from .linear import RESIDUAL, STORE, linear, linear_deferred
 
 
 class PagedAttention(Mixer):
@@ -45,16 +45,16 @@ class PagedAttention(Mixer):
         T, Hq, Hkv, D = ctx.n_tokens, self.Hq, self.Hkv, self.D
         qw = Hq * D
         qkv = ctx.buf("attn_qkv", (ctx.token_capacity, (Hq + 2 * Hkv) * D), self.dtype)
-        if cache.writes:
-            linear(x, self.w_qkv, qkv, STORE, ctx, M=T)
-        else:  # this run of the layer reads another run's keys and values
-            linear(x, self.w_qkv[:qw], qkv, STORE, ctx, M=T)
+        w = self.w_qkv if cache.writes else self.w_qkv[:qw]   # a run that reads another run's cache needs q only
+        part = linear_deferred(x, w, ctx, T) if ctx.defer_residuals else None
+        if part is None:
+            linear(x, w, qkv, STORE, ctx, M=T)
         rot = self.position.rotary() if self.position is not None else None
         table = ctx.block_tables[cache.group]
         ops.rope_cache_write(qkv, T, ctx.positions, ctx.req_of_token, table,
                              rot.cos_sin if rot is not None else None, cache.plane, cache.page_stride,
                              cache.page_size, Hq, Hkv, D, rot.rope_dim if rot is not None else 0,
-                             rot.pairing if rot is not None else 0, cache.writes, ctx.err)
+                             rot.pairing if rot is not None else 0, cache.writes, ctx.err, partials=part)
         out = ctx.buf("attn_out", (ctx.token_capacity, qw), self.dtype)
         if ops.attention_flash_supported(self.dtype, D):
             self._flash(qkv, out, ctx, cache, table)

@@ -18,6 +18,10 @@ PositionEncoding `rotary()` returns the table a rotating mixer needs, or None;
                 `on_embedding(h, ctx)` may add to the embedded tokens.
 Block           `forward(h, ctx, cache)` runs its parts on the residual stream `h`.
 
+A built-in part may leave its residual sum pending in `ctx` (StepContext.pending_residual)
+for the next norm to add; whoever reads or writes `residual` by other means calls
+`ctx.flush_residual()` first (PreNormBlock does so before every mixer and feed-forward).
+
 `ctx` is the `StepContext` of the batch (engine/batch.py): which token belongs to which
 request, positions, block tables, and the scratch allocator.
 """

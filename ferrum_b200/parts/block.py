@@ -21,6 +21,8 @@ class PreNormBlock(Part):
 
     def forward(self, h, ctx, cache):
         x = self.norm1.forward(h, ctx)
+        ctx.flush_residual()            # no-op when the norm took the pending sum itself
         self.mixer.forward(x, ctx, cache, h)
         x = self.norm2.forward(h, ctx)
+        ctx.flush_residual()
         self.ffn.forward(x, ctx, h)

@@ -20,5 +20,5 @@ class RMSNorm(Norm):
         n = n_rows if n_rows is not None else ctx.n_tokens
         cap = ctx.want_capacity if rows is not None else ctx.token_capacity
         out = ctx.buf(tag + ("_rows" if rows is not None else ""), (cap, self.width), self.out_dtype)
-        ops.rmsnorm(h, self.w_weight, out, self.eps, rows=rows, n_rows=n)
+        ops.rmsnorm(h, self.w_weight, out, self.eps, rows=rows, n_rows=n, partials=ctx.take_pending_residual(h))
         return out

@@ -415,3 +415,49 @@ def test_sampling_matches_plain(ops, V):
     freq = np.bincount(out.cpu().numpy(), minlength=4) / n
     p = np.exp([2.0, 1, 0, -1]); p /= p.sum()
     assert np.abs(freq - p).max() < 0.03, (freq, p)
+
+
+# ---------------------------------------------------------------- deferred reduction
+@pytest.mark.parametrize("M,N,K", [(1, 384, 512), (8, 6144, 4096), (33, 1000, 264), (64, 4096, 2048)])
+def test_gemm_deferred_partials_and_their_consumers(ops, M, N, K):
+    """The product left as partials, summed by each kind of consumer: the residual reduce,
+    the norm that adds a pending residual, and (two products) the SwiGLU reduce."""
+    if not ops.gemm_tc_can_defer(M, N, K, False):
+        pytest.skip("shape cannot defer")
+    g = torch.Generator(device="cuda").manual_seed(31)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.1).bfloat16()
+    ref = x.double() @ w.double().T
+    e = err_flag()
+    floats, _ = ops.gemm_tc_workspace(M, N, K, False)
+    ws = torch.empty(floats, device="cuda")
+    part = ops.gemm_tc_deferred(x, w, e, ws)
+    h0 = torch.randn(M, N, device="cuda", generator=g)
+    h = h0.clone()
+    ops.residual_reduce(h, M, part)
+    assert e.item() == 0
+    assert ((h.double() - (h0.double() + ref)).abs() <= lim(ref, 2e-5) * math.sqrt(K)).all()
+    # same numbers as the kernel's own reduction: both add the partials in K order
+    floats2, tiles = ops.gemm_tc_workspace(M, N, K, False)
+    own = h0.clone()
+    ops.gemm_tc(x, w, own, ops.TC_RESIDUAL, e, torch.empty(floats2, device="cuda"),
+                torch.zeros(tiles, dtype=torch.int32, device="cuda"))
+    assert torch.equal(own, h)
+    # the norm adds the pending sum, writes the residual back and normalises it
+    part = ops.gemm_tc_deferred(x, w, e, ws)
+    h2 = h0.clone()
+    wn = 1 + 0.1 * torch.randn(N, device="cuda", generator=g)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ops.rmsnorm(h2, wn, out, 1e-5, partials=part)
+    assert torch.equal(h2, h)
+    want = torch.from_numpy(P.rms_norm(h.double().cpu().numpy(), wn.double().cpu().numpy(), 1e-5)).cuda()
+    assert ((out.double() - want).abs() <= lim(want, 8e-3)).all()
+    if N % 2 == 0 and ops.gemm_tc_can_defer(M, N // 2, K, True):
+        F = N // 2
+        part = ops.gemm_tc_deferred(x, w, e, ws, N=F, dual_offset=F)
+        act = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+        ops.swiglu_reduce(act, M, F, part)
+        gate, up = ref[:, :F], ref[:, F:]
+        want = gate / (1 + torch.exp(-gate)) * up
+        assert ((act.double() - want).abs() <= lim(want, 1e-2)).all()
+    assert e.item() == 0

@@ -97,6 +97,7 @@ def test_norm_and_feed_forward_parts(cuda, dtype):
     assert np.abs(x[:T].double().cpu().numpy() - ref_x).max() <= tol
     res = h.clone()
     ffn.forward(x, ctx, res)
+    ctx.flush_residual()           # the residual sum may be left for the next norm; ask for it now
     wgu = ffn.w_gate_up.double().cpu().numpy()
     xin = x[:T].double().cpu().numpy()
     ref = h.double().cpu().numpy() + P.swiglu_ffn(xin, wgu[:F], wgu[F:], ffn.w_down_weight.double().cpu().numpy())
