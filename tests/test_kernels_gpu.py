@@ -454,7 +454,8 @@ def test_gemm_deferred_partials_and_their_consumers(ops, M, N, K):
     assert ((out.double() - want).abs() <= lim(want, 8e-3)).all()
     if N % 2 == 0 and ops.gemm_tc_can_defer(M, N // 2, K, True):
         F = N // 2
-        part = ops.gemm_tc_deferred(x, w, e, ws, N=F, dual_offset=F)
+        ws2 = torch.empty(ops.gemm_tc_workspace(M, F, K, True)[0], device="cuda")
+        part = ops.gemm_tc_deferred(x, w, e, ws2, N=F, dual_offset=F)
         act = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
         ops.swiglu_reduce(act, M, F, part)
         gate, up = ref[:, :F], ref[:, F:]
