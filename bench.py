@@ -262,7 +262,7 @@ def main():
         dt = time.perf_counter() - t0
         assert got == B * K, (got, B * K)
         e2e = {"value": round(got / dt, 1), "unit": "tok/s", "h2d_bytes_per_step": int(eng.runner.ctx.h2d_bytes),
-               "d2h_bytes_per_step": 4 * (B + 1), "ms_per_step": round(dt / K * 1e3, 3)}
+               "d2h_bytes_per_step": int(eng.sampler.d2h_bytes), "ms_per_step": round(dt / K * 1e3, 3)}
 
     line = {
         "metric": "decode tok/s (Llama-3.1-8B bf16, batch 8, context 8192)", "value": round(value, 1), "unit": "tok/s",

@@ -3,7 +3,7 @@
 Everything between a request's token ids and its next token: typed configuration and a
 model registry, safetensors/GGUF weights, a model put together from parts, a paged cache
 manager, one step function for mixed batches, a continuous batcher, samplers, and
-hand-written CUDA kernels.  See DESIGN.md for what each package owns.
+hand-written CUDA kernels.
 """
 __version__ = "0.1.0"
 

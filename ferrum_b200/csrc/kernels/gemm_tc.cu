@@ -477,7 +477,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const int n0 = (int)(tile % tiles_n) * 2 * TILE_N + (int)rank * TILE_N;
         const int t0 = (int)(tile / tiles_n) * PAIR_BT + (int)rank * (PAIR_BT / 2);
         const uint32_t a = smem_base + s * PAIR_STAGE_BYTES;
-        const uint32_t leader_full = map_to_cta(full_bar(s), 0);
+        const uint32_t leader_full = map_to_cta(full_bar(s), 0);  // (measured: this loop is not the limit; the copies are)
         if (rank == 0) mbar_expect_tx(full_bar(s), 2 * PAIR_STAGE_BYTES);
         tma_load_2d_pair(a, &tmap_w, leader_full, kb * TILE_K, n0);
         tma_load_2d_pair(a + A_BYTES, &tmap_x, leader_full, kb * TILE_K, t0);
@@ -568,8 +568,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const uint32_t acc_addr = lane_addr + buf * ACC_COLS;
       const uint32_t leader_acc_empty = map_to_cta(acc_empty_bar(buf), 0);
       if (whole && p.epilogue == TC_RESIDUAL) {
-        // 32 columns per round: the residual loads are issued before the accumulator is read,
-        // so that a round costs one memory latency, not two
+        // 32 columns at a time: the residual loads are issued before the accumulator is read,
+        // so that each batch costs one memory latency, not two
         float* out = (float*)p.out + (size_t)t0 * p.ldo + n;
         const size_t ld = (size_t)p.ldo;
 #pragma unroll 1

@@ -20,6 +20,7 @@ from ..cache import CacheStorage
 from ..config import registry
 from ..errors import ConfigError, InvalidRequest
 from ..ops import lib as ops
+from ..sampling import DeviceSampler
 from ..weights import init_random, load_weights
 from .batch import StepEntry
 from .runner import ModelRunner
@@ -102,13 +103,7 @@ class Engine:
         sc.eos_token_id = -1 if eos is None else int(eos)
         self.scheduler = host.module().Scheduler(self.cache.manager, sc)
         self._next_id = 0
-        n = int(max_batch_seqs)
-        pin = lambda dt: torch.empty(n + 1, dtype=dt).pin_memory()
-        dev = lambda dt: torch.empty(n + 1, dtype=dt, device=device)
-        self._inv_t = (pin(torch.float32), dev(torch.float32))
-        self._seeds = (pin(torch.int64), dev(torch.int64))
-        self._counters = (pin(torch.int32), dev(torch.int32))
-        self._ids = (pin(torch.int32), dev(torch.int32))
+        self.sampler = DeviceSampler(max_batch_seqs, device)
 
     # ------------------------------------------------------------------ requests
     def submit(self, prompt_tokens: Sequence[int], max_new_tokens: int, sampling: SamplingParams = None,
@@ -148,28 +143,11 @@ class Engine:
         return self._events(self.scheduler.commit(ids))
 
     def _sample(self, logits, rows):
-        """One id per wanted row, chosen on the device; the ids and the device error flag
-        come back to the host in one copy."""
-        n = len(rows)
-        ids_h, ids_d = self._ids
-        if any(p.temperature > 0 for p in rows):
-            (it_h, it_d), (sd_h, sd_d), (ct_h, ct_d) = self._inv_t, self._seeds, self._counters
-            for i, p in enumerate(rows):
-                it_h[i] = float(np.float32(1.0 / p.temperature)) if p.temperature > 0 else 0.0
-                sd_h[i] = int(np.uint64(p.seed).astype(np.int64))
-                ct_h[i] = p.counter
-            for h, d in (self._inv_t, self._seeds, self._counters):
-                d[:n].copy_(h[:n], non_blocking=True)
-            ops.sample(logits, n, ids_d, self.runner.ctx.err, it_d[:n], sd_d[:n], ct_d[:n])
-        else:
-            ops.sample(logits, n, ids_d, self.runner.ctx.err)
-        ids_d[n:n + 1].copy_(self.runner.ctx.err)
-        ids_h[:n + 1].copy_(ids_d[:n + 1], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        out = ids_h[:n + 1].tolist()
-        if out[n]:
+        """One id per wanted row, chosen on the device (sampling/sampler.py)."""
+        ids, code = self.sampler.sample(logits, rows, self.runner.ctx.err)
+        if code:
             self.runner.check_device_errors()
-        return out[:n]
+        return ids
 
     @staticmethod
     def _events(raw):
