@@ -59,11 +59,102 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * inv * w[i]);
 }
 
+// The norm of a few rows spread over a cluster of CTAs: with 8 rows and one CTA per row the
+// kernel is a chain of memory latencies on 8 SMs.  Here NORM_CLUSTER CTAs share a row; each
+// sums its slice (adding pending partials if any), the slices' sums of squares are exchanged
+// through distributed shared memory and added in rank order, so the result is the same
+// whichever CTA finishes first.
+constexpr int NORM_CLUSTER = 8;
+
+__device__ __forceinline__ unsigned norm_cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void norm_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float norm_peer_value(const float* local, unsigned rank) {
+  unsigned addr = (unsigned)__cvta_generic_to_shared(local), peer;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+  return v;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+rmsnorm_cluster_kernel(float* __restrict__ h, const float* __restrict__ w, TOut* __restrict__ out,
+                       const int* __restrict__ rows, int E, float eps, const PartialLayout L) {
+  __shared__ float red[32];
+  __shared__ float slice_ss;
+  __shared__ PartialTable tab;
+  if (L.ws != nullptr) build_partial_table(L, tab);
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.x;
+  const unsigned rank = norm_cluster_rank();
+  const int src = rows ? rows[r] : r;
+  const int per = (E + NORM_CLUSTER - 1) / NORM_CLUSTER;
+  const int lo = rank * per, hi = min(E, lo + per);
+  float* hr = h + (size_t)src * E;
+  float ss = 0.f;
+#pragma unroll 2
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    float v = hr[i];
+    if (L.ws != nullptr) {
+      v += partial_sum(L, tab, src, i);
+      hr[i] = v;
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) slice_ss = ss;
+  norm_cluster_sync();
+  float total = 0.f;
+#pragma unroll
+  for (unsigned c = 0; c < NORM_CLUSTER; ++c) total += norm_peer_value(&slice_ss, c);
+  const float inv = 1.0f / sqrtf(total / (float)E + eps);
+  TOut* o = out + (size_t)r * E;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) o[i] = from_f32<TOut>(hr[i] * inv * w[i]);
+  norm_cluster_sync();  // nobody leaves while a peer may still read its slice sum
+}
+
+template <typename TOut>
+static cudaError_t launch_norm_cluster(float* h, const float* w, TOut* out, const int* rows, int n_rows, int E, float eps,
+                                       const PartialLayout& L, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_rows, NORM_CLUSTER);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = NORM_CLUSTER;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ferrum_dependent_launch_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, rmsnorm_cluster_kernel<TOut>, h, w, out, rows, E, eps, L);
+}
+
+// Rows at or below this count take the cluster kernel.
+constexpr int NORM_CLUSTER_MAX_ROWS = 64;
+
 FERRUM_API int ferrum_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows,
                               int n_rows, int E, float eps, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_rows >= 0 && E > 0, "rmsnorm: bad sizes rows=%d E=%d", n_rows, E);
   FERRUM_CHECK_ARG(eps > 0.f, "rmsnorm: eps must be positive");
   if (n_rows == 0) return 0;
+  if (n_rows <= NORM_CLUSTER_MAX_ROWS && E >= 128 && (out_dtype == FERRUM_F32 || out_dtype == FERRUM_BF16)) {
+    const PartialLayout none{nullptr, 0, 0, 0, 0};
+    cudaError_t e = out_dtype == FERRUM_F32
+        ? launch_norm_cluster<float>(const_cast<float*>(x), w, (float*)out, rows, n_rows, E, eps, none, stream)
+        : launch_norm_cluster<__nv_bfloat16>(const_cast<float*>(x), w, (__nv_bfloat16*)out, rows, n_rows, E, eps, none, stream);
+    FERRUM_CHECK_ARG(e == cudaSuccess, "rmsnorm: cluster launch failed: %s", cudaGetErrorString(e));
+    return 0;
+  }
   const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
   if (out_dtype == FERRUM_F32)
     launch_kernel(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)out, rows, E, eps);
@@ -134,6 +225,13 @@ FERRUM_API int ferrum_rmsnorm_reduce(float* h, const float* w, void* out, int ou
   PartialLayout L;
   if (int r = make_layout(partials, layout, &L)) return r;
   FERRUM_CHECK_ARG(E <= L.tiles * 128, "rmsnorm_reduce: the partials cover %d features, the rows have %d", L.tiles * 128, E);
+  if (n_rows <= NORM_CLUSTER_MAX_ROWS && E >= 128 && (out_dtype == FERRUM_F32 || out_dtype == FERRUM_BF16)) {
+    cudaError_t e = out_dtype == FERRUM_F32
+        ? launch_norm_cluster<float>(h, w, (float*)out, rows, n_rows, E, eps, L, stream)
+        : launch_norm_cluster<__nv_bfloat16>(h, w, (__nv_bfloat16*)out, rows, n_rows, E, eps, L, stream);
+    FERRUM_CHECK_ARG(e == cudaSuccess, "rmsnorm_reduce: cluster launch failed: %s", cudaGetErrorString(e));
+    return 0;
+  }
   const int threads = E >= 2048 ? 1024 : (E >= 512 ? 256 : 128);  // many loads per element: many threads
   if (out_dtype == FERRUM_F32)
     launch_kernel(rmsnorm_reduce_kernel<float>, n_rows, threads, 0, stream, h, w, (float*)out, rows, E, eps, L);

@@ -44,7 +44,7 @@ def test_embedding(ops, dtype, V, E, T):
 
 # ---------------------------------------------------------------- rmsnorm
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("E,T,eps", [(80, 5, 3e-6), (1537, 9, 1e-5), (4096, 3, 1e-5)])
+@pytest.mark.parametrize("E,T,eps", [(80, 5, 3e-6), (1537, 9, 1e-5), (4096, 3, 1e-5), (2048, 70, 1e-5)])
 def test_rmsnorm(ops, out_dtype, E, T, eps):
     g = torch.Generator(device="cuda").manual_seed(2)
     x = torch.randn(T, E, device="cuda", generator=g) * 3
