@@ -368,8 +368,8 @@ __global__ void __launch_bounds__(D / 4 < 32 ? 32 : D / 4)
 combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* part_ml, const int* q_start,
                const int* req_of_token, const int* req_tile0, const int* tile_info, const int* token_list, int G,
                int Hkv, int BM) {
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const int t = token_list ? token_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int req = req_of_token[t];
   const int kvh = head / G;

@@ -11,8 +11,8 @@
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int E, int V, int* __restrict__ err) {
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;
@@ -44,8 +44,8 @@ template <typename TOut>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TOut* __restrict__ out, const int* __restrict__ rows, int E, float eps) {
   __shared__ float red[32];
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * E;
   float ss = 0.f;
@@ -57,6 +57,52 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   const float inv = 1.0f / sqrtf(ss / (float)E + eps);
   TOut* o = out + (size_t)r * E;
   for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * inv * w[i]);
+}
+
+// Many rows of a width that is a multiple of 4: one block per row, float4 loads, the row kept
+// in registers between the sum of squares and the scaling (read once, written once).
+constexpr int NORM_VEC_MAX = 4;  // float4 per thread
+template <typename TOut>
+__global__ void __launch_bounds__(512)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ out,
+                   const int* __restrict__ rows, int E, float eps) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * E);
+  const int n4 = E >> 2;
+  float4 v[NORM_VEC_MAX];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NORM_VEC_MAX; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    v[k] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(v[k].x, v[k].x, ss);
+    ss = fmaf(v[k].y, v[k].y, ss);
+    ss = fmaf(v[k].z, v[k].z, ss);
+    ss = fmaf(v[k].w, v[k].w, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)E + eps);
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  TOut* o = out + (size_t)r * E;
+#pragma unroll
+  for (int k = 0; k < NORM_VEC_MAX; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i >= n4) continue;
+    const float4 g = w4[i];
+    const float a = v[k].x * inv * g.x, b = v[k].y * inv * g.y, c = v[k].z * inv * g.z, d = v[k].w * inv * g.w;
+    if (sizeof(TOut) == 4) {
+      reinterpret_cast<float4*>(o)[i] = make_float4(a, b, c, d);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(o)[i] = pk;
+    }
+  }
 }
 
 // The norm of a few rows spread over a cluster of CTAs: with 8 rows and one CTA per row the
@@ -90,8 +136,8 @@ rmsnorm_cluster_kernel(float* __restrict__ h, const float* __restrict__ w, TOut*
   __shared__ float slice_ss;
   __shared__ PartialTable tab;
   if (L.ws != nullptr) build_partial_table(L, tab);
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const unsigned rank = norm_cluster_rank();
   const int src = rows ? rows[r] : r;
@@ -155,6 +201,17 @@ FERRUM_API int ferrum_rmsnorm(const float* x, const float* w, void* out, int out
     FERRUM_CHECK_ARG(e == cudaSuccess, "rmsnorm: cluster launch failed: %s", cudaGetErrorString(e));
     return 0;
   }
+  if (E % 4 == 0 && E >= 512 && E <= 4 * NORM_VEC_MAX * 512 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
+      ((uintptr_t)out & 15) == 0 && (out_dtype == FERRUM_F32 || out_dtype == FERRUM_BF16)) {
+    const int n4 = E / 4;
+    const int vthreads = n4 >= 2048 ? 512 : (n4 >= 512 ? 256 : 128);
+    if (out_dtype == FERRUM_F32)
+      launch_kernel(rmsnorm_vec_kernel<float>, n_rows, vthreads, 0, stream, x, w, (float*)out, rows, E, eps);
+    else
+      launch_kernel(rmsnorm_vec_kernel<__nv_bfloat16>, n_rows, vthreads, 0, stream, x, w, (__nv_bfloat16*)out, rows, E, eps);
+    FERRUM_CHECK_LAUNCH("rmsnorm");
+    return 0;
+  }
   const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
   if (out_dtype == FERRUM_F32)
     launch_kernel(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)out, rows, E, eps);
@@ -174,8 +231,8 @@ __global__ void rmsnorm_reduce_kernel(float* __restrict__ h, const float* __rest
   __shared__ float red[32];
   __shared__ PartialTable tab;
   build_partial_table(L, tab);   // shapes only: may run before the dependency wait
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* hr = h + (size_t)src * E;
@@ -196,8 +253,8 @@ __global__ void rmsnorm_reduce_kernel(float* __restrict__ h, const float* __rest
 __global__ void residual_reduce_kernel(float* __restrict__ h, int E, const PartialLayout L) {
   __shared__ PartialTable tab;
   build_partial_table(L, tab);
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   float* hr = h + (size_t)blockIdx.x * E;
   for (int i = threadIdx.x; i < E; i += blockDim.x) hr[i] += partial_sum(L, tab, blockIdx.x, i);
 }
@@ -269,8 +326,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
                                   const PartialLayout L) {
   __shared__ PartialTable tab;
   if (L.ws != nullptr) build_partial_table(L, tab);
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = R >> 1;
@@ -354,6 +411,96 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
   }
 }
 
+// Many tokens, bfloat16, the whole head rotated (R == D, D a multiple of 16): a thread rotates
+// eight pairs with 16-byte loads and stores, or copies eight value elements.  Same formulas and
+// the same error codes as the kernel above.
+__global__ void __launch_bounds__(256)
+rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ positions,
+                      const int* __restrict__ req_of_token, const int* __restrict__ block_table, int table_width,
+                      const float* __restrict__ cos_sin, int n_pos, __nv_bfloat16* __restrict__ kv_plane,
+                      long long page_stride, int page_size, int Hq, int Hkv, int D, int pairing, int write_kv,
+                      int n_tokens, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
+  const int chunks = D >> 4;                         // rotation items per head
+  const int rot_items = (Hq + Hkv) * chunks;
+  const int per_token = rot_items + (write_kv ? Hkv * (D >> 3) : 0);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n_tokens * per_token) return;
+  const int t = (int)(idx / per_token), item = (int)(idx % per_token);
+  const int pos = positions[t];
+  const int half = D >> 1;
+  if (pos < 0 || pos >= n_pos) {
+    if (item == 0) atomicExch(err, 2);
+    return;
+  }
+  __nv_bfloat16* row = qkv + (size_t)t * ld;
+  __nv_bfloat16* kdst = nullptr;
+  if (write_kv) {
+    const int lp = pos / page_size;
+    if (lp >= table_width) {
+      if (item == 0) atomicExch(err, 3);
+      return;
+    }
+    const int page = block_table[(size_t)req_of_token[t] * table_width + lp];
+    if (page < 0) {
+      if (item == 0) atomicExch(err, 4);
+      return;
+    }
+    kdst = kv_plane + (size_t)page * page_stride + (size_t)(pos % page_size) * D;
+  }
+  if (item >= rot_items) {  // a value chunk
+    const int w = item - rot_items, h = w / (D >> 3), c = w % (D >> 3);
+    const uint4 v = *reinterpret_cast<const uint4*>(row + (size_t)(Hq + Hkv + h) * D + c * 8);
+    *reinterpret_cast<uint4*>(kdst + (size_t)(Hkv + h) * page_size * D + c * 8) = v;
+    return;
+  }
+  const int h = item / chunks, c = item % chunks;
+  if (h >= Hq && !write_kv) return;
+  __nv_bfloat16* src = row + (size_t)h * D;
+  const int o0 = pairing == 0 ? c * 16 : c * 8, o1 = pairing == 0 ? c * 16 + 8 : half + c * 8;
+  uint4 r0 = *reinterpret_cast<const uint4*>(src + o0), r1 = *reinterpret_cast<const uint4*>(src + o1);
+  const __nv_bfloat16* e0 = reinterpret_cast<const __nv_bfloat16*>(&r0);
+  const __nv_bfloat16* e1 = reinterpret_cast<const __nv_bfloat16*>(&r1);
+  const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + ((size_t)pos * half + c * 8) * 2);
+  uint4 w0, w1;
+  __nv_bfloat16* f0 = reinterpret_cast<__nv_bfloat16*>(&w0);
+  __nv_bfloat16* f1 = reinterpret_cast<__nv_bfloat16*>(&w1);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {  // pairs 2k and 2k+1 of this chunk
+    const float4 cs = cs4[k];  // cos, sin, cos, sin
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int i = 2 * k + q;
+      const float cv = q == 0 ? cs.x : cs.z, sv = q == 0 ? cs.y : cs.w;
+      float x0, x1;
+      if (pairing == 0) {  // elements 2i and 2i+1 of the 16 loaded
+        x0 = __bfloat162float(i < 4 ? e0[2 * i] : e1[2 * i - 8]);
+        x1 = __bfloat162float(i < 4 ? e0[2 * i + 1] : e1[2 * i - 7]);
+      } else {
+        x0 = __bfloat162float(e0[i]);
+        x1 = __bfloat162float(e1[i]);
+      }
+      const __nv_bfloat16 a = __float2bfloat16_rn(x0 * cv - x1 * sv), b = __float2bfloat16_rn(x0 * sv + x1 * cv);
+      if (pairing == 0) {
+        if (i < 4) {
+          f0[2 * i] = a;
+          f0[2 * i + 1] = b;
+        } else {
+          f1[2 * i - 8] = a;
+          f1[2 * i - 7] = b;
+        }
+      } else {
+        f0[i] = a;
+        f1[i] = b;
+      }
+    }
+  }
+  __nv_bfloat16* dst = h < Hq ? src : kdst + (size_t)(h - Hq) * page_size * D;
+  *reinterpret_cast<uint4*>(dst + o0) = w0;
+  *reinterpret_cast<uint4*>(dst + o1) = w1;
+}
+
 FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int ld, const int* positions,
                                        const int* req_of_token, const int* block_table, int table_width,
                                        const float* cos_sin, int n_pos, void* kv_plane, long long page_stride,
@@ -371,6 +518,16 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
     if (int r = make_layout(partials, layout, &L)) return r;
     FERRUM_CHECK_ARG((write_kv ? Hq + 2 * Hkv : Hq) * D <= L.tiles * 128 && n_tokens <= L.acc_cols,
                      "rope: the partials do not cover the rows");
+  }
+  if (dtype == FERRUM_BF16 && n_tokens > 64 && partials == nullptr && R == D && D % 16 == 0 && ld % 8 == 0 &&
+      ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)cos_sin & 15) == 0 &&
+      (!write_kv || (((uintptr_t)kv_plane & 15) == 0 && page_stride % 8 == 0))) {
+    const long long items = (long long)n_tokens * ((Hq + Hkv) * (D / 16) + (write_kv ? Hkv * (D / 8) : 0));
+    launch_kernel(rope_cache_vec_kernel, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, stream, (__nv_bfloat16*)qkv, ld,
+                  positions, req_of_token, block_table, table_width, cos_sin, n_pos, (__nv_bfloat16*)kv_plane, page_stride,
+                  page_size, Hq, Hkv, D, pairing, write_kv, n_tokens, err_flag);
+    FERRUM_CHECK_LAUNCH("rope_cache_write");
+    return 0;
   }
   const int threads = 256;
   // few tokens: several blocks per token, four head slots each, so that the row (and the
@@ -393,8 +550,8 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
 // act[t, f] = silu(gu[t, f]) * gu[t, F + f], silu(g) = g / (1 + exp(-g)), in float32.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int F, int ld_in, int ld_out) {
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const int t = blockIdx.y;
   const T* g = gu + (size_t)t * ld_in;
   const T* u = g + F;
@@ -405,13 +562,35 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
   }
 }
 
+// bfloat16 rows of 16-byte multiples: eight features per thread, 16-byte loads and stores.
+__global__ void __launch_bounds__(256)
+swiglu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int F, int ld_in, int ld_out) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;  // group of eight features
+  if (i * 8 >= F) return;
+  const uint4 g = *reinterpret_cast<const uint4*>(gu + (size_t)t * ld_in + i * 8);
+  const uint4 u = *reinterpret_cast<const uint4*>(gu + (size_t)t * ld_in + F + i * 8);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+  uint4 o;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 gv = __bfloat1622float2(g2[k]), uv = __bfloat1622float2(u2[k]);
+    o2[k] = __floats2bfloat162_rn(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y);
+  }
+  *reinterpret_cast<uint4*>(act + (size_t)t * ld_out + i * 8) = o;
+}
+
 // act[t, f] = silu(gate) * up where gate and up are still partials of a two-product launch
 // (columns t and acc_cols / 2 + t of the partial tiles).
 __global__ void swiglu_reduce_kernel(__nv_bfloat16* __restrict__ act, int F, int ld_out, const PartialLayout L) {
   __shared__ PartialTable tab;
   build_partial_table(L, tab);
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const int t = blockIdx.y;
   __nv_bfloat16* o = act + (size_t)t * ld_out;
   for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F; f += gridDim.x * blockDim.x) {
@@ -438,6 +617,13 @@ FERRUM_API int ferrum_swiglu(const void* gu, void* act, int dtype, int n_tokens,
   FERRUM_CHECK_ARG(n_tokens >= 0 && F > 0 && ld_in >= 2 * F && ld_out >= F, "swiglu: bad sizes T=%d F=%d", n_tokens, F);
   if (n_tokens == 0) return 0;
   FERRUM_CHECK_ARG(n_tokens <= 65535, "swiglu: more than 65535 tokens in one call");
+  if (dtype == FERRUM_BF16 && F % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && ((uintptr_t)gu & 15) == 0 &&
+      ((uintptr_t)act & 15) == 0) {
+    dim3 vgrid((F / 8 + 255) / 256, n_tokens);
+    launch_kernel(swiglu_vec_kernel, vgrid, dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, F, ld_in, ld_out);
+    FERRUM_CHECK_LAUNCH("swiglu");
+    return 0;
+  }
   dim3 grid((F + 255) / 256 > 64 ? 64 : (F + 255) / 256, n_tokens);
   if (dtype == FERRUM_F32)
     launch_kernel(swiglu_kernel<float>, grid, 256, 0, stream, (const float*)gu, (float*)act, F, ld_in, ld_out);

@@ -49,6 +49,7 @@ struct TcParams {
   int epilogue;
   int dual_offset;   // row of the second weight tile relative to the first (DUAL)
   int defer;         // 1: leave every segment's float32 partial in the workspace; the next kernel sums them
+  int out_tma;       // 1: the pair kernel writes `out` through its tensor map (staged in shared memory)
 };
 
 constexpr int TILE_N = 128;  // weight rows per tile (the instruction's M)
@@ -62,7 +63,7 @@ struct TcConfig {
   static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
   // few tokens: the CTA is a streaming engine and half the shared memory leaves room for a
   // second CTA on the SM (the next launch's, see the dependent-launch prologue)
-  static constexpr int BUDGET = (BT <= 64 && !DUAL ? 100 : 196) * 1024;
+  static constexpr int BUDGET = 196 * 1024;
   static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 10 ? 10 : (BUDGET / STAGE_BYTES);
   static constexpr int ACC_COLS = BT * (DUAL ? 2 : 1);
   static constexpr int ALL_COLS = 2 * ACC_COLS;  // two accumulators
@@ -404,10 +405,17 @@ constexpr int PAIR_BT = 256;                              // tokens per tile pai
 constexpr int PAIR_B_BYTES = (PAIR_BT / 2) * TILE_K * 2;  // each CTA stages half of the tokens
 constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
 constexpr int PAIR_STAGES = 6;
-constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+// The epilogue's staging: two buffers of 32 tokens x 128 features (float32 at most).  A thread
+// owns one feature of 32 tokens at a time; written to `out` directly that is 32 scattered
+// read-modify-writes per thread and the epilogue, not the tensor cores, sets the pace of short
+// products.  Staged, the tile leaves as one bulk store (or float32 add) per 32 tokens.
+constexpr int PAIR_OUT_ROWS = 32;
+constexpr int PAIR_OUT_BYTES = PAIR_OUT_ROWS * TILE_N * 4;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + 2 * PAIR_OUT_BYTES;
 
 __global__ void __launch_bounds__(192, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                    const __grid_constant__ CUtensorMap tmap_out, const TcParams p) {
   constexpr int STAGES = PAIR_STAGES;
   constexpr int ACC_COLS = PAIR_BT;
   extern __shared__ uint8_t smem_raw[];
@@ -438,6 +446,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     is_last = 0;
     prefetch_tensormap(&tmap_w);
     prefetch_tensormap(&tmap_x);
+    if (p.out_tma) prefetch_tensormap(&tmap_out);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);   // the leader's: its producer's expect_tx; bytes arrive from both CTAs
       mbar_init(empty_bar(s), 1);  // one multicast commit of the leader's MMA thread
@@ -546,9 +555,48 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     const int ep_tid = threadIdx.x - 64;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const size_t tile_floats = (size_t)ACC_COLS * TILE_N;
+    uint8_t* out_stage = smem + STAGES * PAIR_STAGE_BYTES + 256;
+    const bool staged = p.out_tma != 0;
+    int emitted = 0;  // staged stores issued so far; buffer = emitted & 1
     int seg = 0;
     long long u = u_begin;
     pdl_wait();
+    // 32 token columns c0.. of this thread's feature go to `out`: staged and sent through the
+    // tensor map (which clips at M and N), or written by the thread itself.
+    auto emit32 = [&](int t0, int c0, int n0_cta, const float (&v)[32]) {
+      if (staged) {
+        const int b = emitted & 1;
+        if (ep_tid == 0) bulk_wait_read<1>();  // the store that last used this buffer has read it
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (p.epilogue == TC_RESIDUAL) {
+          float* st = (float*)(out_stage + b * PAIR_OUT_BYTES);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) st[j * TILE_N + n_local] = v[j];
+        } else {
+          __nv_bfloat16* st = (__nv_bfloat16*)(out_stage + b * PAIR_OUT_BYTES);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) st[j * TILE_N + n_local] = __float2bfloat16_rn(v[j]);
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ep_tid == 0) {
+          const uint32_t src = smem_u32(out_stage + b * PAIR_OUT_BYTES);
+          if (p.epilogue == TC_RESIDUAL) tma_reduce_add_2d(&tmap_out, src, n0_cta, t0 + c0);
+          else tma_store_2d(&tmap_out, src, n0_cta, t0 + c0);
+          bulk_commit();
+        }
+        ++emitted;
+      } else if (n0_cta + n_local < p.N) {
+        float lo[16], hi[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          lo[j] = v[j];
+          hi[j] = v[16 + j];
+        }
+        tc_apply16(p, t0 + c0, n0_cta + n_local, lo, lo);
+        tc_apply16(p, t0 + c0 + 16, n0_cta + n_local, hi, hi);
+      }
+    };
     while (u < u_end) {
       const long long tile = u / nkb;
       const int kb0 = (int)(u % nkb);
@@ -567,7 +615,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const int n = n0 + n_local;
       const uint32_t acc_addr = lane_addr + buf * ACC_COLS;
       const uint32_t leader_acc_empty = map_to_cta(acc_empty_bar(buf), 0);
-      if (whole && p.epilogue == TC_RESIDUAL) {
+      if (whole && p.epilogue == TC_RESIDUAL && !staged) {
         // 32 columns at a time: the residual loads are issued before the accumulator is read,
         // so that each batch costs one memory latency, not two
         float* out = (float*)p.out + (size_t)t0 * p.ldo + n;
@@ -589,10 +637,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
       } else if (whole) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < PAIR_BT; c0 += 16) {
-          float v0[16];
-          tmem_ld16(acc_addr + c0, v0);
-          if (n < p.N) tc_apply16(p, t0 + c0, n, v0, v0);
+        for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
+          float v[32];
+          tmem_ld16(acc_addr + c0, &v[0]);
+          tmem_ld16(acc_addr + c0 + 16, &v[16]);
+          emit32(t0, c0, n0, v);
         }
         tc_fence_before();
         __syncwarp();
@@ -621,28 +670,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           if (is_last) *counter = 0;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (is_last) {
+        if (is_last) {  // the same for the four warps: they go through emit32's barriers together
           __threadfence();
-          if (n < p.N) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 16) {
-              float a0[16];
+          for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
+            float a0[32];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) a0[j] = 0.f;
-              for (int cc = c_first; cc <= c_last; ++cc) {  // K order
-                const float* wsp = p.workspace + (((size_t)cc * 2 + ((U * cc / P) / nkb == tile ? 0 : 1)) * 2 + rank) * tile_floats +
-                                   (size_t)c0 * TILE_N + n_local;
+            for (int j = 0; j < 32; ++j) a0[j] = 0.f;
+            for (int cc = c_first; cc <= c_last; ++cc) {  // K order
+              const float* wsp = p.workspace + (((size_t)cc * 2 + ((U * cc / P) / nkb == tile ? 0 : 1)) * 2 + rank) * tile_floats +
+                                 (size_t)c0 * TILE_N + n_local;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) a0[j] += __ldcg(wsp + (size_t)j * TILE_N);
-              }
-              tc_apply16(p, t0 + c0, n, a0, a0);
+              for (int j = 0; j < 32; ++j) a0[j] += __ldcg(wsp + (size_t)j * TILE_N);
             }
+            emit32(t0, c0, n0, a0);
           }
         }
       }
       u = seg_end;
       ++seg;
     }
+    if (staged && ep_tid == 0) bulk_wait_all();  // shared memory and `out` are settled before the CTA leaves
     tc_fence_before();
   }
 
@@ -683,8 +731,9 @@ struct MapKey {
   const void* ptr;
   long long rows, cols, ld;
   int box_rows;
+  int kind;  // 0: bfloat16 operand, 64-column boxes, 128-byte swizzle; 1 / 2: float32 / bfloat16 output, 128-column boxes
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && kind == o.kind;
   }
 };
 struct MapKeyHash {
@@ -693,7 +742,7 @@ struct MapKeyHash {
     h = h * 1000003u ^ std::hash<long long>()(k.rows);
     h = h * 1000003u ^ std::hash<long long>()(k.cols);
     h = h * 1000003u ^ std::hash<long long>()(k.ld);
-    h = h * 1000003u ^ std::hash<int>()(k.box_rows);
+    h = h * 1000003u ^ std::hash<int>()(k.box_rows * 4 + k.kind);
     return h;
   }
 };
@@ -701,10 +750,11 @@ struct MapKeyHash {
 // A tensor map of a row-major bfloat16 matrix [rows, cols] with row stride ld, read in
 // boxes of box_rows x 64 with the 128-byte swizzle; out-of-range elements read as zero.
 // Maps are pure functions of their key and are kept for reuse.
-static int get_tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+static int get_tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out,
+                          int kind = 0) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  MapKey key{ptr, rows, cols, ld, box_rows};
+  MapKey key{ptr, rows, cols, ld, box_rows, kind};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
@@ -716,14 +766,16 @@ static int get_tensor_map(const void* ptr, long long rows, long long cols, long 
   EncodeTiledFn fn = get_encode_fn();
   FERRUM_CHECK_ARG(fn != nullptr, "gemm_tc: the driver does not export cuTensorMapEncodeTiled");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (kind == 1 ? 4 : 2)};
+  cuuint32_t box[2] = {(cuuint32_t)(kind == 0 ? TILE_K : TILE_N), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult r = fn(out, kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  kind == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  FERRUM_CHECK_ARG(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows=%lld cols=%lld ld=%lld)",
-                   (int)r, rows, cols, ld);
+  FERRUM_CHECK_ARG(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows=%lld cols=%lld ld=%lld kind=%d)",
+                   (int)r, rows, cols, ld, kind);
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 8192) cache.clear();
   cache.emplace(key, *out);
@@ -748,7 +800,8 @@ static bool g_pair_kernel = true;
 // The CTA-pair kernel can be switched off (every shape then runs on the single-CTA kernel).
 FERRUM_API void ferrum_set_gemm_pair_kernel(int on) { g_pair_kernel = on != 0; }
 
-static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int n_ctas, cudaStream_t stream) {
+static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const TcParams& p, int n_ctas,
+                          cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
@@ -769,7 +822,7 @@ static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const Tc
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ferrum_dependent_launch_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, mo, p);
   FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc: pair kernel launch failed: %s", cudaGetErrorString(e));
   FERRUM_CHECK_LAUNCH("gemm_tc_pair");
   return 0;
@@ -847,7 +900,14 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
     int pairs = n_ctas / 2;
     if (pairs > units) pairs = (int)units;
     if (int r = get_tensor_map(x, M, K, ldx, PAIR_BT / 2, &mx)) return r;
-    return launch_tc_pair(mw, mx, p, 2 * pairs, stream);
+    // the output through a tensor map where its rows are 16-byte multiples; else by the threads
+    CUtensorMap mo = mw;
+    const int esize = epilogue == TC_RESIDUAL ? 4 : 2;
+    if ((epilogue == TC_RESIDUAL || epilogue == TC_STORE_BF16) && ((uintptr_t)out & 15) == 0 && ((long long)ldo * esize) % 16 == 0) {
+      if (int r = get_tensor_map(out, M, N, ldo, PAIR_OUT_ROWS, &mo, epilogue == TC_RESIDUAL ? 1 : 2)) return r;
+      p.out_tma = 1;
+    }
+    return launch_tc_pair(mw, mx, mo, p, 2 * pairs, stream);
   }
   if (int r = get_tensor_map(x, M, K, ldx, bt, &mx)) return r;
 #define TC_CASE(BT_)                                                         \

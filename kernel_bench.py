@@ -36,6 +36,7 @@ def main():
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--deferred", action="store_true", help="gemm: leave the partials to the consumer (as decoding does)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--no-dependent-launch", action="store_true", help="plain stream order between the launches")
     args = ap.parse_args()
@@ -98,6 +99,10 @@ def main():
             o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
             epi = ops.TC_SWIGLU if dual else ops.TC_STORE_BF16
         runs = [lambda w=w: ops.gemm_tc(x, w, o, epi, err, ws, cnt, N=N, dual_offset=N if dual else 0) for w in weights]
+        if args.deferred:
+            if not ops.gemm_tc_can_defer(M, N, K, dual):
+                sys.exit("this shape cannot defer its reduction")
+            runs = [lambda w=w: ops.gemm_tc_deferred(x, w, err, ws, N=N, dual_offset=N if dual else 0) for w in weights]
         wb = N * K * 2 * (2 if dual else 1)
         work = {"bytes": wb + M * K * 2 + M * N * (4 if args.epilogue == "residual" else 2),
                 "flops": 2.0 * M * N * K * (2 if dual else 1), "bound": "hbm" if M <= 128 else "tensor"}

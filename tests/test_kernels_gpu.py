@@ -325,13 +325,22 @@ def test_attention_flash_finds_one_far_key(ops, far_key, qlen):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("pairing", ["adjacent", "half"])
-@pytest.mark.parametrize("Hq,Hkv,D,R", [(4, 2, 16, 16), (3, 1, 48, 32), (2, 2, 128, 128)])
-def test_rope_cache_write(ops, dtype, pairing, Hq, Hkv, D, R):
+@pytest.mark.parametrize("Hq,Hkv,D,R", [(4, 2, 16, 16), (3, 1, 48, 32), (2, 2, 128, 128), (5, 1, 48, 48)])
+@pytest.mark.parametrize("many", [False, True])
+def test_rope_cache_write(ops, dtype, pairing, Hq, Hkv, D, R, many):
     from ferrum_b200.parts.rope import RotaryEmbedding
     ps, n_pos = 8, 300
     rot = RotaryEmbedding(D, R, 10000.0, None, pairing, n_pos, "cuda")
     positions = [0, 1, 7, 8, 9, 250, 299, 64]
     req = [0, 0, 0, 0, 0, 1, 1, 1]
+    if many:   # the many-token kernels; every (request, position) once
+        extra = [p for p in np.random.default_rng(5).permutation(n_pos).tolist() if p not in positions][:90]
+        positions = positions + extra
+        req = req + [i % 2 for i in range(len(extra))]
+        taken = set()
+        for i, pr in enumerate(zip(req, positions)):
+            assert pr not in taken
+            taken.add(pr)
     T = len(positions)
     g = torch.Generator(device="cuda").manual_seed(10)
     qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", generator=g).to(dtype)
