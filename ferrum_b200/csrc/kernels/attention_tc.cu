@@ -1,0 +1,616 @@
+// Paged causal GQA attention for prompt portions on the tcgen05 matrix unit (bfloat16).
+//
+// One CTA handles one work item x one KV head.  An item is a pair of row tiles of one request
+// and a key range [kv_begin, kv_end).  A row tile is `tok` consecutive tokens x the G query
+// heads of the KV head (tok = 128 / G, so tok * G <= 128 rows: row r is token r / G, head
+// r % G); a TMA box over (head size, heads, tokens) puts it in shared memory as the 128-row
+// K-major operand of the instruction.  Keys and values come page by page with TMA into
+// 64-key stages.  Per 64 keys and row tile:
+//   S = Q K^T          tcgen05.mma 128 x 64 x D into tensor memory
+//   P = exp2(S - m)    128 threads, one per row, read S from tensor memory, keep the running
+//                      maximum and sum in float32 and write P (bfloat16) to shared memory
+//   O += P V           tcgen05.mma 128 x D x 64, V as the MN-major operand straight from the
+//                      page layout, O in tensor memory
+// The two row tiles take turns on the matrix unit: while the threads of one compute P, the
+// products of the other run.  The running maximum is only moved (and O rescaled, in tensor
+// memory, by the row's own thread) when it grows by more than 2^8; until then P is computed
+// against the older maximum, which changes nothing in the quotient O / l.
+//
+// Roles (320 threads): warp 0 = TMA producer, warp 1 = tensor memory owner and MMA issuer,
+// warps 2..5 = rows of tile 0, warps 6..9 = rows of tile 1.  Every wait is bounded; on a
+// timeout the kernel raises the error flag, lets copies in flight land, frees its tensor
+// memory and returns.  An item whose key range is a split writes (m, l, O) partials in the
+// layout of the mma.sync kernel (attention_flash.cu) and `attention_combine` merges them.
+// Same formulas as the float32 kernel (attention_generic.cu; the reference computes them one
+// head and one position at a time, crates/model/src/llama.rs:220-247).
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int TC_BN = 64;       // keys per stage
+constexpr int TC_STAGES = 3;
+constexpr int TC_THREADS = 320;
+constexpr float TC_LAZY = 8.0f;  // the running maximum moves when it grows by more than this (log2 units)
+
+struct AttnTcParams {
+  __nv_bfloat16* out;
+  const int* block_table;
+  const int* q_start;   // [R + 1] first token of each request in this batch
+  const int* pos0;      // [R] cached positions before this step
+  const int* work;      // [n_work][8]: req, row0, kv_begin, kv_end, n_splits, part_slot, -, -
+  float* part_o;        // [slot][2 * tok * G][D]
+  float* part_ml;       // [slot][2 * tok * G][2]
+  int* err;
+  int ldo, page_size, page_shift, table_width;
+  int Hkv, G, tok, window;
+  float scale_log2;
+};
+
+template <int D>
+struct AttnTcConfig {
+  static constexpr int HALVES = D / 64;
+  static constexpr int Q_TILE_BYTES = HALVES * 128 * 128;       // 128 rows x 128 bytes per 64 columns
+  static constexpr int KV_HALF_BYTES = TC_BN * 128;
+  static constexpr int KV_STAGE_BYTES = HALVES * KV_HALF_BYTES;
+  static constexpr int P_TILE_BYTES = 128 * 128;                 // 128 rows x 64 keys
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + 2 * Q_TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + TC_STAGES * KV_STAGE_BYTES;
+  static constexpr int OFF_P = OFF_V + TC_STAGES * KV_STAGE_BYTES;
+  static constexpr int OFF_BARS = OFF_P + 2 * P_TILE_BYTES;
+  static constexpr int N_BARS = 1 + 4 * TC_STAGES + 6;
+  static constexpr int SMEM_BYTES = OFF_BARS + N_BARS * 8 + 1024 /*alignment slack*/;
+  static constexpr int S_COL = 0;                 // S of tile t: columns t * 64 ..
+  static constexpr int O_COL = 2 * TC_BN;         // O of tile t: columns O_COL + t * D ..
+  static constexpr int TMEM_COLS = (2 * TC_BN + 2 * D) <= 256 ? 256 : 512;
+};
+
+// MN-major shared-memory operand with the 128-byte swizzle: 64 elements along N (128 bytes)
+// x 8 along K form a 1024-byte atom; atoms follow each other along K at `sbo` bytes and along
+// N at `lbo` bytes.  This is the layout a TMA box of (64 columns, rows) leaves when the rows
+// are the K index, which is how value pages lie in the cache.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+// 32 lanes x 32 columns of 32-bit from tensor memory (thread i: lane base + i)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
+      "[%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n\t"
+      "tcgen05.wait::st.sync.aligned;" ::"r"(taddr),
+      "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+      "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+      "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+      "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+      "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+      "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+      "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+      "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const AttnTcParams p) {
+  using Cfg = AttnTcConfig<D>;
+  constexpr int HALVES = Cfg::HALVES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.y;
+  const int* wk = p.work + (size_t)blockIdx.x * 8;
+  const int req = wk[0], row0 = wk[1], kv_begin = wk[2], kv_end = wk[3], n_splits = wk[4];
+  if (n_splits == 0 || kv_end <= kv_begin) return;  // padding of a fixed-size work list (uniform for the CTA)
+  const int part = wk[5] * p.Hkv + kvh;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + Cfg::OFF_BARS;
+  const uint32_t q_full = bar_base;
+  auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar_base + 8u * (1 + TC_STAGES + s); };
+  auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * TC_STAGES + s); };
+  auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * TC_STAGES + s); };
+  auto s_ready = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + t); };
+  auto p_ready = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + 2 + t); };
+  auto o_done = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + 4 + t); };
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_kv);
+    mbar_init(q_full, 1);
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_ready(t), 1);
+      mbar_init(p_ready(t), 128);
+      mbar_init(o_done(t), 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_p = &abort_flag;
+  // a whole warp waits and decides together, so that the warp-wide instructions after the wait
+  // (tensor-memory loads, votes) are never entered by a part of it
+  auto wait_all = [&](uint32_t bar, uint32_t parity) {
+    const bool got = mbar_wait(bar, parity, abort_p);
+    return __all_sync(0xffffffffu, got) != 0;
+  };
+  pdl_wait();
+
+  const int G = p.G, tok = p.tok;
+  const int qs = p.q_start[req];
+  const int q_len = p.q_start[req + 1] - qs;
+  const int pos0 = p.pos0[req];
+  const int tok0 = row0 / G;                       // first token of the item within its request
+  const int kv0 = kv_begin & ~(TC_BN - 1);         // stages start on 64-key borders: whole pages
+  const int n_j = (kv_end - kv0 + TC_BN - 1) / TC_BN;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * HALVES * tok * G * 128);
+      for (int t = 0; t < 2; ++t)
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_3d(smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES + h * 128 * 128, &map_q, q_full, h * 64, kvh * G,
+                      qs + tok0 + t * tok);
+      const int ps = p.page_size;
+      const int pages_per_stage = TC_BN / ps;
+      const int* bt = p.block_table + (size_t)req * p.table_width;
+      for (int j = 0; j < n_j; ++j) {
+        const int s = j % TC_STAGES;
+        const uint32_t parity = ((j / TC_STAGES) & 1) ^ 1;
+        const int lp0 = (kv0 + j * TC_BN) >> p.page_shift;
+        if (!mbar_wait(k_empty(s), parity, abort_p)) {
+          abort_flag = 1;
+          atomicExch(p.err, 20);
+          break;
+        }
+        mbar_expect_tx(k_full(s), Cfg::KV_STAGE_BYTES);
+        for (int i = 0; i < pages_per_stage; ++i) {
+          const int lp = lp0 + i;
+          const int page = lp < p.table_width ? bt[lp] : -1;  // a missing page reads as zeros (masked keys)
+          const int y = ((page < 0 ? -1 : page) * 2 * p.Hkv + kvh) * ps;
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_2d(smem_base + Cfg::OFF_K + s * Cfg::KV_STAGE_BYTES + h * Cfg::KV_HALF_BYTES + i * ps * 128, &map_kv,
+                        k_full(s), h * 64, y);
+        }
+        if (!mbar_wait(v_empty(s), parity, abort_p)) {
+          abort_flag = 1;
+          atomicExch(p.err, 21);
+          break;
+        }
+        mbar_expect_tx(v_full(s), Cfg::KV_STAGE_BYTES);
+        for (int i = 0; i < pages_per_stage; ++i) {
+          const int lp = lp0 + i;
+          const int page = lp < p.table_width ? bt[lp] : -1;
+          const int y = (((page < 0 ? -1 : page) * 2 + (page < 0 ? 0 : 1)) * p.Hkv + kvh) * ps;
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_2d(smem_base + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES + h * Cfg::KV_HALF_BYTES + i * ps * 128, &map_kv,
+                        v_full(s), h * 64, y);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    const uint32_t idesc_qk = umma_idesc_bf16(128, TC_BN);
+    const uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B (values) is MN-major
+    auto issue_qk = [&](int t, int s) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int h = kk >> 2, in = kk & 3;
+        const uint64_t a = umma_desc_k_sw128(smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES + h * 128 * 128) + (uint64_t)(in * 2);
+        const uint64_t b = umma_desc_k_sw128(smem_base + Cfg::OFF_K + s * Cfg::KV_STAGE_BYTES + h * Cfg::KV_HALF_BYTES) + (uint64_t)(in * 2);
+        umma_bf16(tmem_base + Cfg::S_COL + t * TC_BN, a, b, idesc_qk, kk > 0);
+      }
+    };
+    auto issue_pv = [&](int t, int s, bool accumulate) {
+#pragma unroll
+      for (int kk = 0; kk < TC_BN / 16; ++kk) {
+        const uint64_t a = umma_desc_k_sw128(smem_base + Cfg::OFF_P + t * Cfg::P_TILE_BYTES) + (uint64_t)(kk * 2);
+        const uint64_t b = umma_desc_mn_sw128(smem_base + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES + kk * 16 * 128,
+                                              Cfg::KV_HALF_BYTES, 1024);
+        umma_bf16(tmem_base + Cfg::O_COL + t * D, a, b, idesc_pv, accumulate || kk > 0);
+      }
+    };
+    bool ok = wait_all(q_full, 0) && wait_all(k_full(0), 0);
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0) atomicExch(p.err, 22);
+    } else {
+      tc_fence_after();
+      if (lane == 0) {
+        issue_qk(0, 0);
+        umma_commit(s_ready(0));
+        issue_qk(1, 0);
+        umma_commit(s_ready(1));
+        umma_commit(k_empty(0));
+      }
+      __syncwarp();
+    }
+    for (int j = 0; ok && j < n_j; ++j) {
+      const int s = j % TC_STAGES;
+      const bool last = j + 1 == n_j;
+      const int s2 = (j + 1) % TC_STAGES;
+      ok = wait_all(v_full(s), (j / TC_STAGES) & 1);
+      if (ok && !last) ok = wait_all(k_full(s2), ((j + 1) / TC_STAGES) & 1);
+      if (!ok) {
+        abort_flag = 1;
+        if (lane == 0) atomicExch(p.err, 23);
+        break;
+      }
+      if (last) {
+        // Rows of the last stage past the key range may never have been written (or hold another
+        // request's values): a zero weight times a stray NaN would still be a NaN, so they are cleared.
+        const int first_bad = kv_end - (kv0 + j * TC_BN);
+        if (first_bad < TC_BN) {
+          uint8_t* v = smem + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES;
+          const int n16 = (TC_BN - first_bad) * 8;  // 16-byte pieces per 64-column half
+          for (int h = 0; h < HALVES; ++h)
+            for (int i = lane; i < n16; i += 32)
+              *reinterpret_cast<uint4*>(v + h * Cfg::KV_HALF_BYTES + first_bad * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+          fence_proxy_async();
+        }
+        __syncwarp();
+      }
+      for (int t = 0; t < 2 && ok; ++t) {
+        ok = wait_all(p_ready(t), j & 1);
+        if (!ok) {
+          abort_flag = 1;
+          if (lane == 0) atomicExch(p.err, 24);
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          issue_pv(t, s, j > 0);
+          if (t == 1) umma_commit(v_empty(s));
+          if (last) umma_commit(o_done(t));
+          if (!last) {
+            issue_qk(t, s2);
+            umma_commit(s_ready(t));
+            if (t == 1) umma_commit(k_empty(s2));
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax and output: one thread per row
+    const int t = (warp - 2) >> 2;            // row tile of this warp
+    const int quarter = warp & 3;             // the tensor-memory lanes this warp may touch
+    const int r = quarter * 32 + lane;        // row of the tile
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int tok_in_req = tok0 + t * tok + r / G;
+    const bool row_valid = r < tok * G && tok_in_req < q_len;
+    const int qpos = pos0 + tok_in_req;
+    // the tile's rows see keys up to qpos_min without a mask, none beyond qpos_max
+    const int tile_first = tok0 + t * tok;
+    const int qpos_min = pos0 + tile_first;
+    const int qpos_max = pos0 + min(q_len - 1, tile_first + tok - 1);
+    const bool tile_full = tok * G == 128 && tile_first + tok <= q_len;  // every row of the tile exists
+    uint8_t* p_tile = smem + Cfg::OFF_P + t * Cfg::P_TILE_BYTES;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_j; ++j) {
+      ok = wait_all(s_ready(t), j & 1);
+      if (!ok) {
+        abort_flag = 1;
+        if (lane == 0) atomicExch(p.err, 25);
+        break;
+      }
+      tc_fence_after();
+      float s[TC_BN];
+      tmem_ld32(lane_addr + Cfg::S_COL + t * TC_BN, &s[0]);
+      tmem_ld32(lane_addr + Cfg::S_COL + t * TC_BN + 32, &s[32]);
+      const int key0 = kv0 + j * TC_BN;
+      const bool unmasked = tile_full && key0 + TC_BN - 1 <= qpos_min && key0 >= kv_begin && key0 + TC_BN <= kv_end &&
+                            (p.window == 0 || key0 > qpos_max - p.window);
+      if (!unmasked) {
+        const int hi = row_valid ? min(qpos, kv_end - 1) : -1;                                  // last visible key
+        const int lo = max(kv_begin, p.window > 0 ? qpos - p.window + 1 : 0);                   // first visible key
+#pragma unroll
+        for (int c = 0; c < TC_BN; ++c) {
+          const int key = key0 + c;
+          if (key > hi || key < lo) s[c] = -INFINITY;
+        }
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int c = 1; c < TC_BN; ++c) mx = fmaxf(mx, s[c]);
+      const float cand = fmaxf(m_run, mx * p.scale_log2);
+      const bool grow = cand > m_run + TC_LAZY;   // also true for the first finite maximum
+      if (__any_sync(0xffffffffu, grow)) {
+        const float f = m_run == -INFINITY ? 0.f : fast_exp2(m_run - cand);  // cand is finite where m_run is
+        l_run *= f;
+        if (j > 0) {  // O of the earlier stages is complete (S of this stage was committed after it)
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            float o[32];
+            tmem_ld32(lane_addr + Cfg::O_COL + t * D + c0, o);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] *= f;
+            tmem_st32(lane_addr + Cfg::O_COL + t * D + c0, o);
+          }
+        }
+        m_run = cand;
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      const uint32_t row_base = smem_u32(p_tile) + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < TC_BN / 8; ++ch) {
+        float e[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) e[c] = fast_exp2(fmaf(s[ch * 8 + c], p.scale_log2, -m_use));
+        l0 += e[0] + e[4];
+        l1 += e[1] + e[5];
+        l2 += e[2] + e[6];
+        l3 += e[3] + e[7];
+        const uint32_t dst = row_base + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack2_bf16(e[0], e[1])), "r"(pack2_bf16(e[2], e[3])),
+                     "r"(pack2_bf16(e[4], e[5])), "r"(pack2_bf16(e[6], e[7]))
+                     : "memory");
+      }
+      l_run += (l0 + l1) + (l2 + l3);
+      fence_proxy_async();   // P is read by the matrix unit
+      tc_fence_before();     // and this thread's tensor-memory accesses precede the products that follow
+      mbar_arrive(p_ready(t));
+    }
+    if (ok) ok = wait_all(o_done(t), 0);
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0) atomicExch(p.err, 26);
+    } else {
+      tc_fence_after();
+      const bool whole = n_splits == 1;
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      __nv_bfloat16* orow = p.out + (size_t)(qs + tok_in_req) * p.ldo + (size_t)(kvh * G + r % G) * D;
+      const size_t prow = (size_t)part * (2 * tok * G) + t * tok * G + r;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        float o[32];
+        tmem_ld32(lane_addr + Cfg::O_COL + t * D + c0, o);  // every lane takes part in the load
+        if (!row_valid) continue;
+        if (whole) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 v;
+            v.x = pack2_bf16(o[c] * inv, o[c + 1] * inv);
+            v.y = pack2_bf16(o[c + 2] * inv, o[c + 3] * inv);
+            v.z = pack2_bf16(o[c + 4] * inv, o[c + 5] * inv);
+            v.w = pack2_bf16(o[c + 6] * inv, o[c + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            *reinterpret_cast<float4*>(p.part_o + prow * D + c0 + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+        }
+      }
+      if (!whole && row_valid) {
+        p.part_ml[prow * 2] = m_run;
+        p.part_ml[prow * 2 + 1] = l_run;
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) {
+    // let TMA copies that were already issued land before the CTA's shared memory goes away
+    const long long t0c = clock64();
+    while (clock64() - t0c < 2000000LL) {
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+struct AttnMapKey {
+  const void* ptr;
+  long long a, b, c;
+  int kind;
+  bool operator==(const AttnMapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c && kind == o.kind; }
+};
+struct AttnMapKeyHash {
+  size_t operator()(const AttnMapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    h = h * 1000003u ^ std::hash<long long>()(k.a);
+    h = h * 1000003u ^ std::hash<long long>()(k.b);
+    h = h * 1000003u ^ std::hash<long long>()(k.c * 2 + k.kind);
+    return h;
+  }
+};
+std::mutex g_map_mu;
+std::unordered_map<AttnMapKey, CUtensorMap, AttnMapKeyHash> g_maps;
+
+bool lookup_map(const AttnMapKey& key, CUtensorMap* out) {
+  std::lock_guard<std::mutex> g(g_map_mu);
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) return false;
+  *out = it->second;
+  return true;
+}
+void keep_map(const AttnMapKey& key, const CUtensorMap& m) {
+  std::lock_guard<std::mutex> g(g_map_mu);
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps.emplace(key, m);
+}
+
+// Queries [rows, ld] bfloat16 seen as (D, Hq, rows); a box is 64 columns x G heads x tok tokens.
+int query_map(const void* q, long long rows, int ldq, int Hq, int D, int G, int tok, CUtensorMap* out) {
+  AttnMapKey key{q, rows, (long long)ldq * 4096 + D, (long long)Hq * 65536 + G * 256 + tok, 0};
+  if (lookup_map(key, out)) return 0;
+  EncodeTiledFn fn = encode_fn();
+  FERRUM_CHECK_ARG(fn != nullptr, "attention_tc: the driver does not export cuTensorMapEncodeTiled");
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Hq, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)ldq * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)tok};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FERRUM_CHECK_ARG(r == CUDA_SUCCESS, "attention_tc: encoding the query map failed with code %d", (int)r);
+  keep_map(key, *out);
+  return 0;
+}
+
+// The cache plane [pages, 2, Hkv, page_size, D] seen as rows of D; a box is 64 columns x one page of one head.
+int cache_map(const void* plane, long long n_pages, int Hkv, int page_size, int D, CUtensorMap* out) {
+  AttnMapKey key{plane, n_pages, (long long)Hkv * 65536 + page_size, D, 1};
+  if (lookup_map(key, out)) return 0;
+  EncodeTiledFn fn = encode_fn();
+  FERRUM_CHECK_ARG(fn != nullptr, "attention_tc: the driver does not export cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)(n_pages * 2 * Hkv * page_size)};
+  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(plane), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FERRUM_CHECK_ARG(r == CUDA_SUCCESS, "attention_tc: encoding the cache map failed with code %d", (int)r);
+  keep_map(key, *out);
+  return 0;
+}
+
+template <int D>
+int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const AttnTcParams& p, int n_work, cudaStream_t stream) {
+  using Cfg = AttnTcConfig<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    FERRUM_CHECK_ARG(e == cudaSuccess, "attention_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  launch_kernel(attention_tc_kernel<D>, dim3(n_work, p.Hkv), dim3(TC_THREADS), Cfg::SMEM_BYTES, stream, mq, mkv, p);
+  FERRUM_CHECK_LAUNCH("attention_tc");
+  return 0;
+}
+
+}  // namespace
+
+// Tokens per row tile for a group of G query heads per KV head, or 0 when this kernel does not
+// take the shape (head sizes 64 and 128; pages of 8, 16, 32 or 64 keys; at most 128 heads per group).
+FERRUM_API int ferrum_attention_tc_tokens(int D, int G, int page_size) {
+  if (D != 64 && D != 128) return 0;
+  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return 0;
+  if (G < 1 || G > 128) return 0;
+  return 128 / G;
+}
+
+// Items of 2 * tokens * G rows (see ferrum_attention_tc_tokens) in the work-list format of
+// ferrum_attention_flash; grid (n_work, Hkv).  q has q_rows rows of ldq elements (the buffer's
+// capacity, of which the batch may use fewer); the plane has n_pages pages.
+FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, void* out, int ldo, const void* kv_plane,
+                                   long long page_stride, long long n_pages, int page_size, const int* block_table,
+                                   int table_width, const int* q_start, const int* pos0, const int* work, int n_work,
+                                   float* part_o, float* part_ml, int Hq, int Hkv, int D, float scale, int window,
+                                   int* err_flag, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_tc: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
+  const int G = Hq / Hkv;
+  const int tok = ferrum_attention_tc_tokens(D, G, page_size);
+  FERRUM_CHECK_ARG(tok > 0, "attention_tc: head size %d, group %d, page size %d is not built; use attention_flash", D, G, page_size);
+  FERRUM_CHECK_ARG(err_flag != nullptr, "attention_tc: the error flag is required");
+  FERRUM_CHECK_ARG(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                   ((uintptr_t)kv_plane & 15) == 0, "attention_tc: operands must be 16-byte aligned");
+  FERRUM_CHECK_ARG(page_stride == 2LL * Hkv * page_size * D, "attention_tc: the plane's pages must be dense "
+                   "(stride %lld, expected %lld)", page_stride, 2LL * Hkv * page_size * D);
+  FERRUM_CHECK_ARG(n_pages > 0 && n_pages * 2 * Hkv * page_size < (1LL << 31), "attention_tc: %lld pages are more than the "
+                   "row index of the cache map holds", n_pages);
+  FERRUM_CHECK_ARG(table_width > 0 && window >= 0 && n_work >= 0 && q_rows > 0, "attention_tc: bad arguments");
+  if (n_work == 0) return 0;
+  AttnTcParams p;
+  p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.q_start = q_start; p.pos0 = pos0; p.work = work;
+  p.part_o = part_o; p.part_ml = part_ml; p.err = err_flag;
+  p.ldo = ldo; p.page_size = page_size; p.table_width = table_width;
+  p.page_shift = 0;
+  while ((1 << p.page_shift) < page_size) ++p.page_shift;
+  p.Hkv = Hkv; p.G = G; p.tok = tok; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  CUtensorMap mq, mkv;
+  if (int r = query_map(q, q_rows, ldq, Hq, D, G, tok, &mq)) return r;
+  if (int r = cache_map(kv_plane, n_pages, Hkv, page_size, D, &mkv)) return r;
+  if (D == 64) return launch_attention_tc<64>(mq, mkv, p, n_work, stream);
+  return launch_attention_tc<128>(mq, mkv, p, n_work, stream);
+}

@@ -6,8 +6,9 @@ still fills the GPU.  The plan depends on the batch (lengths, positions), on the
 G = Hq / Hkv and on the window, not on the layer, so it is built once per step and used by
 every layer with the same (G, window).
 
-Requests with at most 16 rows (decoded tokens) go to the 16-row kernel, the others to the
-64-row kernel; each class has its own work list.  A work item is
+Requests with at most 16 rows (decoded tokens) go to the 16-row kernel, requests with at
+least TC_MIN_ROWS rows to the tcgen05 kernel where it takes the layer's shape (its items are
+pairs of 128-row tiles), the others to the 64-row kernel; each class has its own work list.  A work item is
 [request, first row, key begin, key end, number of splits, partial slot, KV head, 0]; an item
 with zero splits is padding.  The 64-row class runs a grid of (items, KV heads).  The 16-row
 class runs a balanced list: every CTA slot of the GPU gets an equal share of all (request,
@@ -30,6 +31,8 @@ import torch
 N_SMS = 148
 CLASSES = (16, 64)
 MIN_SPLIT_KEYS = {16: 256, 64: 1024}
+TC_MIN_ROWS = 128           # a request with fewer rows would leave the 128-row tiles mostly empty
+TC_MIN_SPLIT_KEYS = 2048
 
 
 CTA_SLOTS = 3 * N_SMS      # the 16-row kernel keeps three CTAs on an SM (registers and shared memory)
@@ -55,12 +58,13 @@ def _tiles(q_len, pos0, G, window, bm, sel):
     return n_tiles, req_of_tile, row0, lo, hi
 
 
-def _grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start):
+def _grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start, slots=CTA_SLOTS, min_split=None, kind="flash"):
     """One item per (tile, key split); the kernel runs it once per KV head."""
     n_tiles, req_of_tile, row0, lo, hi = _tiles(q_len, pos0, G, window, bm, sel)
     length = hi - lo
     # about one item per CTA slot of the GPU, never splits shorter than the minimum
-    chunk = int(max(MIN_SPLIT_KEYS[bm], -(-int(length.sum()) // max(1, CTA_SLOTS // Hkv))))
+    min_split = MIN_SPLIT_KEYS[bm] if min_split is None else min_split
+    chunk = int(max(min_split, -(-int(length.sum()) // max(1, slots // Hkv))))
     chunk = (chunk + 63) // 64 * 64
     n_splits = np.maximum(1, (length + chunk - 1) // chunk)
     T = int(n_splits.sum())
@@ -88,7 +92,7 @@ def _grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start):
     split_reqs = np.unique(req_of_tile[n_splits > 1])
     comb = np.concatenate([np.arange(q_start[r], q_start[r + 1]) for r in split_reqs]).astype(np.int32) \
         if len(split_reqs) else np.zeros(0, dtype=np.int32)
-    return {"bm": bm, "work": work[order].reshape(-1), "n_work": T, "n_slots": int(is_split.sum()) * Hkv,
+    return {"bm": bm, "kind": kind, "work": work[order].reshape(-1), "n_work": T, "n_slots": int(is_split.sum()) * Hkv,
             "tile_info": info.reshape(-1), "req_tile0": req_tile0, "comb": comb,
             "cta_items": np.zeros(0, dtype=np.int32), "n_ctas": 0}
 
@@ -132,32 +136,38 @@ def _balanced_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start):
     split_reqs = np.unique(r_idx[is_split])
     comb = np.concatenate([np.arange(q_start[sel[r]], q_start[sel[r] + 1]) for r in split_reqs]).astype(np.int32) \
         if len(split_reqs) else np.zeros(0, dtype=np.int32)
-    return {"bm": bm, "work": work.reshape(-1), "n_work": n_seg, "n_slots": int(is_split.sum()),
+    return {"bm": bm, "kind": "flash", "work": work.reshape(-1), "n_work": n_seg, "n_slots": int(is_split.sum()),
             "tile_info": info.reshape(-1), "req_tile0": req_tile0, "comb": comb, "cta_items": cta_items, "n_ctas": P}
 
 
-def build_host(q_len, pos0, G, window, Hkv):
-    """numpy description of both classes: None or a dict of int32 arrays per class."""
+def build_host(q_len, pos0, G, window, Hkv, tc_tokens=0):
+    """numpy description of the classes (16 rows, 64 rows, tcgen05 tile pairs): None or a dict
+    of int32 arrays per class.  tc_tokens: tokens per 128-row tile of the tcgen05 kernel, 0
+    where it does not take the layer's shape."""
     q_len = np.asarray(q_len, dtype=np.int64)
     pos0 = np.asarray(pos0, dtype=np.int64)
     R = len(q_len)
     rows = q_len * G
     q_start = np.concatenate([[0], np.cumsum(q_len)])
+    to_tc = (rows >= TC_MIN_ROWS) if tc_tokens > 0 else np.zeros(R, dtype=bool)
     out = []
     for bm in CLASSES:
-        sel = np.nonzero((rows <= 16) if bm == 16 else (rows > 16))[0]
+        sel = np.nonzero((rows <= 16) if bm == 16 else ((rows > 16) & ~to_tc))[0]
         if len(sel) == 0:
             out.append(None)
         elif bm == 16:
             out.append(_balanced_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start))
         else:
             out.append(_grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start))
+    sel = np.nonzero(to_tc)[0]
+    out.append(_grid_class(q_len, pos0, G, window, Hkv, 2 * tc_tokens * G, sel, R, q_start, slots=N_SMS,
+                           min_split=TC_MIN_SPLIT_KEYS, kind="tc") if len(sel) else None)
     return out
 
 
 @dataclass
 class ClassPlan:
-    bm: int
+    bm: int                                     # rows per item
     n_work: int = 0                             # grid size (includes padding items)
     work: Optional[torch.Tensor] = None        # int32 [n_work * 8]
     n_slots: int = 0                            # partial slots to provide
@@ -167,6 +177,7 @@ class ClassPlan:
     n_comb: int = 0
     cta_items: Optional[torch.Tensor] = None    # balanced list: first item of every CTA (+ end)
     n_ctas: int = 0
+    kind: str = "flash"                         # "flash": the mma.sync kernel; "tc": the tcgen05 kernel
 
 
 class AttentionPlans:
@@ -218,24 +229,24 @@ class AttentionPlans:
         cp.cta_items, cp.n_ctas = dev[o3:total], CTA_SLOTS if fixed else d.n_ctas
         # the merge visits every token; those whose keys were not split return at once
         cp.comb_tokens, cp.n_comb = None, (ctx.n_tokens if (fixed or d.n_slots) else 0)
-        return [cp, None]
+        return [cp, None, None]
 
-    def get(self, ctx, G, window, Hkv, fixed=False) -> List[Optional[ClassPlan]]:
+    def get(self, ctx, G, window, Hkv, fixed=False, tc_tokens=0) -> List[Optional[ClassPlan]]:
         """fixed=True (a decode-only batch under a CUDA graph): the 16-row list is padded to
         `item_capacity` items and the merge visits every token, so that the launch shapes
         depend on the number of requests only."""
-        key = (G, window, Hkv)
+        key = (G, window, Hkv, tc_tokens)
         if key in self._plans:
             return self._plans[key]
         if max(ctx.h_q_len) * G <= 16:
             plans = self._decode_plans(ctx, key, G, window, Hkv, fixed)     # native fast path
             self._plans[key] = plans
             return plans
-        host = build_host(ctx.h_q_len, ctx.h_pos0, G, window, Hkv)
+        host = build_host(ctx.h_q_len, ctx.h_pos0, G, window, Hkv, tc_tokens)
         R = len(ctx.h_q_len)
         if fixed:
             h = host[0]
-            if h is None or host[1] is not None:
+            if h is None or host[1] is not None or host[2] is not None:
                 raise ValueError("a fixed-shape plan needs a batch of decoded tokens only")
             cap = item_capacity(R, Hkv)
             if h["n_work"] > cap or h["n_ctas"] > CTA_SLOTS:
@@ -268,6 +279,7 @@ class AttentionPlans:
                 views.append(dev[o:o + h[name].size])
                 o += h[name].size
             cp = ClassPlan(h["bm"], h["n_work"], views[0], h["n_slots"])
+            cp.kind = h["kind"]
             cp.tile_info, cp.req_tile0 = views[1], views[2]
             if h["n_ctas"]:
                 cp.cta_items, cp.n_ctas = views[4], h["n_ctas"]

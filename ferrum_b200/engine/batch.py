@@ -179,9 +179,10 @@ class StepContext:
         self._attn_plans.reset()
         self.pending_residual = None
 
-    def attention_plans(self, G, window, Hkv):
-        """The step's work lists for the tensor-core attention kernel (built on first use)."""
-        return self._attn_plans.get(self, G, window, Hkv, fixed=self.fixed_shapes)
+    def attention_plans(self, G, window, Hkv, tc_tokens=0):
+        """The step's work lists for the tensor-core attention kernels (built on first use).
+        tc_tokens: tokens per row tile of the tcgen05 kernel, 0 where it does not apply."""
+        return self._attn_plans.get(self, G, window, Hkv, fixed=self.fixed_shapes, tc_tokens=tc_tokens)
 
     # ------------------------------------------------------------------ pending residual sum
     def take_pending_residual(self, h):

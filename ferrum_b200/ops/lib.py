@@ -286,6 +286,29 @@ def attention_flash(q, out, kv_plane, page_stride, page_size, block_table, q_sta
                                         c_float(scale), c_int(window), c_int(bm), _stream()), "attention_flash")
 
 
+def attention_tc_tokens(D, G, page_size, kv_plane=None, page_stride=0):
+    """Tokens per 128-row tile of the tcgen05 attention kernel for this head size, group size
+    and page size; 0 where the kernel does not apply (other sizes, float32, pages that are
+    not dense in the plane)."""
+    if kv_plane is not None and (kv_plane.dtype != torch.bfloat16 or kv_plane.dim() != 5 or
+                                 page_stride != kv_plane[0].numel()):
+        return 0
+    return int(lib().ferrum_attention_tc_tokens(c_int(D), c_int(G), c_int(page_size)))
+
+
+def attention_tc(q, out, kv_plane, page_stride, page_size, block_table, q_start, pos0, work, n_work, part_o, part_ml,
+                 Hq, Hkv, D, scale, window, err):
+    """tcgen05 attention over work items of 2 * attention_tc_tokens * G rows (prompt portions)."""
+    _need(q, torch.bfloat16, "q", 2); _need(out, torch.bfloat16, "out", 2); _need(kv_plane, torch.bfloat16, "kv_plane")
+    _need(block_table, torch.int32, "block_table", 2); _need(work, torch.int32, "work", 1)
+    _check(lib().ferrum_attention_tc(_ptr(q), c_int(q.stride(0)), c_longlong(q.shape[0]), _ptr(out), c_int(out.stride(0)),
+                                     _ptr(kv_plane), c_longlong(page_stride), c_longlong(kv_plane.shape[0]),
+                                     c_int(page_size), _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),
+                                     _ptr(pos0), _ptr(work), c_int(n_work), _ptr(part_o), _ptr(part_ml), c_int(Hq),
+                                     c_int(Hkv), c_int(D), c_float(scale), c_int(window), _ptr(err), _stream()),
+           "attention_tc")
+
+
 def attention_combine(out, part_o, part_ml, q_start, req_of_token, req_tile0, tile_info, token_list, n_tokens, Hq, Hkv,
                       D, bm):
     """Merges the key-range splits written by attention_flash into `out`."""

@@ -28,6 +28,7 @@ class PagedAttention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.w_q_weight = self.w_k_weight = self.w_v_weight = self.w_output_weight = None
         self.w_qkv = None
+        self._tc_tokens = {}     # cache shape -> tokens per tile of the tcgen05 kernel (0: not applicable)
 
     def param_specs(self):
         q, kv = self.Hq * self.D, self.Hkv * self.D
@@ -67,16 +68,25 @@ class PagedAttention(Mixer):
         """Tensor-core path: one launch per row-tile class of the step's plan, plus a merge
         launch where key ranges were split."""
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
-        for plan in ctx.attention_plans(Hq // Hkv, self.window, Hkv):
+        shape_key = (cache.page_size, cache.page_stride, cache.plane.dtype, cache.plane.dim())
+        tc_tokens = self._tc_tokens.get(shape_key)
+        if tc_tokens is None:
+            tc_tokens = self._tc_tokens[shape_key] = ops.attention_tc_tokens(D, Hq // Hkv, cache.page_size, cache.plane,
+                                                                             cache.page_stride)
+        for plan in ctx.attention_plans(Hq // Hkv, self.window, Hkv, tc_tokens):
             if plan is None:
                 continue
             part_o = part_ml = None
             if plan.n_slots:
                 part_o = ctx.buf("attn_part_o", (plan.n_slots * plan.bm * D,), torch.float32)
                 part_ml = ctx.buf("attn_part_ml", (plan.n_slots * plan.bm * 2,), torch.float32)
-            ops.attention_flash(qkv, out, cache.plane, cache.page_stride, cache.page_size, table, ctx.q_start,
-                                ctx.pos0, plan.work, plan.n_work, part_o, part_ml, Hq, Hkv, D, self.scale,
-                                self.window, plan.bm, plan.cta_items, plan.n_ctas)
+            if plan.kind == "tc":
+                ops.attention_tc(qkv, out, cache.plane, cache.page_stride, cache.page_size, table, ctx.q_start, ctx.pos0,
+                                 plan.work, plan.n_work, part_o, part_ml, Hq, Hkv, D, self.scale, self.window, ctx.err)
+            else:
+                ops.attention_flash(qkv, out, cache.plane, cache.page_stride, cache.page_size, table, ctx.q_start,
+                                    ctx.pos0, plan.work, plan.n_work, part_o, part_ml, Hq, Hkv, D, self.scale,
+                                    self.window, plan.bm, plan.cta_items, plan.n_ctas)
             if plan.n_comb:
                 ops.attention_combine(out, part_o, part_ml, ctx.q_start, ctx.req_of_token, plan.req_tile0,
                                       plan.tile_info, plan.comb_tokens, plan.n_comb, Hq, Hkv, D, plan.bm)

@@ -255,9 +255,9 @@ def test_attention_finds_one_far_key(ops, dtype, far_key):
     assert np.abs(got - ref).max() <= (1e-4 if dtype == torch.float32 else 2e-2)
 
 
-def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window):
+def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window, use_tc=False, counts=None):
     """Drive the tensor-core attention the way the attention part does: plan, launch per
-    row-tile class, merge splits."""
+    row-tile class (the tcgen05 kernel for its class when use_tc), merge splits."""
     from ferrum_b200.engine.attn_plan import build_host
     T = sum(qlens)
     out = torch.full((T, Hq * D), float("nan"), device="cuda", dtype=torch.bfloat16)
@@ -266,14 +266,25 @@ def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window):
     req = np.repeat(np.arange(len(lens)), qlens).astype(np.int32)
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.int32).cuda()
     n_split_items = 0
-    for h in build_host(qlens, pos0, Hq // Hkv, window, Hkv):
+    tc_tokens = ops.attention_tc_tokens(D, Hq // Hkv, ps, plane, plane.stride(0)) if use_tc else 0
+    assert tc_tokens > 0 or not use_tc
+    e = err_flag()
+    for h in build_host(qlens, pos0, Hq // Hkv, window, Hkv, tc_tokens):
         if h is None:
             continue
         part_o = torch.empty(max(1, h["n_slots"] * h["bm"] * D), device="cuda")
         part_ml = torch.empty(max(1, h["n_slots"] * h["bm"] * 2), device="cuda")
-        ops.attention_flash(q, out, plane, plane.stride(0), ps, table, dev(qs), dev(pos0), dev(h["work"]), h["n_work"],
-                            part_o, part_ml, Hq, Hkv, D, 1.0 / math.sqrt(D), window, h["bm"],
-                            dev(h["cta_items"]) if h["n_ctas"] else None, h["n_ctas"])
+        if counts is not None:
+            counts[h["kind"]] = counts.get(h["kind"], 0) + h["n_work"]
+            counts["split_" + h["kind"]] = counts.get("split_" + h["kind"], 0) + h["n_slots"]
+        if h["kind"] == "tc":
+            ops.attention_tc(q, out, plane, plane.stride(0), ps, table, dev(qs), dev(pos0), dev(h["work"]), h["n_work"],
+                             part_o, part_ml, Hq, Hkv, D, 1.0 / math.sqrt(D), window, e)
+            assert e.item() == 0
+        else:
+            ops.attention_flash(q, out, plane, plane.stride(0), ps, table, dev(qs), dev(pos0), dev(h["work"]), h["n_work"],
+                                part_o, part_ml, Hq, Hkv, D, 1.0 / math.sqrt(D), window, h["bm"],
+                                dev(h["cta_items"]) if h["n_ctas"] else None, h["n_ctas"])
         if h["comb"].size:
             ops.attention_combine(out, part_o, part_ml, dev(qs), dev(req), dev(h["req_tile0"]), dev(h["tile_info"]),
                                   dev(h["comb"]), int(h["comb"].size), Hq, Hkv, D, h["bm"])
@@ -303,6 +314,65 @@ def test_attention_flash(ops, Hq, Hkv, D, ps, window):
         got = out[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
         assert np.abs(got - ref).max() <= 1.5e-2, (r, np.abs(got - ref).max())
         t0 += ql
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(4, 2, 64, 16, 0), (6, 2, 64, 8, 0), (8, 1, 128, 16, 0), (32, 8, 128, 16, 0),
+                                                (3, 3, 128, 32, 0), (4, 2, 64, 64, 21), (8, 2, 128, 16, 300),
+                                                (10, 2, 128, 16, 0), (14, 2, 64, 16, 90)])
+def test_attention_tc(ops, Hq, Hkv, D, ps, window):
+    """The tcgen05 kernel on prompt portions: a whole prompt, a late portion of a long request
+    (its key range is split), a portion that ends inside a tile, beside decoded tokens that
+    stay on the other kernel.  Groups that do not divide 128 leave padding rows in the tiles."""
+    lens = [137, 5400, 65, 1, 700, 333]
+    qlens = [137, 130, 1, 1, 450, 200]
+    plane, table, ks, vs = paged_setup(lens, Hkv, D, ps, torch.bfloat16, 27)
+    g = torch.Generator(device="cuda").manual_seed(28)
+    T = sum(qlens)
+    q = torch.randn(T, Hq * D, device="cuda", generator=g).bfloat16()
+    counts = {}
+    out, _ = run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window, use_tc=True, counts=counts)
+    assert counts.get("tc", 0) > 0 and (window > 0 or counts.get("split_tc", 0) > 0), counts
+    t0 = 0
+    for r, (n, ql) in enumerate(zip(lens, qlens)):
+        qfull = np.zeros((n, Hq, D))
+        qfull[n - ql:] = q[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
+        ref = P.attention(qfull, ks[r].double().cpu().numpy(), vs[r].double().cpu().numpy(), window)[n - ql:]
+        got = out[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
+        assert np.isfinite(got).all(), r
+        assert np.abs(got - ref).max() <= 1.5e-2, (r, np.abs(got - ref).max())
+        t0 += ql
+
+
+@pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 1023, 1024, 2047, 2048, 2999])
+def test_attention_tc_finds_one_far_key(ops, far_key):
+    """One strongly matching key among 3000, at stage, page and split edges, for a prompt portion
+    on the tcgen05 kernel."""
+    Hq = Hkv = 2; D = 64; ps = 16; n = 3000; qlen = 200
+    plane, table, ks, vs = paged_setup([n], Hkv, D, ps, torch.bfloat16, 19)
+    kq = ks[0][far_key].float()
+    qrow = (kq * (40.0 * math.sqrt(D) / kq.pow(2).sum(-1, keepdim=True))).reshape(1, Hq * D)
+    q = qrow.repeat(qlen, 1).bfloat16()
+    out, _ = run_flash(ops, q, [n], [qlen], table, plane, ps, Hq, Hkv, D, 0, use_tc=True)
+    want = vs[0][far_key].float().reshape(1, Hq * D)
+    sees = max(0, far_key - (n - qlen))          # rows before this one come before the key
+    assert (out[sees:].float() - want).abs().max().item() <= 2e-2
+
+
+def test_attention_tc_ignores_what_lies_past_the_keys(ops):
+    """Rows of the last page beyond the request's length hold NaN: no weight may touch them."""
+    Hq, Hkv, D, ps = 4, 2, 128, 16
+    lens, qlens = [200], [200]
+    plane, table, ks, vs = paged_setup(lens, Hkv, D, ps, torch.bfloat16, 33)
+    last_page = table[0, (lens[0] - 1) // ps].item()
+    plane[last_page, :, :, lens[0] % ps:] = float("nan")
+    g = torch.Generator(device="cuda").manual_seed(34)
+    q = torch.randn(200, Hq * D, device="cuda", generator=g).bfloat16()
+    out, _ = run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, 0, use_tc=True)
+    qfull = q.double().cpu().numpy().reshape(200, Hq, D)
+    ref = P.attention(qfull, ks[0].double().cpu().numpy(), vs[0].double().cpu().numpy(), 0)
+    got = out.double().cpu().numpy().reshape(200, Hq, D)
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 1.5e-2
 
 
 @pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 1023, 1024, 2999])
