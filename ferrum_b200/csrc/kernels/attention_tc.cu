@@ -11,13 +11,15 @@
 //                      maximum and sum in float32 and write P (bfloat16) to shared memory
 //   O += P V           tcgen05.mma 128 x D x 64, V as the MN-major operand straight from the
 //                      page layout, O in tensor memory
-// The two row tiles take turns on the matrix unit: while the threads of one compute P, the
-// products of the other run.  The running maximum is only moved (and O rescaled, in tensor
+// S has two buffers per row tile, so the matrix unit computes the scores of the stage after next
+// while the threads of a tile work on P: a tile's threads never wait for a product that
+// depends on their own P, and the two tiles share the matrix unit.  The running maximum is only moved (and O rescaled, in tensor
 // memory, by the row's own thread) when it grows by more than 2^8; until then P is computed
 // against the older maximum, which changes nothing in the quotient O / l.
 //
-// Roles (320 threads): warp 0 = TMA producer, warp 1 = tensor memory owner and MMA issuer,
-// warps 2..5 = rows of tile 0, warps 6..9 = rows of tile 1.  Every wait is bounded; on a
+// Roles (352 threads): warp 0 = TMA producer, warp 1 = tensor memory owner and MMA issuer of
+// tile 0, warps 2..5 = rows of tile 0, warps 6..9 = rows of tile 1, warp 10 = MMA issuer of tile
+// 1 (one issuing thread each: while one does its waits and commits, the other's products run).  Every wait is bounded; on a
 // timeout the kernel raises the error flag, lets copies in flight land, frees its tensor
 // memory and returns.  An item whose key range is a split writes (m, l, O) partials in the
 // layout of the mma.sync kernel (attention_flash.cu) and `attention_combine` merges them.
@@ -35,7 +37,7 @@ namespace {
 
 constexpr int TC_BN = 64;       // keys per stage
 constexpr int TC_STAGES = 3;
-constexpr int TC_THREADS = 320;
+constexpr int TC_THREADS = 352;
 constexpr float TC_LAZY = 8.0f;  // the running maximum moves when it grows by more than this (log2 units)
 
 struct AttnTcParams {
@@ -64,11 +66,12 @@ struct AttnTcConfig {
   static constexpr int OFF_V = OFF_K + TC_STAGES * KV_STAGE_BYTES;
   static constexpr int OFF_P = OFF_V + TC_STAGES * KV_STAGE_BYTES;
   static constexpr int OFF_BARS = OFF_P + 2 * P_TILE_BYTES;
-  static constexpr int N_BARS = 1 + 4 * TC_STAGES + 6;
+  static constexpr int N_BARS = 1 + 4 * TC_STAGES + 8;
   static constexpr int SMEM_BYTES = OFF_BARS + N_BARS * 8 + 1024 /*alignment slack*/;
-  static constexpr int S_COL = 0;                 // S of tile t: columns t * 64 ..
-  static constexpr int O_COL = 2 * TC_BN;         // O of tile t: columns O_COL + t * D ..
-  static constexpr int TMEM_COLS = (2 * TC_BN + 2 * D) <= 256 ? 256 : 512;
+  static constexpr int S_COL = 0;                 // S of tile t, buffer b: columns (2 t + b) * 64 ..
+  static constexpr int O_COL = 4 * TC_BN;         // O of tile t: columns O_COL + t * D ..
+  static constexpr int TMEM_COLS = 512;
+  static_assert(O_COL + 2 * D <= TMEM_COLS, "accumulators do not fit tensor memory");
 };
 
 // MN-major shared-memory operand with the 128-byte swizzle: 64 elements along N (128 bytes)
@@ -146,8 +149,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvh = blockIdx.y;
-  const int* wk = p.work + (size_t)blockIdx.x * 8;
+  // heads vary fastest in the grid: the work list is sorted by length, and this way the longest
+  // items of every head start first
+  const int kvh = blockIdx.x;
+  const int* wk = p.work + (size_t)blockIdx.y * 8;
   const int req = wk[0], row0 = wk[1], kv_begin = wk[2], kv_end = wk[3], n_splits = wk[4];
   if (n_splits == 0 || kv_end <= kv_begin) return;  // padding of a fixed-size work list (uniform for the CTA)
   const int part = wk[5] * p.Hkv + kvh;
@@ -159,9 +164,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   auto k_empty = [&](int s) { return bar_base + 8u * (1 + TC_STAGES + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * TC_STAGES + s); };
   auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * TC_STAGES + s); };
-  auto s_ready = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + t); };
-  auto p_ready = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + 2 + t); };
-  auto o_done = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + 4 + t); };
+  auto s_ready = [&](int t, int b) { return bar_base + 8u * (1 + 4 * TC_STAGES + 2 * t + b); };
+  auto p_ready = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + 4 + t); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + 6 + t); };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -170,14 +175,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     mbar_init(q_full, 1);
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(k_full(s), 1);
-      mbar_init(k_empty(s), 1);
+      mbar_init(k_empty(s), 2);   // one commit per issuer
       mbar_init(v_full(s), 1);
-      mbar_init(v_empty(s), 1);
+      mbar_init(v_empty(s), 2);
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(s_ready(t), 1);
+      mbar_init(s_ready(t, 0), 1);
+      mbar_init(s_ready(t, 1), 1);
       mbar_init(p_ready(t), 128);
-      mbar_init(o_done(t), 1);
+      mbar_init(pv_done(t), 1);
     }
     fence_barrier_init();
   }
@@ -208,130 +214,128 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    // Lane 0 waits and posts the byte counts; lane i fetches page i of the stage (its table
+    // entry is read one stage ahead, so that the lookups of a stage overlap instead of queueing).
     if (lane == 0) {
       mbar_expect_tx(q_full, 2 * HALVES * tok * G * 128);
       for (int t = 0; t < 2; ++t)
         for (int h = 0; h < HALVES; ++h)
           tma_load_3d(smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES + h * 128 * 128, &map_q, q_full, h * 64, kvh * G,
                       qs + tok0 + t * tok);
-      const int ps = p.page_size;
-      const int pages_per_stage = TC_BN / ps;
-      const int* bt = p.block_table + (size_t)req * p.table_width;
-      for (int j = 0; j < n_j; ++j) {
-        const int s = j % TC_STAGES;
-        const uint32_t parity = ((j / TC_STAGES) & 1) ^ 1;
-        const int lp0 = (kv0 + j * TC_BN) >> p.page_shift;
-        if (!mbar_wait(k_empty(s), parity, abort_p)) {
-          abort_flag = 1;
-          atomicExch(p.err, 20);
-          break;
-        }
-        mbar_expect_tx(k_full(s), Cfg::KV_STAGE_BYTES);
-        for (int i = 0; i < pages_per_stage; ++i) {
-          const int lp = lp0 + i;
-          const int page = lp < p.table_width ? bt[lp] : -1;  // a missing page reads as zeros (masked keys)
-          const int y = ((page < 0 ? -1 : page) * 2 * p.Hkv + kvh) * ps;
-          for (int h = 0; h < HALVES; ++h)
-            tma_load_2d(smem_base + Cfg::OFF_K + s * Cfg::KV_STAGE_BYTES + h * Cfg::KV_HALF_BYTES + i * ps * 128, &map_kv,
-                        k_full(s), h * 64, y);
-        }
-        if (!mbar_wait(v_empty(s), parity, abort_p)) {
-          abort_flag = 1;
-          atomicExch(p.err, 21);
-          break;
-        }
-        mbar_expect_tx(v_full(s), Cfg::KV_STAGE_BYTES);
-        for (int i = 0; i < pages_per_stage; ++i) {
-          const int lp = lp0 + i;
-          const int page = lp < p.table_width ? bt[lp] : -1;
-          const int y = (((page < 0 ? -1 : page) * 2 + (page < 0 ? 0 : 1)) * p.Hkv + kvh) * ps;
-          for (int h = 0; h < HALVES; ++h)
-            tma_load_2d(smem_base + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES + h * Cfg::KV_HALF_BYTES + i * ps * 128, &map_kv,
-                        v_full(s), h * 64, y);
-        }
-      }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc_qk = umma_idesc_bf16(128, TC_BN);
-    const uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B (values) is MN-major
-    auto issue_qk = [&](int t, int s) {
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const int h = kk >> 2, in = kk & 3;
-        const uint64_t a = umma_desc_k_sw128(smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES + h * 128 * 128) + (uint64_t)(in * 2);
-        const uint64_t b = umma_desc_k_sw128(smem_base + Cfg::OFF_K + s * Cfg::KV_STAGE_BYTES + h * Cfg::KV_HALF_BYTES) + (uint64_t)(in * 2);
-        umma_bf16(tmem_base + Cfg::S_COL + t * TC_BN, a, b, idesc_qk, kk > 0);
-      }
+    const int ps = p.page_size;
+    const int pages_per_stage = TC_BN / ps;
+    const int* bt = p.block_table + (size_t)req * p.table_width;
+    auto page_of = [&](int j) {  // this lane's page of stage j; a missing page reads as zeros (masked keys)
+      const int lp = ((kv0 + j * TC_BN) >> p.page_shift) + lane;
+      return (lane < pages_per_stage && j < n_j && lp < p.table_width) ? bt[lp] : -1;
     };
-    auto issue_pv = [&](int t, int s, bool accumulate) {
-#pragma unroll
-      for (int kk = 0; kk < TC_BN / 16; ++kk) {
-        const uint64_t a = umma_desc_k_sw128(smem_base + Cfg::OFF_P + t * Cfg::P_TILE_BYTES) + (uint64_t)(kk * 2);
-        const uint64_t b = umma_desc_mn_sw128(smem_base + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES + kk * 16 * 128,
-                                              Cfg::KV_HALF_BYTES, 1024);
-        umma_bf16(tmem_base + Cfg::O_COL + t * D, a, b, idesc_pv, accumulate || kk > 0);
-      }
-    };
-    bool ok = wait_all(q_full, 0) && wait_all(k_full(0), 0);
-    if (!ok) {
-      abort_flag = 1;
-      if (lane == 0) atomicExch(p.err, 22);
-    } else {
-      tc_fence_after();
-      if (lane == 0) {
-        issue_qk(0, 0);
-        umma_commit(s_ready(0));
-        issue_qk(1, 0);
-        umma_commit(s_ready(1));
-        umma_commit(k_empty(0));
-      }
-      __syncwarp();
-    }
-    for (int j = 0; ok && j < n_j; ++j) {
+    int page = page_of(0);
+    bool ok = true;
+    for (int j = 0; j < n_j; ++j) {
       const int s = j % TC_STAGES;
-      const bool last = j + 1 == n_j;
-      const int s2 = (j + 1) % TC_STAGES;
-      ok = wait_all(v_full(s), (j / TC_STAGES) & 1);
-      if (ok && !last) ok = wait_all(k_full(s2), ((j + 1) / TC_STAGES) & 1);
+      const uint32_t parity = ((j / TC_STAGES) & 1) ^ 1;
+      const int next_page = page_of(j + 1);
+      const int pg = page < 0 ? -1 : page;
+      const uint32_t dst = s * Cfg::KV_STAGE_BYTES + lane * ps * 128;
+      if (lane == 0) {
+        ok = mbar_wait(k_empty(s), parity, abort_p);
+        if (ok) mbar_expect_tx(k_full(s), Cfg::KV_STAGE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) {
         abort_flag = 1;
-        if (lane == 0) atomicExch(p.err, 23);
+        if (lane == 0) atomicExch(p.err, 20);
         break;
       }
-      if (last) {
-        // Rows of the last stage past the key range may never have been written (or hold another
-        // request's values): a zero weight times a stray NaN would still be a NaN, so they are cleared.
-        const int first_bad = kv_end - (kv0 + j * TC_BN);
-        if (first_bad < TC_BN) {
-          uint8_t* v = smem + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES;
-          const int n16 = (TC_BN - first_bad) * 8;  // 16-byte pieces per 64-column half
-          for (int h = 0; h < HALVES; ++h)
-            for (int i = lane; i < n16; i += 32)
-              *reinterpret_cast<uint4*>(v + h * Cfg::KV_HALF_BYTES + first_bad * 128 + i * 16) = make_uint4(0, 0, 0, 0);
-          fence_proxy_async();
-        }
-        __syncwarp();
+      if (lane < pages_per_stage) {
+        const int y = (pg * 2 * p.Hkv + kvh) * ps;
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_2d(smem_base + Cfg::OFF_K + dst + h * Cfg::KV_HALF_BYTES, &map_kv, k_full(s), h * 64, y);
       }
-      for (int t = 0; t < 2 && ok; ++t) {
-        ok = wait_all(p_ready(t), j & 1);
+      if (lane == 0) {
+        ok = mbar_wait(v_empty(s), parity, abort_p);
+        if (ok) mbar_expect_tx(v_full(s), Cfg::KV_STAGE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) {
+        abort_flag = 1;
+        if (lane == 0) atomicExch(p.err, 21);
+        break;
+      }
+      if (lane < pages_per_stage) {
+        const int y = ((pg * 2 + (page < 0 ? 0 : 1)) * p.Hkv + kvh) * ps;
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_2d(smem_base + Cfg::OFF_V + dst + h * Cfg::KV_HALF_BYTES, &map_kv, v_full(s), h * 64, y);
+      }
+      page = next_page;
+    }
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------ MMA issuer of one row tile
+    if (lane == 0) {
+      const int t = warp == 1 ? 0 : 1;
+      const uint32_t idesc_qk = umma_idesc_bf16(128, TC_BN);
+      const uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B (values) is MN-major
+      const uint32_t q_addr = smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES;
+      const uint64_t p_desc = umma_desc_k_sw128(smem_base + Cfg::OFF_P + t * Cfg::P_TILE_BYTES);
+      const uint32_t o_tmem = tmem_base + Cfg::O_COL + t * D;
+      auto issue_qk = [&](int s, int buf) {
+        const uint32_t k_addr = smem_base + Cfg::OFF_K + s * Cfg::KV_STAGE_BYTES;
+        const uint32_t s_tmem = tmem_base + Cfg::S_COL + (2 * t + buf) * TC_BN;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const int h = kk >> 2, in = kk & 3;
+          umma_bf16(s_tmem, umma_desc_k_sw128(q_addr + h * 128 * 128) + (uint64_t)(in * 2),
+                    umma_desc_k_sw128(k_addr + h * Cfg::KV_HALF_BYTES) + (uint64_t)(in * 2), idesc_qk, kk > 0);
+        }
+      };
+      auto issue_pv = [&](int s, bool accumulate) {
+        const uint64_t v_desc = umma_desc_mn_sw128(smem_base + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES, Cfg::KV_HALF_BYTES, 1024);
+#pragma unroll
+        for (int kk = 0; kk < TC_BN / 16; ++kk)  // 16 keys on: 32 bytes of a P row, 16 rows of V
+          umma_bf16(o_tmem, p_desc + (uint64_t)(kk * 2), v_desc + (uint64_t)(kk * 16 * 128 >> 4), idesc_pv, accumulate || kk > 0);
+      };
+      // the scores of stages 0 and 1 go ahead; in the loop the scores of stage j + 2 follow P V of stage j
+      bool ok = mbar_wait(q_full, 0, abort_p);
+      for (int jj = 0; ok && jj < 2 && jj < n_j; ++jj) {
+        ok = mbar_wait(k_full(jj), 0, abort_p);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(jj, jj);
+        umma_commit(s_ready(t, jj));
+        umma_commit(k_empty(jj));
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicExch(p.err, 22);
+      }
+      for (int j = 0; ok && j < n_j; ++j) {
+        const int s = j % TC_STAGES;
+        const int jn = j + 2;
+        const bool more = jn < n_j;
+        const int s2 = jn % TC_STAGES;
+        ok = mbar_wait(v_full(s), (j / TC_STAGES) & 1, abort_p);
+        if (ok && more) ok = mbar_wait(k_full(s2), (jn / TC_STAGES) & 1, abort_p);
         if (!ok) {
           abort_flag = 1;
-          if (lane == 0) atomicExch(p.err, 24);
+          atomicExch(p.err, 23);
+          break;
+        }
+        ok = mbar_wait(p_ready(t), j & 1, abort_p);
+        if (!ok) {
+          abort_flag = 1;
+          atomicExch(p.err, 24);
           break;
         }
         tc_fence_after();
-        if (lane == 0) {
-          issue_pv(t, s, j > 0);
-          if (t == 1) umma_commit(v_empty(s));
-          if (last) umma_commit(o_done(t));
-          if (!last) {
-            issue_qk(t, s2);
-            umma_commit(s_ready(t));
-            if (t == 1) umma_commit(k_empty(s2));
-          }
+        issue_pv(s, j > 0);
+        umma_commit(pv_done(t));
+        umma_commit(v_empty(s));
+        if (more) {
+          issue_qk(s2, j & 1);
+          umma_commit(s_ready(t, j & 1));
+          umma_commit(k_empty(s2));
         }
-        __syncwarp();
       }
     }
   } else {
@@ -352,7 +356,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_j; ++j) {
-      ok = wait_all(s_ready(t), j & 1);
+      const int buf = j & 1;
+      ok = wait_all(s_ready(t, buf), (j >> 1) & 1);
       if (!ok) {
         abort_flag = 1;
         if (lane == 0) atomicExch(p.err, 25);
@@ -360,8 +365,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       tc_fence_after();
       float s[TC_BN];
-      tmem_ld32(lane_addr + Cfg::S_COL + t * TC_BN, &s[0]);
-      tmem_ld32(lane_addr + Cfg::S_COL + t * TC_BN + 32, &s[32]);
+      tmem_ld32(lane_addr + Cfg::S_COL + (2 * t + buf) * TC_BN, &s[0]);
+      tmem_ld32(lane_addr + Cfg::S_COL + (2 * t + buf) * TC_BN + 32, &s[32]);
       const int key0 = kv0 + j * TC_BN;
       const bool unmasked = tile_full && key0 + TC_BN - 1 <= qpos_min && key0 >= kv_begin && key0 + TC_BN <= kv_end &&
                             (p.window == 0 || key0 > qpos_max - p.window);
@@ -374,15 +379,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           if (key > hi || key < lo) s[c] = -INFINITY;
         }
       }
-      float mx = s[0];
+      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
 #pragma unroll
-      for (int c = 1; c < TC_BN; ++c) mx = fmaxf(mx, s[c]);
+      for (int c = 4; c < TC_BN; c += 4) {
+        mx0 = fmaxf(mx0, s[c]);
+        mx1 = fmaxf(mx1, s[c + 1]);
+        mx2 = fmaxf(mx2, s[c + 2]);
+        mx3 = fmaxf(mx3, s[c + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float cand = fmaxf(m_run, mx * p.scale_log2);
+      bool pv_waited = j == 0;   // P V of the stage before has finished: O is at rest and P may be overwritten
       const bool grow = cand > m_run + TC_LAZY;   // also true for the first finite maximum
       if (__any_sync(0xffffffffu, grow)) {
         const float f = m_run == -INFINITY ? 0.f : fast_exp2(m_run - cand);  // cand is finite where m_run is
         l_run *= f;
-        if (j > 0) {  // O of the earlier stages is complete (S of this stage was committed after it)
+        if (j > 0) {
+          ok = wait_all(pv_done(t), (j - 1) & 1);
+          pv_waited = true;
+          if (!ok) {
+            abort_flag = 1;
+            if (lane == 0) atomicExch(p.err, 27);
+            break;
+          }
+          tc_fence_after();
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
             float o[32];
@@ -396,27 +416,59 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      uint32_t pk[TC_BN / 2];
+#pragma unroll
+      for (int c = 0; c < TC_BN; c += 4) {
+        const float e0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_use)), e1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_use));
+        const float e2 = fast_exp2(fmaf(s[c + 2], p.scale_log2, -m_use)), e3 = fast_exp2(fmaf(s[c + 3], p.scale_log2, -m_use));
+        l0 += e0;
+        l1 += e1;
+        l2 += e2;
+        l3 += e3;
+        pk[c / 2] = pack2_bf16(e0, e1);
+        pk[c / 2 + 1] = pack2_bf16(e2, e3);
+      }
+      l_run += (l0 + l1) + (l2 + l3);
+      if (!pv_waited) {
+        ok = wait_all(pv_done(t), (j - 1) & 1);
+        if (!ok) {
+          abort_flag = 1;
+          if (lane == 0) atomicExch(p.err, 27);
+          break;
+        }
+      }
+      if (j + 1 == n_j && kv_end - key0 < TC_BN) {
+        // Rows of the last stage past the key range may never have been written (or hold another
+        // request's values): a zero weight times a stray NaN would still be a NaN.  The tile's
+        // threads clear them once the stage has landed, before they announce P (both tiles write
+        // the same zeros).
+        const int s_last = j % TC_STAGES;
+        ok = wait_all(v_full(s_last), (j / TC_STAGES) & 1);
+        if (!ok) {
+          abort_flag = 1;
+          if (lane == 0) atomicExch(p.err, 28);
+          break;
+        }
+        const int first_bad = kv_end - key0;
+        uint8_t* v = smem + Cfg::OFF_V + s_last * Cfg::KV_STAGE_BYTES;
+        const int n16 = (TC_BN - first_bad) * 8;  // 16-byte pieces per 64-column half
+        for (int h = 0; h < HALVES; ++h)
+          for (int i = r; i < n16; i += 128)
+            *reinterpret_cast<uint4*>(v + h * Cfg::KV_HALF_BYTES + first_bad * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+      }
       const uint32_t row_base = smem_u32(p_tile) + r * 128;
 #pragma unroll
       for (int ch = 0; ch < TC_BN / 8; ++ch) {
-        float e[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) e[c] = fast_exp2(fmaf(s[ch * 8 + c], p.scale_log2, -m_use));
-        l0 += e[0] + e[4];
-        l1 += e[1] + e[5];
-        l2 += e[2] + e[6];
-        l3 += e[3] + e[7];
         const uint32_t dst = row_base + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack2_bf16(e[0], e[1])), "r"(pack2_bf16(e[2], e[3])),
-                     "r"(pack2_bf16(e[4], e[5])), "r"(pack2_bf16(e[6], e[7]))
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[ch * 4]), "r"(pk[ch * 4 + 1]), "r"(pk[ch * 4 + 2]),
+                     "r"(pk[ch * 4 + 3])
                      : "memory");
       }
-      l_run += (l0 + l1) + (l2 + l3);
       fence_proxy_async();   // P is read by the matrix unit
       tc_fence_before();     // and this thread's tensor-memory accesses precede the products that follow
       mbar_arrive(p_ready(t));
     }
-    if (ok) ok = wait_all(o_done(t), 0);
+    if (ok) ok = wait_all(pv_done(t), (n_j - 1) & 1);
     if (!ok) {
       abort_flag = 1;
       if (lane == 0) atomicExch(p.err, 26);
@@ -563,7 +615,7 @@ int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const Att
     FERRUM_CHECK_ARG(e == cudaSuccess, "attention_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  launch_kernel(attention_tc_kernel<D>, dim3(n_work, p.Hkv), dim3(TC_THREADS), Cfg::SMEM_BYTES, stream, mq, mkv, p);
+  launch_kernel(attention_tc_kernel<D>, dim3(p.Hkv, n_work), dim3(TC_THREADS), Cfg::SMEM_BYTES, stream, mq, mkv, p);
   FERRUM_CHECK_LAUNCH("attention_tc");
   return 0;
 }
@@ -580,7 +632,7 @@ FERRUM_API int ferrum_attention_tc_tokens(int D, int G, int page_size) {
 }
 
 // Items of 2 * tokens * G rows (see ferrum_attention_tc_tokens) in the work-list format of
-// ferrum_attention_flash; grid (n_work, Hkv).  q has q_rows rows of ldq elements (the buffer's
+// ferrum_attention_flash; grid (Hkv, n_work).  q has q_rows rows of ldq elements (the buffer's
 // capacity, of which the batch may use fewer); the plane has n_pages pages.
 FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, void* out, int ldo, const void* kv_plane,
                                    long long page_stride, long long n_pages, int page_size, const int* block_table,
@@ -600,6 +652,7 @@ FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, voi
                    "row index of the cache map holds", n_pages);
   FERRUM_CHECK_ARG(table_width > 0 && window >= 0 && n_work >= 0 && q_rows > 0, "attention_tc: bad arguments");
   if (n_work == 0) return 0;
+  FERRUM_CHECK_ARG(n_work <= 65535, "attention_tc: %d work items are more than one launch takes", n_work);
   AttnTcParams p;
   p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.q_start = q_start; p.pos0 = pos0; p.work = work;
   p.part_o = part_o; p.part_ml = part_ml; p.err = err_flag;
