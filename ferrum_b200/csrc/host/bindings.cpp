@@ -17,7 +17,7 @@ static void raise_as(const char* cls, const char* what) {
 
 PYBIND11_MODULE(_host, m) {
   m.doc() = "native cache manager and scheduler of ferrum_b200";
-  m.attr("ABI") = 2;
+  m.attr("ABI") = 3;
 
   py::register_exception_translator([](std::exception_ptr p) {
     try {
@@ -113,6 +113,8 @@ PYBIND11_MODULE(_host, m) {
       .def("plan", &Scheduler::plan)
       .def("commit", &Scheduler::commit)
       .def("abandon", &Scheduler::abandon)
+      .def("plan_ahead", &Scheduler::plan_ahead)
+      .def("planned", &Scheduler::planned)
       .def("queued", &Scheduler::queued)
       .def("active", &Scheduler::active)
       .def("idle", &Scheduler::idle)

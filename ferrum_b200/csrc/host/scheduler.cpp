@@ -42,7 +42,11 @@ void Scheduler::submit(uint64_t id, std::vector<int32_t> prompt, int max_new_tok
 }
 
 void Scheduler::cancel(uint64_t id) {
-  if (planned_) throw SchedulerError("cancel between plan and commit");
+  if (!ahead_.empty()) throw SchedulerError("cancel between plan_ahead and commit");
+  // a planned row of the request is void from here on: the batch may be running already, what it
+  // computes for the row is ignored (pages it frees are handed out to later steps only)
+  for (auto& e : plan_)
+    if (e.id == id) e.slot = -1;
   for (auto it = queue_.begin(); it != queue_.end(); ++it)
     if (it->id == id) {
       queue_.erase(it);
@@ -176,7 +180,39 @@ void Scheduler::finish(size_t idx) {
 
 void Scheduler::abandon() {
   plan_.clear();
+  ahead_.clear();
   planned_ = false;
+}
+
+std::vector<PlanEntry> Scheduler::plan_ahead() {
+  if (!planned_ || !ahead_.empty() || !pending_.empty() || !queue_.empty()) return {};
+  if (plan_.size() != active_.size() || (int)plan_.size() > cfg_.max_batch_tokens) return {};
+  std::vector<int> need(cache_->n_groups(), 0);
+  std::vector<size_t> seq_of;
+  for (auto& e : plan_) {
+    if (!e.sample || e.slot < 0) return {};
+    size_t idx = active_.size();
+    for (size_t i = 0; i < active_.size(); ++i)
+      if (active_[i].id == e.id) idx = i;
+    if (idx == active_.size()) return {};
+    const Seq& s = active_[idx];
+    if (s.generated + 1 >= s.max_new) return {};  // this step's token is its last: the batch changes
+    const int len_after = e.pos0 + (int)e.tokens.size();
+    if (len_after + 1 > cfg_.max_model_len) return {};
+    const auto miss = cache_->pages_missing(s.slot, len_after + 1);
+    for (size_t g = 0; g < miss.size(); ++g) need[g] += miss[g];
+    seq_of.push_back(idx);
+  }
+  for (size_t g = 0; g < need.size(); ++g)
+    if (need[g] > cache_->free_pages((int)g)) return {};  // the ordinary plan decides who is preempted
+  for (size_t k = 0; k < plan_.size(); ++k) {
+    const PlanEntry& e = plan_[k];
+    const Seq& s = active_[seq_of[k]];
+    const int len_after = e.pos0 + (int)e.tokens.size();
+    cache_->grow(s.slot, len_after + 1);
+    ahead_.push_back(PlanEntry{s.id, s.slot, len_after, {-1}, true, s.temperature, s.seed, s.generated + 1});
+  }
+  return ahead_;
 }
 
 std::vector<Event> Scheduler::commit(const std::vector<int32_t>& sampled) {
@@ -195,6 +231,10 @@ std::vector<Event> Scheduler::commit(const std::vector<int32_t>& sampled) {
   ++stats_.steps;
   size_t k = 0;
   for (auto& e : plan_) {
+    if (e.slot < 0) {  // void row of a batch planned ahead: its sequence ended before the batch was read
+      k += e.sample;
+      continue;
+    }
     size_t idx = active_.size();
     for (size_t i = 0; i < active_.size(); ++i)
       if (active_[i].id == e.id) idx = i;
@@ -226,6 +266,19 @@ std::vector<Event> Scheduler::commit(const std::vector<int32_t>& sampled) {
   }
   plan_.clear();
   planned_ = false;
+  if (!ahead_.empty()) {
+    // the batch planned ahead is the current one now; rows of sequences that ended are void
+    for (auto& a : ahead_) {
+      size_t idx = active_.size();
+      for (size_t i = 0; i < active_.size(); ++i)
+        if (active_[i].id == a.id) idx = i;
+      if (idx == active_.size()) a.slot = -1;
+      else a.tokens[0] = active_[idx].tokens.back();
+    }
+    plan_.swap(ahead_);
+    ahead_.clear();
+    planned_ = true;
+  }
   return events;
 }
 

@@ -10,6 +10,12 @@
 // one forward call per sequence; several prompts may get a portion in the same step; and
 // temperature sampling is accepted.
 //
+// A step may be planned one ahead: between plan() and commit(), plan_ahead() gives the batch that
+// follows if no sampled row draws a stopping token, with token ids still unknown, so that the
+// engine can put it on the GPU's queue before it has read the current step's tokens.  commit()
+// then turns it into the current plan; a row whose sequence did stop (or was cancelled) is void:
+// its slot is -1, the GPU computes it for nothing and its sampled id is ignored.
+//
 // When pages run out: a decoding sequence that needs a page takes it from the most recently
 // admitted running sequence, which is preempted: its pages and slot are freed and it goes
 // back to the head of the queue with prompt := prompt + tokens generated so far, to be
@@ -79,6 +85,13 @@ class Scheduler {
   std::vector<Event> commit(const std::vector<int32_t>& sampled);
   // The batch did not run: forget the plan, every sequence is as before the step.
   void abandon();
+  // Between plan() and commit(): the next step's batch, if it is decided already whatever tokens
+  // this step draws short of a stopping token (every planned row samples and has tokens left to
+  // generate, nothing is queued, every active sequence is in the plan, pages suffice without
+  // preemption).  Its pages are reserved; each entry carries the one token id -1 (the id this
+  // step draws for its row, same order).  Empty when the next batch cannot be told yet.
+  std::vector<PlanEntry> plan_ahead();
+  bool planned() const { return planned_; }
 
   int queued() const { return (int)queue_.size(); }
   int active() const { return (int)active_.size(); }
@@ -110,6 +123,7 @@ class Scheduler {
   std::deque<Seq> queue_;
   std::vector<Seq> active_;
   std::vector<PlanEntry> plan_;
+  std::vector<PlanEntry> ahead_;  // plan_ahead()'s batch until commit() makes it the plan
   std::vector<Event> pending_;   // events decided while planning, delivered by the next commit
   bool planned_ = false;
   uint64_t clock_ = 0;

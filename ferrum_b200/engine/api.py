@@ -73,10 +73,13 @@ class StepEvent:
     reason: Optional[str] = None
 
 
+_NOTHING_SAMPLED = object()      # stands for the ticket of a batch without sampled rows
+
+
 class Engine:
     def __init__(self, model_path=None, dtype="bfloat16", random_weights=False, seed=0, page_size=16,
                  num_pages=None, max_batch_tokens=2048, max_batch_seqs=64, chunk_size=0, max_model_len=None,
-                 gpu_memory_fraction=0.85, device="cuda", model=None):
+                 gpu_memory_fraction=0.85, device="cuda", model=None, plan_ahead=True):
         ops.require_cuda()
         if model is None:
             model, td = load_model(model_path, dtype, device, max_positions=max_model_len,
@@ -104,6 +107,8 @@ class Engine:
         self.scheduler = host.module().Scheduler(self.cache.manager, sc)
         self._next_id = 0
         self.sampler = DeviceSampler(max_batch_seqs, device)
+        self.plan_ahead = bool(plan_ahead)
+        self._in_flight = None       # the sampling ticket of a batch that is on the GPU's queue
 
     # ------------------------------------------------------------------ requests
     def submit(self, prompt_tokens: Sequence[int], max_new_tokens: int, sampling: SamplingParams = None,
@@ -124,30 +129,51 @@ class Engine:
 
     # ------------------------------------------------------------------ one step
     def step(self) -> List[StepEvent]:
-        """Plan a batch, run it, sample on the device, read the ids back, commit."""
-        plan = self.scheduler.plan()
-        if not plan:
-            return self._events(self.scheduler.commit([]))
+        """Plan a batch, run it, sample on the device, read the ids back, commit.
+
+        While the GPU runs the batch the scheduler is asked for the one after it
+        (`plan_ahead`); if that is decided already, it is queued behind the running one, with
+        its token ids taken on the device from where the sampling kernel leaves them, and the
+        next call finds it in flight.  The events returned are always those of one step."""
+        if self._in_flight is None:
+            plan = self.scheduler.plan()
+            if not plan:
+                return self._events(self.scheduler.commit([]))
+            try:
+                self._in_flight = self._launch(plan)
+            except Exception:
+                self.scheduler.abandon()
+                raise
+        ticket, self._in_flight = self._in_flight, None
+        following = None
         try:
-            entries, rows = [], []
-            for p in plan:
-                n = len(p.tokens)
-                entries.append(StepEntry(p.slot, p.pos0, p.tokens, [n - 1] if p.sample else []))
-                if p.sample:
-                    rows.append(p)
-            logits = self.runner.step(entries, commit=False, check=False)
-            ids = self._sample(logits, rows) if rows else []
+            if self.plan_ahead and ticket is not _NOTHING_SAMPLED:
+                ahead = self.scheduler.plan_ahead()
+                if ahead:
+                    following = self._launch(ahead, ahead_of_commit=True)
+            ids = []
+            if ticket is not _NOTHING_SAMPLED:
+                ids, code = self.sampler.collect(ticket)
+                if code:
+                    self.runner.check_device_errors()
         except Exception:
             self.scheduler.abandon()
             raise
-        return self._events(self.scheduler.commit(ids))
+        events = self.scheduler.commit(ids)
+        self._in_flight = following
+        return self._events(events)
 
-    def _sample(self, logits, rows):
-        """One id per wanted row, chosen on the device (sampling/sampler.py)."""
-        ids, code = self.sampler.sample(logits, rows, self.runner.ctx.err)
-        if code:
-            self.runner.check_device_errors()
-        return ids
+    def _launch(self, plan, ahead_of_commit=False):
+        """Queues the batch and its sampling on the GPU; returns the sampling's ticket."""
+        entries, rows = [], []
+        for p in plan:
+            n = len(p.tokens)
+            entries.append(StepEntry(p.slot, p.pos0, p.tokens, [n - 1] if p.sample else []))
+            if p.sample:
+                rows.append(p)
+        logits = self.runner.step(entries, commit=False, check=False, ahead_of_commit=ahead_of_commit,
+                                  tokens_on_device=self.sampler.ids_device if ahead_of_commit else None)
+        return self.sampler.launch(logits, rows, self.runner.ctx.err) if rows else _NOTHING_SAMPLED
 
     @staticmethod
     def _events(raw):

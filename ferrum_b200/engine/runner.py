@@ -50,10 +50,15 @@ class ModelRunner:
         self._seen = {}
         self.graph_replays = 0
 
-    def step(self, entries: List[StepEntry], commit=True, check=True):
+    def step(self, entries: List[StepEntry], commit=True, check=True, ahead_of_commit=False, tokens_on_device=None):
         """Returns float32 logits [n_wanted, V] on the device (a view that the next step
         overwrites), in the order of the entries and of their `want` lists; None when no
-        logits are wanted.  With commit=False the caller advances the cache lengths itself."""
+        logits are wanted.  With commit=False the caller advances the cache lengths itself.
+
+        ahead_of_commit: the step is queued before the one ahead of it has been committed, so an
+        entry starts past its request's committed length, where that step ends (the caller
+        vouches for it).  tokens_on_device: an int32 device tensor whose first entries replace the token ids
+        of the batch, one token per entry (ids that an earlier kernel of the stream leaves there)."""
         mgr = self.cache.manager
         if not entries:
             return None
@@ -65,7 +70,7 @@ class ModelRunner:
                 raise InvalidRequest("a request appears twice in one step")
             seen.add(e.slot)
             have = mgr.seq_len(e.slot)
-            if e.pos0 != have:
+            if e.pos0 != have and not (ahead_of_commit and e.pos0 > have):
                 raise CacheError(f"position0 {e.pos0} does not match sequence length {have}")
             mgr.grow(e.slot, e.pos0 + len(e.tokens))      # no-op when the scheduler already reserved
             if e.pos0 == 0:
@@ -80,6 +85,10 @@ class ModelRunner:
         n_tok = sum(len(e.tokens) for e in entries)
         ops.set_dependent_launch(n_tok <= 32 or n_tok >= 512)
         self.ctx.fill(entries, mgr if self.cache.n_groups else [])
+        if tokens_on_device is not None:
+            if n_tok != len(entries):
+                raise InvalidRequest("tokens on the device stand for one token per entry")
+            self.ctx.token_ids[:n_tok].copy_(tokens_on_device[:n_tok], non_blocking=True)
         logits = self._run_decode() if decode_only else self.model.forward(self.ctx, self.cache)
         if commit:
             for e in entries:

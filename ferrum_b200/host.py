@@ -9,7 +9,7 @@ from .ops import build
 
 _mod = None
 _lock = threading.Lock()
-ABI = 2
+ABI = 3
 
 
 def module():

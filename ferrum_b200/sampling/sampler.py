@@ -15,39 +15,72 @@ import torch
 from ..ops import lib as ops
 
 
+class Ticket:
+    """A launched sampling whose ids have not been read yet."""
+    __slots__ = ("n", "host", "event")
+
+    def __init__(self, n, host, event):
+        self.n, self.host, self.event = n, host, event
+
+
 class DeviceSampler:
-    """Owns the small pinned and device buffers a step's sampling needs; one instance per engine."""
+    """Owns the small pinned and device buffers a step's sampling needs; one instance per engine.
+
+    `launch` enqueues the kernel and the copy of its ids to the host and returns at once;
+    `collect` waits for that copy.  Two samplings may be in flight (the engine queues the next
+    step before it reads this one), so the pinned buffers are rings; the ids of the latest
+    launch also stay on the device (`ids_device`) for a step that takes its tokens from there."""
+
+    DEPTH = 4
 
     def __init__(self, max_rows: int, device="cuda"):
+        from ..engine.batch import PinnedRing
         n = int(max_rows)
-        pin = lambda dt: torch.empty(n + 1, dtype=dt).pin_memory()
+        self.device = device
         dev = lambda dt: torch.empty(n + 1, dtype=dt, device=device)
-        self._inv_t = (pin(torch.float32), dev(torch.float32))
-        self._seeds = (pin(torch.int64), dev(torch.int64))
-        self._counters = (pin(torch.int32), dev(torch.int32))
-        self._ids = (pin(torch.int32), dev(torch.int32))
+        self._inv_t = (PinnedRing(n + 1, torch.float32, device, self.DEPTH), dev(torch.float32))
+        self._seeds = (PinnedRing(n + 1, torch.int64, device, self.DEPTH), dev(torch.int64))
+        self._counters = (PinnedRing(n + 1, torch.int32, device, self.DEPTH), dev(torch.int32))
+        self._ids_host = [torch.empty(n + 1, dtype=torch.int32).pin_memory() for _ in range(self.DEPTH)]
+        self._events = [torch.cuda.Event() for _ in range(self.DEPTH)]
+        self._turn = 0
+        self.ids_device = dev(torch.int32)
         self.d2h_bytes = 0
 
-    def sample(self, logits, rows, err):
-        """rows: objects with `temperature`, `seed`, `counter`, one per row of `logits`.
-        Returns (ids, device error code): the ids and the error flag travel to the host in
-        one copy, followed by the only synchronisation of the step."""
+    def launch(self, logits, rows, err) -> Ticket:
+        """rows: objects with `temperature`, `seed`, `counter`, one per row of `logits`.  The ids
+        and the error flag travel to the host in one copy."""
         n = len(rows)
-        ids_h, ids_d = self._ids
+        ids_d = self.ids_device
         if any(r.temperature > 0 for r in rows):
-            (it_h, it_d), (sd_h, sd_d), (ct_h, ct_d) = self._inv_t, self._seeds, self._counters
+            (it_r, it_d), (sd_r, sd_d), (ct_r, ct_d) = self._inv_t, self._seeds, self._counters
+            it_h, sd_h, ct_h = it_r.next(), sd_r.next(), ct_r.next()
             for i, r in enumerate(rows):
                 it_h[i] = float(np.float32(1.0 / r.temperature)) if r.temperature > 0 else 0.0
                 sd_h[i] = int(np.uint64(r.seed).astype(np.int64))
                 ct_h[i] = r.counter
-            for h, d in (self._inv_t, self._seeds, self._counters):
+            for ring, h, d in ((it_r, it_h, it_d), (sd_r, sd_h, sd_d), (ct_r, ct_h, ct_d)):
                 d[:n].copy_(h[:n], non_blocking=True)
+                ring.sent()
             ops.sample(logits, n, ids_d, err, it_d[:n], sd_d[:n], ct_d[:n])
         else:
             ops.sample(logits, n, ids_d, err)
         ids_d[n:n + 1].copy_(err)
-        ids_h[:n + 1].copy_(ids_d[:n + 1], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        self._turn = (self._turn + 1) % self.DEPTH
+        host, event = self._ids_host[self._turn], self._events[self._turn]
+        host[:n + 1].copy_(ids_d[:n + 1], non_blocking=True)
+        event.record()
         self.d2h_bytes = 4 * (n + 1)
-        out = ids_h[:n + 1].tolist()
-        return out[:n], out[n]
+        return Ticket(n, host, event)
+
+    @staticmethod
+    def collect(ticket: Ticket):
+        """(ids, device error code) of a launch; the wait for its copy is the step's only
+        synchronisation."""
+        ticket.event.synchronize()
+        out = ticket.host[:ticket.n + 1].tolist()
+        return out[:ticket.n], out[ticket.n]
+
+    def sample(self, logits, rows, err):
+        """launch + collect."""
+        return self.collect(self.launch(logits, rows, err))

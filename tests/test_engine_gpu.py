@@ -121,3 +121,40 @@ def test_missing_extension_or_device_fails_loudly(cuda, monkeypatch):
     monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
     with pytest.raises(KernelError, match="CUDA device only"):
         lib.require_cuda()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_queued_ahead_change_nothing(cuda, model_dirs, dtype):
+    """The engine queues the next decode step before it has read the current one's tokens (the
+    ids go from the sampling kernel to the next step on the device).  Same tokens, same finish
+    reasons as with one step at a time: greedy and temperature rows, a request that stops on a
+    token (its row of the step already queued is computed for nothing), one cancelled in flight."""
+    from ferrum_b200 import SamplingParams
+    vocab = TINY["D"][0]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 70 + n) for n in (5, 19, 2, 11)]
+    probe = engine(model_dirs, "D", dtype, plan_ahead=False).generate([prompts[2]], max_new_tokens=12)[0]
+
+    def run(ahead):
+        eng = engine(model_dirs, "D", dtype, plan_ahead=ahead)
+        ids = [eng.submit(p, 12, SamplingParams(0.7 if i == 1 else 0.0, 1.0, 3), stop_tokens=[probe[5]] if i == 2 else [])
+               for i, p in enumerate(prompts)]
+        out, reasons, steps = {i: [] for i in ids}, {}, 0
+        while len(reasons) < 3:
+            for ev in eng.step():
+                if ev.kind == "token":
+                    out[ev.id].append(ev.token)
+                else:
+                    reasons[ev.id] = ev.reason
+            steps += 1
+            if steps == 4:
+                eng.cancel(ids[3])
+            assert steps < 100
+        while eng.step():
+            pass
+        assert eng.stats()["pages_used"] == [0] and eng.stats()["active"] == 0
+        return [out[i] for i in ids[:3]], reasons
+
+    one_by_one, r0 = run(False)
+    queued, r1 = run(True)
+    assert queued == one_by_one and r0 == r1
+    assert one_by_one[2] == probe[:probe.index(probe[5]) + 1] and r0[2] == "stop"

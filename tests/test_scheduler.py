@@ -221,3 +221,139 @@ def test_random_workloads_finish_with_the_tokens_each_request_would_get_alone(se
         assert out.get(rid, []) == exp, rid
     assert set(reasons) == set(want)
     assert c.free_pages(0) == c.group(0).num_pages and c.check() == ""
+
+
+# ---------------------------------------------------------------- a step planned ahead
+def run_ahead(sched, cache, next_token, max_steps=5000, log=None):
+    """The engine's loop with one step planned ahead: the batch that follows is asked for before
+    the current one's tokens are known, and is 'launched' with unknown token ids."""
+    out, reasons = {}, {}
+    in_flight = None       # rows (request ids) of a batch that was launched ahead
+    aheads = 0
+    for _ in range(max_steps):
+        if sched.idle() and in_flight is None:
+            break
+        if in_flight is None:
+            plan = sched.plan()
+            if not plan:
+                for ev in sched.commit([]):
+                    assert ev.kind == 1
+                    reasons[ev.id] = ev.reason
+                continue
+            for p in plan:
+                assert cache.seq_len(p.slot) == p.pos0
+            in_flight = [(p.id, p.pos0 + len(p.tokens) - 1) for p in plan if p.sample]
+        rows, in_flight = in_flight, None
+        ahead = sched.plan_ahead()
+        if ahead:
+            aheads += 1
+            assert [a.id for a in ahead] == [r[0] for r in rows]            # same rows, same order
+            for a, (_, last_pos) in zip(ahead, rows):
+                assert list(a.tokens) == [-1] and a.sample
+                assert a.pos0 == last_pos + 1 > cache.seq_len(a.slot)         # right after the uncommitted step
+                assert cache.pages_missing(a.slot, a.pos0 + 1) == [0]        # its page is reserved
+            in_flight = [(a.id, a.pos0) for a in ahead]
+            if log is not None:
+                log.append([a.id for a in ahead])
+        # the GPU computes every launched row, also rows that turn out void; ids are passed for all
+        sampled = [next_token(rid, pos) for rid, pos in rows]
+        for ev in sched.commit(sampled):
+            if ev.kind == 0:
+                out.setdefault(ev.id, []).append(ev.token)
+            else:
+                reasons[ev.id] = ev.reason
+        assert cache.check() == ""
+    assert sched.idle() and in_flight is None
+    return out, reasons, aheads
+
+
+def test_plan_ahead_continues_a_decoding_batch_and_voids_rows_that_stop():
+    s, c = make(eos=50)
+    s.submit(1, [1, 2, 3], 6)
+    s.submit(2, [4, 5], 6)
+    tok = lambda rid, pos: 50 if (rid, pos) == (2, 3) else 7          # request 2 draws EOS as its third token
+    log = []
+    out, reasons, aheads = run_ahead(s, c, tok, log=log)
+    assert out == {1: [7] * 6, 2: [7, 7, 50]}
+    assert reasons == {1: 1, 2: 0}
+    # ahead of the prompts' step and of two decode steps both rows were queued; the row of request 2
+    # in the third of them was void; with one request left the plan went ahead again
+    assert log[:3] == [[1, 2], [1, 2], [1, 2]] and [1] in log
+    assert c.free_pages(0) == c.group(0).num_pages
+
+
+def test_plan_ahead_declines_when_the_next_batch_is_not_decided():
+    s, c = make(budget=4)
+    s.submit(1, [1, 2, 3, 4, 5, 6], 3)              # six prompt tokens, four per step
+    assert s.plan_ahead() == []                      # nothing planned
+    plan = s.plan()
+    assert not plan[0].sample and s.plan_ahead() == []      # a prompt portion: the next step is known, but not sampled
+    s.commit([])
+    s.plan()
+    s.submit(2, [9], 2)
+    assert s.plan_ahead() == []                      # someone is queued: the next batch admits them
+    s.abandon()
+    s, c = make()
+    s.submit(1, [1, 2], 2)
+    s.plan()
+    assert [a.pos0 for a in s.plan_ahead()] == [2]   # first token now, the second one follows
+    assert s.plan_ahead() == []                      # asked twice
+    s.commit([7])
+    assert s.planned()                               # the batch planned ahead is the plan now
+    assert s.plan_ahead() == []                      # its token is the last one
+    evs = s.commit([8])
+    assert [(e.kind, e.token) for e in evs] == [(0, 8), (1, -1)]
+    assert s.idle() and c.free_pages(0) == c.group(0).num_pages
+
+
+def test_plan_ahead_leaves_a_shortage_of_pages_to_the_ordinary_plan():
+    s, c = make(pages=3, page_size=2, max_requests=2)
+    s.submit(1, [1, 2], 4)
+    s.submit(2, [3, 4], 4)
+    s.plan()                                         # a page each for the prompts, one page free
+    assert s.plan_ahead() == []                      # both would need a new page
+    s.commit([7, 7])
+    out, reasons, _ = run_ahead(s, c, lambda rid, pos: 7)
+    assert sorted(reasons) == [1, 2] and c.check() == ""
+
+
+def test_cancel_while_a_batch_is_in_flight_voids_its_row():
+    s, c = make()
+    s.submit(1, [1, 2], 5)
+    s.submit(2, [3], 5)
+    s.plan()
+    assert len(s.plan_ahead()) == 2
+    with pytest.raises(SchedulerError, match="plan_ahead"):
+        s.cancel(2)
+    s.commit([7, 7])
+    s.cancel(2)                                      # its row of the batch in flight is void now
+    evs = s.commit([8, 9])
+    assert [(e.id, e.token) for e in evs if e.kind == 0] == [(1, 8)]
+    assert s.active() == 1 and c.check() == ""
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_with_steps_planned_ahead(seed):
+    rng = random.Random(100 + seed)
+    eos = rng.choice([-1, 50])
+    s, c = make(pages=rng.choice([12, 20, 40]), page_size=rng.choice([2, 4, 8]), max_requests=rng.choice([2, 3, 5]),
+                budget=rng.choice([3, 8, 33]), chunk=rng.choice([0, 2, 5]), eos=eos)
+    tok = lambda rid, pos: (rid * 13 + pos * 5 + seed) % 97
+    want = {}
+    cap = c.capacity_tokens()
+    for rid in range(12):
+        n, new = rng.randint(1, 20), rng.randint(0, 15)
+        if n + new > cap:
+            continue
+        s.submit(rid, [rng.randrange(97) for _ in range(n)], new)
+        exp = []
+        for i in range(new):
+            exp.append(tok(rid, n - 1 + i))
+            if exp[-1] == eos:
+                break
+        want[rid] = exp
+    out, reasons, aheads = run_ahead(s, c, tok)
+    for rid, exp in want.items():
+        assert out.get(rid, []) == exp, rid
+    assert set(reasons) == set(want)
+    assert c.free_pages(0) == c.group(0).num_pages and c.check() == ""
