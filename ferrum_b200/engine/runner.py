@@ -78,12 +78,7 @@ class ModelRunner:
                     s[e.slot].zero_()                      # a request starts from an all-zero state
         decode_only = self.use_graphs and all(len(e.tokens) == 1 for e in entries)
         self.ctx.fixed_shapes = decode_only
-        # Dependent launch lets the next kernel's blocks start (and wait) while a kernel still
-        # runs.  It pays for steps of a few tokens, where launch latency dominates, and for
-        # long prompts; with some tens of tokens the waiting blocks of wide elementwise
-        # kernels cost the running kernel more than the overlap gains (measured at 64).
         n_tok = sum(len(e.tokens) for e in entries)
-        ops.set_dependent_launch(n_tok <= 32 or n_tok >= 512)
         self.ctx.fill(entries, mgr if self.cache.n_groups else [])
         if tokens_on_device is not None:
             if n_tok != len(entries):
