@@ -40,6 +40,7 @@ struct FlashParams {
   long long page_stride;
   int ldq, ldo, page_size, page_shift, table_width;
   int Hq, Hkv, G, window;
+  int trigger_early;    // let the kernels that follow in the stream start (and wait) while this one runs
   float scale_log2;
 };
 
@@ -338,9 +339,15 @@ template <int D, int WM, int WN>
 __global__ void __launch_bounds__(WM * WN * 32)
 flash_kernel(const FlashParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  // No early pdl_launch() here: blocks of the next kernels that sit on the SMs waiting for
-  // this one to finish slow a large attention grid down by a third (measured at 64 requests).
+  // Blocks of the next kernels that sit on the SMs waiting for this one to finish slow a large
+  // attention grid down by a third (measured at 64 requests), so the dependents are released
+  // early only on request: with a few decoded tokens the merge kernel's blocks are tiny, and
+  // the blocks of the product after it move in as this kernel's blocks leave and fetch their
+  // first weight tiles while the slowest blocks here finish.
+  if (p.trigger_early) pdl_launch();
+  TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0, TRACE_FLASH);
   pdl_wait();
+  TRACE_MARK(TRACE_WAITED);
   if (p.cta_items == nullptr) {
     const int* wk = p.work + (size_t)blockIdx.x * 8;
     // with one item per (CTA, head) the item's partial slot is per head
@@ -349,6 +356,7 @@ flash_kernel(const FlashParams p) {
     for (int i = 0; i < 8; ++i) item[i] = wk[i];
     item[5] = item[5] * p.Hkv + blockIdx.y;
     flash_item<D, WM, WN>(p, item, blockIdx.y, smem_raw);
+    TRACE_MARK(TRACE_EXIT);
     return;
   }
   const int begin = p.cta_items[blockIdx.x], end = p.cta_items[blockIdx.x + 1];
@@ -357,6 +365,7 @@ flash_kernel(const FlashParams p) {
     flash_item<D, WM, WN>(p, wk, wk[6], smem_raw);
     __syncthreads();  // the next item's loads reuse the shared memory the merge just read
   }
+  TRACE_MARK(TRACE_EXIT);
 }
 
 
@@ -368,8 +377,11 @@ __global__ void __launch_bounds__(D / 4 < 32 ? 32 : D / 4)
 combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* part_ml, const int* q_start,
                const int* req_of_token, const int* req_tile0, const int* tile_info, const int* token_list, int G,
                int Hkv, int BM) {
+  TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0, TRACE_COMBINE);
   pdl_launch();
   pdl_wait();
+  TRACE_MARK(TRACE_WAITED);
+  TRACE_MARK(TRACE_EXIT);
   const int t = token_list ? token_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int req = req_of_token[t];
   const int kvh = head / G;
@@ -419,6 +431,8 @@ int launch_flash(const FlashParams& p, int n_work, int n_ctas, cudaStream_t stre
 
 }  // namespace
 
+FERRUM_TRACE_READER(ferrum_trace_flash)
+
 FERRUM_API int ferrum_attention_flash_supported(int D, int bm) { return (D == 64 || D == 128) && (bm == 16 || bm == 64); }
 
 // work: [n_work][8] int32 on the device (see FlashParams).  bm: 16 (a few rows per request,
@@ -428,7 +442,7 @@ FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo
                                       long long page_stride, int page_size, const int* block_table, int table_width,
                                       const int* q_start, const int* pos0, const int* work, int n_work,
                                       const int* cta_items, int n_ctas, float* part_o, float* part_ml, int Hq, int Hkv,
-                                      int D, float scale, int window, int bm, cudaStream_t stream) {
+                                      int D, float scale, int window, int bm, int trigger_early, cudaStream_t stream) {
   FERRUM_CHECK_ARG(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_flash: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
   FERRUM_CHECK_ARG(ferrum_attention_flash_supported(D, bm), "attention_flash: head size %d with row tile %d is not built; "
                    "use the generic kernel", D, bm);
@@ -447,6 +461,7 @@ FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo
   for (int b = 0; b < 30; ++b)
     if ((1 << b) == page_size) p.page_shift = b;
   p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.window = window;
+  p.trigger_early = trigger_early;
   p.scale_log2 = scale * 1.4426950408889634f;
   if (D == 64 && bm == 16) return launch_flash<64, 1, 4>(p, n_work, n_ctas, stream);
   if (D == 64 && bm == 64) return launch_flash<64, 4, 1>(p, n_work, n_ctas, stream);

@@ -57,6 +57,53 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---- kernel timeline (only in a build with -DFERRUM_TRACE, see ops/build.py)
+// Block 0 of an instrumented kernel records three points of the GPU's global timer: entry,
+// return from the dependency wait, exit.  Each translation unit has its own ring of records
+// [kind, t_entry, t_waited, t_exit] and exports a reader.  Without the macro nothing is
+// compiled in.
+#ifdef FERRUM_TRACE
+constexpr int TRACE_RECORDS = 8192;
+static __device__ unsigned long long g_trace[TRACE_RECORDS * 4];
+static __device__ unsigned int g_trace_n;
+__device__ __forceinline__ unsigned long long trace_clock() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ int trace_begin(int kind) {
+  const unsigned i = atomicAdd(&g_trace_n, 1u) % TRACE_RECORDS;
+  g_trace[i * 4 + 0] = (unsigned long long)kind;
+  g_trace[i * 4 + 1] = trace_clock();
+  g_trace[i * 4 + 2] = 0;
+  g_trace[i * 4 + 3] = 0;
+  return (int)i;
+}
+// `first` is true in the one thread of the grid that keeps the record
+#define TRACE_BEGIN(first, kind) const int trace_slot_ = (first) ? trace_begin(kind) : -1
+#define TRACE_MARK(field)                                              \
+  do {                                                                 \
+    if (trace_slot_ >= 0) g_trace[trace_slot_ * 4 + (field)] = trace_clock(); \
+  } while (0)
+#define FERRUM_TRACE_READER(name)                                                                  \
+  FERRUM_API int name(unsigned long long* out, unsigned int* n) {                                 \
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;                                          \
+    cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * TRACE_RECORDS * 4);            \
+    cudaMemcpyFromSymbol(n, g_trace_n, sizeof(unsigned int));                                      \
+    const unsigned int zero = 0;                                                                   \
+    cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));                                            \
+    return 0;                                                                                      \
+  }
+#else
+#define TRACE_BEGIN(first, kind) ((void)0)
+#define TRACE_MARK(field) ((void)0)
+#define FERRUM_TRACE_READER(name)
+#endif
+constexpr int TRACE_WAITED = 2, TRACE_EXIT = 3;
+// kinds: 1 product (+ output features / 64 * 16, + 8 for the two-product kernel), 2 norm, 3 rotary,
+// 4 swiglu_reduce, 5 attention (mma.sync), 6 combine
+constexpr int TRACE_GEMM = 1, TRACE_NORM = 2, TRACE_ROPE = 3, TRACE_SWIGLU_REDUCE = 4, TRACE_FLASH = 5, TRACE_COMBINE = 6;
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

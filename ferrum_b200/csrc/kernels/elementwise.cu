@@ -107,25 +107,23 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TOu
 
 // The norm of a few rows spread over a cluster of CTAs: with 8 rows and one CTA per row the
 // kernel is a chain of memory latencies on 8 SMs.  Here NORM_CLUSTER CTAs share a row; each
-// sums its slice (adding pending partials if any), the slices' sums of squares are exchanged
-// through distributed shared memory and added in rank order, so the result is the same
-// whichever CTA finishes first.
+// sums its slice (adding pending partials if any) and keeps it in registers, sends its sum of
+// squares to every CTA of the cluster through distributed shared memory, and adds the eight
+// sums in rank order, so the result is the same whichever CTA finishes first.
 constexpr int NORM_CLUSTER = 8;
+constexpr int NORM_KEEP = 4;  // elements a thread keeps between the two passes (more are read again)
 
 __device__ __forceinline__ unsigned norm_cluster_rank() {
   unsigned r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ void norm_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float norm_peer_value(const float* local, unsigned rank) {
+__device__ __forceinline__ void norm_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void norm_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void norm_store_to_peer(float* local, unsigned rank, float v) {
   unsigned addr = (unsigned)__cvta_generic_to_shared(local), peer;
-  float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
-  return v;
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(peer), "f"(v) : "memory");
 }
 
 template <typename TOut>
@@ -133,20 +131,39 @@ __global__ void __launch_bounds__(256)
 rmsnorm_cluster_kernel(float* __restrict__ h, const float* __restrict__ w, TOut* __restrict__ out,
                        const int* __restrict__ rows, int E, float eps, const PartialLayout L) {
   __shared__ float red[32];
-  __shared__ float slice_ss;
+  __shared__ float slice_sums[NORM_CLUSTER];   // written by the CTAs of the cluster, one entry each
   __shared__ PartialTable tab;
+  TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0, TRACE_NORM);
+  // A CTA's shared memory may be written by a peer only once the CTA is known to run: every CTA
+  // arrives here and waits for the others before it sends its sum (by then they have long arrived).
+  norm_cluster_arrive();
   if (L.ws != nullptr) build_partial_table(L, tab);
   pdl_launch();
   pdl_wait();
+  TRACE_MARK(TRACE_WAITED);
   const int r = blockIdx.x;
   const unsigned rank = norm_cluster_rank();
   const int src = rows ? rows[r] : r;
   const int per = (E + NORM_CLUSTER - 1) / NORM_CLUSTER;
   const int lo = rank * per, hi = min(E, lo + per);
   float* hr = h + (size_t)src * E;
+  float keep[NORM_KEEP];
   float ss = 0.f;
-#pragma unroll 2
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+#pragma unroll
+  for (int k = 0; k < NORM_KEEP; ++k) {
+    const int i = lo + threadIdx.x + k * 256;
+    float v = 0.f;
+    if (i < hi) {
+      v = hr[i];
+      if (L.ws != nullptr) {
+        v += partial_sum(L, tab, src, i);
+        hr[i] = v;
+      }
+    }
+    keep[k] = v;
+    ss = fmaf(v, v, ss);
+  }
+  for (int i = lo + threadIdx.x + NORM_KEEP * 256; i < hi; i += 256) {  // rows wider than 8192
     float v = hr[i];
     if (L.ws != nullptr) {
       v += partial_sum(L, tab, src, i);
@@ -155,15 +172,22 @@ rmsnorm_cluster_kernel(float* __restrict__ h, const float* __restrict__ w, TOut*
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, red);
-  if (threadIdx.x == 0) slice_ss = ss;
-  norm_cluster_sync();
+  norm_cluster_wait();
+  if (threadIdx.x < NORM_CLUSTER) norm_store_to_peer(&slice_sums[rank], threadIdx.x, ss);
+  norm_cluster_arrive();
+  norm_cluster_wait();
   float total = 0.f;
 #pragma unroll
-  for (unsigned c = 0; c < NORM_CLUSTER; ++c) total += norm_peer_value(&slice_ss, c);
+  for (int c = 0; c < NORM_CLUSTER; ++c) total += slice_sums[c];
   const float inv = 1.0f / sqrtf(total / (float)E + eps);
   TOut* o = out + (size_t)r * E;
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) o[i] = from_f32<TOut>(hr[i] * inv * w[i]);
-  norm_cluster_sync();  // nobody leaves while a peer may still read its slice sum
+#pragma unroll
+  for (int k = 0; k < NORM_KEEP; ++k) {
+    const int i = lo + threadIdx.x + k * 256;
+    if (i < hi) o[i] = from_f32<TOut>(keep[k] * inv * w[i]);
+  }
+  for (int i = lo + threadIdx.x + NORM_KEEP * 256; i < hi; i += 256) o[i] = from_f32<TOut>(hr[i] * inv * w[i]);
+  TRACE_MARK(TRACE_EXIT);
 }
 
 template <typename TOut>
@@ -325,9 +349,11 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
                                   int Hkv, int D, int R, int pairing, int write_kv, int* __restrict__ err,
                                   const PartialLayout L) {
   __shared__ PartialTable tab;
+  TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0, TRACE_ROPE);
   if (L.ws != nullptr) build_partial_table(L, tab);
   pdl_launch();
   pdl_wait();
+  TRACE_MARK(TRACE_WAITED);
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = R >> 1;
@@ -409,6 +435,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
       vdst[(size_t)h * page_size * D + d] = v[w];
     }
   }
+  TRACE_MARK(TRACE_EXIT);
 }
 
 // Many tokens, bfloat16, the whole head rotated (R == D, D a multiple of 16): a thread rotates
@@ -588,15 +615,18 @@ swiglu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restric
 // (columns t and acc_cols / 2 + t of the partial tiles).
 __global__ void swiglu_reduce_kernel(__nv_bfloat16* __restrict__ act, int F, int ld_out, const PartialLayout L) {
   __shared__ PartialTable tab;
+  TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0, TRACE_SWIGLU_REDUCE);
   build_partial_table(L, tab);
   pdl_launch();
   pdl_wait();
+  TRACE_MARK(TRACE_WAITED);
   const int t = blockIdx.y;
   __nv_bfloat16* o = act + (size_t)t * ld_out;
   for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F; f += gridDim.x * blockDim.x) {
     const float g = partial_sum(L, tab, t, f), u = partial_sum(L, tab, L.acc_cols / 2 + t, f);
     o[f] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
   }
+  TRACE_MARK(TRACE_EXIT);
 }
 
 FERRUM_API int ferrum_swiglu_reduce(void* act, int n_tokens, int F, int ld_out, const float* partials, const int* layout,
@@ -634,3 +664,5 @@ FERRUM_API int ferrum_swiglu(const void* gu, void* act, int dtype, int n_tokens,
   FERRUM_CHECK_LAUNCH("swiglu");
   return 0;
 }
+
+FERRUM_TRACE_READER(ferrum_trace_elementwise)

@@ -50,6 +50,7 @@ struct TcParams {
   int dual_offset;   // row of the second weight tile relative to the first (DUAL)
   int defer;         // 1: leave every segment's float32 partial in the workspace; the next kernel sums them
   int out_tma;       // 1: the pair kernel writes `out` through its tensor map (staged in shared memory)
+  int stream_weights;  // 1: every weight tile is read once in this launch: its L2 lines are the first to go
 };
 
 constexpr int TILE_N = 128;  // weight rows per tile (the instruction's M)
@@ -148,6 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
 
+  TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0, TRACE_GEMM + (p.N / 64) * 16 + (DUAL ? 8 : 0));
   if (threadIdx.x == 0) {
     abort_flag = 0;
     is_last = 0;
@@ -180,6 +182,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       uint32_t phase = 0;
       long long tile = u_begin / nkb;
       int kb = (int)(u_begin % nkb);
+      const bool stream_w = p.stream_weights != 0;
+      auto load_w = [&](uint32_t dst, uint32_t bar, int x, int y) {
+        if (stream_w) tma_load_2d_hint(dst, &tmap_w, bar, x, y, L2_EVICT_FIRST);
+        else tma_load_2d(dst, &tmap_w, bar, x, y);
+      };
       // The weights never change, so the first ring of weight tiles is requested before the
       // kernel ahead of this one in the stream has finished; the activations it writes are
       // requested after the dependency wait.
@@ -190,8 +197,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         for (int i = 0; i < pre; ++i) {
           const uint32_t a = smem_base + i * Cfg::STAGE_BYTES;
           mbar_expect_tx(full_bar(i), Cfg::STAGE_BYTES);
-          tma_load_2d(a, &tmap_w, full_bar(i), k * TILE_K, (int)(tl % tiles_n) * TILE_N);
-          if (DUAL) tma_load_2d(a + A_BYTES, &tmap_w, full_bar(i), k * TILE_K, p.dual_offset + (int)(tl % tiles_n) * TILE_N);
+          load_w(a, full_bar(i), k * TILE_K, (int)(tl % tiles_n) * TILE_N);
+          if (DUAL) load_w(a + A_BYTES, full_bar(i), k * TILE_K, p.dual_offset + (int)(tl % tiles_n) * TILE_N);
           if (++k == nkb) {
             k = 0;
             ++tl;
@@ -199,6 +206,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
       }
       pdl_wait();
+      TRACE_MARK(TRACE_WAITED);
       pdl_launch();
       for (int i = 0; i < pre; ++i) {
         const uint32_t a = smem_base + i * Cfg::STAGE_BYTES;
@@ -219,8 +227,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int n0 = (int)(tile % tiles_n) * TILE_N, t0 = (int)(tile / tiles_n) * BT;
         const uint32_t a = smem_base + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
-        tma_load_2d(a, &tmap_w, full_bar(s), kb * TILE_K, n0);
-        if (DUAL) tma_load_2d(a + A_BYTES, &tmap_w, full_bar(s), kb * TILE_K, p.dual_offset + n0);
+        load_w(a, full_bar(s), kb * TILE_K, n0);
+        if (DUAL) load_w(a + A_BYTES, full_bar(s), kb * TILE_K, p.dual_offset + n0);
         tma_load_2d(a + A_BYTES * (DUAL ? 2 : 1), &tmap_x, full_bar(s), kb * TILE_K, t0);
         if (++s == STAGES) {
           s = 0;
@@ -390,6 +398,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+  TRACE_MARK(TRACE_EXIT);
 }
 
 // ------------------------------------------------------------------ the CTA-pair kernel
@@ -892,6 +901,7 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
     if (n_ctas > units) n_ctas = (int)units;
   }
   TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset, 0};
+  p.stream_weights = (M + bt - 1) / bt == 1;  // one token tile: no weight tile is read twice
   CUtensorMap mw, mx;
   if (int r = get_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
   if (bt == PAIR_BT && !dual && g_pair_kernel && n_ctas >= 2) {
@@ -971,6 +981,7 @@ FERRUM_API int ferrum_gemm_tc_deferred(const void* x, const void* w, int M, int 
   if (int r = get_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
   if (int r = get_tensor_map(x, M, K, ldx, bt, &mx)) return r;
   TcParams p{nullptr, workspace, nullptr, err_flag, M, N, K, 0, dual ? TC_SWIGLU : TC_STORE_F32, dual_offset, 1};
+  p.stream_weights = 1;  // deferred mode has one token tile: no weight tile is read twice
   switch (bt) {
     case 16: return dual ? launch_tc<16, true>(mw, mx, p, n_ctas, stream) : launch_tc<16, false>(mw, mx, p, n_ctas, stream);
     case 32: return dual ? launch_tc<32, true>(mw, mx, p, n_ctas, stream) : launch_tc<32, false>(mw, mx, p, n_ctas, stream);
@@ -1071,3 +1082,5 @@ FERRUM_API int ferrum_gemm_tc_noalloc(const void* x, const void* w, void* out, i
   }
   FERRUM_CHECK_ARG(false, "gemm_tc_noalloc: no kernel for token tile %d", bt);
 }
+
+FERRUM_TRACE_READER(ferrum_trace_gemm)

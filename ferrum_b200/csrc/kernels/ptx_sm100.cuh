@@ -66,6 +66,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// The same load with an L2 eviction priority for the lines it brings in (a 64-bit policy word;
+// L2_EVICT_FIRST marks data that is read once, so that it does not push out what is read again).
+constexpr uint64_t L2_EVICT_FIRST = 0x12F0000000000000ull;
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(
+          dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+
 // Stores from shared memory through a tensor map (elements outside the tensor are not written).
 // The issuing thread commits them in groups and waits on its own groups.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {

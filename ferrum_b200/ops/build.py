@@ -81,15 +81,23 @@ def _run_all(cmds, what):
                 raise KernelError(f"build failed: {' '.join(c)}\n{out}")
 
 
+def trace_build():
+    """FERRUM_KERNEL_TRACE=1 selects a second library, built with -DFERRUM_TRACE, whose kernels
+    record a timeline (see csrc/kernels/common.cuh and `kernel_bench.py timeline`)."""
+    return os.environ.get("FERRUM_KERNEL_TRACE", "0") == "1"
+
+
 def build_kernels(force=False, verbose_ptxas=False):
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
     hdrs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cuh")))
     if not srcs:
         raise KernelError("no kernel sources found")
-    if not force and not _newer(srcs + hdrs, KERNEL_LIB):
-        return KERNEL_LIB
+    trace = trace_build()
+    target = KERNEL_LIB[:-3] + "_trace.so" if trace else KERNEL_LIB
+    if not force and not _newer(srcs + hdrs, target):
+        return target
     nvcc = _find("nvcc", ["/usr/local/cuda/bin"])
-    bdir = os.path.join(PKG, "_build")
+    bdir = os.path.join(PKG, "_build", "trace") if trace else os.path.join(PKG, "_build")
     os.makedirs(bdir, exist_ok=True)
     objs, cmds = [], []
     for s in srcs:
@@ -100,16 +108,18 @@ def build_kernels(force=False, verbose_ptxas=False):
                    "-c", s, "-o", o]
             if verbose_ptxas:
                 cmd[1:1] = ["-Xptxas", "-v"]
+            if trace:
+                cmd[1:1] = ["-DFERRUM_TRACE"]
             cmds.append(cmd)
     if cmds:
         _run_all(cmds, f"{len(cmds)} CUDA source(s) for sm_100a")
-    tmp = KERNEL_LIB + f".tmp{os.getpid()}"
+    tmp = target + f".tmp{os.getpid()}"
     link = [nvcc, *NVCC_ARCH, "-shared", "-o", tmp, *objs]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise KernelError(f"link failed: {' '.join(link)}\n{r.stdout}")
-    os.replace(tmp, KERNEL_LIB)
-    return KERNEL_LIB
+    os.replace(tmp, target)
+    return target
 
 
 def build_host(force=False):

@@ -24,7 +24,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 1
+ABI = 2
 
 
 def lib():
@@ -280,8 +280,9 @@ def attention_flash_supported(dtype, D, page_stride=0):
 
 
 def attention_flash(q, out, kv_plane, page_stride, page_size, block_table, q_start, pos0, work, n_work, part_o,
-                    part_ml, Hq, Hkv, D, scale, window, bm, cta_items=None, n_ctas=0):
-    """Tensor-core attention over the work items of one row-tile class (bm 16 or 64)."""
+                    part_ml, Hq, Hkv, D, scale, window, bm, cta_items=None, n_ctas=0, trigger_early=False):
+    """Tensor-core attention over the work items of one row-tile class (bm 16 or 64).
+    trigger_early: the kernels that follow in the stream may start while this one runs."""
     _need(q, torch.bfloat16, "q", 2); _need(out, torch.bfloat16, "out", 2); _need(kv_plane, torch.bfloat16, "kv_plane")
     _need(block_table, torch.int32, "block_table", 2); _need(work, torch.int32, "work", 1)
     _check(lib().ferrum_attention_flash(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(kv_plane),
@@ -289,7 +290,8 @@ def attention_flash(q, out, kv_plane, page_stride, page_size, block_table, q_sta
                                         c_int(block_table.shape[1]), _ptr(q_start), _ptr(pos0), _ptr(work),
                                         c_int(n_work), _ptr(cta_items), c_int(n_ctas), _ptr(part_o), _ptr(part_ml),
                                         c_int(Hq), c_int(Hkv), c_int(D),
-                                        c_float(scale), c_int(window), c_int(bm), _stream()), "attention_flash")
+                                        c_float(scale), c_int(window), c_int(bm), c_int(1 if trigger_early else 0),
+                                        _stream()), "attention_flash")
 
 
 def attention_tc_tokens(D, G, page_size, kv_plane=None, page_stride=0):

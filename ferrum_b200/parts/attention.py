@@ -17,6 +17,11 @@ from .base import CacheNeed, Mixer, PagedKVNeed, ParamSpec
 from .linear import RESIDUAL, STORE, linear, linear_deferred
 
 
+# Up to this many tokens in a step the attention kernel lets the kernels after it start early
+# (see attention_flash.cu); with more, their waiting blocks cost more than the overlap gains.
+EARLY_TRIGGER_MAX_TOKENS = 16
+
+
 class PagedAttention(Mixer):
     graph_safe = True
 
@@ -86,7 +91,8 @@ class PagedAttention(Mixer):
             else:
                 ops.attention_flash(qkv, out, cache.plane, cache.page_stride, cache.page_size, table, ctx.q_start,
                                     ctx.pos0, plan.work, plan.n_work, part_o, part_ml, Hq, Hkv, D, self.scale,
-                                    self.window, plan.bm, plan.cta_items, plan.n_ctas)
+                                    self.window, plan.bm, plan.cta_items, plan.n_ctas,
+                                    trigger_early=ctx.n_tokens <= EARLY_TRIGGER_MAX_TOKENS)
             if plan.n_comb:
                 ops.attention_combine(out, part_o, part_ml, ctx.q_start, ctx.req_of_token, plan.req_tile0,
                                       plan.tile_info, plan.comb_tokens, plan.n_comb, Hq, Hkv, D, plan.bm)

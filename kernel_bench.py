@@ -7,6 +7,11 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py attn_prefill [--tokens 2048]
     python kernel_bench.py gemm --tokens 8 --n 6144 --k 4096 [--epilogue store|residual|swiglu] [--copies 8]
     python kernel_bench.py rmsnorm|rope --tokens 8
+    FERRUM_KERNEL_TRACE=1 python kernel_bench.py timeline [--batch 8] [--context 8192] [--layers 4]
+`timeline` runs decode steps of a model with `--layers` layers on the library built with the
+kernel trace (block 0 of every instrumented kernel records the GPU's global timer at entry,
+after its dependency wait and at exit) and prints one line per launch of the last step: what
+each kernel costs once its inputs are there, and what the hand-over between kernels costs.
 Shapes default to Llama-3.1-8B (32 query heads, 8 KV heads, head size 128, width 4096).
 """
 import argparse
@@ -21,7 +26,7 @@ sys.path.insert(0, ROOT)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemm", "rmsnorm", "rope"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemm", "rmsnorm", "rope", "timeline"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=8)
@@ -41,6 +46,8 @@ def main():
     ap.add_argument("--no-dependent-launch", action="store_true", help="plain stream order between the launches")
     args = ap.parse_args()
 
+    if args.kernel == "timeline":
+        return timeline(args)
     import torch
     from bench import peaks
     from ferrum_b200.engine.batch import StepContext, StepEntry
@@ -157,6 +164,70 @@ def main():
     print(json.dumps({"kernel": args.kernel, "us": round(us, 2), "GBps": round(gbs, 1), "TFLOPs": round(tf, 2),
                       "bound": work["bound"], "frac_of_peak": round(frac, 4), "peaks": pk["source"],
                       "args": {k: v for k, v in vars(args).items() if k != "kernel"}}))
+    return 0
+
+
+def timeline(args):
+    import ctypes
+    import torch
+    from bench import LLAMA31_8B
+    from ferrum_b200.cache.storage import CacheStorage
+    from ferrum_b200.config import registry
+    from ferrum_b200.engine.batch import StepEntry
+    from ferrum_b200.engine.runner import ModelRunner
+    from ferrum_b200.ops import build, lib as ops
+    from ferrum_b200.weights import init_random
+    if not build.trace_build():
+        sys.exit("timeline needs the trace build: set FERRUM_KERNEL_TRACE=1")
+    B, C = args.batch, args.context
+    cfgd = dict(LLAMA31_8B)
+    cfgd["num_hidden_layers"] = args.layers
+    arch = registry.lookup("LlamaForCausalLM")
+    model = arch.build(arch.read_config(cfgd), torch.bfloat16, "cuda", max_positions=C + 64)
+    init_random(model, 0)
+    cache = CacheStorage(model, torch.bfloat16, "cuda", page_size=args.page_size, max_tokens=B * (C + 64), max_requests=B,
+                         max_model_len=C + 64)
+    runner = ModelRunner(model, cache, max_batch_tokens=max(B, 16), max_batch_requests=B)
+    slots = [cache.open() for _ in range(B)]
+    for s in slots:
+        cache.manager.grow(s, C - 1)
+        cache.manager.commit(s, C - 1)
+    ids = torch.empty(B, dtype=torch.int32, device="cuda")
+
+    def step(i):
+        logits = runner.step([StepEntry(s, C - 1 + i, [7], [0]) for s in slots], check=False)
+        ops.sample(logits, B, ids, runner.ctx.err)
+
+    readers = [getattr(ops.lib(), n) for n in ("ferrum_trace_gemm", "ferrum_trace_elementwise", "ferrum_trace_flash")]
+
+    def read():
+        out = []
+        for fn in readers:
+            buf = (ctypes.c_ulonglong * (8192 * 4))()
+            n = ctypes.c_uint(0)
+            if fn(buf, ctypes.byref(n)):
+                sys.exit("reading the trace failed")
+            out += [tuple(buf[i * 4 + k] for k in range(4)) for i in range(min(n.value, 8192))]
+        return sorted(out, key=lambda e: e[1])
+
+    for i in range(6):          # warm-up; the decode graph is captured on the second step
+        step(i)
+    read()
+    step(6)
+    ev = read()
+    names = {2: "norm", 3: "rotary+cache", 4: "swiglu_reduce", 5: "attention", 6: "combine"}
+    t0, prev_exit = ev[0][1], None
+    print(f"decode step, batch {B}, context {C}, {args.layers} layers; microseconds; block 0 of each launch")
+    print(f"{'kernel':22s} {'entry':>9s} {'waited':>9s} {'exit':>9s} | {'work':>7s} {'hand-over':>9s}")
+    for kind, entry, waited, exit_ in ev:
+        if kind % 16 == 1:
+            name = f"product N={kind // 16 * 64}" + (" x2" if kind & 8 else "")
+        else:
+            name = names.get(kind, str(kind))
+        hand = (waited - prev_exit) / 1e3 if prev_exit else 0.0
+        print(f"{name:22s} {(entry - t0) / 1e3:9.2f} {(waited - t0) / 1e3:9.2f} {(exit_ - t0) / 1e3:9.2f} | "
+              f"{(exit_ - waited) / 1e3:7.2f} {hand:9.2f}")
+        prev_exit = exit_
     return 0
 
 
