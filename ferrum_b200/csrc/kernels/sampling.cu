@@ -37,7 +37,7 @@ constexpr int SAMPLE_CLUSTER = 8;
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ inv_temperature,
               const unsigned long long* __restrict__ seeds, const int* __restrict__ counters,
-              int* __restrict__ out_ids, int* __restrict__ err) {
+              int* __restrict__ out_ids, int* __restrict__ also_to, int* __restrict__ err) {
   __shared__ Best red[32];
   __shared__ Best slice_best[SAMPLE_CLUSTER];
   pdl_launch();
@@ -101,13 +101,15 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     return;
   }
   out_ids[r] = best.i;
+  if (also_to != nullptr) also_to[r] = best.i;
   if (best.i < 0) atomicExch(err, 6);
 }
 
-// inv_temperature[r] == 0 (or a null array) means greedy for row r.
+// inv_temperature[r] == 0 (or a null array) means greedy for row r.  also_to (may be null) receives
+// the ids as well: the token buffer of a step that is queued behind this one.
 FERRUM_API int ferrum_sample(const float* logits, int ld, int n_rows, int V, const float* inv_temperature,
-                             const unsigned long long* seeds, const int* counters, int* out_ids, int* err_flag,
-                             cudaStream_t stream) {
+                             const unsigned long long* seeds, const int* counters, int* out_ids, int* also_to,
+                             int* err_flag, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_rows >= 0 && V > 0 && ld >= V, "sample: bad sizes rows=%d V=%d ld=%d", n_rows, V, ld);
   FERRUM_CHECK_ARG(!inv_temperature || (seeds && counters), "sample: temperature given without seeds and counters");
   if (n_rows == 0) return 0;
@@ -126,7 +128,7 @@ FERRUM_API int ferrum_sample(const float* logits, int ld, int n_rows, int V, con
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ferrum_dependent_launch_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, V, inv_temperature, seeds, counters, out_ids, err_flag);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, V, inv_temperature, seeds, counters, out_ids, also_to, err_flag);
   FERRUM_CHECK_ARG(e == cudaSuccess, "sample: launch failed: %s", cudaGetErrorString(e));
   FERRUM_CHECK_LAUNCH("sample");
   return 0;

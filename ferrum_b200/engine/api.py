@@ -97,8 +97,9 @@ class Engine:
                                     (self.max_model_len * max_batch_seqs + page_size - 1) // page_size))
         self.cache = CacheStorage(model, td, device, page_size=page_size, num_pages=num_pages,
                                   max_requests=max_batch_seqs, max_model_len=self.max_model_len)
+        self.sampler = DeviceSampler(max_batch_seqs, device)
         self.runner = ModelRunner(model, self.cache, max_batch_tokens=max_batch_tokens,
-                                  max_batch_requests=max_batch_seqs)
+                                  max_batch_requests=max_batch_seqs, err=self.sampler.err)
         sc = host.module().SchedulerConfig()
         sc.max_batch_tokens, sc.max_batch_seqs, sc.chunk_size = int(max_batch_tokens), int(max_batch_seqs), int(chunk_size)
         sc.max_model_len, sc.n_vocab = self.max_model_len, model.n_vocab
@@ -106,7 +107,6 @@ class Engine:
         sc.eos_token_id = -1 if eos is None else int(eos)
         self.scheduler = host.module().Scheduler(self.cache.manager, sc)
         self._next_id = 0
-        self.sampler = DeviceSampler(max_batch_seqs, device)
         self.plan_ahead = bool(plan_ahead)
         self._in_flight = None       # the sampling ticket of a batch that is on the GPU's queue
 
@@ -133,7 +133,7 @@ class Engine:
 
         While the GPU runs the batch the scheduler is asked for the one after it
         (`plan_ahead`); if that is decided already, it is queued behind the running one, with
-        its token ids taken on the device from where the sampling kernel leaves them, and the
+        its token ids already on the device, where the sampling kernel of this step writes them, and the
         next call finds it in flight.  The events returned are always those of one step."""
         if self._in_flight is None:
             plan = self.scheduler.plan()
@@ -172,8 +172,9 @@ class Engine:
             if p.sample:
                 rows.append(p)
         logits = self.runner.step(entries, commit=False, check=False, ahead_of_commit=ahead_of_commit,
-                                  tokens_on_device=self.sampler.ids_device if ahead_of_commit else None)
-        return self.sampler.launch(logits, rows, self.runner.ctx.err) if rows else _NOTHING_SAMPLED
+                                  tokens_on_device=ahead_of_commit)
+        # the ids also go where a step queued behind this one looks for its tokens
+        return self.sampler.launch(logits, rows, also_to=self.runner.ctx.token_store) if rows else _NOTHING_SAMPLED
 
     @staticmethod
     def _events(raw):

@@ -78,15 +78,18 @@ class PinnedRing:
 class StepContext:
     """Built once per runner; `fill` rewrites it for each step."""
 
-    def __init__(self, device, max_tokens, max_requests, table_widths: List[int]):
+    def __init__(self, device, max_tokens, max_requests, table_widths: List[int], err=None):
+        """err: an int32 device tensor of one element to use as the kernels' error flag (the
+        engine puts it next to the sampled ids so that both reach the host in one copy)."""
         self.device = device
         self.max_tokens, self.max_requests = int(max_tokens), int(max_requests)
         self.table_widths = list(table_widths)
         self.scratch = Scratch(device)
-        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        self.err = err if err is not None else torch.zeros(1, dtype=torch.int32, device=device)
         n_small = 4 * self.max_tokens + 3 * self.max_requests + 1
         self._host = PinnedRing(n_small, torch.int32, device)
         self._dev = torch.empty(n_small, dtype=torch.int32, device=device)
+        self.token_store = self._dev       # a step's token ids are its first entries
         self._bt_host = [PinnedRing(self.max_requests * w, torch.int32, device) for w in self.table_widths]
         self._bt_dev = [torch.empty((self.max_requests, w), dtype=torch.int32, device=device) for w in self.table_widths]
         self._splitk_counters = torch.zeros(4096, dtype=torch.int32, device=device)
@@ -103,9 +106,11 @@ class StepContext:
         self.token_capacity = self.want_capacity = 0
 
     # ------------------------------------------------------------------ per step
-    def fill(self, entries: List[StepEntry], tables, token_capacity=None):
+    def fill(self, entries: List[StepEntry], tables, token_capacity=None, keep_token_ids=False):
         """tables: the native CacheManager whose block tables the entries' slots index, or
-        explicit rows, tables[g][r] being the row of entry r in group g."""
+        explicit rows, tables[g][r] being the row of entry r in group g.  keep_token_ids: the
+        device already holds this step's token ids (`token_store`, written by an earlier kernel
+        of the stream); the entries' own ids are placeholders and are not uploaded."""
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         if R > self.max_requests or T > self.max_tokens:
@@ -148,9 +153,10 @@ class StepContext:
                 t += n
         qstart[R] = T
         total = o + 3 * R + 1
-        self._dev[:total].copy_(host[:total], non_blocking=True)
+        first = T if keep_token_ids else 0
+        self._dev[first:total].copy_(host[first:total], non_blocking=True)
         self._host.sent()
-        self.h2d_bytes = total * 4
+        self.h2d_bytes = (total - first) * 4
         d = self._dev
         self.token_ids, self.positions, self.req_of_token = d[0:T], d[T:2 * T], d[2 * T:3 * T]
         self.want_rows = d[3 * T:3 * T + W]

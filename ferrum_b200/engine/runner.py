@@ -33,7 +33,8 @@ class _CapturedStep:
 
 
 class ModelRunner:
-    def __init__(self, model, cache: CacheStorage, max_batch_tokens=2048, max_batch_requests=None, use_graphs=True):
+    def __init__(self, model, cache: CacheStorage, max_batch_tokens=2048, max_batch_requests=None, use_graphs=True,
+                 err=None):
         """use_graphs: steps that bring one token per request (decoding) are captured in a
         CUDA graph per (requests, wanted rows) the second time that shape is seen, and
         replayed afterwards; every other step is launched kernel by kernel."""
@@ -43,22 +44,23 @@ class ModelRunner:
         self.max_batch_tokens = int(max_batch_tokens)
         self.max_batch_requests = int(max_batch_requests or cache.max_requests)
         widths = [cache.table_width] * cache.n_groups
-        self.ctx = StepContext(self.device, self.max_batch_tokens, self.max_batch_requests, widths)
+        self.ctx = StepContext(self.device, self.max_batch_tokens, self.max_batch_requests, widths, err=err)
         self.ctx.cache = cache
         self.use_graphs = bool(use_graphs) and model.all_graph_safe()
         self._graphs = {}
         self._seen = {}
         self.graph_replays = 0
 
-    def step(self, entries: List[StepEntry], commit=True, check=True, ahead_of_commit=False, tokens_on_device=None):
+    def step(self, entries: List[StepEntry], commit=True, check=True, ahead_of_commit=False, tokens_on_device=False):
         """Returns float32 logits [n_wanted, V] on the device (a view that the next step
         overwrites), in the order of the entries and of their `want` lists; None when no
         logits are wanted.  With commit=False the caller advances the cache lengths itself.
 
         ahead_of_commit: the step is queued before the one ahead of it has been committed, so an
         entry starts past its request's committed length, where that step ends (the caller
-        vouches for it).  tokens_on_device: an int32 device tensor whose first entries replace the token ids
-        of the batch, one token per entry (ids that an earlier kernel of the stream leaves there)."""
+        vouches for it).  tokens_on_device: the token ids of the batch, one per entry, are already in
+        `ctx.token_store` (an earlier kernel of the stream leaves them there); the entries carry
+        placeholders."""
         mgr = self.cache.manager
         if not entries:
             return None
@@ -79,11 +81,9 @@ class ModelRunner:
         decode_only = self.use_graphs and all(len(e.tokens) == 1 for e in entries)
         self.ctx.fixed_shapes = decode_only
         n_tok = sum(len(e.tokens) for e in entries)
-        self.ctx.fill(entries, mgr if self.cache.n_groups else [])
-        if tokens_on_device is not None:
-            if n_tok != len(entries):
-                raise InvalidRequest("tokens on the device stand for one token per entry")
-            self.ctx.token_ids[:n_tok].copy_(tokens_on_device[:n_tok], non_blocking=True)
+        if tokens_on_device and n_tok != len(entries):
+            raise InvalidRequest("tokens on the device stand for one token per entry")
+        self.ctx.fill(entries, mgr if self.cache.n_groups else [], keep_token_ids=bool(tokens_on_device))
         logits = self._run_decode() if decode_only else self.model.forward(self.ctx, self.cache)
         if commit:
             for e in entries:

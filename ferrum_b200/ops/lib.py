@@ -24,7 +24,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 2
+ABI = 3
 
 
 def lib():
@@ -333,12 +333,13 @@ def swiglu(gu, act, n_tokens, F):
                                c_int(gu.stride(0)), c_int(act.stride(0)), _stream()), "swiglu")
 
 
-def sample(logits, n_rows, out_ids, err, inv_temperature=None, seeds=None, counters=None):
-    """out_ids[r] = argmax, or the Gumbel-max draw where inv_temperature[r] != 0."""
+def sample(logits, n_rows, out_ids, err, inv_temperature=None, seeds=None, counters=None, also_to=None):
+    """out_ids[r] = argmax, or the Gumbel-max draw where inv_temperature[r] != 0.  `also_to`
+    (int32) receives the ids as well."""
     _need(logits, torch.float32, "logits", 2); _need(out_ids, torch.int32, "out_ids", 1)
     if inv_temperature is not None:
         _need(inv_temperature, torch.float32, "inv_temperature", 1)
         _need(seeds, torch.int64, "seeds", 1); _need(counters, torch.int32, "counters", 1)
     _check(lib().ferrum_sample(_ptr(logits), c_int(logits.stride(0)), c_int(n_rows), c_int(logits.shape[1]),
-                               _ptr(inv_temperature), _ptr(seeds), _ptr(counters), _ptr(out_ids), _ptr(err),
-                               _stream()), "sample")
+                               _ptr(inv_temperature), _ptr(seeds), _ptr(counters), _ptr(out_ids), _ptr(also_to),
+                               _ptr(err), _stream()), "sample")

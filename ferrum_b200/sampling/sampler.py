@@ -44,13 +44,20 @@ class DeviceSampler:
         self._ids_host = [torch.empty(n + 1, dtype=torch.int32).pin_memory() for _ in range(self.DEPTH)]
         self._events = [torch.cuda.Event() for _ in range(self.DEPTH)]
         self._turn = 0
+        self.max_rows = n
         self.ids_device = dev(torch.int32)
+        self.ids_device.zero_()
+        # the kernels' error flag sits behind the ids, so that one copy brings both to the host
+        self.err = self.ids_device[n:n + 1]
         self.d2h_bytes = 0
 
-    def launch(self, logits, rows, err) -> Ticket:
+    def launch(self, logits, rows, also_to=None) -> Ticket:
         """rows: objects with `temperature`, `seed`, `counter`, one per row of `logits`.  The ids
-        and the error flag travel to the host in one copy."""
-        n = len(rows)
+        and the error flag (`self.err`, which the step's kernels must have been given) travel to
+        the host in one copy.  also_to: an int32 device tensor that receives the ids as well."""
+        n, err = len(rows), self.err
+        if n > self.max_rows:
+            raise ValueError(f"{n} rows to sample, the sampler was made for {self.max_rows}")
         ids_d = self.ids_device
         if any(r.temperature > 0 for r in rows):
             (it_r, it_d), (sd_r, sd_d), (ct_r, ct_d) = self._inv_t, self._seeds, self._counters
@@ -62,15 +69,14 @@ class DeviceSampler:
             for ring, h, d in ((it_r, it_h, it_d), (sd_r, sd_h, sd_d), (ct_r, ct_h, ct_d)):
                 d[:n].copy_(h[:n], non_blocking=True)
                 ring.sent()
-            ops.sample(logits, n, ids_d, err, it_d[:n], sd_d[:n], ct_d[:n])
+            ops.sample(logits, n, ids_d, err, it_d[:n], sd_d[:n], ct_d[:n], also_to=also_to)
         else:
-            ops.sample(logits, n, ids_d, err)
-        ids_d[n:n + 1].copy_(err)
+            ops.sample(logits, n, ids_d, err, also_to=also_to)
         self._turn = (self._turn + 1) % self.DEPTH
         host, event = self._ids_host[self._turn], self._events[self._turn]
-        host[:n + 1].copy_(ids_d[:n + 1], non_blocking=True)
+        host.copy_(ids_d, non_blocking=True)
         event.record()
-        self.d2h_bytes = 4 * (n + 1)
+        self.d2h_bytes = 4 * (self.max_rows + 1)
         return Ticket(n, host, event)
 
     @staticmethod
@@ -78,9 +84,9 @@ class DeviceSampler:
         """(ids, device error code) of a launch; the wait for its copy is the step's only
         synchronisation."""
         ticket.event.synchronize()
-        out = ticket.host[:ticket.n + 1].tolist()
-        return out[:ticket.n], out[ticket.n]
+        out = ticket.host.tolist()
+        return out[:ticket.n], out[-1]
 
-    def sample(self, logits, rows, err):
+    def sample(self, logits, rows):
         """launch + collect."""
-        return self.collect(self.launch(logits, rows, err))
+        return self.collect(self.launch(logits, rows))

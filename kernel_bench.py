@@ -61,7 +61,10 @@ def main():
     runs = []
 
     if args.kernel in ("attn_decode", "attn_prefill"):
-        from ferrum_b200.parts import PagedAttention
+        from ferrum_b200.parts import PagedAttention, attention as attention_part
+        # In a step a product follows the attention kernel; here attention launches follow each
+        # other, and released early they would only take each other's places on the SMs.
+        attention_part.EARLY_TRIGGER_MAX_TOKENS = 0
         decode = args.kernel == "attn_decode"
         R = args.batch if decode else 1
         qlen = 1 if decode else args.tokens
