@@ -462,6 +462,10 @@ def test_argmax_rules(ops):
     e = err_flag()
     ops.sample(logits, 3, ids, e)
     assert ids.cpu().tolist() == [1, -1, 0] and e.item() == 6
+    # a second destination gets the same ids (the token buffer of a step queued behind this one)
+    again = torch.full((5,), 77, dtype=torch.int32, device="cuda")
+    ops.sample(logits, 3, ids, e, also_to=again)
+    assert again.cpu().tolist() == [1, -1, 0, 77, 77]
 
 
 @pytest.mark.parametrize("V", [301, 128256])
