@@ -392,17 +392,36 @@ combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* pa
   const int r = pr % BM;
   const int d = threadIdx.x * 4;
   if (d >= D) return;
-  float M = -INFINITY;
-  for (int s = 0; s < n; ++s) M = fmaxf(M, part_ml[((size_t)(first + s * stride) * BM + r) * 2]);
-  float L = 0.f;
+  // Eight splits at a time, all their loads in flight together (the kernel is a chain of memory
+  // latencies otherwise); the running maximum is carried from one group to the next.  Splits are
+  // taken in slot order, so the result does not depend on which block finished first.
+  constexpr int GROUP = 8;
+  float M = -INFINITY, L = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < n; ++s) {
-    const size_t slot = (size_t)(first + s * stride) * BM + r;
-    const float ms = part_ml[slot * 2];
-    const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-    L += part_ml[slot * 2 + 1] * f;
-    const float4 v = *reinterpret_cast<const float4*>(part_o + slot * D + d);
-    acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+  for (int s0 = 0; s0 < n; s0 += GROUP) {
+    float ms[GROUP], ls[GROUP];
+    float4 v[GROUP];
+#pragma unroll
+    for (int k = 0; k < GROUP; ++k) {
+      const bool have = s0 + k < n;
+      const size_t slot = (size_t)(first + (have ? s0 + k : 0) * stride) * BM + r;
+      ms[k] = have ? __ldcg(part_ml + slot * 2) : -INFINITY;
+      ls[k] = have ? __ldcg(part_ml + slot * 2 + 1) : 0.f;
+      v[k] = have ? __ldcg(reinterpret_cast<const float4*>(part_o + slot * D + d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float m_new = M;
+#pragma unroll
+    for (int k = 0; k < GROUP; ++k) m_new = fmaxf(m_new, ms[k]);
+    const float keep = M == -INFINITY ? 0.f : exp2f(M - m_new);
+    L *= keep;
+    acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+#pragma unroll
+    for (int k = 0; k < GROUP; ++k) {
+      const float f = ms[k] == -INFINITY ? 0.f : exp2f(ms[k] - m_new);
+      L += ls[k] * f;
+      acc.x += v[k].x * f; acc.y += v[k].y * f; acc.z += v[k].z * f; acc.w += v[k].w * f;
+    }
+    M = m_new;
   }
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   uint2 packed;
