@@ -31,6 +31,21 @@ LLAMA31_8B = {
     "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 8192},
 }
+# Two more shapes that the reference's workloads name (its configs 3 and 4), for `--model`.
+LLAMA2_7B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 32, "num_attention_heads": 32,
+    "num_key_value_heads": 32, "head_dim": 128, "intermediate_size": 11008, "vocab_size": 32000,
+    "rope_theta": 10000.0, "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+LLAMA32_3B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 3072, "num_hidden_layers": 28, "num_attention_heads": 24,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192, "vocab_size": 128256,
+    "rope_theta": 500000.0, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+}
+MODELS = {"llama31-8b": ("Llama-3.1-8B", LLAMA31_8B), "llama2-7b": ("Llama-2-7B", LLAMA2_7B),
+          "llama32-3b": ("Llama-3.2-3B", LLAMA32_3B)}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -117,6 +132,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--model", default="llama31-8b", choices=sorted(MODELS), help="layer sizes (random weights)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--skip-points", action="store_true")
@@ -139,7 +155,8 @@ def main():
     from ferrum_b200.weights import init_random
 
     pk = peaks()
-    cfgd = dict(LLAMA31_8B)
+    model_name, shape = MODELS[args.model]
+    cfgd = dict(shape)
     full_layers = cfgd["num_hidden_layers"]
     if args.layers:
         cfgd["num_hidden_layers"] = args.layers
@@ -269,15 +286,15 @@ def main():
                "warmup": e2e_warm}
 
     line = {
-        "metric": "decode tok/s (Llama-3.1-8B bf16, batch 8, context 8192)", "value": round(value, 1), "unit": "tok/s",
+        "metric": f"decode tok/s ({model_name} bf16, batch {B}, context {ctx_len})", "value": round(value, 1), "unit": "tok/s",
         "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "Llama-3.1-8B shape, random weights N(0,0.02)", "layers": L, "layers_full_model": full_layers,
+        "config": {"model": f"{model_name} shape, random weights N(0,0.02)", "layers": L, "layers_full_model": full_layers,
                    "hidden": cfgd["hidden_size"], "heads": cfgd["num_attention_heads"],
                    "kv_heads": cfgd["num_key_value_heads"], "head_dim": cfgd["head_dim"],
                    "intermediate": cfgd["intermediate_size"], "vocab": cfgd["vocab_size"], "global_batch": B,
                    "seq_len": ctx_len, "context_len": ctx_len, "page_size": page, "prefill_tokens": 2048,
-                   "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)",
+                   "parallelism": "single GPU", "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.0f} GB of weights per step)",
                    "sampling": "greedy on device, inside the step"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill, "roofline": roofline,
         "points": points,
