@@ -557,9 +557,9 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
     return 0;
   }
   const int threads = 256;
-  // few tokens: several blocks per token, four head slots each, so that the row (and the
-  // partials behind it) is read by many SMs at once
-  const dim3 grid(n_tokens, n_tokens <= 64 ? (Hq + 2 * Hkv + 3) / 4 : 1);
+  // few tokens, or a product still in partials (several loads per element): several blocks per
+  // token, four head slots each, so that a row is read by many SMs at once
+  const dim3 grid(n_tokens, (n_tokens <= 64 || partials != nullptr) ? (Hq + 2 * Hkv + 3) / 4 : 1);
   if (dtype == FERRUM_F32)
     launch_kernel(rope_cache_kernel<float>, grid, threads, 0, stream, (float*)qkv, ld, positions, req_of_token, block_table,
         table_width, cos_sin, n_pos, (float*)kv_plane, page_stride, page_size, Hq, Hkv, D, R, pairing, write_kv, err_flag, L);

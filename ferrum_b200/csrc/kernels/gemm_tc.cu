@@ -940,8 +940,10 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
 // (fence, counter, reload) is a serial tail of several microseconds per launch.  In deferred
 // mode the kernel stops after writing its float32 partials; the kernel that consumes the
 // product (RMSNorm, the rotary kernel, ...) adds them while it reads, in K order, with
-// partial_sum() of partials.cuh.  Requirements: one token tile (M <= 64) and at most one
-// output tile per CTA, so that a CTA writes at most two partials.
+// partial_sum() of partials.cuh.  Requirements: one token tile (M <= 256, or 128 for two
+// products) and at most one output tile per CTA, so that a CTA writes at most two partials.
+// With 65 to 256 tokens the in-kernel reduction is worse still: the last arriver of a tile
+// reads several 64 to 128 KB partials and read-modify-writes the output on its own.
 FERRUM_API int ferrum_gemm_tc_can_defer(int M, int N, int K, int dual, int n_ctas) {
   if (n_ctas <= 0) n_ctas = sm_count();
   const int bt = ferrum_gemm_tc_token_tile(M, dual);
@@ -950,7 +952,7 @@ FERRUM_API int ferrum_gemm_tc_can_defer(int M, int N, int K, int dual, int n_cta
   if (n_ctas > units) n_ctas = (int)units;
   // at most 8 CTAs may share a tile (the consumers keep that many loads in flight per element)
   const long long per = units / n_ctas;
-  return M > 0 && bt <= 64 && tiles <= n_ctas && per > 0 && ((K + TILE_K - 1) / TILE_K) / per + 2 <= 8;
+  return M > 0 && M <= bt && tiles <= n_ctas && per > 0 && ((K + TILE_K - 1) / TILE_K) / per + 2 <= 8;
 }
 
 // layout[0..3] = k-blocks per tile, tiles, CTAs, columns per partial: what partial_sum() needs.
@@ -964,7 +966,7 @@ FERRUM_API int ferrum_gemm_tc_deferred(const void* x, const void* w, int M, int 
   const bool dual = dual_offset > 0;
   FERRUM_CHECK_ARG(w_rows >= N + dual_offset, "gemm_tc_deferred: w has %d rows, needs %d", w_rows, N + dual_offset);
   FERRUM_CHECK_ARG(ferrum_gemm_tc_can_defer(M, N, K, dual, n_ctas), "gemm_tc_deferred: shape M=%d N=%d K=%d cannot defer its "
-                   "reduction (more than 64 tokens, or more output tiles than CTAs)", M, N, K);
+                   "reduction (more than one token tile, or more output tiles than CTAs)", M, N, K);
   if (n_ctas <= 0) n_ctas = sm_count();
   const int bt = ferrum_gemm_tc_token_tile(M, dual);
   const int nkb = (K + TILE_K - 1) / TILE_K, tiles = (N + TILE_N - 1) / TILE_N;
@@ -986,6 +988,9 @@ FERRUM_API int ferrum_gemm_tc_deferred(const void* x, const void* w, int M, int 
     case 16: return dual ? launch_tc<16, true>(mw, mx, p, n_ctas, stream) : launch_tc<16, false>(mw, mx, p, n_ctas, stream);
     case 32: return dual ? launch_tc<32, true>(mw, mx, p, n_ctas, stream) : launch_tc<32, false>(mw, mx, p, n_ctas, stream);
     case 64: return dual ? launch_tc<64, true>(mw, mx, p, n_ctas, stream) : launch_tc<64, false>(mw, mx, p, n_ctas, stream);
+    case 128: return dual ? launch_tc<128, true>(mw, mx, p, n_ctas, stream) : launch_tc<128, false>(mw, mx, p, n_ctas, stream);
+    case 256:
+      if (!dual) return launch_tc<256, false>(mw, mx, p, n_ctas, stream);
   }
   FERRUM_CHECK_ARG(false, "gemm_tc_deferred: no kernel for token tile %d", bt);
 }

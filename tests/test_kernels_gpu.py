@@ -501,7 +501,8 @@ def test_sampling_matches_plain(ops, V):
 
 
 # ---------------------------------------------------------------- deferred reduction
-@pytest.mark.parametrize("M,N,K", [(1, 384, 512), (8, 6144, 4096), (33, 1000, 264), (64, 4096, 2048)])
+@pytest.mark.parametrize("M,N,K", [(1, 384, 512), (8, 6144, 4096), (33, 1000, 264), (64, 4096, 2048), (100, 4096, 4096),
+                                   (200, 2048, 1024), (256, 4096, 14336)])
 def test_gemm_deferred_partials_and_their_consumers(ops, M, N, K):
     """The product left as partials, summed by each kind of consumer: the residual reduce,
     the norm that adds a pending residual, and (two products) the SwiGLU reduce."""
@@ -525,7 +526,10 @@ def test_gemm_deferred_partials_and_their_consumers(ops, M, N, K):
     own = h0.clone()
     ops.gemm_tc(x, w, own, ops.TC_RESIDUAL, e, torch.empty(floats2, device="cuda"),
                 torch.zeros(tiles, dtype=torch.int32, device="cuda"))
-    assert torch.equal(own, h)
+    if ops.gemm_tc_token_tile(M, False) <= 128:
+        assert torch.equal(own, h)
+    else:   # more than 128 tokens: the kernel's own reduction runs on CTA pairs, which cut K elsewhere
+        assert ((own.double() - (h0.double() + ref)).abs() <= lim(ref, 2e-5) * math.sqrt(K)).all()
     # the norm adds the pending sum, writes the residual back and normalises it
     part = ops.gemm_tc_deferred(x, w, e, ws)
     h2 = h0.clone()
