@@ -329,6 +329,14 @@ def test_attention_tc(ops, Hq, Hkv, D, ps, window):
     g = torch.Generator(device="cuda").manual_seed(28)
     T = sum(qlens)
     q = torch.randn(T, Hq * D, device="cuda", generator=g).bfloat16()
+    if window > 0:
+        # pages that every query's window has passed are given back, as the cache manager does:
+        # their table entries are -1 and their contents belong to someone else (NaN here)
+        for r, (n, ql) in enumerate(zip(lens, qlens)):
+            first_needed = max(0, n - ql - window + 1) // ps
+            for lp in range(first_needed):
+                plane[table[r, lp].item()] = float("nan")
+                table[r, lp] = -1
     counts = {}
     out, _ = run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window, use_tc=True, counts=counts)
     assert counts.get("tc", 0) > 0 and (window > 0 or counts.get("split_tc", 0) > 0), counts
