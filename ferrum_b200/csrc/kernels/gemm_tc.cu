@@ -424,7 +424,8 @@ constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + 2 
 
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                    const __grid_constant__ CUtensorMap tmap_out, const TcParams p) {
+                    const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_ws,
+                    const TcParams p) {
   constexpr int STAGES = PAIR_STAGES;
   constexpr int ACC_COLS = PAIR_BT;
   extern __shared__ uint8_t smem_raw[];
@@ -455,7 +456,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     is_last = 0;
     prefetch_tensormap(&tmap_w);
     prefetch_tensormap(&tmap_x);
-    if (p.out_tma) prefetch_tensormap(&tmap_out);
+    if (p.out_tma) {
+      prefetch_tensormap(&tmap_out);
+      prefetch_tensormap(&tmap_ws);
+    }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);   // the leader's: its producer's expect_tx; bytes arrive from both CTAs
       mbar_init(empty_bar(s), 1);  // one multicast commit of the leader's MMA thread
@@ -570,31 +574,39 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     int seg = 0;
     long long u = u_begin;
     pdl_wait();
+    // A staging buffer, once the bulk store that last used it has read it; and its way out:
+    // through a tensor map (which clips at the tensor's edges), as a store or a float32 add.
+    auto stage_acquire = [&]() {
+      const int b = emitted & 1;
+      if (ep_tid == 0) bulk_wait_read<1>();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      return out_stage + b * PAIR_OUT_BYTES;
+    };
+    auto stage_send = [&](uint8_t* st, const CUtensorMap* map, bool add, int x, int y) {
+      fence_proxy_async();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ep_tid == 0) {
+        if (add) tma_reduce_add_2d(map, smem_u32(st), x, y);
+        else tma_store_2d(map, smem_u32(st), x, y);
+        bulk_commit();
+      }
+      ++emitted;
+    };
     // 32 token columns c0.. of this thread's feature go to `out`: staged and sent through the
     // tensor map (which clips at M and N), or written by the thread itself.
     auto emit32 = [&](int t0, int c0, int n0_cta, const float (&v)[32]) {
       if (staged) {
-        const int b = emitted & 1;
-        if (ep_tid == 0) bulk_wait_read<1>();  // the store that last used this buffer has read it
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint8_t* stage = stage_acquire();
         if (p.epilogue == TC_RESIDUAL) {
-          float* st = (float*)(out_stage + b * PAIR_OUT_BYTES);
+          float* st = (float*)stage;
 #pragma unroll
           for (int j = 0; j < 32; ++j) st[j * TILE_N + n_local] = v[j];
         } else {
-          __nv_bfloat16* st = (__nv_bfloat16*)(out_stage + b * PAIR_OUT_BYTES);
+          __nv_bfloat16* st = (__nv_bfloat16*)stage;
 #pragma unroll
           for (int j = 0; j < 32; ++j) st[j * TILE_N + n_local] = __float2bfloat16_rn(v[j]);
         }
-        fence_proxy_async();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ep_tid == 0) {
-          const uint32_t src = smem_u32(out_stage + b * PAIR_OUT_BYTES);
-          if (p.epilogue == TC_RESIDUAL) tma_reduce_add_2d(&tmap_out, src, n0_cta, t0 + c0);
-          else tma_store_2d(&tmap_out, src, n0_cta, t0 + c0);
-          bulk_commit();
-        }
-        ++emitted;
+        stage_send(stage, &tmap_out, p.epilogue == TC_RESIDUAL, n0_cta, t0 + c0);
       } else if (n0_cta + n_local < p.N) {
         float lo[16], hi[16];
 #pragma unroll
@@ -659,13 +671,30 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         // half-tile partial -> workspace [cluster][end][rank][column][lane]
         const int c_first = unit_owner(tile * nkb, U, P), c_last = unit_owner(tile * nkb + nkb - 1, U, P);
         const int n_contrib = c_last - c_first + 1;
-        float* ws = p.workspace + (((size_t)cluster * 2 + (u_begin / nkb == tile ? 0 : 1)) * 2 + rank) * tile_floats;
+        const size_t my_slot = ((size_t)cluster * 2 + (u_begin / nkb == tile ? 0 : 1)) * 2 + rank;
+        float* ws = p.workspace + my_slot * tile_floats;
+        if (staged) {
+          // the partial leaves like the output: 32 columns at a time through shared memory, as bulk
+          // stores into the workspace seen as rows of 128 floats
 #pragma unroll 1
-        for (int c0 = 0; c0 < ACC_COLS; c0 += 16) {
-          float v[16];
-          tmem_ld16(acc_addr + c0, v);
+          for (int c0 = 0; c0 < ACC_COLS; c0 += 32) {
+            float v[32];
+            tmem_ld16(acc_addr + c0, &v[0]);
+            tmem_ld16(acc_addr + c0 + 16, &v[16]);
+            float* st = (float*)stage_acquire();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) ws[(size_t)(c0 + j) * TILE_N + n_local] = v[j];
+            for (int j = 0; j < 32; ++j) st[j * TILE_N + n_local] = v[j];
+            stage_send((uint8_t*)st, &tmap_ws, false, 0, (int)(my_slot * ACC_COLS) + c0);
+          }
+          if (ep_tid == 0) bulk_wait_all();  // the partial is written before it is announced
+        } else {
+#pragma unroll 1
+          for (int c0 = 0; c0 < ACC_COLS; c0 += 16) {
+            float v[16];
+            tmem_ld16(acc_addr + c0, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ws[(size_t)(c0 + j) * TILE_N + n_local] = v[j];
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -679,7 +708,53 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           if (is_last) *counter = 0;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (is_last) {  // the same for the four warps: they go through emit32's barriers together
+        if (is_last && staged) {
+          // The last arriver adds the partials in K order.  A thread takes four neighbouring
+          // features of eight columns, two contributors at a time: 16-byte loads, 16 of them in
+          // flight per thread (with one load of 4 bytes per feature and column this reduction,
+          // not the products, set the time of a product of a few hundred tokens).
+          __threadfence();
+          const int q4 = (ep_tid & 31) * 4, cg = (ep_tid >> 5) * 8;
+          auto slot_of = [&](int cc) { return ((size_t)cc * 2 + ((U * cc / P) / nkb == tile ? 0 : 1)) * 2 + rank; };
+#pragma unroll 1
+          for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
+            float4 acc[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int cc = c_first; cc <= c_last; cc += 2) {
+              const bool two = cc + 1 <= c_last;
+              const float4* a = reinterpret_cast<const float4*>(p.workspace + slot_of(cc) * tile_floats + (size_t)(c0 + cg) * TILE_N + q4);
+              const float4* b = reinterpret_cast<const float4*>(p.workspace + slot_of(two ? cc + 1 : cc) * tile_floats +
+                                                                (size_t)(c0 + cg) * TILE_N + q4);
+              float4 va[8], vb[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                va[k] = __ldcg(a + k * (TILE_N / 4));
+                vb[k] = two ? __ldcg(b + k * (TILE_N / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {  // first cc, then cc + 1: K order
+                acc[k].x += va[k].x; acc[k].y += va[k].y; acc[k].z += va[k].z; acc[k].w += va[k].w;
+                acc[k].x += vb[k].x; acc[k].y += vb[k].y; acc[k].z += vb[k].z; acc[k].w += vb[k].w;
+              }
+            }
+            uint8_t* stage = stage_acquire();
+            if (p.epilogue == TC_RESIDUAL) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) *reinterpret_cast<float4*>((float*)stage + (cg + k) * TILE_N + q4) = acc[k];
+            } else {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(acc[k].x, acc[k].y), hi = __floats2bfloat162_rn(acc[k].z, acc[k].w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>((__nv_bfloat16*)stage + (cg + k) * TILE_N + q4) = pk;
+              }
+            }
+            stage_send(stage, &tmap_out, p.epilogue == TC_RESIDUAL, n0, t0 + c0);
+          }
+        } else if (is_last) {  // the same for the four warps: they go through emit32 together
           __threadfence();
 #pragma unroll 1
           for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
@@ -809,8 +884,8 @@ static bool g_pair_kernel = true;
 // The CTA-pair kernel can be switched off (every shape then runs on the single-CTA kernel).
 FERRUM_API void ferrum_set_gemm_pair_kernel(int on) { g_pair_kernel = on != 0; }
 
-static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const TcParams& p, int n_ctas,
-                          cudaStream_t stream) {
+static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const CUtensorMap& ms,
+                          const TcParams& p, int n_ctas, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
@@ -831,7 +906,7 @@ static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CU
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ferrum_dependent_launch_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, mo, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, mo, ms, p);
   FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc: pair kernel launch failed: %s", cudaGetErrorString(e));
   FERRUM_CHECK_LAUNCH("gemm_tc_pair");
   return 0;
@@ -917,7 +992,13 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
       if (int r = get_tensor_map(out, M, N, ldo, PAIR_OUT_ROWS, &mo, epilogue == TC_RESIDUAL ? 1 : 2)) return r;
       p.out_tma = 1;
     }
-    return launch_tc_pair(mw, mx, mo, p, 2 * pairs, stream);
+    // the workspace as rows of 128 floats (one row per column of a partial half tile)
+    CUtensorMap ms = mw;
+    if (p.out_tma) {
+      FERRUM_CHECK_ARG(((uintptr_t)workspace & 15) == 0, "gemm_tc: the workspace must be 16-byte aligned");
+      if (int r = get_tensor_map(workspace, workspace_floats / TILE_N, TILE_N, TILE_N, PAIR_OUT_ROWS, &ms, 1)) return r;
+    }
+    return launch_tc_pair(mw, mx, mo, ms, p, 2 * pairs, stream);
   }
   if (int r = get_tensor_map(x, M, K, ldx, bt, &mx)) return r;
 #define TC_CASE(BT_)                                                         \
