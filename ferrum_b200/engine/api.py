@@ -132,9 +132,10 @@ class Engine:
         """Plan a batch, run it, sample on the device, read the ids back, commit.
 
         While the GPU runs the batch the scheduler is asked for the one after it
-        (`plan_ahead`); if that is decided already, it is queued behind the running one, with
-        its token ids already on the device, where the sampling kernel of this step writes them, and the
-        next call finds it in flight.  The events returned are always those of one step."""
+        (`plan_ahead`); if that is decided already, it is queued behind the running one (its
+        token ids are on the device already: this step's sampling kernel writes them where the
+        next step reads its tokens), and the next call finds it in flight.  The events returned
+        are always those of one step."""
         if self._in_flight is None:
             plan = self.scheduler.plan()
             if not plan:

@@ -28,8 +28,9 @@ class DeviceSampler:
 
     `launch` enqueues the kernel and the copy of its ids to the host and returns at once;
     `collect` waits for that copy.  Two samplings may be in flight (the engine queues the next
-    step before it reads this one), so the pinned buffers are rings; the ids of the latest
-    launch also stay on the device (`ids_device`) for a step that takes its tokens from there."""
+    step before it reads this one), so the pinned buffers are rings.  The kernel can write the
+    ids to a second place on the device as well (`also_to`): the token buffer of a step that is
+    queued behind this one.  The kernels' error flag lives behind the ids (`err`)."""
 
     DEPTH = 4
 
