@@ -589,26 +589,43 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
   }
 }
 
-// bfloat16 rows of 16-byte multiples: eight features per thread, 16-byte loads and stores.
+// bfloat16 rows of 16-byte multiples: 16-byte loads and stores, SWIGLU_VEC groups of eight features
+// per thread with all their loads issued before the arithmetic.
+constexpr int SWIGLU_VEC = 4;
 __global__ void __launch_bounds__(256)
 swiglu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int F, int ld_in, int ld_out) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.y;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;  // group of eight features
-  if (i * 8 >= F) return;
-  const uint4 g = *reinterpret_cast<const uint4*>(gu + (size_t)t * ld_in + i * 8);
-  const uint4 u = *reinterpret_cast<const uint4*>(gu + (size_t)t * ld_in + F + i * 8);
-  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
-  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-  uint4 o;
-  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+  const int groups = F >> 3;
+  const int i0 = blockIdx.x * (blockDim.x * SWIGLU_VEC) + threadIdx.x;  // this thread's groups: i0 + k * blockDim.x
+  const __nv_bfloat16* row = gu + (size_t)t * ld_in;
+  uint4 g[SWIGLU_VEC], u[SWIGLU_VEC];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const float2 gv = __bfloat1622float2(g2[k]), uv = __bfloat1622float2(u2[k]);
-    o2[k] = __floats2bfloat162_rn(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y);
+  for (int k = 0; k < SWIGLU_VEC; ++k) {
+    const int i = i0 + k * blockDim.x;
+    if (i < groups) {
+      g[k] = *reinterpret_cast<const uint4*>(row + i * 8);
+      u[k] = *reinterpret_cast<const uint4*>(row + F + i * 8);
+    }
   }
-  *reinterpret_cast<uint4*>(act + (size_t)t * ld_out + i * 8) = o;
+#pragma unroll
+  for (int k = 0; k < SWIGLU_VEC; ++k) {
+    const int i = i0 + k * blockDim.x;
+    if (i >= groups) continue;
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g[k]);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u[k]);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 gv = __bfloat1622float2(g2[j]), uv = __bfloat1622float2(u2[j]);
+      // fast exponential and division, as in the products' own SwiGLU epilogues: the result is
+      // rounded to bfloat16, and the arithmetic, not the memory, set this kernel's time
+      o2[j] = __floats2bfloat162_rn(__fdividef(gv.x, 1.0f + __expf(-gv.x)) * uv.x, __fdividef(gv.y, 1.0f + __expf(-gv.y)) * uv.y);
+    }
+    *reinterpret_cast<uint4*>(act + (size_t)t * ld_out + i * 8) = o;
+  }
 }
 
 // act[t, f] = silu(gate) * up where gate and up are still partials of a two-product launch
@@ -649,7 +666,7 @@ FERRUM_API int ferrum_swiglu(const void* gu, void* act, int dtype, int n_tokens,
   FERRUM_CHECK_ARG(n_tokens <= 65535, "swiglu: more than 65535 tokens in one call");
   if (dtype == FERRUM_BF16 && F % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && ((uintptr_t)gu & 15) == 0 &&
       ((uintptr_t)act & 15) == 0) {
-    dim3 vgrid((F / 8 + 255) / 256, n_tokens);
+    dim3 vgrid((F / 8 + 256 * SWIGLU_VEC - 1) / (256 * SWIGLU_VEC), n_tokens);
     launch_kernel(swiglu_vec_kernel, vgrid, dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, F, ld_in, ld_out);
     FERRUM_CHECK_LAUNCH("swiglu");
     return 0;
