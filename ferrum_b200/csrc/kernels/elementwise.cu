@@ -441,7 +441,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
 // Many tokens, bfloat16, the whole head rotated (R == D, D a multiple of 16): a thread rotates
 // eight pairs with 16-byte loads and stores, or copies eight value elements.  Same formulas and
 // the same error codes as the kernel above.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ positions,
                       const int* __restrict__ req_of_token, const int* __restrict__ block_table, int table_width,
                       const float* __restrict__ cos_sin, int n_pos, __nv_bfloat16* __restrict__ kv_plane,
@@ -452,9 +452,8 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __rest
   const int chunks = D >> 4;                         // rotation items per head
   const int rot_items = (Hq + Hkv) * chunks;
   const int per_token = rot_items + (write_kv ? Hkv * (D >> 3) : 0);
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (long long)n_tokens * per_token) return;
-  const int t = (int)(idx / per_token), item = (int)(idx % per_token);
+  const int t = blockIdx.y, item = blockIdx.x * blockDim.x + threadIdx.x;   // the grid is (items, tokens)
+  if (item >= per_token) return;
   const int pos = positions[t];
   const int half = D >> 1;
   if (pos < 0 || pos >= n_pos) {
@@ -546,11 +545,11 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
     FERRUM_CHECK_ARG((write_kv ? Hq + 2 * Hkv : Hq) * D <= L.tiles * 128 && n_tokens <= L.acc_cols,
                      "rope: the partials do not cover the rows");
   }
-  if (dtype == FERRUM_BF16 && n_tokens > 64 && partials == nullptr && R == D && D % 16 == 0 && ld % 8 == 0 &&
+  if (dtype == FERRUM_BF16 && n_tokens > 64 && n_tokens <= 65535 && partials == nullptr && R == D && D % 16 == 0 && ld % 8 == 0 &&
       ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)cos_sin & 15) == 0 &&
       (!write_kv || (((uintptr_t)kv_plane & 15) == 0 && page_stride % 8 == 0))) {
-    const long long items = (long long)n_tokens * ((Hq + Hkv) * (D / 16) + (write_kv ? Hkv * (D / 8) : 0));
-    launch_kernel(rope_cache_vec_kernel, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, stream, (__nv_bfloat16*)qkv, ld,
+    const int per_token = (Hq + Hkv) * (D / 16) + (write_kv ? Hkv * (D / 8) : 0);
+    launch_kernel(rope_cache_vec_kernel, dim3((per_token + 127) / 128, n_tokens), dim3(128), 0, stream, (__nv_bfloat16*)qkv, ld,
                   positions, req_of_token, block_table, table_width, cos_sin, n_pos, (__nv_bfloat16*)kv_plane, page_stride,
                   page_size, Hq, Hkv, D, pairing, write_kv, n_tokens, err_flag);
     FERRUM_CHECK_LAUNCH("rope_cache_write");
