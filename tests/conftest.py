@@ -36,6 +36,13 @@ TINY_D = {
                      "original_max_position_embeddings": 32},
     "max_position_embeddings": 1024, "rms_norm_eps": 2e-5, "tie_word_embeddings": True,
 }
+# Not tiny: wide enough for the kernels that only many tokens and many tiles reach (CTA-pair
+# products cut across several CTAs, tcgen05 attention over several items, split key ranges).
+MID_E = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 1024, "num_hidden_layers": 2, "num_attention_heads": 8,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 2816, "vocab_size": 1500, "rope_theta": 500000.0,
+    "rope_scaling": None, "max_position_embeddings": 2048, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
 TINY = {"A": (TINY_A, 0, "float32"), "B": (TINY_B, 1, "bfloat16"), "C": (TINY_C, 2, "float32"),
         "D": (TINY_D, 3, "bfloat16")}
 
@@ -49,7 +56,7 @@ def model_dirs(tmp_path_factory):
     """name -> folder with config.json + model.safetensors, written by the random-weights mode."""
     from ferrum_b200.weights import write_random_model
     out = {}
-    for name, (cfg, seed, dtype) in TINY.items():
+    for name, (cfg, seed, dtype) in list(TINY.items()) + [("E", (MID_E, 5, "bfloat16"))]:
         d = tmp_path_factory.mktemp("tiny_" + name)
         write_random_model(cfg, str(d), seed, dtype=dtype)
         out[name] = str(d)

@@ -113,6 +113,27 @@ def test_mixed_batches_with_page_reuse(cuda, model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_wide_model_with_many_tokens_per_step(cuda, model_dirs, dtype):
+    """A model wide enough (1024 features, head size 128) and steps long enough for the kernels
+    that the tiny configurations never reach: products of 300 to 400 tokens on CTA pairs, cut
+    across several CTAs; products of 200 tokens whose reduction is left to the next kernel;
+    tcgen05 attention over several work items, with and without history; decoded tokens of one
+    request beside a prompt portion of another."""
+    from conftest import MID_E
+    vocab = MID_E["vocab_size"]
+    a, b = random_tokens(730, vocab, 31), random_tokens(215, vocab, 32)
+    r = Replay(session(model_dirs, "E", dtype, 1152))
+    r.step([("a", a[:400], "all")])
+    r.step([("a", a[400:700], "all")])
+    r.step([("a", a[700:701], "all"), ("b", b[:200], "all")])
+    for i in range(15):
+        r.step([("a", a[701 + i:702 + i], "all"), ("b", b[200 + i:201 + i], "all")])
+    r.step([("a", a[716:730], "all")], end=["a", "b"])
+    assert_close(r.logits("a", len(a)), plain_logits(model_dirs["E"], dtype, a), dtype, "wide a")
+    assert_close(r.logits("b", len(b)), plain_logits(model_dirs["E"], dtype, b), dtype, "wide b")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(cuda, model_dirs, dtype):
     """Several hundred tokens one by one: many pages, many page edges."""
     vocab = TINY["C"][0]["vocab_size"]
