@@ -17,9 +17,9 @@
 // memory, by the row's own thread) when it grows by more than 2^8; until then P is computed
 // against the older maximum, which changes nothing in the quotient O / l.
 //
-// Roles (352 threads): warp 0 = TMA producer, warp 1 = tensor memory owner and MMA issuer of
-// tile 0, warps 2..5 = rows of tile 0, warps 6..9 = rows of tile 1, warp 10 = MMA issuer of tile
-// 1 (one issuing thread each: while one does its waits and commits, the other's products run).  Every wait is bounded; on a
+// Roles (352 threads): warp 0 = TMA producer, warps 1 and 2 = MMA issuers of tile 0 and 1 (one
+// issuing thread each: while one does its waits and commits, the other's products run; warp 1
+// also owns the tensor memory), warps 3..6 = rows of tile 0, warps 7..10 = rows of tile 1.  Every wait is bounded; on a
 // timeout the kernel raises the error flag, lets copies in flight land, frees its tensor
 // memory and returns.  An item whose key range is a split writes (m, l, O) partials in the
 // layout of the mma.sync kernel (attention_flash.cu) and `attention_combine` merges them.
@@ -35,9 +35,6 @@ using namespace sm100;
 
 namespace {
 
-constexpr int TC_BN = 64;       // keys per stage
-constexpr int TC_STAGES = 3;
-constexpr int TC_THREADS = 352;
 constexpr float TC_LAZY = 8.0f;  // the running maximum moves when it grows by more than this (log2 units)
 
 struct AttnTcParams {
@@ -54,24 +51,29 @@ struct AttnTcParams {
   float scale_log2;
 };
 
-template <int D>
+// NT row tiles per CTA, BN keys per stage, NS stages of keys and of values.
+template <int D, int NT, int BN, int NS>
 struct AttnTcConfig {
-  static constexpr int HALVES = D / 64;
+  static constexpr int HALVES = D / 64;                          // 64-column spans of a head
+  static constexpr int SPANS = BN / 64;                          // 64-key spans of a stage (rows of P)
   static constexpr int Q_TILE_BYTES = HALVES * 128 * 128;       // 128 rows x 128 bytes per 64 columns
-  static constexpr int KV_HALF_BYTES = TC_BN * 128;
+  static constexpr int KV_HALF_BYTES = BN * 128;
   static constexpr int KV_STAGE_BYTES = HALVES * KV_HALF_BYTES;
-  static constexpr int P_TILE_BYTES = 128 * 128;                 // 128 rows x 64 keys
+  static constexpr int P_TILE_BYTES = SPANS * 128 * 128;         // 128 rows x BN keys
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + 2 * Q_TILE_BYTES;
-  static constexpr int OFF_V = OFF_K + TC_STAGES * KV_STAGE_BYTES;
-  static constexpr int OFF_P = OFF_V + TC_STAGES * KV_STAGE_BYTES;
-  static constexpr int OFF_BARS = OFF_P + 2 * P_TILE_BYTES;
-  static constexpr int N_BARS = 1 + 4 * TC_STAGES + 8;
+  static constexpr int OFF_K = OFF_Q + NT * Q_TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + NS * KV_STAGE_BYTES;
+  static constexpr int OFF_P = OFF_V + NS * KV_STAGE_BYTES;
+  static constexpr int OFF_BARS = OFF_P + NT * P_TILE_BYTES;
+  static constexpr int N_BARS = 1 + 4 * NS + 4 * NT;
   static constexpr int SMEM_BYTES = OFF_BARS + N_BARS * 8 + 1024 /*alignment slack*/;
-  static constexpr int S_COL = 0;                 // S of tile t, buffer b: columns (2 t + b) * 64 ..
-  static constexpr int O_COL = 4 * TC_BN;         // O of tile t: columns O_COL + t * D ..
+  static constexpr int S_COL = 0;                 // S of tile t, buffer b: columns (2 t + b) * BN ..
+  static constexpr int O_COL = NT * 2 * BN;       // O of tile t: columns O_COL + t * D ..
   static constexpr int TMEM_COLS = 512;
-  static_assert(O_COL + 2 * D <= TMEM_COLS, "accumulators do not fit tensor memory");
+  static constexpr int THREADS = 32 * (1 + NT + 4 * NT);   // producer, one issuer and four softmax warps per tile
+  static_assert(O_COL + NT * D <= TMEM_COLS, "accumulators do not fit tensor memory");
+  static_assert(SMEM_BYTES <= 232448, "stages do not fit shared memory");
+  static_assert(BN % 64 == 0 && BN <= 256, "a stage is one or more 64-key spans");
 };
 
 // MN-major shared-memory operand with the 128-byte swizzle: 64 elements along N (128 bytes)
@@ -138,10 +140,10 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int D>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int D, int NT, int BN, int NS>
+__global__ void __launch_bounds__(AttnTcConfig<D, NT, BN, NS>::THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const AttnTcParams p) {
-  using Cfg = AttnTcConfig<D>;
+  using Cfg = AttnTcConfig<D, NT, BN, NS>;
   constexpr int HALVES = Cfg::HALVES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -161,25 +163,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t bar_base = smem_base + Cfg::OFF_BARS;
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto k_empty = [&](int s) { return bar_base + 8u * (1 + TC_STAGES + s); };
-  auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * TC_STAGES + s); };
-  auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * TC_STAGES + s); };
-  auto s_ready = [&](int t, int b) { return bar_base + 8u * (1 + 4 * TC_STAGES + 2 * t + b); };
-  auto p_ready = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + 4 + t); };
-  auto pv_done = [&](int t) { return bar_base + 8u * (1 + 4 * TC_STAGES + 6 + t); };
+  auto k_empty = [&](int s) { return bar_base + 8u * (1 + NS + s); };
+  auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * NS + s); };
+  auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * NS + s); };
+  auto s_ready = [&](int t, int b) { return bar_base + 8u * (1 + 4 * NS + 2 * t + b); };
+  auto p_ready = [&](int t) { return bar_base + 8u * (1 + 4 * NS + 2 * NT + t); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (1 + 4 * NS + 3 * NT + t); };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_kv);
     mbar_init(q_full, 1);
-    for (int s = 0; s < TC_STAGES; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(k_full(s), 1);
-      mbar_init(k_empty(s), 2);   // one commit per issuer
+      mbar_init(k_empty(s), NT);   // one commit per issuer
       mbar_init(v_full(s), 1);
-      mbar_init(v_empty(s), 2);
+      mbar_init(v_empty(s), NT);
     }
-    for (int t = 0; t < 2; ++t) {
+    for (int t = 0; t < NT; ++t) {
       mbar_init(s_ready(t, 0), 1);
       mbar_init(s_ready(t, 1), 1);
       mbar_init(p_ready(t), 128);
@@ -208,80 +210,73 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int qs = p.q_start[req];
   const int q_len = p.q_start[req + 1] - qs;
   const int pos0 = p.pos0[req];
-  const int tok0 = row0 / G;                       // first token of the item within its request
-  const int kv0 = kv_begin & ~(TC_BN - 1);         // stages start on 64-key borders: whole pages
-  const int n_j = (kv_end - kv0 + TC_BN - 1) / TC_BN;
+  const int tok0 = row0 / G;                  // first token of the item within its request
+  const int kv0 = kv_begin & ~(BN - 1);       // stages start on BN-key borders: whole pages
+  const int n_j = (kv_end - kv0 + BN - 1) / BN;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    // Lane 0 waits and posts the byte counts; lane i fetches page i of the stage (its table
-    // entry is read one stage ahead, so that the lookups of a stage overlap instead of queueing).
+    // Lane 0 waits and posts the byte counts; lane i fetches page i of a stage (its table entry
+    // is read one stage ahead, so that the lookups of a stage overlap instead of queueing).  The
+    // keys of stage j + 1 are requested before the values of stage j: the scores run ahead.
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * HALVES * tok * G * 128);
-      for (int t = 0; t < 2; ++t)
+      mbar_expect_tx(q_full, NT * HALVES * tok * G * 128);
+      for (int t = 0; t < NT; ++t)
         for (int h = 0; h < HALVES; ++h)
           tma_load_3d(smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES + h * 128 * 128, &map_q, q_full, h * 64, kvh * G,
                       qs + tok0 + t * tok);
     }
     const int ps = p.page_size;
-    const int pages_per_stage = TC_BN / ps;
+    const int pages_per_stage = BN / ps;
     const int* bt = p.block_table + (size_t)req * p.table_width;
     auto page_of = [&](int j) {  // this lane's page of stage j; a missing page reads as zeros (masked keys)
-      const int lp = ((kv0 + j * TC_BN) >> p.page_shift) + lane;
-      return (lane < pages_per_stage && j < n_j && lp < p.table_width) ? bt[lp] : -1;
+      const int lp = ((kv0 + j * BN) >> p.page_shift) + lane;
+      return (lane < pages_per_stage && j >= 0 && j < n_j && lp < p.table_width) ? bt[lp] : -1;
     };
-    int page = page_of(0);
+    // one stage of keys (kv = 0) or values (kv = 1); false on a timeout
+    auto load_stage = [&](int j, int kv, int page) {
+      const int s = j % NS;
+      const uint32_t parity = ((j / NS) & 1) ^ 1;
+      const uint32_t full = kv ? v_full(s) : k_full(s);
+      bool ok = true;
+      if (lane == 0) {
+        ok = mbar_wait(kv ? v_empty(s) : k_empty(s), parity, abort_p);
+        if (ok) mbar_expect_tx(full, Cfg::KV_STAGE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return false;
+      if (lane < pages_per_stage) {
+        const int y = page < 0 ? -ps : ((page * 2 + kv) * p.Hkv + kvh) * ps;   // a negative row: the box reads as zeros
+        const uint32_t dst = smem_base + (kv ? Cfg::OFF_V : Cfg::OFF_K) + s * Cfg::KV_STAGE_BYTES + lane * ps * 128;
+        for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * Cfg::KV_HALF_BYTES, &map_kv, full, h * 64, y);
+      }
+      return true;
+    };
+    int page_v = -1, page_k = page_of(0);
     bool ok = true;
-    for (int j = 0; j < n_j; ++j) {
-      const int s = j % TC_STAGES;
-      const uint32_t parity = ((j / TC_STAGES) & 1) ^ 1;
-      const int next_page = page_of(j + 1);
-      const int pg = page < 0 ? -1 : page;
-      const uint32_t dst = s * Cfg::KV_STAGE_BYTES + lane * ps * 128;
-      if (lane == 0) {
-        ok = mbar_wait(k_empty(s), parity, abort_p);
-        if (ok) mbar_expect_tx(k_full(s), Cfg::KV_STAGE_BYTES);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) {
-        abort_flag = 1;
-        if (lane == 0) atomicExch(p.err, 20);
-        break;
-      }
-      if (lane < pages_per_stage) {
-        const int y = (pg * 2 * p.Hkv + kvh) * ps;
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_2d(smem_base + Cfg::OFF_K + dst + h * Cfg::KV_HALF_BYTES, &map_kv, k_full(s), h * 64, y);
-      }
-      if (lane == 0) {
-        ok = mbar_wait(v_empty(s), parity, abort_p);
-        if (ok) mbar_expect_tx(v_full(s), Cfg::KV_STAGE_BYTES);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) {
-        abort_flag = 1;
-        if (lane == 0) atomicExch(p.err, 21);
-        break;
-      }
-      if (lane < pages_per_stage) {
-        const int y = ((pg * 2 + (page < 0 ? 0 : 1)) * p.Hkv + kvh) * ps;
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_2d(smem_base + Cfg::OFF_V + dst + h * Cfg::KV_HALF_BYTES, &map_kv, v_full(s), h * 64, y);
-      }
-      page = next_page;
+    for (int j = 0; ok && j <= n_j; ++j) {   // keys of stage j, then values of stage j - 1
+      const int next_k = page_of(j + 1);
+      if (j < n_j) ok = load_stage(j, 0, page_k);
+      if (ok && j > 0) ok = load_stage(j - 1, 1, page_v);
+      page_v = page_k;
+      page_k = next_k;
     }
-  } else if (warp == 1 || warp == 10) {
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0) atomicExch(p.err, 20);
+    }
+  } else if (warp <= NT) {
     // ------------------------------------------------------------ MMA issuer of one row tile
     if (lane == 0) {
-      const int t = warp == 1 ? 0 : 1;
-      const uint32_t idesc_qk = umma_idesc_bf16(128, TC_BN);
+      const int t = warp - 1;
+      const uint32_t idesc_qk = umma_idesc_bf16(128, BN);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B (values) is MN-major
       const uint32_t q_addr = smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES;
-      const uint64_t p_desc = umma_desc_k_sw128(smem_base + Cfg::OFF_P + t * Cfg::P_TILE_BYTES);
+      const uint32_t p_addr = smem_base + Cfg::OFF_P + t * Cfg::P_TILE_BYTES;
       const uint32_t o_tmem = tmem_base + Cfg::O_COL + t * D;
       auto issue_qk = [&](int s, int buf) {
         const uint32_t k_addr = smem_base + Cfg::OFF_K + s * Cfg::KV_STAGE_BYTES;
-        const uint32_t s_tmem = tmem_base + Cfg::S_COL + (2 * t + buf) * TC_BN;
+        const uint32_t s_tmem = tmem_base + Cfg::S_COL + (2 * t + buf) * BN;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const int h = kk >> 2, in = kk & 3;
@@ -290,32 +285,34 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
       };
       auto issue_pv = [&](int s, bool accumulate) {
-        const uint64_t v_desc = umma_desc_mn_sw128(smem_base + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES, Cfg::KV_HALF_BYTES, 1024);
+        const uint32_t v_addr = smem_base + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < TC_BN / 16; ++kk)  // 16 keys on: 32 bytes of a P row, 16 rows of V
-          umma_bf16(o_tmem, p_desc + (uint64_t)(kk * 2), v_desc + (uint64_t)(kk * 16 * 128 >> 4), idesc_pv, accumulate || kk > 0);
+        for (int kk = 0; kk < BN / 16; ++kk) {  // 16 keys on: 32 bytes of a P row (per 64-key span), 16 rows of V
+          const int span = kk >> 2, in = kk & 3;
+          umma_bf16(o_tmem, umma_desc_k_sw128(p_addr + span * 128 * 128) + (uint64_t)(in * 2),
+                    umma_desc_mn_sw128(v_addr + kk * 16 * 128, Cfg::KV_HALF_BYTES, 1024), idesc_pv, accumulate || kk > 0);
+        }
       };
       // the scores of stages 0 and 1 go ahead; in the loop the scores of stage j + 2 follow P V of stage j
       bool ok = mbar_wait(q_full, 0, abort_p);
       for (int jj = 0; ok && jj < 2 && jj < n_j; ++jj) {
-        ok = mbar_wait(k_full(jj), 0, abort_p);
+        ok = mbar_wait(k_full(jj % NS), (jj / NS) & 1, abort_p);
         if (!ok) break;
         tc_fence_after();
-        issue_qk(jj, jj);
+        issue_qk(jj % NS, jj);
         umma_commit(s_ready(t, jj));
-        umma_commit(k_empty(jj));
+        umma_commit(k_empty(jj % NS));
       }
       if (!ok) {
         abort_flag = 1;
         atomicExch(p.err, 22);
       }
       for (int j = 0; ok && j < n_j; ++j) {
-        const int s = j % TC_STAGES;
+        const int s = j % NS;
         const int jn = j + 2;
         const bool more = jn < n_j;
-        const int s2 = jn % TC_STAGES;
-        ok = mbar_wait(v_full(s), (j / TC_STAGES) & 1, abort_p);
-        if (ok && more) ok = mbar_wait(k_full(s2), (jn / TC_STAGES) & 1, abort_p);
+        const int s2 = jn % NS;
+        ok = mbar_wait(v_full(s), (j / NS) & 1, abort_p);
         if (!ok) {
           abort_flag = 1;
           atomicExch(p.err, 23);
@@ -332,6 +329,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         umma_commit(pv_done(t));
         umma_commit(v_empty(s));
         if (more) {
+          ok = mbar_wait(k_full(s2), (jn / NS) & 1, abort_p);
+          if (!ok) {
+            abort_flag = 1;
+            atomicExch(p.err, 23);
+            break;
+          }
+          tc_fence_after();
           issue_qk(s2, j & 1);
           umma_commit(s_ready(t, j & 1));
           umma_commit(k_empty(s2));
@@ -340,7 +344,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else {
     // ------------------------------------------------------------ softmax and output: one thread per row
-    const int t = (warp - 2) >> 2;            // row tile of this warp
+    const int t = (warp - 1 - NT) >> 2;       // row tile of this warp
     const int quarter = warp & 3;             // the tensor-memory lanes this warp may touch
     const int r = quarter * 32 + lane;        // row of the tile
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -364,24 +368,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         break;
       }
       tc_fence_after();
-      float s[TC_BN];
-      tmem_ld32(lane_addr + Cfg::S_COL + (2 * t + buf) * TC_BN, &s[0]);
-      tmem_ld32(lane_addr + Cfg::S_COL + (2 * t + buf) * TC_BN + 32, &s[32]);
-      const int key0 = kv0 + j * TC_BN;
-      const bool unmasked = tile_full && key0 + TC_BN - 1 <= qpos_min && key0 >= kv_begin && key0 + TC_BN <= kv_end &&
+      float s[BN];
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(lane_addr + Cfg::S_COL + (2 * t + buf) * BN + c0, &s[c0]);
+      const int key0 = kv0 + j * BN;
+      const bool unmasked = tile_full && key0 + BN - 1 <= qpos_min && key0 >= kv_begin && key0 + BN <= kv_end &&
                             (p.window == 0 || key0 > qpos_max - p.window);
       if (!unmasked) {
         const int hi = row_valid ? min(qpos, kv_end - 1) : -1;                                  // last visible key
         const int lo = max(kv_begin, p.window > 0 ? qpos - p.window + 1 : 0);                   // first visible key
 #pragma unroll
-        for (int c = 0; c < TC_BN; ++c) {
+        for (int c = 0; c < BN; ++c) {
           const int key = key0 + c;
           if (key > hi || key < lo) s[c] = -INFINITY;
         }
       }
       float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
 #pragma unroll
-      for (int c = 4; c < TC_BN; c += 4) {
+      for (int c = 4; c < BN; c += 4) {
         mx0 = fmaxf(mx0, s[c]);
         mx1 = fmaxf(mx1, s[c + 1]);
         mx2 = fmaxf(mx2, s[c + 2]);
@@ -416,9 +420,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-      uint32_t pk[TC_BN / 2];
+      uint32_t pk[BN / 2];
 #pragma unroll
-      for (int c = 0; c < TC_BN; c += 4) {
+      for (int c = 0; c < BN; c += 4) {
         const float e0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_use)), e1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_use));
         const float e2 = fast_exp2(fmaf(s[c + 2], p.scale_log2, -m_use)), e3 = fast_exp2(fmaf(s[c + 3], p.scale_log2, -m_use));
         l0 += e0;
@@ -437,13 +441,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           break;
         }
       }
-      if (j + 1 == n_j && kv_end - key0 < TC_BN) {
+      if (j + 1 == n_j && kv_end - key0 < BN) {
         // Rows of the last stage past the key range may never have been written (or hold another
         // request's values): a zero weight times a stray NaN would still be a NaN.  The tile's
-        // threads clear them once the stage has landed, before they announce P (both tiles write
+        // threads clear them once the stage has landed, before they announce P (all tiles write
         // the same zeros).
-        const int s_last = j % TC_STAGES;
-        ok = wait_all(v_full(s_last), (j / TC_STAGES) & 1);
+        const int s_last = j % NS;
+        ok = wait_all(v_full(s_last), (j / NS) & 1);
         if (!ok) {
           abort_flag = 1;
           if (lane == 0) atomicExch(p.err, 28);
@@ -451,15 +455,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         const int first_bad = kv_end - key0;
         uint8_t* v = smem + Cfg::OFF_V + s_last * Cfg::KV_STAGE_BYTES;
-        const int n16 = (TC_BN - first_bad) * 8;  // 16-byte pieces per 64-column half
+        const int n16 = (BN - first_bad) * 8;  // 16-byte pieces per 64-column half
         for (int h = 0; h < HALVES; ++h)
           for (int i = r; i < n16; i += 128)
             *reinterpret_cast<uint4*>(v + h * Cfg::KV_HALF_BYTES + first_bad * 128 + i * 16) = make_uint4(0, 0, 0, 0);
       }
       const uint32_t row_base = smem_u32(p_tile) + r * 128;
 #pragma unroll
-      for (int ch = 0; ch < TC_BN / 8; ++ch) {
-        const uint32_t dst = row_base + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4);
+      for (int ch = 0; ch < BN / 8; ++ch) {   // 16-byte chunk ch of the row: span ch / 8, swizzled within the span
+        const uint32_t dst = row_base + (uint32_t)(ch >> 3) * (128 * 128) + ((((uint32_t)ch & 7u) ^ ((uint32_t)r & 7u)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[ch * 4]), "r"(pk[ch * 4 + 1]), "r"(pk[ch * 4 + 2]),
                      "r"(pk[ch * 4 + 3])
                      : "memory");
@@ -477,7 +481,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const bool whole = n_splits == 1;
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       __nv_bfloat16* orow = p.out + (size_t)(qs + tok_in_req) * p.ldo + (size_t)(kvh * G + r % G) * D;
-      const size_t prow = (size_t)part * (2 * tok * G) + t * tok * G + r;
+      const size_t prow = (size_t)part * (NT * tok * G) + t * tok * G + r;
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) {
         float o[32];
@@ -606,34 +610,40 @@ int cache_map(const void* plane, long long n_pages, int Hkv, int page_size, int 
   return 0;
 }
 
-template <int D>
+template <int D, int NT, int BN, int NS>
 int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const AttnTcParams& p, int n_work, cudaStream_t stream) {
-  using Cfg = AttnTcConfig<D>;
+  using Cfg = AttnTcConfig<D, NT, BN, NS>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<D, NT, BN, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     FERRUM_CHECK_ARG(e == cudaSuccess, "attention_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  launch_kernel(attention_tc_kernel<D>, dim3(p.Hkv, n_work), dim3(TC_THREADS), Cfg::SMEM_BYTES, stream, mq, mkv, p);
+  launch_kernel(attention_tc_kernel<D, NT, BN, NS>, dim3(p.Hkv, n_work), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, mq, mkv, p);
   FERRUM_CHECK_LAUNCH("attention_tc");
   return 0;
 }
 
+// The shape in use: two row tiles per CTA that share three stages of 64 keys.  One tile with
+// stages of 128 keys (half the waits and fences per key, no second tile to fill the matrix unit
+// while the first computes P) was measured slower: 67.8 against 51.8 us for a 2048-token prompt.
+constexpr int TC_TILES = 2, TC_BN = 64, TC_STAGES = 3;
+
 }  // namespace
 
-// Tokens per row tile for a group of G query heads per KV head, or 0 when this kernel does not
-// take the shape (head sizes 64 and 128; pages of 8, 16, 32 or 64 keys; at most 128 heads per group).
+// Tokens per work item for a group of G query heads per KV head (an item is TC_TILES tiles of
+// 128 / G tokens), or 0 when this kernel does not take the shape: head sizes 64 and 128; pages
+// of 8 to 64 keys, a power of two; at most 128 heads per group.
 FERRUM_API int ferrum_attention_tc_tokens(int D, int G, int page_size) {
   if (D != 64 && D != 128) return 0;
-  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return 0;
+  if (page_size < 8 || page_size > TC_BN || (page_size & (page_size - 1)) != 0) return 0;
   if (G < 1 || G > 128) return 0;
-  return 128 / G;
+  return TC_TILES * (128 / G);
 }
 
-// Items of 2 * tokens * G rows (see ferrum_attention_tc_tokens) in the work-list format of
-// ferrum_attention_flash; grid (Hkv, n_work).  q has q_rows rows of ldq elements (the buffer's
-// capacity, of which the batch may use fewer); the plane has n_pages pages.
+// Items of ferrum_attention_tc_tokens * G rows in the work-list format of ferrum_attention_flash;
+// grid (Hkv, n_work).  q has q_rows rows of ldq elements (the buffer's capacity, of which the
+// batch may use fewer); the plane has n_pages pages.
 FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, void* out, int ldo, const void* kv_plane,
                                    long long page_stride, long long n_pages, int page_size, const int* block_table,
                                    int table_width, const int* q_start, const int* pos0, const int* work, int n_work,
@@ -641,7 +651,7 @@ FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, voi
                                    int* err_flag, cudaStream_t stream) {
   FERRUM_CHECK_ARG(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_tc: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
   const int G = Hq / Hkv;
-  const int tok = ferrum_attention_tc_tokens(D, G, page_size);
+  const int tok = ferrum_attention_tc_tokens(D, G, page_size) / TC_TILES;
   FERRUM_CHECK_ARG(tok > 0, "attention_tc: head size %d, group %d, page size %d is not built; use attention_flash", D, G, page_size);
   FERRUM_CHECK_ARG(err_flag != nullptr, "attention_tc: the error flag is required");
   FERRUM_CHECK_ARG(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
@@ -664,6 +674,6 @@ FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, voi
   CUtensorMap mq, mkv;
   if (int r = query_map(q, q_rows, ldq, Hq, D, G, tok, &mq)) return r;
   if (int r = cache_map(kv_plane, n_pages, Hkv, page_size, D, &mkv)) return r;
-  if (D == 64) return launch_attention_tc<64>(mq, mkv, p, n_work, stream);
-  return launch_attention_tc<128>(mq, mkv, p, n_work, stream);
+  if (D == 64) return launch_attention_tc<64, TC_TILES, TC_BN, TC_STAGES>(mq, mkv, p, n_work, stream);
+  return launch_attention_tc<128, TC_TILES, TC_BN, TC_STAGES>(mq, mkv, p, n_work, stream);
 }

@@ -8,7 +8,7 @@ every layer with the same (G, window).
 
 Requests with at most 16 rows (decoded tokens) go to the 16-row kernel, requests with at
 least TC_MIN_ROWS rows to the tcgen05 kernel where it takes the layer's shape (its items are
-pairs of 128-row tiles), the others to the 64-row kernel; each class has its own work list.  A work item is
+one or two 128-row tiles), the others to the 64-row kernel; each class has its own work list.  A work item is
 [request, first row, key begin, key end, number of splits, partial slot, KV head, 0]; an item
 with zero splits is padding.  The 64-row class runs a grid of (items, KV heads).  The 16-row
 class runs a balanced list: every CTA slot of the GPU gets an equal share of all (request,
@@ -142,7 +142,7 @@ def _balanced_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start):
 
 def build_host(q_len, pos0, G, window, Hkv, tc_tokens=0):
     """numpy description of the classes (16 rows, 64 rows, tcgen05 tile pairs): None or a dict
-    of int32 arrays per class.  tc_tokens: tokens per 128-row tile of the tcgen05 kernel, 0
+    of int32 arrays per class.  tc_tokens: tokens per work item of the tcgen05 kernel, 0
     where it does not take the layer's shape."""
     q_len = np.asarray(q_len, dtype=np.int64)
     pos0 = np.asarray(pos0, dtype=np.int64)
@@ -160,7 +160,7 @@ def build_host(q_len, pos0, G, window, Hkv, tc_tokens=0):
         else:
             out.append(_grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start))
     sel = np.nonzero(to_tc)[0]
-    out.append(_grid_class(q_len, pos0, G, window, Hkv, 2 * tc_tokens * G, sel, R, q_start, slots=N_SMS,
+    out.append(_grid_class(q_len, pos0, G, window, Hkv, tc_tokens * G, sel, R, q_start, slots=N_SMS,
                            min_split=TC_MIN_SPLIT_KEYS, kind="tc") if len(sel) else None)
     return out
 

@@ -24,7 +24,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 3
+ABI = 4
 
 
 def lib():
@@ -295,9 +295,9 @@ def attention_flash(q, out, kv_plane, page_stride, page_size, block_table, q_sta
 
 
 def attention_tc_tokens(D, G, page_size, kv_plane=None, page_stride=0):
-    """Tokens per 128-row tile of the tcgen05 attention kernel for this head size, group size
-    and page size; 0 where the kernel does not apply (other sizes, float32, pages that are
-    not dense in the plane)."""
+    """Tokens per work item of the tcgen05 attention kernel for this head size, group size and
+    page size (an item has that many tokens x G rows); 0 where the kernel does not apply (other
+    sizes, float32, pages that are not dense in the plane)."""
     if kv_plane is not None and (kv_plane.dtype != torch.bfloat16 or kv_plane.dim() != 5 or
                                  page_stride != kv_plane[0].numel()):
         return 0
@@ -306,7 +306,7 @@ def attention_tc_tokens(D, G, page_size, kv_plane=None, page_stride=0):
 
 def attention_tc(q, out, kv_plane, page_stride, page_size, block_table, q_start, pos0, work, n_work, part_o, part_ml,
                  Hq, Hkv, D, scale, window, err):
-    """tcgen05 attention over work items of 2 * attention_tc_tokens * G rows (prompt portions)."""
+    """tcgen05 attention over work items of attention_tc_tokens * G rows (prompt portions)."""
     _need(q, torch.bfloat16, "q", 2); _need(out, torch.bfloat16, "out", 2); _need(kv_plane, torch.bfloat16, "kv_plane")
     _need(block_table, torch.int32, "block_table", 2); _need(work, torch.int32, "work", 1)
     _check(lib().ferrum_attention_tc(_ptr(q), c_int(q.stride(0)), c_longlong(q.shape[0]), _ptr(out), c_int(out.stride(0)),
