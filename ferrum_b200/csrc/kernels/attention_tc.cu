@@ -8,9 +8,13 @@
 // 64-key stages.  Per 64 keys and row tile:
 //   S = Q K^T          tcgen05.mma 128 x 64 x D into tensor memory
 //   P = exp2(S - m)    128 threads, one per row, read S from tensor memory, keep the running
-//                      maximum and sum in float32 and write P (bfloat16) to shared memory
-//   O += P V           tcgen05.mma 128 x D x 64, V as the MN-major operand straight from the
-//                      page layout, O in tensor memory
+//                      maximum and sum in float32 and write P (bfloat16) back over the first
+//                      half of the same columns
+//   O += P V           tcgen05.mma 128 x D x 64 with P as the tensor-memory operand and V as the
+//                      MN-major operand straight from the page layout, O in tensor memory
+// P never passes through shared memory: the matrix unit fetches its shared-memory operands at
+// about 64 bytes a cycle, and with Q re-read for every 64 keys that fetch, not the arithmetic,
+// is what a stage costs (16 x 6 KB for the scores, 8 x 4 KB for the values).
 // S has two buffers per row tile, so the matrix unit computes the scores of the stage after next
 // while the threads of a tile work on P: a tile's threads never wait for a product that
 // depends on their own P, and the two tiles share the matrix unit.  The running maximum is only moved (and O rescaled, in tensor
@@ -55,17 +59,14 @@ struct AttnTcParams {
 template <int D, int NT, int BN, int NS>
 struct AttnTcConfig {
   static constexpr int HALVES = D / 64;                          // 64-column spans of a head
-  static constexpr int SPANS = BN / 64;                          // 64-key spans of a stage (rows of P)
   static constexpr int Q_TILE_BYTES = HALVES * 128 * 128;       // 128 rows x 128 bytes per 64 columns
   static constexpr int KV_HALF_BYTES = BN * 128;
   static constexpr int KV_STAGE_BYTES = HALVES * KV_HALF_BYTES;
-  static constexpr int P_TILE_BYTES = SPANS * 128 * 128;         // 128 rows x BN keys
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + NT * Q_TILE_BYTES;
   static constexpr int OFF_V = OFF_K + NS * KV_STAGE_BYTES;
-  static constexpr int OFF_P = OFF_V + NS * KV_STAGE_BYTES;
-  static constexpr int OFF_BARS = OFF_P + NT * P_TILE_BYTES;
-  static constexpr int N_BARS = 1 + 4 * NS + 4 * NT;
+  static constexpr int OFF_BARS = OFF_V + NS * KV_STAGE_BYTES;
+  static constexpr int N_BARS = 1 + 4 * NS + 6 * NT;
   static constexpr int SMEM_BYTES = OFF_BARS + N_BARS * 8 + 1024 /*alignment slack*/;
   static constexpr int S_COL = 0;                 // S of tile t, buffer b: columns (2 t + b) * BN ..
   static constexpr int O_COL = NT * 2 * BN;       // O of tile t: columns O_COL + t * D ..
@@ -130,6 +131,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n\t"
+      "tcgen05.wait::st.sync.aligned;" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+      "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+      "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+      "r"(v[31])
+      : "memory");
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -167,8 +180,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * NS + s); };
   auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * NS + s); };
   auto s_ready = [&](int t, int b) { return bar_base + 8u * (1 + 4 * NS + 2 * t + b); };
-  auto p_ready = [&](int t) { return bar_base + 8u * (1 + 4 * NS + 2 * NT + t); };
-  auto pv_done = [&](int t) { return bar_base + 8u * (1 + 4 * NS + 3 * NT + t); };
+  auto p_ready = [&](int t, int b) { return bar_base + 8u * (1 + 4 * NS + 2 * NT + 2 * t + b); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (1 + 4 * NS + 4 * NT + t); };
+  auto o_done = [&](int t) { return bar_base + 8u * (1 + 4 * NS + 5 * NT + t); };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -184,8 +198,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int t = 0; t < NT; ++t) {
       mbar_init(s_ready(t, 0), 1);
       mbar_init(s_ready(t, 1), 1);
-      mbar_init(p_ready(t), 128);
+      mbar_init(p_ready(t, 0), 128);
+      mbar_init(p_ready(t, 1), 128);
       mbar_init(pv_done(t), 1);
+      mbar_init(o_done(t), 1);
     }
     fence_barrier_init();
   }
@@ -272,7 +288,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint32_t idesc_qk = umma_idesc_bf16(128, BN);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B (values) is MN-major
       const uint32_t q_addr = smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES;
-      const uint32_t p_addr = smem_base + Cfg::OFF_P + t * Cfg::P_TILE_BYTES;
       const uint32_t o_tmem = tmem_base + Cfg::O_COL + t * D;
       auto issue_qk = [&](int s, int buf) {
         const uint32_t k_addr = smem_base + Cfg::OFF_K + s * Cfg::KV_STAGE_BYTES;
@@ -284,14 +299,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     umma_desc_k_sw128(k_addr + h * Cfg::KV_HALF_BYTES) + (uint64_t)(in * 2), idesc_qk, kk > 0);
         }
       };
-      auto issue_pv = [&](int s, bool accumulate) {
+      auto issue_pv = [&](int s, int buf, bool accumulate) {
         const uint32_t v_addr = smem_base + Cfg::OFF_V + s * Cfg::KV_STAGE_BYTES;
+        const uint32_t p_tmem = tmem_base + Cfg::S_COL + (2 * t + buf) * BN;  // P lies over the scores it came from
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {  // 16 keys on: 32 bytes of a P row (per 64-key span), 16 rows of V
-          const int span = kk >> 2, in = kk & 3;
-          umma_bf16(o_tmem, umma_desc_k_sw128(p_addr + span * 128 * 128) + (uint64_t)(in * 2),
-                    umma_desc_mn_sw128(v_addr + kk * 16 * 128, Cfg::KV_HALF_BYTES, 1024), idesc_pv, accumulate || kk > 0);
-        }
+        for (int kk = 0; kk < BN / 16; ++kk)  // 16 keys on: 8 columns of P, 16 rows of V
+          umma_bf16_ts(o_tmem, p_tmem + kk * 8, umma_desc_mn_sw128(v_addr + kk * 16 * 128, Cfg::KV_HALF_BYTES, 1024), idesc_pv,
+                       accumulate || kk > 0);
       };
       // the scores of stages 0 and 1 go ahead; in the loop the scores of stage j + 2 follow P V of stage j
       bool ok = mbar_wait(q_full, 0, abort_p);
@@ -318,15 +332,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           atomicExch(p.err, 23);
           break;
         }
-        ok = mbar_wait(p_ready(t), j & 1, abort_p);
+        ok = mbar_wait(p_ready(t, j & 1), (j >> 1) & 1, abort_p);
         if (!ok) {
           abort_flag = 1;
           atomicExch(p.err, 24);
           break;
         }
         tc_fence_after();
-        issue_pv(s, j > 0);
+        issue_pv(s, j & 1, j > 0);
         umma_commit(pv_done(t));
+        if (j + 1 == n_j) umma_commit(o_done(t));
         umma_commit(v_empty(s));
         if (more) {
           ok = mbar_wait(k_full(s2), (jn / NS) & 1, abort_p);
@@ -356,7 +371,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int qpos_min = pos0 + tile_first;
     const int qpos_max = pos0 + min(q_len - 1, tile_first + tok - 1);
     const bool tile_full = tok * G == 128 && tile_first + tok <= q_len;  // every row of the tile exists
-    uint8_t* p_tile = smem + Cfg::OFF_P + t * Cfg::P_TILE_BYTES;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_j; ++j) {
@@ -393,14 +407,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float cand = fmaxf(m_run, mx * p.scale_log2);
-      bool pv_waited = j == 0;   // P V of the stage before has finished: O is at rest and P may be overwritten
       const bool grow = cand > m_run + TC_LAZY;   // also true for the first finite maximum
       if (__any_sync(0xffffffffu, grow)) {
         const float f = m_run == -INFINITY ? 0.f : fast_exp2(m_run - cand);  // cand is finite where m_run is
         l_run *= f;
         if (j > 0) {
           ok = wait_all(pv_done(t), (j - 1) & 1);
-          pv_waited = true;
           if (!ok) {
             abort_flag = 1;
             if (lane == 0) atomicExch(p.err, 27);
@@ -433,14 +445,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         pk[c / 2 + 1] = pack2_bf16(e2, e3);
       }
       l_run += (l0 + l1) + (l2 + l3);
-      if (!pv_waited) {
-        ok = wait_all(pv_done(t), (j - 1) & 1);
-        if (!ok) {
-          abort_flag = 1;
-          if (lane == 0) atomicExch(p.err, 27);
-          break;
-        }
-      }
       if (j + 1 == n_j && kv_end - key0 < BN) {
         // Rows of the last stage past the key range may never have been written (or hold another
         // request's values): a zero weight times a stray NaN would still be a NaN.  The tile's
@@ -459,20 +463,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int h = 0; h < HALVES; ++h)
           for (int i = r; i < n16; i += 128)
             *reinterpret_cast<uint4*>(v + h * Cfg::KV_HALF_BYTES + first_bad * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+        fence_proxy_async();   // the matrix unit reads these rows
       }
-      const uint32_t row_base = smem_u32(p_tile) + r * 128;
+      // P replaces the first half of the scores' columns (every score of the row is in registers
+      // by now); the scores of stage j + 2 come to these columns only after P V of this stage
 #pragma unroll
-      for (int ch = 0; ch < BN / 8; ++ch) {   // 16-byte chunk ch of the row: span ch / 8, swizzled within the span
-        const uint32_t dst = row_base + (uint32_t)(ch >> 3) * (128 * 128) + ((((uint32_t)ch & 7u) ^ ((uint32_t)r & 7u)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[ch * 4]), "r"(pk[ch * 4 + 1]), "r"(pk[ch * 4 + 2]),
-                     "r"(pk[ch * 4 + 3])
-                     : "memory");
-      }
-      fence_proxy_async();   // P is read by the matrix unit
-      tc_fence_before();     // and this thread's tensor-memory accesses precede the products that follow
-      mbar_arrive(p_ready(t));
+      for (int c0 = 0; c0 < BN / 2; c0 += 32) tmem_st32u(lane_addr + Cfg::S_COL + (2 * t + buf) * BN + c0, &pk[c0]);
+      tc_fence_before();     // this thread's tensor-memory accesses precede the products that follow
+      // A warp may be a stage ahead of the tile's other warps (the next scores do not wait for
+      // this P), so odd and even stages announce P on barriers of their own: an arrival is never
+      // counted for the stage that the others still work on, and a barrier is used again only
+      // after the scores of two stages on, which follow the product that waited for it.
+      mbar_arrive(p_ready(t, buf));
     }
-    if (ok) ok = wait_all(pv_done(t), (n_j - 1) & 1);
+    // (not pv_done: a thread that never had to rescale has not followed its phases, and the
+    // product of the stage before the last may still be running)
+    if (ok) ok = wait_all(o_done(t), 0);
     if (!ok) {
       abort_flag = 1;
       if (lane == 0) atomicExch(p.err, 26);
