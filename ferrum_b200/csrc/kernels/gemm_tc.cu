@@ -25,6 +25,7 @@
 //
 // Every mbarrier wait is bounded; on a timeout the kernel raises the error flag, lets the
 // copies in flight land, frees its tensor memory and returns.
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -51,6 +52,8 @@ struct TcParams {
   int defer;         // 1: leave every segment's float32 partial in the workspace; the next kernel sums them
   int out_tma;       // 1: the pair kernel writes `out` through its tensor map (staged in shared memory)
   int stream_weights;  // 1: every weight tile is read once in this launch: its L2 lines are the first to go
+  int gated;           // 1 (pair kernel): weight rows come interleaved (gate i, up i, gate i + 1, ...), N counts these
+                       // rows, and the epilogue writes silu(gate) * up for N / 2 features
 };
 
 constexpr int TILE_N = 128;  // weight rows per tile (the instruction's M)
@@ -501,7 +504,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const uint32_t a = smem_base + s * PAIR_STAGE_BYTES;
         const uint32_t leader_full = map_to_cta(full_bar(s), 0);  // (measured: this loop is not the limit; the copies are)
         if (rank == 0) mbar_expect_tx(full_bar(s), 2 * PAIR_STAGE_BYTES);
-        tma_load_2d_pair(a, &tmap_w, leader_full, kb * TILE_K, n0);
+        if (p.gated) tma_load_3d_pair(a, &tmap_w, leader_full, kb * TILE_K, 0, n0 >> 1);  // (k, gate | up, feature)
+        else tma_load_2d_pair(a, &tmap_w, leader_full, kb * TILE_K, n0);
         tma_load_2d_pair(a + A_BYTES, &tmap_x, leader_full, kb * TILE_K, t0);
         if (++s == STAGES) {
           s = 0;
@@ -656,6 +660,29 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+      } else if (whole && p.gated) {
+        // Even lanes hold a feature's gate, odd lanes its up product.  The two exchange halves of
+        // their 32 tokens, so that each ends with both values of 16 tokens, and the tile leaves
+        // as 32 tokens x 64 features of bfloat16.
+        const int odd = lane & 1;
+#pragma unroll 1
+        for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
+          float v[32];
+          tmem_ld16(acc_addr + c0, &v[0]);
+          tmem_ld16(acc_addr + c0 + 16, &v[16]);
+          uint8_t* stage = stage_acquire();
+          __nv_bfloat16* st = (__nv_bfloat16*)stage + (odd * 16) * (TILE_N / 2) + (n_local >> 1);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float theirs = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[16 + j], 1);
+            const float g = odd ? theirs : v[j], up = odd ? v[16 + j] : theirs;
+            st[j * (TILE_N / 2)] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * up);
+          }
+          stage_send(stage, &tmap_out, false, n0 >> 1, t0 + c0);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
       } else if (whole) {
 #pragma unroll 1
         for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
@@ -739,6 +766,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               }
             }
             uint8_t* stage = stage_acquire();
+            if (p.gated) {  // four neighbouring rows are two (gate, up) pairs
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const __nv_bfloat162 o2 = __floats2bfloat162_rn(acc[k].x / (1.0f + __expf(-acc[k].x)) * acc[k].y,
+                                                                acc[k].z / (1.0f + __expf(-acc[k].z)) * acc[k].w);
+                *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)stage + (cg + k) * (TILE_N / 2) + (q4 >> 1)) = o2;
+              }
+              stage_send(stage, &tmap_out, false, n0 >> 1, t0 + c0);
+              continue;
+            }
             if (p.epilogue == TC_RESIDUAL) {
 #pragma unroll
               for (int k = 0; k < 8; ++k) *reinterpret_cast<float4*>((float*)stage + (cg + k) * TILE_N + q4) = acc[k];
@@ -815,7 +852,8 @@ struct MapKey {
   const void* ptr;
   long long rows, cols, ld;
   int box_rows;
-  int kind;  // 0: bfloat16 operand, 64-column boxes, 128-byte swizzle; 1 / 2: float32 / bfloat16 output, 128-column boxes
+  int kind;  // 0: bfloat16 operand, 64-column boxes, 128-byte swizzle; 1 / 2: float32 / bfloat16 output, 128-column boxes;
+             // 3: bfloat16 output, 64-column boxes; 4: gate and up rows of a weight interleaved (box_rows = rows between them)
   bool operator==(const MapKey& o) const {
     return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && kind == o.kind;
   }
@@ -826,7 +864,7 @@ struct MapKeyHash {
     h = h * 1000003u ^ std::hash<long long>()(k.rows);
     h = h * 1000003u ^ std::hash<long long>()(k.cols);
     h = h * 1000003u ^ std::hash<long long>()(k.ld);
-    h = h * 1000003u ^ std::hash<int>()(k.box_rows * 4 + k.kind);
+    h = h * 1000003u ^ std::hash<long long>()((long long)k.box_rows * 8 + k.kind);
     return h;
   }
 };
@@ -849,15 +887,25 @@ static int get_tensor_map(const void* ptr, long long rows, long long cols, long 
   }
   EncodeTiledFn fn = get_encode_fn();
   FERRUM_CHECK_ARG(fn != nullptr, "gemm_tc: the driver does not export cuTensorMapEncodeTiled");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * (kind == 1 ? 4 : 2)};
-  cuuint32_t box[2] = {(cuuint32_t)(kind == 0 ? TILE_K : TILE_N), (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  kind == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r;
+  if (kind == 4) {
+    // [rows] features of a gate block and of an up block `box_rows` rows further on, seen as
+    // (k, gate | up, feature): a box of 64 x 2 x 64 lands as 128 rows gate 0, up 0, gate 1, ...
+    cuuint64_t dims[3] = {(cuuint64_t)cols, 2, (cuuint64_t)rows};
+    cuuint64_t strides[2] = {(cuuint64_t)box_rows * (cuuint64_t)ld * 2, (cuuint64_t)ld * 2};
+    cuuint32_t box[3] = {(cuuint32_t)TILE_K, 2, (cuuint32_t)(TILE_N / 2)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (kind == 1 ? 4 : 2)};
+    cuuint32_t box[2] = {(cuuint32_t)(kind == 0 ? TILE_K : (kind == 3 ? TILE_N / 2 : TILE_N)), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    r = fn(out, kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+           kind == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   FERRUM_CHECK_ARG(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows=%lld cols=%lld ld=%lld kind=%d)",
                    (int)r, rows, cols, ld, kind);
   std::lock_guard<std::mutex> g(mu);
@@ -941,7 +989,9 @@ FERRUM_API long long ferrum_gemm_tc_workspace(int M, int N, int K, int dual, int
   const int bt = ferrum_gemm_tc_token_tile(M, dual);
   if (n_ctas <= 0) n_ctas = sm_count();
   // counters: one per 128-row tile; the pair kernel numbers them by 256-row tile and half
-  const long long tiles = 2LL * ((N + 2 * TILE_N - 1) / (2 * TILE_N)) * ((M + bt - 1) / bt);
+  long long tiles = 2LL * ((N + 2 * TILE_N - 1) / (2 * TILE_N)) * ((M + bt - 1) / bt);
+  if (dual && M > TILE_N)  // may run on the pair kernel as one product of 2 N interleaved rows
+    tiles = std::max(tiles, 2LL * ((2LL * N + 2 * TILE_N - 1) / (2 * TILE_N)) * ((M + PAIR_BT - 1) / PAIR_BT));
   if (n_tiles) *n_tiles = (int)tiles;
   return 2LL * n_ctas * (long long)(bt * (dual ? 2 : 1)) * TILE_N;
 }
@@ -978,6 +1028,25 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
   TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset, 0};
   p.stream_weights = (M + bt - 1) / bt == 1;  // one token tile: no weight tile is read twice
   CUtensorMap mw, mx;
+  if (dual && M > TILE_N && g_pair_kernel && n_ctas >= 2 && ((uintptr_t)out & 15) == 0 && ldo % 8 == 0) {
+    // Two products of many tokens: the pair kernel computes them as one product whose weight
+    // rows alternate between gate and up (a three-dimensional tensor map interleaves them on
+    // the way into shared memory), and its epilogue applies the activation.
+    p.N = 2 * N;
+    p.gated = 1;
+    p.stream_weights = 0;
+    const long long units = (long long)((p.N + 2 * TILE_N - 1) / (2 * TILE_N)) * ((M + PAIR_BT - 1) / PAIR_BT) * ((K + TILE_K - 1) / TILE_K);
+    int pairs = n_ctas / 2;
+    if (pairs > units) pairs = (int)units;
+    CUtensorMap mo, ms;
+    if (int r = get_tensor_map(w, N, K, ldw, dual_offset, &mw, 4)) return r;
+    if (int r = get_tensor_map(x, M, K, ldx, PAIR_BT / 2, &mx)) return r;
+    if (int r = get_tensor_map(out, M, N, ldo, PAIR_OUT_ROWS, &mo, 3)) return r;
+    FERRUM_CHECK_ARG(((uintptr_t)workspace & 15) == 0, "gemm_tc: the workspace must be 16-byte aligned");
+    if (int r = get_tensor_map(workspace, workspace_floats / TILE_N, TILE_N, TILE_N, PAIR_OUT_ROWS, &ms, 1)) return r;
+    p.out_tma = 1;
+    return launch_tc_pair(mw, mx, mo, ms, p, 2 * pairs, stream);
+  }
   if (int r = get_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
   if (bt == PAIR_BT && !dual && g_pair_kernel && n_ctas >= 2) {
     // many tokens: pairs of CTAs on 256 x 256 tiles; each CTA stages 128 tokens

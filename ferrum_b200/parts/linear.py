@@ -61,13 +61,7 @@ def linear_swiglu(x, w_gate_up, act, F, ctx, M=None):
         ops.swiglu_reduce(act, M, F, part)
         return
     ctx.flush_residual()
-    if ops.gemm_tc_token_tile(M, False) > ops.gemm_tc_token_tile(M, True):
-        # many tokens: the CTA-pair kernel (one product per launch) moves fewer bytes per flop
-        # than the two-product kernel, which more than pays for a separate activation pass
-        gu = ctx.buf("ffn_gate_up", (ctx.token_capacity, 2 * F), act.dtype)
-        ws, cnt = ctx.gemm_scratch(M, 2 * F, K, False)
-        ops.gemm_tc(x, w_gate_up, gu, ops.TC_STORE_BF16, ctx.err, ws, cnt, M=M)
-        ops.swiglu(gu, act, M, F)
-        return
+    # (with many tokens the library runs both products as one on its CTA-pair kernel, gate and
+    # up rows interleaved, and applies the activation in that kernel's epilogue)
     ws, cnt = ctx.gemm_scratch(M, F, K, True)
     ops.gemm_tc(x, w_gate_up, act, ops.TC_SWIGLU, ctx.err, ws, cnt, M=M, N=F, dual_offset=F)

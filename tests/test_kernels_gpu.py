@@ -151,7 +151,8 @@ def test_gemm_tc(ops, M, N, K, n_ctas):
     assert torch.equal(again, out)        # shared tiles are summed in K order: run-to-run identical
 
 
-@pytest.mark.parametrize("M,F,K", [(3, 172 * 2, 64), (16, 256, 96), (40, 200, 320), (130, 384, 256), (300, 128, 128)])
+@pytest.mark.parametrize("M,F,K", [(3, 172 * 2, 64), (16, 256, 96), (40, 200, 320), (130, 384, 256), (300, 128, 128),
+                                   (129, 72, 64), (515, 200, 320), (700, 1000, 2048)])
 @pytest.mark.parametrize("n_ctas", [0, 2, 5])
 def test_gemm_tc_swiglu(ops, M, F, K, n_ctas):
     g = torch.Generator(device="cuda").manual_seed(6)
