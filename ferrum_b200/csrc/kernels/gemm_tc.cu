@@ -410,9 +410,87 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 // cluster compute a 256 x 256 tile with one tcgen05.mma.cta_group::2 per K step: each CTA
 // loads its own 128 weight rows and its own 128 tokens (32 KB per stage instead of 48 KB for
 // the same flops), the leader issues the MMAs, and each CTA's tensor memory receives its 128
-// rows of the product, which its own epilogue warps read back.  The stream-K bookkeeping is
-// that of the single-CTA kernel with the cluster in the role of the CTA and the 128-row half
-// tile in the role of the tile.  No multicast loads are used.
+// rows of the product, which its own epilogue warps read back.  Partial tiles are handled as
+// in the single-CTA kernel with the cluster in the role of the CTA and the 128-row half tile
+// in the role of the tile.  No multicast loads are used.
+// Which parts of which tiles a cluster computes.  Whole waves first: in wave w cluster c takes
+// tile w * P + c with all its k-blocks and writes it out itself, so neighbouring clusters work
+// on neighbouring tiles at the same k-block and share their operands in the L2.  For the R
+// tiles that are left (fewer than P) there are two ways.  As a rule R clusters take one more
+// whole tile each and the others are done.  Only where that idles much (long tiles, few of
+// them: (P - R) / P of a tile is PAIR_STREAMK_MIN_KB k-blocks or more) the left-over tiles are cut
+// stream-K fashion: their units (tile, k-block) form a line that is divided evenly among the
+// first Pr clusters, and a tile that several clusters share is summed from float32 partials
+// by the last of them to arrive.  That costs a cluster some tens of microseconds (partial out,
+// partials in), which is why short tiles are not cut.  Tiles are numbered through groups of
+// PAIR_GROUP_T token tiles, token tile fastest: a wave then reads about P / 8 weight tiles and
+// 8 token tiles instead of P weight tiles and one token tile, and with many tokens the
+// weights stream from memory once per group instead of once per token tile.
+constexpr int PAIR_GROUP_T = 8;
+constexpr int PAIR_STREAMK_MIN_KB = 100;
+struct PairSchedule {
+  int nkb, tiles_n, tiles_t, P, cluster, waves, Pr, whole_extra;
+  long long full_tiles, Ur, r_begin, r_end;
+  __device__ PairSchedule(int tiles_n_, int tiles_t_, int nkb_, int P_, int cluster_)
+      : nkb(nkb_), tiles_n(tiles_n_), tiles_t(tiles_t_), P(P_), cluster(cluster_) {
+    const long long tiles = (long long)tiles_n * tiles_t;
+    const int R = (int)(tiles % P);
+    waves = (int)(tiles / P);
+    whole_extra = 0;
+    Ur = 0;
+    Pr = 0;
+    r_begin = r_end = 0;
+    if (R > 0 && (long long)(P - R) * nkb < (long long)PAIR_STREAMK_MIN_KB * P) {
+      whole_extra = R;
+    } else if (R > 0) {
+      // few tiles left over would each be cut among many clusters: cut the last whole wave with them
+      if (waves > 0 && 2 * R < P) --waves;
+      Ur = (tiles - (long long)waves * P) * nkb;
+      Pr = (int)min((long long)P, Ur);   // every sharing cluster owns at least one unit
+      r_begin = cluster < Pr ? Ur * cluster / Pr : 0;
+      r_end = cluster < Pr ? Ur * (cluster + 1) / Pr : 0;
+    }
+    full_tiles = (long long)waves * P;
+  }
+  // this cluster's s-th segment: its tile and k-blocks [kb0, kb1); false when there is none
+  __device__ bool segment(int s, long long& tile, int& kb0, int& kb1) const {
+    if (s < waves) {
+      tile = (long long)s * P + cluster;
+      kb0 = 0;
+      kb1 = nkb;
+      return true;
+    }
+    if (whole_extra > 0) {
+      if (s > waves || cluster >= whole_extra) return false;
+      tile = full_tiles + cluster;
+      kb0 = 0;
+      kb1 = nkb;
+      return true;
+    }
+    const int r = s - waves;
+    const long long rt = r_begin / nkb + r;  // tile of the remainder
+    if (rt * nkb >= r_end) return false;
+    tile = full_tiles + rt;
+    kb0 = r == 0 ? (int)(r_begin % nkb) : 0;
+    kb1 = (int)min((long long)nkb, r_end - rt * nkb);
+    return true;
+  }
+  __device__ void coords(long long tile, int& n_idx, int& t_idx) const {
+    const long long per_group = (long long)PAIR_GROUP_T * tiles_n;
+    const int g = (int)(tile / per_group);
+    const int t_first = g * PAIR_GROUP_T;
+    const int gt = min(PAIR_GROUP_T, tiles_t - t_first);
+    const int r = (int)(tile - g * per_group);
+    t_idx = t_first + r % gt;
+    n_idx = r / gt;
+  }
+  // the clusters that share a tile of the remainder, and the slot (0: the tile in which the
+  // cluster's range begins, 1: the other) in which cluster cc leaves its partial of it
+  __device__ int first_owner(long long tile) const { return unit_owner((tile - full_tiles) * nkb, Ur, Pr); }
+  __device__ int last_owner(long long tile) const { return unit_owner((tile - full_tiles) * nkb + nkb - 1, Ur, Pr); }
+  __device__ int slot_of(int cc, long long tile) const { return (Ur * cc / Pr) / nkb == tile - full_tiles ? 0 : 1; }
+};
+
 constexpr int PAIR_BT = 256;                              // tokens per tile pair
 constexpr int PAIR_B_BYTES = (PAIR_BT / 2) * TILE_K * 2;  // each CTA stages half of the tokens
 constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
@@ -444,8 +522,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   const int nkb = (p.K + TILE_K - 1) / TILE_K;
   const int tiles_n = (p.N + 2 * TILE_N - 1) / (2 * TILE_N);  // 256-row tiles
   const int tiles_t = (p.M + PAIR_BT - 1) / PAIR_BT;
-  const long long U = (long long)tiles_n * tiles_t * nkb;
-  const long long u_begin = U * cluster / P, u_end = U * (cluster + 1) / P;
+  const PairSchedule sched(tiles_n, tiles_t, nkb, P, cluster);
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_u32(bars);
@@ -453,6 +530,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t fetch_bar = bar_base + 8u * (2 * STAGES + 4);  // partials of other clusters copied into the idle stages
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -471,6 +549,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), 8);  // the leader's: four epilogue warps of each CTA
     }
+    mbar_init(fetch_bar, 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -489,31 +568,33 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
-      long long tile = u_begin / nkb;
-      int kb = (int)(u_begin % nkb);
       pdl_wait();
       pdl_launch();
-      for (long long u = u_begin; u < u_end; ++u) {
-        if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p)) {
-          abort_flag = 1;
-          atomicExch(p.err, 10);
-          break;
-        }
-        const int n0 = (int)(tile % tiles_n) * 2 * TILE_N + (int)rank * TILE_N;
-        const int t0 = (int)(tile / tiles_n) * PAIR_BT + (int)rank * (PAIR_BT / 2);
-        const uint32_t a = smem_base + s * PAIR_STAGE_BYTES;
-        const uint32_t leader_full = map_to_cta(full_bar(s), 0);  // (measured: this loop is not the limit; the copies are)
-        if (rank == 0) mbar_expect_tx(full_bar(s), 2 * PAIR_STAGE_BYTES);
-        if (p.gated) tma_load_3d_pair(a, &tmap_w, leader_full, kb * TILE_K, 0, n0 >> 1);  // (k, gate | up, feature)
-        else tma_load_2d_pair(a, &tmap_w, leader_full, kb * TILE_K, n0);
-        tma_load_2d_pair(a + A_BYTES, &tmap_x, leader_full, kb * TILE_K, t0);
-        if (++s == STAGES) {
-          s = 0;
-          phase ^= 1;
-        }
-        if (++kb == nkb) {
-          kb = 0;
-          ++tile;
+      long long tile;
+      int kb0, kb1;
+      bool ok = true;
+      for (int seg = 0; ok && sched.segment(seg, tile, kb0, kb1); ++seg) {
+        int n_idx, t_idx;
+        sched.coords(tile, n_idx, t_idx);
+        const int n0 = n_idx * 2 * TILE_N + (int)rank * TILE_N;
+        const int t0 = t_idx * PAIR_BT + (int)rank * (PAIR_BT / 2);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p)) {
+            abort_flag = 1;
+            atomicExch(p.err, 10);
+            ok = false;
+            break;
+          }
+          const uint32_t a = smem_base + s * PAIR_STAGE_BYTES;
+          const uint32_t leader_full = map_to_cta(full_bar(s), 0);  // (measured: this loop is not the limit; the copies are)
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * PAIR_STAGE_BYTES);
+          if (p.gated) tma_load_3d_pair(a, &tmap_w, leader_full, kb * TILE_K, 0, n0 >> 1);  // (k, gate | up, feature)
+          else tma_load_2d_pair(a, &tmap_w, leader_full, kb * TILE_K, n0);
+          tma_load_2d_pair(a + A_BYTES, &tmap_x, leader_full, kb * TILE_K, t0);
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
         }
       }
     }
@@ -523,12 +604,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const uint32_t idesc = umma_idesc_bf16(2 * TILE_N, PAIR_BT);
       int s = 0;
       uint32_t phase = 0;
-      int seg = 0;
-      long long u = u_begin;
       bool ok = true;
-      while (ok && u < u_end) {
-        const long long tile = u / nkb;
-        const long long seg_end = min(u_end, (tile + 1) * (long long)nkb);
+      long long tile;
+      int kb0, kb1;
+      for (int seg = 0; ok && sched.segment(seg, tile, kb0, kb1); ++seg) {
         const int buf = seg & 1, use = seg >> 1;
         if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, abort_p)) {
           abort_flag = 1;
@@ -538,7 +617,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         tc_fence_after();
         const uint32_t d0 = tmem_base + buf * ACC_COLS;
         bool first = true;
-        for (; u < seg_end; ++u) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(s), phase, abort_p)) {
             abort_flag = 1;
             atomicExch(p.err, 11);
@@ -562,7 +641,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           }
         }
         if (ok) umma_commit_pair(acc_full_bar(buf), 3);
-        ++seg;
       }
     }
   } else {
@@ -575,8 +653,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     uint8_t* out_stage = smem + STAGES * PAIR_STAGE_BYTES + 256;
     const bool staged = p.out_tma != 0;
     int emitted = 0;  // staged stores issued so far; buffer = emitted & 1
-    int seg = 0;
-    long long u = u_begin;
     pdl_wait();
     // A staging buffer, once the bulk store that last used it has read it; and its way out:
     // through a tensor map (which clips at the tensor's edges), as a store or a float32 add.
@@ -622,11 +698,26 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         tc_apply16(p, t0 + c0 + 16, n0_cta + n_local, hi, hi);
       }
     };
-    while (u < u_end) {
-      const long long tile = u / nkb;
-      const int kb0 = (int)(u % nkb);
-      const long long seg_end = min(u_end, (tile + 1) * (long long)nkb);
-      const bool whole = kb0 == 0 && seg_end == (tile + 1) * (long long)nkb;
+    // The same for interleaved gate and up rows: even lanes hold a feature's gate, odd lanes its
+    // up product.  The two exchange halves of their 32 tokens, so that each ends with both
+    // values of 16 tokens, and the tile leaves as 32 tokens x 64 features of bfloat16.
+    auto emit32_gated = [&](int t0, int c0, int n0_cta, const float (&v)[32]) {
+      const int odd = lane & 1;
+      uint8_t* stage = stage_acquire();
+      __nv_bfloat16* st = (__nv_bfloat16*)stage + (odd * 16) * (TILE_N / 2) + (n_local >> 1);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float theirs = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[16 + j], 1);
+        const float g = odd ? theirs : v[j], up = odd ? v[16 + j] : theirs;
+        st[j * (TILE_N / 2)] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * up);
+      }
+      stage_send(stage, &tmap_out, false, n0_cta >> 1, t0 + c0);
+    };
+    uint32_t fetch_phase = 0;
+    long long tile;
+    int kb0, kb1;
+    for (int seg = 0; sched.segment(seg, tile, kb0, kb1); ++seg) {
+      const bool whole = kb0 == 0 && kb1 == nkb;
       const int buf = seg & 1, use = seg >> 1;
       bool ok = mbar_wait(acc_full_bar(buf), use & 1, abort_p);
       if (!ok) abort_flag = 1;
@@ -636,7 +727,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         break;
       }
       tc_fence_after();
-      const int n0 = (int)(tile % tiles_n) * 2 * TILE_N + (int)rank * TILE_N, t0 = (int)(tile / tiles_n) * PAIR_BT;
+      int n_idx, t_idx;
+      sched.coords(tile, n_idx, t_idx);
+      const int n0 = n_idx * 2 * TILE_N + (int)rank * TILE_N, t0 = t_idx * PAIR_BT;
       const int n = n0 + n_local;
       const uint32_t acc_addr = lane_addr + buf * ACC_COLS;
       const uint32_t leader_acc_empty = map_to_cta(acc_empty_bar(buf), 0);
@@ -661,24 +754,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
       } else if (whole && p.gated) {
-        // Even lanes hold a feature's gate, odd lanes its up product.  The two exchange halves of
-        // their 32 tokens, so that each ends with both values of 16 tokens, and the tile leaves
-        // as 32 tokens x 64 features of bfloat16.
-        const int odd = lane & 1;
 #pragma unroll 1
         for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
           float v[32];
           tmem_ld16(acc_addr + c0, &v[0]);
           tmem_ld16(acc_addr + c0 + 16, &v[16]);
-          uint8_t* stage = stage_acquire();
-          __nv_bfloat16* st = (__nv_bfloat16*)stage + (odd * 16) * (TILE_N / 2) + (n_local >> 1);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float theirs = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[16 + j], 1);
-            const float g = odd ? theirs : v[j], up = odd ? v[16 + j] : theirs;
-            st[j * (TILE_N / 2)] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * up);
-          }
-          stage_send(stage, &tmap_out, false, n0 >> 1, t0 + c0);
+          emit32_gated(t0, c0, n0, v);
         }
         tc_fence_before();
         __syncwarp();
@@ -696,10 +777,74 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
       } else {
         // half-tile partial -> workspace [cluster][end][rank][column][lane]
-        const int c_first = unit_owner(tile * nkb, U, P), c_last = unit_owner(tile * nkb + nkb - 1, U, P);
+        const int c_first = sched.first_owner(tile), c_last = sched.last_owner(tile);
         const int n_contrib = c_last - c_first + 1;
-        const size_t my_slot = ((size_t)cluster * 2 + (u_begin / nkb == tile ? 0 : 1)) * 2 + rank;
+        const size_t my_slot = ((size_t)cluster * 2 + sched.slot_of(cluster, tile)) * 2 + rank;
         float* ws = p.workspace + my_slot * tile_floats;
+        int* const counter = p.counters + tile * 2 + rank;
+        // The cluster that holds a tile's first k-blocks reaches it at the end of its range, as a
+        // rule after the others have left their partials.  If so (and this is the CTA's last
+        // segment, so that the stages lie idle) it does not write a partial of its own: it copies
+        // the others' partials into the stages, one bulk copy each, and adds them to its
+        // accumulator in tensor memory.  The sum runs in K order as in the general case (the
+        // second contributor may do the same: a + b = b + a), so the result is the same bits.
+        {
+          long long t2;
+          int a2, b2;
+          const bool candidate = staged && (cluster == c_first || cluster == c_first + 1) && !sched.segment(seg + 1, t2, a2, b2);
+          if (candidate) {
+            if (ep_tid == 0) is_last = ld_acquire_gpu(counter) == n_contrib - 1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+          const bool fast = candidate && is_last;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (fast) {
+            const float* fetched = (const float*)smem;  // [column][128 rows], as a partial lies in the workspace
+            bool fine = true;
+            for (int cc = c_first; cc <= c_last && fine; ++cc) {
+              if (cc == cluster) continue;
+              const bool final_round = cc == c_last || (cc == c_last - 1 && c_last == cluster);
+              if (ep_tid == 0) {
+                fence_proxy_async();  // the threads' reads of the round before precede these copies
+                const float* src = p.workspace + (((size_t)cc * 2 + sched.slot_of(cc, tile)) * 2 + rank) * tile_floats;
+                mbar_expect_tx(fetch_bar, (uint32_t)(tile_floats * 4));
+                for (int q = 0; q < 4; ++q)
+                  bulk_load(smem_base + q * (uint32_t)tile_floats, src + q * (tile_floats / 4), (uint32_t)tile_floats, fetch_bar);
+              }
+              fine = mbar_wait(fetch_bar, fetch_phase, abort_p);
+              fetch_phase ^= 1;
+              if (!fine) abort_flag = 1;
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              if (abort_flag) {
+                if (ep_tid == 0) atomicExch(p.err, 14);
+                fine = false;
+                break;
+              }
+#pragma unroll 1
+              for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
+                float v[32];
+                tmem_ld16(acc_addr + c0, &v[0]);
+                tmem_ld16(acc_addr + c0 + 16, &v[16]);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += fetched[(size_t)(c0 + j) * TILE_N + n_local];
+                if (!final_round) {
+                  tmem_st16(acc_addr + c0, &v[0]);
+                  tmem_st16(acc_addr + c0 + 16, &v[16]);
+                } else if (p.gated) {
+                  emit32_gated(t0, c0, n0, v);
+                } else {
+                  emit32(t0, c0, n0, v);
+                }
+              }
+              asm volatile("bar.sync 1, 128;" ::: "memory");  // all have read the stages before the next copy lands
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty);
+            if (ep_tid == 0 && fine) *counter = 0;
+            continue;
+          }
+        }
         if (staged) {
           // the partial leaves like the output: 32 columns at a time through shared memory, as bulk
           // stores into the workspace seen as rows of 128 floats
@@ -729,7 +874,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ep_tid == 0) {
-          int* counter = p.counters + tile * 2 + rank;
           const int old = atomicAdd(counter, 1);
           is_last = old == n_contrib - 1;
           if (is_last) *counter = 0;
@@ -742,7 +886,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           // not the products, set the time of a product of a few hundred tokens).
           __threadfence();
           const int q4 = (ep_tid & 31) * 4, cg = (ep_tid >> 5) * 8;
-          auto slot_of = [&](int cc) { return ((size_t)cc * 2 + ((U * cc / P) / nkb == tile ? 0 : 1)) * 2 + rank; };
+          auto slot_of = [&](int cc) { return ((size_t)cc * 2 + sched.slot_of(cc, tile)) * 2 + rank; };
 #pragma unroll 1
           for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
             float4 acc[8];
@@ -799,7 +943,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 #pragma unroll
             for (int j = 0; j < 32; ++j) a0[j] = 0.f;
             for (int cc = c_first; cc <= c_last; ++cc) {  // K order
-              const float* wsp = p.workspace + (((size_t)cc * 2 + ((U * cc / P) / nkb == tile ? 0 : 1)) * 2 + rank) * tile_floats +
+              const float* wsp = p.workspace + (((size_t)cc * 2 + sched.slot_of(cc, tile)) * 2 + rank) * tile_floats +
                                  (size_t)c0 * TILE_N + n_local;
 #pragma unroll
               for (int j = 0; j < 32; ++j) a0[j] += __ldcg(wsp + (size_t)j * TILE_N);
@@ -808,8 +952,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           }
         }
       }
-      u = seg_end;
-      ++seg;
     }
     if (staged && ep_tid == 0) bulk_wait_all();  // shared memory and `out` are settled before the CTA leaves
     tc_fence_before();

@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--epilogue", default="store", choices=["store", "residual", "swiglu"])
+    ap.add_argument("--ctas", type=int, default=0, help="gemm: CTAs of the grid (0 = one per SM)")
     ap.add_argument("--copies", type=int, default=8, help="distinct weight/cache copies cycled through, to defeat L2")
     ap.add_argument("--layers", type=int, default=4, help="cache planes cycled through (attention)")
     ap.add_argument("--iters", type=int, default=20)
@@ -108,7 +109,7 @@ def main():
         else:
             o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
             epi = ops.TC_SWIGLU if dual else ops.TC_STORE_BF16
-        runs = [lambda w=w: ops.gemm_tc(x, w, o, epi, err, ws, cnt, N=N, dual_offset=N if dual else 0) for w in weights]
+        runs = [lambda w=w: ops.gemm_tc(x, w, o, epi, err, ws, cnt, N=N, dual_offset=N if dual else 0, n_ctas=args.ctas) for w in weights]
         if args.deferred:
             if not ops.gemm_tc_can_defer(M, N, K, dual):
                 sys.exit("this shape cannot defer its reduction")
