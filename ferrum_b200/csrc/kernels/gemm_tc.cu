@@ -421,13 +421,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 // them: (P - R) / P of a tile is PAIR_STREAMK_MIN_KB k-blocks or more) the left-over tiles are cut
 // stream-K fashion: their units (tile, k-block) form a line that is divided evenly among the
 // first Pr clusters, and a tile that several clusters share is summed from float32 partials
-// by the last of them to arrive.  That costs a cluster some tens of microseconds (partial out,
-// partials in), which is why short tiles are not cut.  Tiles are numbered through groups of
+// by the cluster that holds its first k-blocks.  That costs some 20 us at the end of the
+// kernel (partials out, a wait, partials in), which is why short tiles are not cut: measured
+// on 2048 x [4096, 14336], cutting 54 left-over tiles of 224 k-blocks (60 k-blocks saved)
+// gains nothing, on 512 x [4096, 14336] (127 saved) it takes 74 us to 60.  Tiles are numbered through groups of
 // PAIR_GROUP_T token tiles, token tile fastest: a wave then reads about P / 8 weight tiles and
 // 8 token tiles instead of P weight tiles and one token tile, and with many tokens the
 // weights stream from memory once per group instead of once per token tile.
 constexpr int PAIR_GROUP_T = 8;
-constexpr int PAIR_STREAMK_MIN_KB = 100;
+constexpr int PAIR_STREAMK_MIN_KB = 80;
+constexpr int PAIR_FINISHER_POLLS = 200;  // of about a microsecond each: how long a tile's finisher waits for the other partials
 struct PairSchedule {
   int nkb, tiles_n, tiles_t, P, cluster, waves, Pr, whole_extra;
   long long full_tiles, Ur, r_begin, r_end;
@@ -782,34 +785,44 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const size_t my_slot = ((size_t)cluster * 2 + sched.slot_of(cluster, tile)) * 2 + rank;
         float* ws = p.workspace + my_slot * tile_floats;
         int* const counter = p.counters + tile * 2 + rank;
-        // The cluster that holds a tile's first k-blocks reaches it at the end of its range, as a
-        // rule after the others have left their partials.  If so (and this is the CTA's last
-        // segment, so that the stages lie idle) it does not write a partial of its own: it copies
-        // the others' partials into the stages, one bulk copy each, and adds them to its
-        // accumulator in tensor memory.  The sum runs in K order as in the general case (the
-        // second contributor may do the same: a + b = b + a), so the result is the same bits.
+        // The cluster that holds a tile's first k-blocks reaches it at the end of its range: it is
+        // the tile's finisher.  It writes no partial of its own.  It waits (a bounded time) until
+        // the others have left theirs, copies them into the idle stages with bulk copies, as many
+        // columns at a time as fit, and adds them to its accumulator from tensor memory in K
+        // order: the same sum, bit for bit, as the general case below, which remains for a finisher
+        // whose wait ran out (the others never wait, so nothing can block).
         {
           long long t2;
           int a2, b2;
-          const bool candidate = staged && (cluster == c_first || cluster == c_first + 1) && !sched.segment(seg + 1, t2, a2, b2);
-          if (candidate) {
-            if (ep_tid == 0) is_last = ld_acquire_gpu(counter) == n_contrib - 1;
+          const int others = n_contrib - 1;
+          // columns per pass: what the stages hold of `others` partials (512 bytes per column)
+          const int pass_cols = min(PAIR_BT, (int)((STAGES * PAIR_STAGE_BYTES) / (others * TILE_N * 4)) & ~31);
+          const bool finisher = staged && cluster == c_first && pass_cols >= 32 && !sched.segment(seg + 1, t2, a2, b2);
+          if (finisher) {
+            if (ep_tid == 0) {
+              int polls = 0;
+              while (ld_acquire_gpu(counter) != others && ++polls < PAIR_FINISHER_POLLS && !*abort_p) __nanosleep(100);
+              is_last = polls < PAIR_FINISHER_POLLS && !*abort_p;
+            }
             asm volatile("bar.sync 1, 128;" ::: "memory");
           }
-          const bool fast = candidate && is_last;
+          const bool fast = finisher && is_last;
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (fast) {
-            const float* fetched = (const float*)smem;  // [column][128 rows], as a partial lies in the workspace
+            const float* fetched = (const float*)smem;  // [contributor][column][128 rows]
             bool fine = true;
-            for (int cc = c_first; cc <= c_last && fine; ++cc) {
-              if (cc == cluster) continue;
-              const bool final_round = cc == c_last || (cc == c_last - 1 && c_last == cluster);
+            for (int cb = 0; cb < PAIR_BT && t0 + cb < p.M && fine; cb += pass_cols) {
+              const int ncols = min(pass_cols, PAIR_BT - cb);
               if (ep_tid == 0) {
-                fence_proxy_async();  // the threads' reads of the round before precede these copies
-                const float* src = p.workspace + (((size_t)cc * 2 + sched.slot_of(cc, tile)) * 2 + rank) * tile_floats;
-                mbar_expect_tx(fetch_bar, (uint32_t)(tile_floats * 4));
-                for (int q = 0; q < 4; ++q)
-                  bulk_load(smem_base + q * (uint32_t)tile_floats, src + q * (tile_floats / 4), (uint32_t)tile_floats, fetch_bar);
+                fence_proxy_async();  // the threads' reads of the pass before precede these copies
+                mbar_expect_tx(fetch_bar, (uint32_t)(others * ncols * TILE_N * 4));
+                for (int i = 0; i < others; ++i) {
+                  const int cc = c_first + 1 + i;
+                  const float* src = p.workspace + (((size_t)cc * 2 + sched.slot_of(cc, tile)) * 2 + rank) * tile_floats + (size_t)cb * TILE_N;
+                  const uint32_t dst = smem_base + (uint32_t)(i * pass_cols * TILE_N * 4);
+                  for (int c = 0; c < ncols; c += 32)  // 16 KB a copy
+                    bulk_load(dst + c * TILE_N * 4, src + (size_t)c * TILE_N, 32 * TILE_N * 4, fetch_bar);
+                }
               }
               fine = mbar_wait(fetch_bar, fetch_phase, abort_p);
               fetch_phase ^= 1;
@@ -821,22 +834,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 break;
               }
 #pragma unroll 1
-              for (int c0 = 0; c0 < PAIR_BT && t0 + c0 < p.M; c0 += 32) {
+              for (int c0 = cb; c0 < cb + ncols && t0 + c0 < p.M; c0 += 32) {
                 float v[32];
                 tmem_ld16(acc_addr + c0, &v[0]);
                 tmem_ld16(acc_addr + c0 + 16, &v[16]);
+                for (int i = 0; i < others; ++i) {
+                  const float* f = fetched + (size_t)i * pass_cols * TILE_N + (size_t)(c0 - cb) * TILE_N + n_local;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += fetched[(size_t)(c0 + j) * TILE_N + n_local];
-                if (!final_round) {
-                  tmem_st16(acc_addr + c0, &v[0]);
-                  tmem_st16(acc_addr + c0 + 16, &v[16]);
-                } else if (p.gated) {
-                  emit32_gated(t0, c0, n0, v);
-                } else {
-                  emit32(t0, c0, n0, v);
+                  for (int j = 0; j < 32; ++j) v[j] += f[j * TILE_N];
                 }
+                if (p.gated) emit32_gated(t0, c0, n0, v);
+                else emit32(t0, c0, n0, v);
               }
-              asm volatile("bar.sync 1, 128;" ::: "memory");  // all have read the stages before the next copy lands
+              asm volatile("bar.sync 1, 128;" ::: "memory");  // all have read the stages before the next copies land
             }
             tc_fence_before();
             __syncwarp();
