@@ -151,6 +151,44 @@ def test_gemm_tc(ops, M, N, K, n_ctas):
     assert torch.equal(again, out)        # shared tiles are summed in K order: run-to-run identical
 
 
+@pytest.mark.parametrize("M,N,K,n_ctas", [(300, 256, 8192, 12), (300, 256, 8192, 40), (300, 256, 8192, 0), (515, 640, 8192, 8),
+                                          (515, 640, 8192, 0), (700, 384, 4096, 6)])
+def test_gemm_tc_pair_shared_tiles(ops, M, N, K, n_ctas):
+    """The CTA-pair kernel where left-over tiles are long enough to be cut among pairs: tiles
+    shared by 3 pairs (the finisher adds the others' partials to its accumulator), by 10 (in
+    several passes), by dozens (the last arriver sums), and a cut that takes the last whole wave
+    with it.  Every epilogue; the float32 result is the same bits from run to run."""
+    g = torch.Generator(device="cuda").manual_seed(15)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.1).bfloat16()
+    ref = x.double() @ w.double().T
+    e = err_flag()
+    ws, cnt = tc_scratch(ops, M, N, K, False, n_ctas)
+    outb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tc(x, w, outb, ops.TC_STORE_BF16, e, ws, cnt, n_ctas=n_ctas)
+    assert ((outb.double() - ref).abs() <= lim(ref, 8e-3)).all(), (outb.double() - ref).abs().max()
+    res = torch.randn(M, N, device="cuda", generator=g)
+    acc = res.clone()
+    ops.gemm_tc(x, w, acc, ops.TC_RESIDUAL, e, ws, cnt, n_ctas=n_ctas)
+    assert ((acc.double() - (res.double() + ref)).abs() <= lim(ref, 2e-5) * math.sqrt(K)).all()
+    again = res.clone()
+    ops.gemm_tc(x, w, again, ops.TC_RESIDUAL, e, ws, cnt, n_ctas=n_ctas)
+    assert torch.equal(again, acc)
+    out = torch.empty(M, N, device="cuda")
+    ops.gemm_tc(x, w, out, ops.TC_STORE_F32, e, ws, cnt, n_ctas=n_ctas)
+    assert ((out.double() - ref).abs() <= lim(ref, 2e-5) * math.sqrt(K)).all()
+    assert cnt.sum().item() == 0 and e.item() == 0
+    # gate and up as one product of interleaved rows
+    F = N // 2
+    gate, up = ref[:, :F], ref[:, F:]
+    want = gate / (1 + torch.exp(-gate)) * up
+    ws2, cnt2 = tc_scratch(ops, M, F, K, True, n_ctas)
+    act = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tc(x, w, act, ops.TC_SWIGLU, e, ws2, cnt2, N=F, dual_offset=F, n_ctas=n_ctas)
+    assert e.item() == 0 and cnt2.sum().item() == 0
+    assert ((act.double() - want).abs() <= lim(want, 1e-2)).all(), (act.double() - want).abs().max()
+
+
 @pytest.mark.parametrize("M,F,K", [(3, 172 * 2, 64), (16, 256, 96), (40, 200, 320), (130, 384, 256), (300, 128, 128),
                                    (129, 72, 64), (515, 200, 320), (700, 1000, 2048)])
 @pytest.mark.parametrize("n_ctas", [0, 2, 5])
