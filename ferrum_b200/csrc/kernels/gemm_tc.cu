@@ -121,7 +121,7 @@ __device__ __forceinline__ void tc_apply16(const TcParams& p, int t_base, int n,
 }
 
 // The CTA that owns unit u when CTA c owns [c*U/P, (c+1)*U/P).
-__device__ __forceinline__ int unit_owner(long long u, long long U, int P) {
+__host__ __device__ __forceinline__ int unit_owner(long long u, long long U, int P) {
   return (int)(((u + 1) * P + U - 1) / U) - 1;
 }
 
@@ -434,7 +434,7 @@ constexpr int PAIR_FINISHER_POLLS = 200;  // of about a microsecond each: how lo
 struct PairSchedule {
   int nkb, tiles_n, tiles_t, P, cluster, waves, Pr, whole_extra;
   long long full_tiles, Ur, r_begin, r_end;
-  __device__ PairSchedule(int tiles_n_, int tiles_t_, int nkb_, int P_, int cluster_)
+  __host__ __device__ PairSchedule(int tiles_n_, int tiles_t_, int nkb_, int P_, int cluster_)
       : nkb(nkb_), tiles_n(tiles_n_), tiles_t(tiles_t_), P(P_), cluster(cluster_) {
     const long long tiles = (long long)tiles_n * tiles_t;
     const int R = (int)(tiles % P);
@@ -449,14 +449,14 @@ struct PairSchedule {
       // few tiles left over would each be cut among many clusters: cut the last whole wave with them
       if (waves > 0 && 2 * R < P) --waves;
       Ur = (tiles - (long long)waves * P) * nkb;
-      Pr = (int)min((long long)P, Ur);   // every sharing cluster owns at least one unit
+      Pr = (int)(Ur < P ? Ur : P);   // every sharing cluster owns at least one unit
       r_begin = cluster < Pr ? Ur * cluster / Pr : 0;
       r_end = cluster < Pr ? Ur * (cluster + 1) / Pr : 0;
     }
     full_tiles = (long long)waves * P;
   }
   // this cluster's s-th segment: its tile and k-blocks [kb0, kb1); false when there is none
-  __device__ bool segment(int s, long long& tile, int& kb0, int& kb1) const {
+  __host__ __device__ bool segment(int s, long long& tile, int& kb0, int& kb1) const {
     if (s < waves) {
       tile = (long long)s * P + cluster;
       kb0 = 0;
@@ -475,23 +475,23 @@ struct PairSchedule {
     if (rt * nkb >= r_end) return false;
     tile = full_tiles + rt;
     kb0 = r == 0 ? (int)(r_begin % nkb) : 0;
-    kb1 = (int)min((long long)nkb, r_end - rt * nkb);
+    kb1 = (int)(r_end - rt * nkb < nkb ? r_end - rt * nkb : nkb);
     return true;
   }
-  __device__ void coords(long long tile, int& n_idx, int& t_idx) const {
+  __host__ __device__ void coords(long long tile, int& n_idx, int& t_idx) const {
     const long long per_group = (long long)PAIR_GROUP_T * tiles_n;
     const int g = (int)(tile / per_group);
     const int t_first = g * PAIR_GROUP_T;
-    const int gt = min(PAIR_GROUP_T, tiles_t - t_first);
+    const int gt = tiles_t - t_first < PAIR_GROUP_T ? tiles_t - t_first : PAIR_GROUP_T;
     const int r = (int)(tile - g * per_group);
     t_idx = t_first + r % gt;
     n_idx = r / gt;
   }
   // the clusters that share a tile of the remainder, and the slot (0: the tile in which the
   // cluster's range begins, 1: the other) in which cluster cc leaves its partial of it
-  __device__ int first_owner(long long tile) const { return unit_owner((tile - full_tiles) * nkb, Ur, Pr); }
-  __device__ int last_owner(long long tile) const { return unit_owner((tile - full_tiles) * nkb + nkb - 1, Ur, Pr); }
-  __device__ int slot_of(int cc, long long tile) const { return (Ur * cc / Pr) / nkb == tile - full_tiles ? 0 : 1; }
+  __host__ __device__ int first_owner(long long tile) const { return unit_owner((tile - full_tiles) * nkb, Ur, Pr); }
+  __host__ __device__ int last_owner(long long tile) const { return unit_owner((tile - full_tiles) * nkb + nkb - 1, Ur, Pr); }
+  __host__ __device__ int slot_of(int cc, long long tile) const { return (Ur * cc / Pr) / nkb == tile - full_tiles ? 0 : 1; }
 };
 
 constexpr int PAIR_BT = 256;                              // tokens per tile pair
@@ -1235,6 +1235,31 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
   }
 #undef TC_CASE
   FERRUM_CHECK_ARG(false, "gemm_tc: no kernel for token tile %d", bt);
+}
+
+// For tests of the schedule on the host: pair `cluster`'s s-th segment when `pairs` pairs
+// compute M tokens x `rows` weight rows (for gate and up as one product: both) over K.
+// out[0..7] = tile, first k-block, one past the last, weight tile index, token tile index, and
+// for a tile that pairs share its first and last contributor and the slot (0 or 1) of this
+// pair's partial (-1 each for a whole tile).  Returns 0 when the pair has no such segment.
+FERRUM_API int ferrum_gemm_pair_schedule(int M, long long rows, int K, int pairs, int cluster, int s, long long* out) {
+  const int nkb = (K + TILE_K - 1) / TILE_K;
+  const int tiles_n = (int)((rows + 2 * TILE_N - 1) / (2 * TILE_N)), tiles_t = (M + PAIR_BT - 1) / PAIR_BT;
+  const PairSchedule sched(tiles_n, tiles_t, nkb, pairs, cluster);
+  long long tile;
+  int kb0, kb1, n_idx, t_idx;
+  if (!sched.segment(s, tile, kb0, kb1)) return 0;
+  sched.coords(tile, n_idx, t_idx);
+  const bool whole = kb0 == 0 && kb1 == nkb;
+  out[0] = tile;
+  out[1] = kb0;
+  out[2] = kb1;
+  out[3] = n_idx;
+  out[4] = t_idx;
+  out[5] = whole ? -1 : sched.first_owner(tile);
+  out[6] = whole ? -1 : sched.last_owner(tile);
+  out[7] = whole ? -1 : sched.slot_of(cluster, tile);
+  return 1;
 }
 
 // ------------------------------------------------------------------ deferred reduction
