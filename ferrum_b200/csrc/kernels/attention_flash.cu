@@ -371,34 +371,42 @@ flash_kernel(const FlashParams p) {
 
 // Merges the splits of every (token, head) whose tile was split.  tile_info: per (tile, KV
 // head) [first part slot, n_splits, slot stride, 0]; req_tile0[r]: index of request r's first
-// tile; token_list: the tokens to visit (null: all n_tokens).
+// tile; token_list: the tokens to visit (null: all n_tokens).  A block is one (token, head):
+// 32 lanes x 4 features, times blockDim.x / 32 warps that share the splits among them (a
+// single decoded request's keys are cut into dozens of splits: one warp would walk them in
+// seven rounds of memory latency).
+constexpr int COMBINE_MAX_WARPS = 8;
 template <int D>
-__global__ void __launch_bounds__(D / 4 < 32 ? 32 : D / 4)
+__global__ void __launch_bounds__(32 * COMBINE_MAX_WARPS)
 combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* part_ml, const int* q_start,
                const int* req_of_token, const int* req_tile0, const int* tile_info, const int* token_list, int G,
                int Hkv, int BM) {
   TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0, TRACE_COMBINE);
   pdl_launch();
-  pdl_wait();
-  TRACE_MARK(TRACE_WAITED);
-  TRACE_MARK(TRACE_EXIT);
+  // The index arrays were copied to the device before the step's first kernel ran: they are
+  // read before the wait for the attention kernel, whose partials come after it.
   const int t = token_list ? token_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int req = req_of_token[t];
   const int kvh = head / G;
   const int pr = (t - q_start[req]) * G + head % G;
   const int* info = tile_info + 4 * ((size_t)(req_tile0[req] + pr / BM) * Hkv + kvh);
   const int first = info[0], n = info[1], stride = info[2];
+  pdl_wait();
+  TRACE_MARK(TRACE_WAITED);
+  TRACE_MARK(TRACE_EXIT);
   if (n <= 1) return;
   const int r = pr % BM;
-  const int d = threadIdx.x * 4;
-  if (d >= D) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int d = lane * 4;
+  const bool active = d < D;
   // Eight splits at a time, all their loads in flight together (the kernel is a chain of memory
-  // latencies otherwise); the running maximum is carried from one group to the next.  Splits are
-  // taken in slot order, so the result does not depend on which block finished first.
+  // latencies otherwise); the running maximum is carried from one group to the next.  Which
+  // warp takes which splits and the order of the sums are fixed, so the result does not depend
+  // on which block of the attention kernel finished first.
   constexpr int GROUP = 8;
   float M = -INFINITY, L = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s0 = 0; s0 < n; s0 += GROUP) {
+  for (int s0 = warp * GROUP; s0 < n && active; s0 += n_warps * GROUP) {
     float ms[GROUP], ls[GROUP];
     float4 v[GROUP];
 #pragma unroll
@@ -423,6 +431,32 @@ combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* pa
     }
     M = m_new;
   }
+  if (n_warps > 1) {  // the warps' sums meet in warp order
+    // (dynamic shared memory, none with one warp: the blocks of this kernel become resident
+    // beside the attention kernel's, which leave little)
+    extern __shared__ float4 combine_smem[];
+    float4(*sm_acc)[32] = reinterpret_cast<float4(*)[32]>(combine_smem);
+    float2(*sm_ml)[32] = reinterpret_cast<float2(*)[32]>(combine_smem + n_warps * 32);
+    sm_ml[warp][lane] = make_float2(M, L);
+    sm_acc[warp][lane] = acc;
+    __syncthreads();
+    if (warp != 0) return;
+    M = -INFINITY;
+    L = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int w = 0; w < n_warps; ++w) {
+      const float2 ml = sm_ml[w][lane];
+      const float4 v = sm_acc[w][lane];
+      const float m_new = fmaxf(M, ml.x);
+      const float keep = M == -INFINITY ? 0.f : exp2f(M - m_new);
+      const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m_new);
+      L = L * keep + ml.y * f;
+      acc.x = acc.x * keep + v.x * f; acc.y = acc.y * keep + v.y * f;
+      acc.z = acc.z * keep + v.z * f; acc.w = acc.w * keep + v.w * f;
+      M = m_new;
+    }
+  }
+  if (!active) return;
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   uint2 packed;
   packed.x = pack_bf16(acc.x * inv, acc.y * inv);
@@ -491,16 +525,19 @@ FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo
 FERRUM_API int ferrum_attention_combine(void* out, int ldo, const float* part_o, const float* part_ml,
                                         const int* q_start, const int* req_of_token, const int* req_tile0,
                                         const int* tile_info, const int* token_list, int n_tokens, int Hq, int Hkv,
-                                        int D, int bm, cudaStream_t stream) {
+                                        int D, int bm, int n_warps, cudaStream_t stream) {
   FERRUM_CHECK_ARG(D == 64 || D == 128, "attention_combine: head size %d is not built", D);
+  FERRUM_CHECK_ARG(n_warps >= 1 && n_warps <= COMBINE_MAX_WARPS, "attention_combine: %d warps per block (1..%d)", n_warps,
+                   COMBINE_MAX_WARPS);
   if (n_tokens == 0) return 0;
   dim3 grid(n_tokens, Hq);
   FERRUM_CHECK_ARG(grid.y <= 65535, "attention_combine: too many heads");
+  const int smem = n_warps > 1 ? n_warps * 32 * (int)(sizeof(float4) + sizeof(float2)) : 0;
   if (D == 64)
-    launch_kernel(combine_kernel<64>, grid, dim3(32), 0, stream, (__nv_bfloat16*)out, ldo, part_o, part_ml, q_start,
+    launch_kernel(combine_kernel<64>, grid, dim3(32 * n_warps), smem, stream, (__nv_bfloat16*)out, ldo, part_o, part_ml, q_start,
                   req_of_token, req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
   else
-    launch_kernel(combine_kernel<128>, grid, dim3(32), 0, stream, (__nv_bfloat16*)out, ldo, part_o, part_ml, q_start,
+    launch_kernel(combine_kernel<128>, grid, dim3(32 * n_warps), smem, stream, (__nv_bfloat16*)out, ldo, part_o, part_ml, q_start,
                   req_of_token, req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
   FERRUM_CHECK_LAUNCH("attention_combine");
   return 0;

@@ -178,6 +178,7 @@ class ClassPlan:
     cta_items: Optional[torch.Tensor] = None    # balanced list: first item of every CTA (+ end)
     n_ctas: int = 0
     kind: str = "flash"                         # "flash": the mma.sync kernel; "tc": the tcgen05 kernel
+    comb_warps: int = 1                         # warps per (token, head) of the merge kernel
 
 
 class AttentionPlans:
@@ -229,6 +230,8 @@ class AttentionPlans:
         cp.cta_items, cp.n_ctas = dev[o3:total], CTA_SLOTS if fixed else d.n_ctas
         # the merge visits every token; those whose keys were not split return at once
         cp.comb_tokens, cp.n_comb = None, (ctx.n_tokens if (fixed or d.n_slots) else 0)
+        # a (request, KV head) gets about CTA_SLOTS / (R * Hkv) splits; one warp takes eight at a time
+        cp.comb_warps = int(min(8, max(1, -(-CTA_SLOTS // (R * Hkv * 8)))))
         return [cp, None, None]
 
     def get(self, ctx, G, window, Hkv, fixed=False, tc_tokens=0) -> List[Optional[ClassPlan]]:

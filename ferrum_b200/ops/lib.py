@@ -24,7 +24,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 4
+ABI = 5
 
 
 def lib():
@@ -318,11 +318,12 @@ def attention_tc(q, out, kv_plane, page_stride, page_size, block_table, q_start,
 
 
 def attention_combine(out, part_o, part_ml, q_start, req_of_token, req_tile0, tile_info, token_list, n_tokens, Hq, Hkv,
-                      D, bm):
-    """Merges the key-range splits written by attention_flash into `out`."""
+                      D, bm, n_warps=1):
+    """Merges the key-range splits written by attention_flash into `out`.  n_warps (1..8): warps
+    per (token, head) that share its splits; more than one pays from about 16 splits on."""
     _check(lib().ferrum_attention_combine(_ptr(out), c_int(out.stride(0)), _ptr(part_o), _ptr(part_ml), _ptr(q_start),
                                           _ptr(req_of_token), _ptr(req_tile0), _ptr(tile_info), _ptr(token_list),
-                                          c_int(n_tokens), c_int(Hq), c_int(Hkv), c_int(D), c_int(bm), _stream()),
+                                          c_int(n_tokens), c_int(Hq), c_int(Hkv), c_int(D), c_int(bm), c_int(n_warps), _stream()),
            "attention_combine")
 
 

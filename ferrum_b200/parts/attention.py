@@ -95,4 +95,4 @@ class PagedAttention(Mixer):
                                     trigger_early=ctx.n_tokens <= EARLY_TRIGGER_MAX_TOKENS)
             if plan.n_comb:
                 ops.attention_combine(out, part_o, part_ml, ctx.q_start, ctx.req_of_token, plan.req_tile0,
-                                      plan.tile_info, plan.comb_tokens, plan.n_comb, Hq, Hkv, D, plan.bm)
+                                      plan.tile_info, plan.comb_tokens, plan.n_comb, Hq, Hkv, D, plan.bm, plan.comb_warps)

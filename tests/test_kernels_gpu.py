@@ -294,7 +294,7 @@ def test_attention_finds_one_far_key(ops, dtype, far_key):
     assert np.abs(got - ref).max() <= (1e-4 if dtype == torch.float32 else 2e-2)
 
 
-def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window, use_tc=False, counts=None):
+def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window, use_tc=False, counts=None, comb_warps=1):
     """Drive the tensor-core attention the way the attention part does: plan, launch per
     row-tile class (the tcgen05 kernel for its class when use_tc), merge splits."""
     from ferrum_b200.engine.attn_plan import build_host
@@ -326,7 +326,7 @@ def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window, use_tc=
                                 dev(h["cta_items"]) if h["n_ctas"] else None, h["n_ctas"])
         if h["comb"].size:
             ops.attention_combine(out, part_o, part_ml, dev(qs), dev(req), dev(h["req_tile0"]), dev(h["tile_info"]),
-                                  dev(h["comb"]), int(h["comb"].size), Hq, Hkv, D, h["bm"])
+                                  dev(h["comb"]), int(h["comb"].size), Hq, Hkv, D, h["bm"], comb_warps)
         n_split_items += h["n_slots"]
     return out, n_split_items
 
@@ -388,6 +388,31 @@ def test_attention_tc(ops, Hq, Hkv, D, ps, window):
         assert np.isfinite(got).all(), r
         assert np.abs(got - ref).max() <= 1.5e-2, (r, np.abs(got - ref).max())
         t0 += ql
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,comb_warps", [(8, 2, 128, 8), (4, 4, 64, 3), (8, 2, 128, 1)])
+def test_attention_merge_of_many_splits(ops, Hq, Hkv, D, comb_warps):
+    """One decoded token over 20000 keys: its (request, head) pairs are cut into dozens of
+    splits, which the merge kernel's warps share; one key far back carries the weight."""
+    ps = 16; n = 20000; far_key = 777
+    plane, table, ks, vs = paged_setup([n], Hkv, D, ps, torch.bfloat16, 31)
+    g = torch.Generator(device="cuda").manual_seed(32)
+    q = torch.randn(1, Hq * D, device="cuda", generator=g).bfloat16()
+    counts = {}
+    out, n_split = run_flash(ops, q, [n], [1], table, plane, ps, Hq, Hkv, D, 0, counts=counts, comb_warps=comb_warps)
+    assert n_split >= 16 * Hkv, n_split
+    G = Hq // Hkv                                              # the last row sees every key: softmax(q k / sqrt(D)) v
+    qd = q.double().reshape(Hkv, G, D)
+    sc = torch.einsum("hgd,nhd->hgn", qd, ks[0].double()) / math.sqrt(D)
+    ref = torch.einsum("hgn,nhd->hgd", torch.softmax(sc, dim=-1), vs[0].double()).reshape(1, Hq * D)
+    assert (out.double() - ref).abs().max().item() <= 1.5e-2
+    # and with one query made to match one key: the split that holds it must win the merge
+    kq = ks[0][far_key].float()
+    q2 = (kq * (40.0 * math.sqrt(D) / kq.pow(2).sum(-1, keepdim=True))).reshape(1, Hkv, 1, D).expand(1, Hkv, Hq // Hkv, D)
+    q2 = q2.reshape(1, Hq * D).bfloat16().contiguous()
+    out2, _ = run_flash(ops, q2, [n], [1], table, plane, ps, Hq, Hkv, D, 0, comb_warps=comb_warps)
+    want = vs[0][far_key].float().reshape(Hkv, 1, D).expand(Hkv, Hq // Hkv, D).reshape(1, Hq * D)
+    assert (out2.float() - want).abs().max().item() <= 2e-2
 
 
 @pytest.mark.parametrize("far_key", [0, 15, 16, 63, 64, 255, 256, 1023, 1024, 2047, 2048, 2999])
