@@ -224,7 +224,7 @@ def timeline(args):
     print(f"decode step, batch {B}, context {C}, {args.layers} layers; microseconds; block 0 of each launch")
     print(f"{'kernel':22s} {'entry':>9s} {'waited':>9s} {'exit':>9s} | {'work':>7s} {'hand-over':>9s}")
     for kind, entry, waited, exit_ in ev:
-        if kind % 16 == 1:
+        if kind % 8 == 1:
             name = f"product N={kind // 16 * 64}" + (" x2" if kind & 8 else "")
         else:
             name = names.get(kind, str(kind))
