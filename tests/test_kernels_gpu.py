@@ -114,7 +114,7 @@ def test_gemm_generic_row_independent_of_batch(ops):
 
 # ---------------------------------------------------------------- tensor-core product
 TC_SHAPES = [(1, 128, 64), (5, 200, 136), (16, 384, 512), (33, 1000, 264), (64, 256, 1024), (100, 130, 4096),
-             (200, 640, 320), (300, 256, 192), (515, 384, 128)]
+             (200, 640, 320), (300, 256, 192), (515, 384, 128), (2500, 640, 128)]   # the last: ten token tiles, two groups
 
 
 def tc_scratch(ops, M, N, K, dual, n_ctas):
