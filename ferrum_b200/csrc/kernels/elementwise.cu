@@ -645,6 +645,58 @@ __global__ void swiglu_reduce_kernel(__nv_bfloat16* __restrict__ act, int F, int
   TRACE_MARK(TRACE_EXIT);
 }
 
+// The same for many tokens: a thread owns four neighbouring features (one 16-byte piece of a
+// partial's column: they share a tile and so their contributors) and walks SWIGLU_REDUCE_TOKENS
+// tokens with the slot addresses it worked out once.  One load and one table lookup per
+// feature and token made this kernel, not memory, the limit at 64 tokens.
+constexpr int SWIGLU_REDUCE_TOKENS = 2;
+__global__ void __launch_bounds__(256)
+swiglu_reduce_vec_kernel(__nv_bfloat16* __restrict__ act, int n_tokens, int F, int ld_out, const PartialLayout L) {
+  __shared__ PartialTable tab;
+  TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1, TRACE_SWIGLU_REDUCE);
+  build_partial_table(L, tab);
+  pdl_launch();
+  pdl_wait();
+  TRACE_MARK(TRACE_WAITED);
+  const int f = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (f >= F) return;
+  const int tile = f >> 7, nl = f & 127;
+  const int fc = tab.first_and_count[tile];
+  const int c_first = fc & 0xFFFF, count = fc >> 16;
+  const unsigned bits = tab.slot_bits[tile];
+  const size_t slot_floats = (size_t)L.acc_cols * 128;
+  const float* base[PARTIAL_MAX_CONTRIB];
+#pragma unroll
+  for (int s = 0; s < PARTIAL_MAX_CONTRIB; ++s)
+    base[s] = L.ws + (size_t)((c_first + (s < count ? s : 0)) * 2 + ((bits >> (s < count ? s : 0)) & 1)) * slot_floats + nl;
+  const int t0 = blockIdx.y * SWIGLU_REDUCE_TOKENS;
+  const int up_col = L.acc_cols / 2;
+#pragma unroll
+  for (int t = t0; t < t0 + SWIGLU_REDUCE_TOKENS; ++t) {  // unrolled: the tokens' loads are in flight together
+    if (t >= n_tokens) break;
+    float4 g[PARTIAL_MAX_CONTRIB], u[PARTIAL_MAX_CONTRIB];
+#pragma unroll
+    for (int s = 0; s < PARTIAL_MAX_CONTRIB; ++s) {  // all loads first, then the sums in contributor (K) order
+      const bool have = s < count;
+      g[s] = have ? __ldcg(reinterpret_cast<const float4*>(base[s] + (size_t)t * 128)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      u[s] = have ? __ldcg(reinterpret_cast<const float4*>(base[s] + (size_t)(up_col + t) * 128)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float4 gs = make_float4(0.f, 0.f, 0.f, 0.f), us = gs;
+#pragma unroll
+    for (int s = 0; s < PARTIAL_MAX_CONTRIB; ++s) {
+      gs.x += g[s].x; gs.y += g[s].y; gs.z += g[s].z; gs.w += g[s].w;
+      us.x += u[s].x; us.y += u[s].y; us.z += u[s].z; us.w += u[s].w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(gs.x / (1.0f + __expf(-gs.x)) * us.x, gs.y / (1.0f + __expf(-gs.y)) * us.y);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(gs.z / (1.0f + __expf(-gs.z)) * us.z, gs.w / (1.0f + __expf(-gs.w)) * us.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(act + (size_t)t * ld_out + f) = pk;
+  }
+  TRACE_MARK(TRACE_EXIT);
+}
+
 FERRUM_API int ferrum_swiglu_reduce(void* act, int n_tokens, int F, int ld_out, const float* partials, const int* layout,
                                     cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && F > 0 && ld_out >= F, "swiglu_reduce: bad sizes");
@@ -652,6 +704,12 @@ FERRUM_API int ferrum_swiglu_reduce(void* act, int n_tokens, int F, int ld_out, 
   PartialLayout L;
   if (int r = make_layout(partials, layout, &L)) return r;
   FERRUM_CHECK_ARG(F <= L.tiles * 128 && n_tokens <= L.acc_cols / 2, "swiglu_reduce: the partials do not cover the rows");
+  if (n_tokens > 16 && F % 4 == 0 && ld_out % 4 == 0 && ((uintptr_t)act & 7) == 0) {
+    dim3 vgrid((F / 4 + 255) / 256, (n_tokens + SWIGLU_REDUCE_TOKENS - 1) / SWIGLU_REDUCE_TOKENS);
+    launch_kernel(swiglu_reduce_vec_kernel, vgrid, dim3(256), 0, stream, (__nv_bfloat16*)act, n_tokens, F, ld_out, L);
+    FERRUM_CHECK_LAUNCH("swiglu_reduce");
+    return 0;
+  }
   dim3 grid((F + 255) / 256 > 32 ? 32 : (F + 255) / 256, n_tokens);
   launch_kernel(swiglu_reduce_kernel, grid, dim3(256), 0, stream, (__nv_bfloat16*)act, F, ld_out, L);
   FERRUM_CHECK_LAUNCH("swiglu_reduce");
