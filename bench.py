@@ -134,7 +134,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--model", default="llama31-8b", choices=sorted(MODELS), help="layer sizes (random weights)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--context", type=int, default=None,
+                    help="cached tokens per request (default 8192; 4096 for llama32-3b and 2048 for llama2-7b, whose batch-64 point fits the memory then)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
@@ -163,6 +164,8 @@ def main():
     L = cfgd["num_hidden_layers"]
     arch = registry.lookup(cfgd["architectures"][0])
     cfg = arch.read_config(cfgd)
+    if args.context is None:
+        args.context = {"llama32-3b": 4096, "llama2-7b": 2048}.get(args.model, 8192)
     ctx_len, B = args.context, args.batch
     max_len = ctx_len + W + K + 128 + 4 * args.batch
     page = 16
