@@ -412,6 +412,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const float f = m_run == -INFINITY ? 0.f : fast_exp2(m_run - cand);  // cand is finite where m_run is
         l_run *= f;
         if (j > 0) {
+          // (the scores of stage j were issued after P V of stage j - 2 and its commit, so that
+          // arrival is in: the barrier is in phase j - 1 or j, and the parity names the right one)
           ok = wait_all(pv_done(t), (j - 1) & 1);
           if (!ok) {
             abort_flag = 1;
