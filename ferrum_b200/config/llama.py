@@ -13,7 +13,7 @@ import json
 import math
 import os
 from dataclasses import asdict, dataclass, field
-from typing import Optional
+from typing import Optional, Tuple
 
 from ..errors import ConfigError
 
@@ -47,7 +47,8 @@ class LlamaConfig:
     rope_pairing: str = "half"             # "half": (i, i+R/2) HF order; "adjacent": (2i, 2i+1) GGUF order
     tie_word_embeddings: bool = False
     bos_token_id: Optional[int] = None
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None     # the first of eos_token_ids
+    eos_token_ids: Tuple[int, ...] = ()    # every id that ends a sequence (config.json may list several)
     stored_dtype: str = "float32"
     name: str = ""
     extra: dict = field(default_factory=dict, compare=False)
@@ -56,6 +57,11 @@ class LlamaConfig:
     def __post_init__(self):
         if self.rope_dim == 0:
             object.__setattr__(self, "rope_dim", self.head_dim)
+        ids = tuple(int(t) for t in self.eos_token_ids)
+        if not ids and self.eos_token_id is not None:
+            ids = (int(self.eos_token_id),)
+        object.__setattr__(self, "eos_token_ids", ids)
+        object.__setattr__(self, "eos_token_id", ids[0] if ids else None)
         self.validate()
 
     def validate(self):
@@ -77,8 +83,7 @@ class LlamaConfig:
             raise ConfigError("invalid rope frequency base")
         if self.rope_pairing not in ("half", "adjacent"):
             raise ConfigError(f"unknown rope pairing {self.rope_pairing!r}")
-        for k in ("bos_token_id", "eos_token_id"):
-            v = getattr(self, k)
+        for v in (self.bos_token_id,) + self.eos_token_ids:
             if v is not None and not (0 <= v < self.n_vocab):
                 raise ConfigError("special token id is outside the vocab")
         rs = self.rope_scaling
@@ -133,8 +138,10 @@ class LlamaConfig:
                  "eos_token_id", "torch_dtype", "dtype", "attention_bias", "mlp_bias", "rope_pairing",
                  "partial_rotary_dim", "model_type", "_name_or_path"}
         eos = d.get("eos_token_id")
-        if isinstance(eos, list):
-            eos = eos[0] if eos else None
+        try:
+            eos_ids = tuple(int(t) for t in eos) if isinstance(eos, (list, tuple)) else (() if eos is None else (int(eos),))
+        except (TypeError, ValueError):
+            raise ConfigError(f"config.json: eos_token_id must be an integer or a list of integers, found {eos!r}") from None
         return LlamaConfig(
             architecture=str(archs[0]),
             n_vocab=int(need("vocab_size")), n_embd=n_embd, n_layer=int(need("num_hidden_layers")),
@@ -147,7 +154,7 @@ class LlamaConfig:
             rope_scaling=scaling,
             rope_pairing=str(d.get("rope_pairing", "half")),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
-            bos_token_id=d.get("bos_token_id"), eos_token_id=eos,
+            bos_token_id=d.get("bos_token_id"), eos_token_ids=eos_ids,
             stored_dtype=str(d.get("torch_dtype") or d.get("dtype") or "float32"),
             name=str(d.get("_name_or_path", "")),
             extra={k: v for k, v in d.items() if k not in known})
@@ -166,7 +173,7 @@ class LlamaConfig:
         return LlamaConfig.from_dict(d)
 
     @staticmethod
-    def from_gguf_metadata(meta: dict, n_vocab_from_tensor: Optional[int] = None) -> "LlamaConfig":
+    def from_gguf_metadata(meta: dict, n_vocab_from_tensor: Optional[int] = None, stored_dtype: str = "float32") -> "LlamaConfig":
         """GGUF keys and defaults of crates/core-types/src/model.rs:64-185.  Differences:
         a `llama3` scaling block is read instead of refused, and the vocabulary size
         may come from `llama.vocab_size` or the embedding tensor when the file carries
@@ -225,7 +232,7 @@ class LlamaConfig:
             tie_word_embeddings=False,     # decided by the tensor list: output.weight absent -> tied
             bos_token_id=meta.get("tokenizer.ggml.bos_token_id"),
             eos_token_id=meta.get("tokenizer.ggml.eos_token_id"),
-            stored_dtype="float16", name=str(meta.get("general.name", "")))
+            stored_dtype=stored_dtype, name=str(meta.get("general.name", "")))
 
     # ------------------------------------------------------------------ writers
     def to_dict(self) -> dict:
@@ -249,8 +256,8 @@ class LlamaConfig:
             d["rope_scaling"] = asdict(self.rope_scaling)
         if self.bos_token_id is not None:
             d["bos_token_id"] = self.bos_token_id
-        if self.eos_token_id is not None:
-            d["eos_token_id"] = self.eos_token_id
+        if self.eos_token_ids:
+            d["eos_token_id"] = self.eos_token_id if len(self.eos_token_ids) == 1 else list(self.eos_token_ids)
         return d
 
     def to_gguf_metadata(self) -> dict:

@@ -21,7 +21,7 @@ class Architecture:
     read_config: Callable[[dict], object]      # config.json dict -> typed config
     build: Callable[..., object]               # (config, dtype, device) -> model (parts put together)
     hf_names: Callable[[object], Dict[str, str]] = None   # typed config -> {file tensor name: model tensor name}
-    read_gguf: Callable[..., object] = None               # (GGUF metadata dict, vocab size seen in the file) -> typed config
+    read_gguf: Callable[..., object] = None               # (opened GGUF file: .metadata, .entries, .shape(), .dtype()) -> typed config
 
 
 _REGISTRY: Dict[str, Architecture] = {}
@@ -59,8 +59,7 @@ def read_config(folder_or_file: str):
         arch = lookup(str(g.metadata.get("general.architecture")))
         if arch.read_gguf is None:
             raise ConfigError(f"architecture {arch.name} cannot be read from GGUF metadata")
-        vocab = g.shape("token_embd.weight")[0] if "token_embd.weight" in g.entries else None
-        return arch, arch.read_gguf(g.metadata, vocab)
+        return arch, arch.read_gguf(g)
     if os.path.isdir(path):
         path = os.path.join(path, "config.json")
     try:

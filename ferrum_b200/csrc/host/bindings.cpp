@@ -17,7 +17,7 @@ static void raise_as(const char* cls, const char* what) {
 
 PYBIND11_MODULE(_host, m) {
   m.doc() = "native cache manager and scheduler of ferrum_b200";
-  m.attr("ABI") = 3;
+  m.attr("ABI") = 4;
 
   py::register_exception_translator([](std::exception_ptr p) {
     try {
@@ -79,7 +79,7 @@ PYBIND11_MODULE(_host, m) {
       .def_readwrite("chunk_size", &SchedulerConfig::chunk_size)
       .def_readwrite("max_model_len", &SchedulerConfig::max_model_len)
       .def_readwrite("n_vocab", &SchedulerConfig::n_vocab)
-      .def_readwrite("eos_token_id", &SchedulerConfig::eos_token_id);
+      .def_readwrite("eos_token_ids", &SchedulerConfig::eos_token_ids);
 
   py::class_<PlanEntry>(m, "PlanEntry")
       .def_readonly("id", &PlanEntry::id)

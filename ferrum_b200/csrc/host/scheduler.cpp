@@ -258,7 +258,7 @@ std::vector<Event> Scheduler::commit(const std::vector<int32_t>& sampled) {
     s.decoding = true;
     events.push_back(Event{0, s.id, next, 0});
     const bool stop = std::find(s.stop.begin(), s.stop.end(), next) != s.stop.end() ||
-                      (cfg_.eos_token_id >= 0 && next == cfg_.eos_token_id);
+                      std::find(cfg_.eos_token_ids.begin(), cfg_.eos_token_ids.end(), next) != cfg_.eos_token_ids.end();
     if (stop || s.generated >= s.max_new) {
       events.push_back(Event{1, s.id, -1, stop ? FINISH_STOP : FINISH_LENGTH});
       finish(idx);

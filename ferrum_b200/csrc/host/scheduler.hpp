@@ -45,7 +45,7 @@ struct SchedulerConfig {
   int chunk_size = 0;            // cap on one prompt portion; 0 = none
   int max_model_len = 0;         // prompt + new tokens may not exceed this; 0 = cache capacity
   int n_vocab = 0;               // token ids must be below this; 0 = unchecked
-  int eos_token_id = -1;         // -1: the model names none
+  std::vector<int32_t> eos_token_ids;  // ids that end a sequence with reason Stop; empty: the model names none
 };
 
 struct PlanEntry {

@@ -103,8 +103,11 @@ class Engine:
         sc = host.module().SchedulerConfig()
         sc.max_batch_tokens, sc.max_batch_seqs, sc.chunk_size = int(max_batch_tokens), int(max_batch_seqs), int(chunk_size)
         sc.max_model_len, sc.n_vocab = self.max_model_len, model.n_vocab
-        eos = getattr(cfg, "eos_token_id", None)
-        sc.eos_token_id = -1 if eos is None else int(eos)
+        eos = getattr(cfg, "eos_token_ids", None)
+        if eos is None:
+            one = getattr(cfg, "eos_token_id", None)
+            eos = () if one is None else (one,)
+        sc.eos_token_ids = [int(t) for t in eos]
         self.scheduler = host.module().Scheduler(self.cache.manager, sc)
         self._next_id = 0
         self.plan_ahead = bool(plan_ahead)

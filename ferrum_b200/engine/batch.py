@@ -75,8 +75,34 @@ class PinnedRing:
             self.events[self.i].record()
 
 
+class PlanStore:
+    """Staging for work lists that a part builds on the host every step: per key a ring of pinned
+    buffers and one device buffer that keeps its address while it is large enough (a captured
+    graph reads it at that address).  `generation` counts the times a device buffer moved."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs = {}
+        self.generation = 0
+
+    def buffers(self, key, n):
+        """(PinnedRing, int32 device buffer) of at least n elements for `key`."""
+        b = self._bufs.get(key)
+        if b is None or b[1].numel() < n:
+            cap = max(1024, 2 * n)
+            b = (PinnedRing(cap, torch.int32, self.device), torch.empty(cap, dtype=torch.int32, device=self.device))
+            self._bufs[key] = b
+            self.generation += 1
+        return b
+
+
 class StepContext:
-    """Built once per runner; `fill` rewrites it for each step."""
+    """Built once per runner; `fill` rewrites it for each step.
+
+    For parts that plan on the host: `step_cache` is a dict that is emptied at every `fill` (a
+    part keeps there what it worked out for this batch, under a key of its own choosing, so that
+    all layers of one shape share it), and `plan_store` hands out buffers that keep their
+    addresses from step to step."""
 
     def __init__(self, device, max_tokens, max_requests, table_widths: List[int], err=None):
         """err: an int32 device tensor of one element to use as the kernels' error flag (the
@@ -93,8 +119,8 @@ class StepContext:
         self._bt_host = [PinnedRing(self.max_requests * w, torch.int32, device) for w in self.table_widths]
         self._bt_dev = [torch.empty((self.max_requests, w), dtype=torch.int32, device=device) for w in self.table_widths]
         self._splitk_counters = torch.zeros(4096, dtype=torch.int32, device=device)
-        from .attn_plan import AttentionPlans
-        self._attn_plans = AttentionPlans(device)
+        self.step_cache: Dict[object, object] = {}
+        self.plan_store = PlanStore(device)
         self.n_tokens = self.n_reqs = self.n_want = 0
         self.fixed_shapes = False     # True while a decode-only batch runs under a CUDA graph
         # A residual product of a few tokens may stay in partials until the next norm adds it
@@ -143,6 +169,9 @@ class StepContext:
                 tok[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
                 pos[t:t + n] = np.arange(e.pos0, e.pos0 + n, dtype=np.int32)
                 req[t:t + n] = r
+                if len(set(e.want)) != len(e.want):
+                    # (a row's pending residual product is added when the row is gathered: once only)
+                    raise ValueError("a wanted index appears twice in one entry")
                 for i in e.want:
                     if not 0 <= i < n:
                         raise ValueError(f"wanted index {i} is outside the entry's {n} tokens")
@@ -182,13 +211,12 @@ class StepContext:
         self.want_capacity = max(W, 1)
         self.max_q_len = max(self.h_q_len) if R else 0
         self.max_kv_len = max((p + n for p, n in zip(self.h_pos0, self.h_q_len)), default=0)
-        self._attn_plans.reset()
+        self.step_cache = {}
         self.pending_residual = None
 
-    def attention_plans(self, G, window, Hkv, tc_tokens=0):
-        """The step's work lists for the tensor-core attention kernels (built on first use).
-        tc_tokens: tokens per row tile of the tcgen05 kernel, 0 where it does not apply."""
-        return self._attn_plans.get(self, G, window, Hkv, fixed=self.fixed_shapes, tc_tokens=tc_tokens)
+    def buffers_generation(self):
+        """Changes whenever a buffer that kernels read may have moved (a captured graph is stale then)."""
+        return (self.scratch.generation, self.plan_store.generation)
 
     # ------------------------------------------------------------------ pending residual sum
     def take_pending_residual(self, h):

@@ -27,8 +27,8 @@ _DEVICE_ERRORS = {
 
 
 class _CapturedStep:
-    def __init__(self, graph, logits, plan_keys, generation, n_launches):
-        self.graph, self.logits, self.plan_keys, self.generation = graph, logits, plan_keys, generation
+    def __init__(self, graph, logits, generation, n_launches):
+        self.graph, self.logits, self.generation = graph, logits, generation
         self.n_launches = n_launches      # kernels one replay launches
 
 
@@ -93,7 +93,7 @@ class ModelRunner:
         return logits[:self.ctx.n_want] if logits is not None else None
 
     def _generation(self):
-        return (self.ctx.scratch.generation, self.ctx._attn_plans.generation)
+        return self.ctx.buffers_generation()
 
     def _run_decode(self):
         """A decode-only batch: replay its graph, or run it kernel by kernel and capture."""
@@ -101,8 +101,7 @@ class ModelRunner:
         key = (ctx.n_reqs, ctx.n_want)
         cap = self._graphs.get(key)
         if cap is not None and cap.generation == self._generation():
-            for k in cap.plan_keys:
-                ctx.attention_plans(*k)          # this step's work lists, into the buffers the graph reads
+            self.model.plan(ctx, self.cache)     # this step's work lists, into the buffers the graph reads
             if cap.generation == self._generation():
                 cap.graph.replay()
                 self.graph_replays += 1
@@ -113,13 +112,12 @@ class ModelRunner:
         if self._seen[key] >= 2:
             # every buffer exists now and the plans of this step are cached: capturing
             # launches nothing and allocates nothing
-            plan_keys = ctx._attn_plans.keys_built()
             graph = torch.cuda.CUDAGraph()
             before = ops.launches
             with torch.cuda.graph(graph):
                 captured = self.model.forward(ctx, self.cache)
             n_launches, ops.launches = ops.launches - before, before      # captured, not launched
-            self._graphs[key] = _CapturedStep(graph, captured, plan_keys, self._generation(), n_launches)
+            self._graphs[key] = _CapturedStep(graph, captured, self._generation(), n_launches)
             if len(self._graphs) > 96:
                 self._graphs.pop(next(iter(self._graphs)))
         return logits

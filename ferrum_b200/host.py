@@ -9,7 +9,7 @@ from .ops import build
 
 _mod = None
 _lock = threading.Lock()
-ABI = 3
+ABI = 4
 
 
 def module():

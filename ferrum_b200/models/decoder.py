@@ -58,6 +58,11 @@ class DecoderModel(Part):
         return self.head.n_vocab
 
     # ------------------------------------------------------------------ the forward pass
+    def plan(self, ctx, cache):
+        """Lets every run's mixer build this step's host-made work lists (see `Mixer.plan`)."""
+        for k, run in enumerate(self.schedule):
+            self.blocks[run.block].mixer.plan(ctx, cache.layer_cache(k))
+
     def forward(self, ctx, cache):
         """Run the batch described by ctx; returns float32 logits [want_capacity, V] whose
         first ctx.n_want rows are valid, or None when nothing is wanted."""

@@ -9,6 +9,8 @@ checkpoint onto them.
 """
 from __future__ import annotations
 
+import dataclasses
+
 from ..config.llama import LlamaConfig
 from ..config.registry import Architecture, register
 from ..parts import OutputHead, PagedAttention, PreNormBlock, RMSNorm, RotaryEmbedding, SwiGLU, TokenEmbedding
@@ -55,5 +57,17 @@ def hf_names(config: LlamaConfig):
     return out
 
 
-register(Architecture("LlamaForCausalLM", LlamaConfig.from_dict, build_llama, hf_names,
-                      LlamaConfig.from_gguf_metadata), "llama")
+def read_gguf(gguf):
+    """Typed config of an opened GGUF file.  A file without a tokenizer (random weights) gives
+    its vocabulary through `llama.vocab_size` or the embedding's row count; the dtype recorded is
+    the one the embedding is stored in."""
+    emb = "token_embd.weight"
+    have = emb in gguf.entries
+    cfg = LlamaConfig.from_gguf_metadata(gguf.metadata, gguf.shape(emb)[0] if have else None)
+    if have:
+        stored = str(gguf.dtype(emb)).replace("torch.", "")
+        cfg = dataclasses.replace(cfg, stored_dtype=stored)
+    return cfg
+
+
+register(Architecture("LlamaForCausalLM", LlamaConfig.from_dict, build_llama, hf_names, read_gguf), "llama")

@@ -89,7 +89,7 @@ def trace_build():
 
 def build_kernels(force=False, verbose_ptxas=False):
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
-    hdrs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cuh")))
+    hdrs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h")))
     if not srcs:
         raise KernelError("no kernel sources found")
     trace = trace_build()

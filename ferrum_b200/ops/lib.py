@@ -53,6 +53,11 @@ def require_cuda(device=None):
     lib()
 
 
+def sm_count():
+    """Multiprocessors of the current CUDA device, as the kernels' own grids count them."""
+    return int(lib().ferrum_gemm_tc_default_ctas())
+
+
 def set_dependent_launch(on: bool):
     """Programmatic dependent launch between the kernels of a step (on by default): a kernel's
     prologue may overlap the tail of the kernel before it.  Off: plain stream order."""

@@ -13,6 +13,7 @@ import math
 import torch
 
 from ..ops import lib as ops
+from . import attention_plan
 from .base import CacheNeed, Mixer, PagedKVNeed, ParamSpec
 from .linear import RESIDUAL, STORE, linear, linear_deferred
 
@@ -23,7 +24,15 @@ EARLY_TRIGGER_MAX_TOKENS = 16
 
 
 class PagedAttention(Mixer):
-    graph_safe = True
+    @property
+    def graph_safe(self):
+        """Decoded tokens run under a CUDA graph when one token's rows (the query heads of a KV
+        head) fit the 16-row tile of the tensor-core kernel, whose padded work list has a shape
+        that depends on the number of requests only; larger groups take the 64-row class, whose
+        grid follows the context lengths.  The generic kernel has no work lists at all."""
+        if not ops.attention_flash_supported(self.dtype, self.D):
+            return True
+        return self.Hq // self.Hkv <= 16
 
     def __init__(self, width, n_head, n_head_kv, head_dim, position, dtype, window=0, scale=None):
         if n_head % n_head_kv:
@@ -69,16 +78,24 @@ class PagedAttention(Mixer):
                                   cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err)
         linear(out, self.w_output_weight, residual, RESIDUAL, ctx, M=T)
 
-    def _flash(self, qkv, out, ctx, cache, table):
-        """Tensor-core path: one launch per row-tile class of the step's plan, plus a merge
-        launch where key ranges were split."""
+    def plan(self, ctx, cache):
+        """The step's work lists of the tensor-core kernels for this layer's shape (None on the
+        generic path, which has none)."""
+        if not ops.attention_flash_supported(self.dtype, self.D):
+            return None
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         shape_key = (cache.page_size, cache.page_stride, cache.plane.dtype, cache.plane.dim())
         tc_tokens = self._tc_tokens.get(shape_key)
         if tc_tokens is None:
             tc_tokens = self._tc_tokens[shape_key] = ops.attention_tc_tokens(D, Hq // Hkv, cache.page_size, cache.plane,
                                                                              cache.page_stride)
-        for plan in ctx.attention_plans(Hq // Hkv, self.window, Hkv, tc_tokens):
+        return attention_plan.plans_for(ctx, Hq // Hkv, self.window, Hkv, tc_tokens)
+
+    def _flash(self, qkv, out, ctx, cache, table):
+        """Tensor-core path: one launch per row-tile class of the step's plan, plus a merge
+        launch where key ranges were split."""
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        for plan in self.plan(ctx, cache):
             if plan is None:
                 continue
             part_o = part_ml = None

@@ -1,4 +1,7 @@
-"""Work lists of the tensor-core attention kernel for one step.
+"""Work lists of the tensor-core attention kernels for one step: the planner that the
+attention mixer brings with it (`PagedAttention.plan`).  The engine knows nothing of it: a
+step's context only offers a per-step cache and buffers that keep their addresses
+(`StepContext.step_cache`, `StepContext.plan_store`).
 
 Every request's rows (tokens x query heads of one KV group) are cut into tiles, and a
 tile's key range may be cut into splits so that a step with few requests and long contexts
@@ -28,14 +31,30 @@ from typing import List, Optional
 import numpy as np
 import torch
 
-N_SMS = 148
 CLASSES = (16, 64)
 MIN_SPLIT_KEYS = {16: 256, 64: 1024}
 TC_MIN_ROWS = 128           # a request with fewer rows would leave the 128-row tiles mostly empty
 TC_MIN_SPLIT_KEYS = 2048
 
 
-CTA_SLOTS = 3 * N_SMS      # the 16-row kernel keeps three CTAs on an SM (registers and shared memory)
+CTAS_PER_SM = 3             # the 16-row kernel keeps three CTAs on an SM (registers and shared memory)
+_slots = {}
+
+
+def sm_count():
+    """Multiprocessors of the current device, asked of the kernel library once per device."""
+    from ..ops import lib as ops
+    dev = torch.cuda.current_device() if torch.cuda.is_available() else -1
+    if dev not in _slots:
+        _slots[dev] = ops.sm_count() if dev >= 0 else 148
+    return _slots[dev]
+
+
+def cta_slots():
+    """CTAs of the 16-row kernel that the device holds at once."""
+    return CTAS_PER_SM * sm_count()
+
+
 # A share may be a single 64-key tile: with few requests or short contexts more CTAs beat
 # longer shares (batch 1, 8192 keys: 3.68 -> 3.55 ms a step; 1024 keys: 3.66 -> 3.39), now that
 # the merge kernel spreads a pair's splits over several warps.
@@ -44,7 +63,7 @@ MIN_TILES_PER_CTA = 1
 
 def item_capacity(n_requests, Hkv):
     """Upper bound of the balanced list's items: one per CTA slot plus one per (request, head)."""
-    return CTA_SLOTS + n_requests * Hkv
+    return cta_slots() + n_requests * Hkv
 
 
 def _tiles(q_len, pos0, G, window, bm, sel):
@@ -61,10 +80,11 @@ def _tiles(q_len, pos0, G, window, bm, sel):
     return n_tiles, req_of_tile, row0, lo, hi
 
 
-def _grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start, slots=CTA_SLOTS, min_split=None, kind="flash"):
+def _grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start, slots=None, min_split=None, kind="flash"):
     """One item per (tile, key split); the kernel runs it once per KV head."""
     n_tiles, req_of_tile, row0, lo, hi = _tiles(q_len, pos0, G, window, bm, sel)
     length = hi - lo
+    slots = cta_slots() if slots is None else slots
     # about one item per CTA slot of the GPU, never splits shorter than the minimum
     min_split = MIN_SPLIT_KEYS[bm] if min_split is None else min_split
     chunk = int(max(min_split, -(-int(length.sum()) // max(1, slots // Hkv))))
@@ -111,7 +131,7 @@ def _balanced_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start):
     pair_tiles = np.repeat(kt, Hkv)                                 # pairs in (request, head) order
     pair_start = np.concatenate([[0], np.cumsum(pair_tiles)])
     U = int(pair_start[-1])
-    P = int(min(CTA_SLOTS, max(1, U // MIN_TILES_PER_CTA)))     # no share shorter than a few tiles
+    P = int(min(cta_slots(), max(1, U // MIN_TILES_PER_CTA)))     # no share shorter than a few tiles
     bounds = (np.arange(P + 1, dtype=np.int64) * U) // P
     cuts = np.unique(np.concatenate([pair_start, bounds]))
     seg_b, seg_e = cuts[:-1], cuts[1:]
@@ -163,7 +183,7 @@ def build_host(q_len, pos0, G, window, Hkv, tc_tokens=0):
         else:
             out.append(_grid_class(q_len, pos0, G, window, Hkv, bm, sel, R, q_start))
     sel = np.nonzero(to_tc)[0]
-    out.append(_grid_class(q_len, pos0, G, window, Hkv, tc_tokens * G, sel, R, q_start, slots=N_SMS,
+    out.append(_grid_class(q_len, pos0, G, window, Hkv, tc_tokens * G, sel, R, q_start, slots=sm_count(),
                            min_split=TC_MIN_SPLIT_KEYS, kind="tc") if len(sel) else None)
     return out
 
@@ -184,115 +204,84 @@ class ClassPlan:
     comb_warps: int = 1                         # warps per (token, head) of the merge kernel
 
 
-class AttentionPlans:
-    """Per-step cache of plans, keyed by (G, window, Hkv); owns the device copies."""
+def _decode_plans(ctx, key, G, window, Hkv, fixed):
+    """Every request brings one row tile: the balanced list, built by the native module
+    straight into the pinned staging buffer."""
+    from .. import host as host_module
+    R = len(ctx.h_q_len)
+    slots = cta_slots()
+    cap = item_capacity(R, Hkv)
+    total = cap * 8 + R * Hkv * 4 + R + slots + 1
+    ring, dev = ctx.plan_store.buffers(("attention", key), total)
+    pinned = ring.next()
+    hi = [p + n for p, n in zip(ctx.h_pos0, ctx.h_q_len)]
+    lo = [max(0, p - window + 1) for p in ctx.h_pos0] if window > 0 else [0] * R
+    d = host_module.module().build_decode_plan(lo, hi, Hkv, slots, MIN_TILES_PER_CTA, cap, slots, bool(fixed),
+                                               pinned.data_ptr())
+    dev[:total].copy_(pinned[:total], non_blocking=True)
+    ring.sent()
+    ctx.h2d_bytes += total * 4
+    o1 = cap * 8
+    o2 = o1 + R * Hkv * 4
+    o3 = o2 + R
+    cp = ClassPlan(16, cap if fixed else d.n_items, dev[:o1], cap if fixed else d.n_slots)
+    cp.tile_info, cp.req_tile0 = dev[o1:o2], dev[o2:o3]
+    cp.cta_items, cp.n_ctas = dev[o3:total], slots if fixed else d.n_ctas
+    # the merge visits every token; those whose keys were not split return at once
+    cp.comb_tokens, cp.n_comb = None, (ctx.n_tokens if (fixed or d.n_slots) else 0)
+    # a (request, KV head) gets about slots / (R * Hkv) splits; one warp takes eight at a time
+    cp.comb_warps = int(min(8, max(1, -(-slots // (R * Hkv * 8)))))
+    return [cp, None, None]
 
-    def __init__(self, device):
-        self.device = device
-        self._plans = {}
-        self._bufs = {}          # key -> (pinned, device) int32 buffers, grow-only
-        self.generation = 0      # bumped whenever a device buffer moves
 
-    def reset(self):
-        self._plans = {}
+def plans_for(ctx, G, window, Hkv, tc_tokens=0) -> List[Optional[ClassPlan]]:
+    """The step's plans for a layer shape (group size, window, KV heads, tokens per tcgen05 tile;
+    0 where that kernel does not apply), one per row-tile class; built on first use in a step and
+    kept in `ctx.step_cache`, so that every layer of the same shape shares them.
 
-    def keys_built(self):
-        return list(self._plans)
-
-    def _buffers(self, key, n):
-        from .batch import PinnedRing
-        b = self._bufs.get(key)
-        if b is None or b[1].numel() < n:
-            cap = max(1024, 2 * n)
-            b = (PinnedRing(cap, torch.int32, self.device), torch.empty(cap, dtype=torch.int32, device=self.device))
-            self._bufs[key] = b
-            self.generation += 1
-        return b
-
-    def _decode_plans(self, ctx, key, G, window, Hkv, fixed):
-        """Every request brings one row tile: the balanced list, built by the native module
-        straight into the pinned staging buffer."""
-        from .. import host as host_module
-        R = len(ctx.h_q_len)
-        cap = item_capacity(R, Hkv)
-        total = cap * 8 + R * Hkv * 4 + R + CTA_SLOTS + 1
-        ring, dev = self._buffers(key, total)
-        pinned = ring.next()
-        hi = [p + n for p, n in zip(ctx.h_pos0, ctx.h_q_len)]
-        lo = [max(0, p - window + 1) for p in ctx.h_pos0] if window > 0 else [0] * R
-        d = host_module.module().build_decode_plan(lo, hi, Hkv, CTA_SLOTS, MIN_TILES_PER_CTA, cap, CTA_SLOTS, bool(fixed),
-                                                   pinned.data_ptr())
-        dev[:total].copy_(pinned[:total], non_blocking=True)
-        ring.sent()
-        ctx.h2d_bytes += total * 4
-        o1 = cap * 8
-        o2 = o1 + R * Hkv * 4
-        o3 = o2 + R
-        cp = ClassPlan(16, cap if fixed else d.n_items, dev[:o1], cap if fixed else d.n_slots)
-        cp.tile_info, cp.req_tile0 = dev[o1:o2], dev[o2:o3]
-        cp.cta_items, cp.n_ctas = dev[o3:total], CTA_SLOTS if fixed else d.n_ctas
-        # the merge visits every token; those whose keys were not split return at once
-        cp.comb_tokens, cp.n_comb = None, (ctx.n_tokens if (fixed or d.n_slots) else 0)
-        # a (request, KV head) gets about CTA_SLOTS / (R * Hkv) splits; one warp takes eight at a time
-        cp.comb_warps = int(min(8, max(1, -(-CTA_SLOTS // (R * Hkv * 8)))))
-        return [cp, None, None]
-
-    def get(self, ctx, G, window, Hkv, fixed=False, tc_tokens=0) -> List[Optional[ClassPlan]]:
-        """fixed=True (a decode-only batch under a CUDA graph): the 16-row list is padded to
-        `item_capacity` items and the merge visits every token, so that the launch shapes
-        depend on the number of requests only."""
-        key = (G, window, Hkv, tc_tokens)
-        if key in self._plans:
-            return self._plans[key]
-        if max(ctx.h_q_len) * G <= 16:
-            plans = self._decode_plans(ctx, key, G, window, Hkv, fixed)     # native fast path
-            self._plans[key] = plans
-            return plans
-        host = build_host(ctx.h_q_len, ctx.h_pos0, G, window, Hkv, tc_tokens)
-        R = len(ctx.h_q_len)
-        if fixed:
-            h = host[0]
-            if h is None or host[1] is not None or host[2] is not None:
-                raise ValueError("a fixed-shape plan needs a batch of decoded tokens only")
-            cap = item_capacity(R, Hkv)
-            if h["n_work"] > cap or h["n_ctas"] > CTA_SLOTS:
-                raise ValueError("attention plan exceeds its fixed capacity")
-            padded = np.zeros(cap * 8, dtype=np.int32)
-            padded[:h["work"].size] = h["work"]
-            # the grid is always CTA_SLOTS wide; CTAs beyond the plan's get an empty range
-            items = np.full(CTA_SLOTS + 1, h["n_work"], dtype=np.int32)
-            items[:h["cta_items"].size] = h["cta_items"]
-            h["work"], h["n_slots"], h["cta_items"], h["n_ctas"] = padded, cap, items, CTA_SLOTS
-        arrays = []
-        for h in host:
-            if h is not None:
-                arrays += [h["work"], h["tile_info"], h["req_tile0"], h["comb"], h["cta_items"]]
-        total = sum(a.size for a in arrays)
-        ring, dev = self._buffers(key, total)
-        pinned = ring.next()
-        if arrays:
-            np.concatenate(arrays, out=pinned.numpy()[:total])
-        dev[:total].copy_(pinned[:total], non_blocking=True)
-        ring.sent()
-        ctx.h2d_bytes += total * 4
-        plans, o = [], 0
-        for h in host:
-            if h is None:
-                plans.append(None)
-                continue
-            views = []
-            for name in ("work", "tile_info", "req_tile0", "comb", "cta_items"):
-                views.append(dev[o:o + h[name].size])
-                o += h[name].size
-            cp = ClassPlan(h["bm"], h["n_work"], views[0], h["n_slots"])
-            cp.kind = h["kind"]
-            cp.tile_info, cp.req_tile0 = views[1], views[2]
-            if h["n_ctas"]:
-                cp.cta_items, cp.n_ctas = views[4], h["n_ctas"]
-            if fixed:
-                cp.comb_tokens, cp.n_comb = None, ctx.n_tokens
-            else:
-                cp.comb_tokens, cp.n_comb = views[3], int(h["comb"].size)
-            plans.append(cp)
-        self._plans[key] = plans
+    While `ctx.fixed_shapes` is set (a decode-only batch that runs under a CUDA graph) the
+    16-row list is padded to `item_capacity` items and the merge visits every token, so that the
+    launch shapes depend on the number of requests only; such a batch must consist of requests
+    with at most 16 rows each (`graph_safe` of the mixer says whether its shape allows that)."""
+    key = (G, window, Hkv, tc_tokens)
+    cache_key = ("attention", key)
+    if cache_key in ctx.step_cache:
+        return ctx.step_cache[cache_key]
+    fixed = ctx.fixed_shapes
+    if max(ctx.h_q_len) * G <= 16:
+        plans = _decode_plans(ctx, key, G, window, Hkv, fixed)     # native fast path
+        ctx.step_cache[cache_key] = plans
         return plans
+    if fixed:
+        raise ValueError("a fixed-shape plan needs requests of at most 16 rows (one decoded token, group size <= 16)")
+    host = build_host(ctx.h_q_len, ctx.h_pos0, G, window, Hkv, tc_tokens)
+    arrays = []
+    for h in host:
+        if h is not None:
+            arrays += [h["work"], h["tile_info"], h["req_tile0"], h["comb"], h["cta_items"]]
+    total = sum(a.size for a in arrays)
+    ring, dev = ctx.plan_store.buffers(cache_key, total)
+    pinned = ring.next()
+    if arrays:
+        np.concatenate(arrays, out=pinned.numpy()[:total])
+    dev[:total].copy_(pinned[:total], non_blocking=True)
+    ring.sent()
+    ctx.h2d_bytes += total * 4
+    plans, o = [], 0
+    for h in host:
+        if h is None:
+            plans.append(None)
+            continue
+        views = []
+        for name in ("work", "tile_info", "req_tile0", "comb", "cta_items"):
+            views.append(dev[o:o + h[name].size])
+            o += h[name].size
+        cp = ClassPlan(h["bm"], h["n_work"], views[0], h["n_slots"])
+        cp.kind = h["kind"]
+        cp.tile_info, cp.req_tile0 = views[1], views[2]
+        if h["n_ctas"]:
+            cp.cta_items, cp.n_ctas = views[4], h["n_ctas"]
+        cp.comb_tokens, cp.n_comb = views[3], int(h["comb"].size)
+        plans.append(cp)
+    ctx.step_cache[cache_key] = plans
+    return plans

@@ -12,7 +12,9 @@ Norm            `forward(h, ctx, rows=None) -> x`: float32 rows in, compute-dtyp
 Mixer           `cache_need()` says what it keeps per request (paged keys/values and/or a
                 fixed-size state); `forward(x, ctx, cache, residual)` adds its output to the
                 float32 `residual` in place.  `cache` is a `LayerCache`: the page plane and
-                the state rows this run of the layer may use.
+                the state rows this run of the layer may use.  A mixer whose kernels read
+                work lists made on the host brings its planner with it: `plan(ctx, cache)`
+                builds the lists of this step (see `Mixer.plan`).
 FeedForward     `forward(x, ctx, residual)` adds its output to `residual` in place.
 PositionEncoding `rotary()` returns the table a rotating mixer needs, or None;
                 `on_embedding(h, ctx)` may add to the embedded tokens.
@@ -111,6 +113,16 @@ class PositionEncoding(Part):
 class Mixer(Part):
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
+
+    def plan(self, ctx, cache) -> None:
+        """Optional: build what this step's kernels need from the host (work lists, split
+        tables) and send it to the device.  `forward` may call it itself; the runner calls it
+        for every run of the schedule before it replays a captured graph, whose kernels read
+        the lists at fixed addresses.  So: keep a step's result in `ctx.step_cache` under a key
+        of the part's own (it is emptied for every batch; layers of one shape then share the
+        work), put the lists into buffers from `ctx.plan_store` (they keep their addresses),
+        and while `ctx.fixed_shapes` is set make grid sizes depend on the batch's sizes only."""
+        return None
 
     def forward(self, x, ctx, cache, residual) -> None:
         raise NotImplementedError

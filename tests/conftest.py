@@ -43,6 +43,13 @@ MID_E = {
     "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 2816, "vocab_size": 1500, "rope_theta": 500000.0,
     "rope_scaling": None, "max_position_embeddings": 2048, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
 }
+# One KV head under 32 query heads: a decoded token has 32 packed rows, more than the 16-row
+# tile of the tensor-core attention kernel holds.
+TINY_G = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 160, "num_hidden_layers": 1, "num_attention_heads": 32,
+    "num_key_value_heads": 1, "head_dim": 64, "intermediate_size": 224, "vocab_size": 333, "rope_theta": 30000.0,
+    "rope_scaling": None, "max_position_embeddings": 512, "rms_norm_eps": 4e-6, "tie_word_embeddings": False,
+}
 TINY = {"A": (TINY_A, 0, "float32"), "B": (TINY_B, 1, "bfloat16"), "C": (TINY_C, 2, "float32"),
         "D": (TINY_D, 3, "bfloat16")}
 
@@ -51,12 +58,23 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 
 
+def pytest_sessionfinish(session, exitstatus):
+    """FERRUM_TEST_STATS=file: write the worst 16-bit error ratios the session saw (the
+    tolerance in helpers.py is set from them)."""
+    path = os.environ.get("FERRUM_TEST_STATS")
+    if path:
+        import json
+        import helpers
+        with open(path, "w") as f:
+            json.dump(dict(sorted(helpers.STATS.items(), key=lambda kv: -kv[1])), f, indent=1)
+
+
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
     """name -> folder with config.json + model.safetensors, written by the random-weights mode."""
     from ferrum_b200.weights import write_random_model
     out = {}
-    for name, (cfg, seed, dtype) in list(TINY.items()) + [("E", (MID_E, 5, "bfloat16"))]:
+    for name, (cfg, seed, dtype) in list(TINY.items()) + [("E", (MID_E, 5, "bfloat16")), ("G", (TINY_G, 6, "bfloat16"))]:
         d = tmp_path_factory.mktemp("tiny_" + name)
         write_random_model(cfg, str(d), seed, dtype=dtype)
         out[name] = str(d)

@@ -6,31 +6,61 @@ import plain_llama as P
 # The reference's tolerance form (docs/ARCHITECTURE.md "Kernel tolerance";
 # tests/accept/tests/kernels_contract.rs:21-24): |x - ref| <= max(1e-6, rel * max(1, |ref|)).
 REL_F32 = 1e-4
-# bfloat16: 8 bits of mantissa in every activation between kernels; the reference's own
-# half-precision acceptance bound is an absolute logit difference (docs/ARCHITECTURE.md:215-222).
-ABS_BF16 = 0.06
+# 16-bit compute: every activation between kernels is rounded to 8 (bfloat16) or 11 (float16) bits
+# of mantissa, so the bound is relative to the spread of the logits it perturbs: per row,
+# max |x - ref| <= C * std(ref row).  C is three times the worst ratio seen over the whole suite
+# on a B200 (bfloat16: 0.029, in the wide model at 400 tokens a step), far below the third of a standard deviation that
+# a fixed absolute bound would let pass.  With it goes the reference's second acceptance rule
+# (docs/ARCHITECTURE.md:215-222; tests/accept/tests/m4_forward.rs:45-62,168-187): the top-1 token
+# agrees on at least 99 % of the rows whose top-2 margin exceeds the bound.
+C_16BIT = {"bfloat16": 0.09, "float16": 0.1}
+TOP1_AGREEMENT = 0.99
+STATS = {}        # what -> worst ratio seen (written out at the end of a session, see conftest.py)
 
 
 def assert_close_f32(x, ref, what=""):
     x, ref = np.asarray(x, dtype=np.float64), np.asarray(ref, dtype=np.float64)
     lim = np.maximum(1e-6, REL_F32 * np.maximum(1.0, np.abs(ref)))
+    assert np.isfinite(x).all(), f"{what}: non-finite values"
     bad = np.abs(x - ref) > lim
     assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} differ, worst {np.abs(x - ref).max():.3e} at {np.argwhere(bad)[0]}"
 
 
-def assert_close_bf16(x, ref, what="", abs_tol=ABS_BF16):
-    x, ref = np.asarray(x, dtype=np.float64), np.asarray(ref, dtype=np.float64)
-    err = np.abs(x - ref)
-    assert err.max() <= abs_tol * max(1.0, np.abs(ref).max()), \
-        f"{what}: worst abs error {err.max():.4f} at {np.unravel_index(err.argmax(), err.shape)}"
+def assert_close_16bit(x, ref, what="", dtype="bfloat16"):
+    """Rows of logits [n, V] against the plain implementation's, for a 16-bit compute dtype."""
+    x, ref = np.atleast_2d(np.asarray(x, dtype=np.float64)), np.atleast_2d(np.asarray(ref, dtype=np.float64))
+    assert x.shape == ref.shape, (x.shape, ref.shape)
+    assert np.isfinite(x).all(), f"{what}: non-finite logits"
+    c = C_16BIT[dtype]
+    spread = ref.std(axis=-1)
+    bound = c * spread
+    err = np.abs(x - ref).max(axis=-1)
+    ratio = err / spread
+    STATS[f"{dtype} {what}"] = max(STATS.get(f"{dtype} {what}", 0.0), float(ratio.max()))
+    worst = int(ratio.argmax())
+    assert (err <= bound).all(), (f"{what}: row {worst} is off by {err[worst]:.4f} = {ratio[worst]:.3f} standard deviations "
+                                  f"of its logits (bound {c}); {int((err > bound).sum())} of {len(err)} rows exceed it")
+    top2 = np.partition(ref, -2, axis=-1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > bound
+    if clear.any():
+        agree = (x.argmax(axis=-1) == ref.argmax(axis=-1))[clear].mean()
+        assert agree >= TOP1_AGREEMENT, f"{what}: top-1 agrees on {agree:.3f} of the {int(clear.sum())} rows with a clear margin"
 
 
 def assert_close(x, ref, dtype, what=""):
-    (assert_close_f32 if dtype == "float32" else assert_close_bf16)(x, ref, what)
+    if dtype == "float32":
+        assert_close_f32(x, ref, what)
+    else:
+        assert_close_16bit(x, ref, what, dtype)
+
+
+def round_to(dtype):
+    """How the plain implementation holds the matrices for an engine that computes in `dtype`."""
+    return {"float32": "stored", "bfloat16": "bfloat16", "float16": "float16"}[dtype]
 
 
 def plain_logits(folder, dtype, tokens):
-    cfg, w = P.read_model(folder, weights_as="bfloat16" if dtype == "bfloat16" else "stored")
+    cfg, w = P.read_model(folder, weights_as=round_to(dtype))
     return P.forward(cfg, w, tokens)
 
 
@@ -68,3 +98,85 @@ class Replay:
 
     def logits(self, rid, n):
         return np.stack([self.rows[(rid, p)] for p in range(n)])
+
+
+# --------------------------------------------------------------------------- the mixed workload
+MIXED_LENS = {"a": 70, "b": 45, "c": 33, "d": 90, "e": 50, "f": 21}
+
+
+def mixed_schedule(lens):
+    """The steps of the mixed workload, as data: [(entries [(id, first token, count)], ended ids)].
+    Up to four live requests, portions of some beside single tokens of others; one request sits
+    a step out now and then; when a request ends the next waiting one takes its place."""
+    cur = {k: 0 for k in lens}
+    live, waiting, step, out = ["a", "b", "c", "d"], ["e", "f"], 0, []
+    pattern = {0: [7, 1, 2, 13], 1: [1, 5, 1, 2], 2: [16, 1, 3, 1], 3: [2, 2, 1, 30]}
+    while live:
+        sizes = pattern[step % 4]
+        entries, ended = [], []
+        for j, k in enumerate(list(live)):
+            if step % 5 == 4 and j == 1:
+                continue                      # a request may sit out a step and go on later
+            n = min(sizes[j % 4], lens[k] - cur[k])
+            if n:
+                entries.append((k, cur[k], n))
+                cur[k] += n
+            if cur[k] >= lens[k]:
+                ended.append(k)
+        out.append((entries, ended))
+        for k in ended:
+            live.remove(k)
+            if waiting:
+                live.append(waiting.pop(0))
+        step += 1
+    return out
+
+
+def peak_pages(schedule, page_size):
+    """Most pages that the live requests of the schedule hold at any time."""
+    held, peak = {}, 0
+    for entries, ended in schedule:
+        for k, first, n in entries:
+            held[k] = -(-(first + n) // page_size)
+        peak = max(peak, sum(held.values()))
+        for k in ended:
+            held.pop(k)
+    return peak
+
+
+def record_owners(owners, manager, slots, group=0):
+    """owners[page] gains the name of every request (name -> slot) that holds the page now."""
+    for k, slot in slots.items():
+        for p in manager.table(group, slot):
+            if p >= 0:
+                owners.setdefault(p, set()).add(k)
+
+
+def pages_were_reused(owners):
+    return any(len(v) > 1 for v in owners.values())
+
+
+def run_mixed(s, toks, schedule):
+    """Replays the schedule; returns the Replay and, per page id, the set of requests that held it."""
+    r = Replay(s)
+    owners = {}
+    for entries, ended in schedule:
+        r.step([(k, toks[k][first:first + n], "all") for k, first, n in entries], end=ended)
+        record_owners(owners, s.cache.manager, s.slots)      # (a request that ended was recorded in earlier steps)
+        assert s.cache.manager.check() == ""
+    return r, owners
+
+
+def mixed_case(model_dirs, name, dtype, page_size=16, model_path=None, **kw):
+    """The mixed workload in a pool of exactly the pages its live requests need at their peak,
+    fewer than all requests need together: pages of finished requests must be handed out again."""
+    from conftest import TINY
+    vocab = TINY[name][0]["vocab_size"]
+    toks = {k: random_tokens(n, vocab, 20 + i) for i, (k, n) in enumerate(MIXED_LENS.items())}
+    schedule = mixed_schedule(MIXED_LENS)
+    pool = peak_pages(schedule, page_size)
+    assert pool < sum(-(-n // page_size) for n in MIXED_LENS.values())
+    from ferrum_b200.engine.trace import TraceSession
+    s = TraceSession(model_path or model_dirs[name], dtype, pool * page_size, page_size=page_size, **kw)
+    assert s.cache.manager.free_pages(0) == pool
+    return s, toks, schedule

@@ -48,6 +48,112 @@ def read_safetensors(path):
     return out
 
 
+def read_gguf(path):
+    """(metadata dict, name -> float64 array) of a GGUF v2/v3 file with F32, F16 or BF16 tensors.
+
+    The layout is the one the reference parses (crates/gguf/src/parse.rs:99-248): magic, version,
+    tensor count, key/value count; key/values (string key, u32 type, value); tensor infos (name,
+    n_dims, dims with the contiguous one first, ggml type, offset); padding to the alignment
+    (`general.alignment`, default 32); data.  Own code: nothing of the product is used."""
+    with open(path, "rb") as f:
+        data = f.read()
+    pos = 0
+
+    def take(fmt):
+        nonlocal pos
+        v = struct.unpack_from(fmt, data, pos)
+        pos += struct.calcsize(fmt)
+        return v[0] if len(v) == 1 else v
+
+    def string():
+        nonlocal pos
+        n = take("<Q")
+        v = data[pos:pos + n].decode("utf-8")
+        pos += n
+        return v
+
+    scalar = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<B", 10: "<Q", 11: "<q", 12: "<d"}
+
+    def value(t):
+        if t == 8:
+            return string()
+        if t == 9:
+            et, n = take("<I"), take("<Q")
+            return [value(et) for _ in range(n)]
+        v = take(scalar[t])
+        return bool(v) if t == 7 else v
+
+    assert data[:4] == b"GGUF"
+    pos = 4
+    version, n_tensors, n_kv = take("<I"), take("<Q"), take("<Q")
+    assert version in (2, 3)
+    meta = {}
+    for _ in range(n_kv):
+        k = string()
+        meta[k] = value(take("<I"))
+    infos = []
+    for _ in range(n_tensors):
+        name = string()
+        nd = take("<I")
+        dims = [take("<Q") for _ in range(nd)]
+        infos.append((name, dims, take("<I"), take("<Q")))
+    align = int(meta.get("general.alignment", 32))
+    base = (pos + align - 1) // align * align
+    out = {}
+    for name, dims, typ, off in infos:
+        n = int(np.prod(dims)) if dims else 1
+        lo = base + off
+        if typ == 0:
+            a = np.frombuffer(data, dtype="<f4", count=n, offset=lo).astype(np.float64)
+        elif typ == 1:
+            a = np.frombuffer(data, dtype="<f2", count=n, offset=lo).astype(np.float64)
+        elif typ == 30:
+            u = np.frombuffer(data, dtype="<u2", count=n, offset=lo).astype(np.uint32) << 16
+            a = u.view(np.float32).astype(np.float64)
+        else:
+            raise ValueError(f"plain reader: ggml type {typ} of {name}")
+        out[name] = a.reshape(dims[::-1])          # the first dimension of the file is the contiguous one
+    return meta, out
+
+
+_GGUF_LAYER = {"attn_norm": "input_layernorm", "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj",
+               "attn_v": "self_attn.v_proj", "attn_output": "self_attn.o_proj", "ffn_norm": "post_attention_layernorm",
+               "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj"}
+
+
+def read_gguf_model(path, weights_as="stored"):
+    """(config dict with this file's own keys, weights under the names `forward` uses) of a GGUF
+    Llama file: metadata keys of crates/core-types/src/model.rs:64-128, tensor names of :35-41.
+    Rows of such a file are in the adjacent-pair order: call forward(..., pairing="adjacent")."""
+    m, t = read_gguf(path)
+    cfg = {"hidden_size": m["llama.embedding_length"], "num_hidden_layers": m["llama.block_count"],
+           "num_attention_heads": m["llama.attention.head_count"],
+           "num_key_value_heads": m.get("llama.attention.head_count_kv", m["llama.attention.head_count"]),
+           "intermediate_size": m["llama.feed_forward_length"], "rms_norm_eps": m["llama.attention.layer_norm_rms_epsilon"],
+           "rope_theta": m.get("llama.rope.freq_base", 10000.0)}
+    if "llama.attention.key_length" in m:
+        cfg["head_dim"] = m["llama.attention.key_length"]
+    if m.get("llama.rope.scaling.type") == "llama3":
+        cfg["rope_scaling"] = {"rope_type": "llama3", "factor": m["llama.rope.scaling.factor"],
+                               "low_freq_factor": m["llama.rope.scaling.low_freq_factor"],
+                               "high_freq_factor": m["llama.rope.scaling.high_freq_factor"],
+                               "original_max_position_embeddings": m["llama.rope.scaling.original_context_length"]}
+    w = {}
+    for name, a in t.items():
+        if name == "token_embd.weight":
+            new = "model.embed_tokens.weight"
+        elif name == "output_norm.weight":
+            new = "model.norm.weight"
+        elif name == "output.weight":
+            new = "lm_head.weight"
+        else:
+            _, i, rest = name.split(".", 2)
+            part, tail = rest.rsplit(".", 1)
+            new = f"model.layers.{i}.{_GGUF_LAYER[part]}.{tail}"
+        w[new] = round_as(a, weights_as) if (weights_as != "stored" and a.ndim == 2) else a
+    return cfg, w
+
+
 def round_bf16(a):
     """Round float64/float32 values to the nearest bfloat16 (ties to even)."""
     f = np.asarray(a, dtype=np.float32)
@@ -56,17 +162,26 @@ def round_bf16(a):
     return r.astype(np.uint32).view(np.float32).astype(np.float64).reshape(f.shape)
 
 
+def round_f16(a):
+    """Round to the nearest IEEE half (ties to even), as crates/core-types/src/dtype.rs:135-154 reads them back."""
+    return np.asarray(a, dtype=np.float64).astype(np.float16).astype(np.float64)
+
+
+def round_as(a, kind):
+    return {"bfloat16": round_bf16, "float16": round_f16}[kind](a)
+
+
 def read_model(folder, weights_as="stored"):
     """(config dict, name -> float64 array) of a folder with config.json + model.safetensors.
 
-    weights_as="bfloat16" rounds matrices (2-D tensors) to bfloat16 first, which is
-    what an engine that computes in bfloat16 holds; 1-D norm weights stay as stored.
+    weights_as="bfloat16" (or "float16") rounds matrices (2-D tensors) to that type first,
+    which is what an engine that computes in it holds; 1-D norm weights stay as stored.
     """
     with open(os.path.join(folder, "config.json")) as f:
         cfg = json.load(f)
     w = read_safetensors(os.path.join(folder, "model.safetensors"))
-    if weights_as == "bfloat16":
-        w = {k: (round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()}
+    if weights_as != "stored":
+        w = {k: (round_as(v, weights_as) if v.ndim == 2 else v) for k, v in w.items()}
     return cfg, w
 
 

@@ -121,3 +121,24 @@ def test_no_page_lost_held_twice_or_freed_twice_under_random_orders(seed):
     for s in list(live):
         m.close(s)
     assert all(m.free_pages(g) == groups[g][2] for g in range(len(groups))) and m.check() == ""
+
+
+def test_the_page_reuse_check_of_the_gpu_tests_can_fail():
+    """The GPU tests assert that some page was held by two requests (helpers.pages_were_reused).
+    Here the same bookkeeping on the manager alone: true when a closed request's pages go to the
+    next one, false when the pool is so large that nothing is ever handed out twice."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import pages_were_reused, record_owners
+    for pool, close_first, expect in ((4, True, True), (8, False, False)):
+        m = manager([(16, 0, pool, 4)])
+        owners, slots = {}, {}
+        slots["a"] = m.open()
+        m.grow(slots["a"], 40)
+        record_owners(owners, m, slots)
+        if close_first:
+            m.close(slots.pop("a"))
+        slots["b"] = m.open()
+        m.grow(slots["b"], 40)
+        record_owners(owners, m, slots)
+        assert pages_were_reused(owners) is expect

@@ -32,6 +32,19 @@ def test_round_trip_through_config_json(tmp_path):
     assert c2 == c and arch.name == "LlamaForCausalLM"
 
 
+def test_a_list_of_end_tokens_is_kept_whole(tmp_path):
+    """Llama-3 instruct files list several ids that end a sequence; every one of them is kept."""
+    c = LlamaConfig.from_dict({**TINY_A, "eos_token_id": [200, 208, 209]})
+    assert c.eos_token_ids == (200, 208, 209) and c.eos_token_id == 200
+    assert LlamaConfig.from_dict(c.to_dict()) == c
+    assert LlamaConfig.from_dict({**TINY_A, "eos_token_id": 7}).eos_token_ids == (7,)
+    assert LlamaConfig.from_dict(TINY_A).eos_token_ids == ()
+    with pytest.raises(ConfigError, match="vocab"):
+        LlamaConfig.from_dict({**TINY_A, "eos_token_id": [3, 999]})
+    with pytest.raises(ConfigError, match="eos_token_id"):
+        LlamaConfig.from_dict({**TINY_A, "eos_token_id": ["x"]})
+
+
 @pytest.mark.parametrize("change,msg", [
     ({"rms_norm_eps": 0.0}, "epsilon"), ({"rms_norm_eps": 1.5}, "epsilon"), ({"num_key_value_heads": 3}, "divisible"),
     ({"head_dim": 15}, "rope"), ({"rope_theta": -1.0}, "frequency"), ({"num_hidden_layers": 0}, "positive"),

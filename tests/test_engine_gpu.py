@@ -17,20 +17,27 @@ def engine(model_dirs, name, dtype, **kw):
 
 
 def check_against_plain(folder, dtype, prompt, got, temperature=0.0, seed=0):
-    """Token by token; under bfloat16 a near-tie may flip a token, after which the two
-    continuations differ legitimately, so the comparison stops there."""
-    cfg, w = P.read_model(folder, weights_as="bfloat16" if dtype == "bfloat16" else "stored")
+    """Token by token, teacher-forced on the engine's own tokens.  In float32 every token equals
+    the plain implementation's.  In a 16-bit dtype a greedy token may differ only where the plain
+    logits have a near-tie: the margin between the plain top-1 and the engine's choice is within
+    twice the logit bound of helpers.C_16BIT (either logit may move by the bound).  The comparison
+    goes on after such a flip, with the engine's token in the context.  Returns the number of
+    tokens that were equal."""
+    from helpers import C_16BIT, round_to
+    cfg, w = P.read_model(folder, weights_as=round_to(dtype))
     toks = list(prompt)
+    same = 0
     for n, t in enumerate(got):
         logits = P.forward(cfg, w, toks)[-1]
         want = P.sample(logits, temperature, seed, n)
-        if t != want:
-            assert dtype == "bfloat16", (n, t, want)
-            z = np.sort(logits)[::-1]
-            assert temperature > 0 or z[0] - logits[t] < 0.05, (n, t, want, z[0] - logits[t])
-            return n
+        if t == want:
+            same += 1
+        else:
+            assert dtype != "float32" and temperature == 0.0, (n, t, want)
+            margin = logits.max() - logits[t]
+            assert margin <= 2 * C_16BIT[dtype] * logits.std(), (n, t, want, margin, logits.std())
         toks.append(t)
-    return len(got)
+    return same
 
 
 @pytest.mark.parametrize("name", ["A", "B", "D"])
@@ -41,9 +48,9 @@ def test_greedy_generation(cuda, model_dirs, name, dtype):
     eng = engine(model_dirs, name, dtype)
     got = eng.generate([prompt], max_new_tokens=16)[0]
     assert len(got) == 16
-    agreed = check_against_plain(model_dirs[name], dtype, prompt, got)
-    assert agreed == 16 or dtype == "bfloat16"
-    assert agreed >= 4
+    same = check_against_plain(model_dirs[name], dtype, prompt, got)
+    assert same == 16 or dtype != "float32"
+    assert same >= 14, same           # near-ties are rare: most tokens are simply equal
 
 
 def test_temperature_generation_float32(cuda, model_dirs):

@@ -99,22 +99,32 @@ def test_config_from_a_gguf_file(tmp_path):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_model_from_gguf_rotates_adjacent_pairs(cuda, tmp_path, dtype):
-    """Tiny B as an F16 GGUF file: the engine's logits equal the plain implementation's with
-    the reference's adjacent-pair rotation on the same (unpermuted) rows."""
+    """The second tiny configuration as an F16 GGUF file: the engine's logits equal the plain
+    implementation's with the reference's adjacent-pair rotation on the same (unpermuted) rows.
+    The plain side reads the file with its own reader and takes every size from the file's own
+    metadata.  Whole and in two portions, in portions of changing size, and mixed with page reuse."""
     from ferrum_b200.engine.trace import TraceSession
-    from ferrum_b200.models.llama import hf_names
-    from ferrum_b200.config import LlamaConfig
-    from helpers import Replay, assert_close, random_tokens
+    from helpers import Replay, assert_close, mixed_case, pages_were_reused, random_tokens, round_to, run_mixed
     path = write_random_gguf(TINY_B, str(tmp_path / "b.gguf"), 1)
-    g = GGUFFile(path)
-    back = {v: k for k, v in hf_names(LlamaConfig.from_dict(TINY_B)).items()}
-    w = {back[n]: g.tensor(n).double().numpy() for n in g.names()}
-    if dtype == "bfloat16":
-        w = {k: (P.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()}
+    cfg, w = P.read_gguf_model(path, weights_as=round_to(dtype))
     toks = random_tokens(60, 512, 70)
-    ref = P.forward(TINY_B, w, toks, pairing="adjacent")
+    ref = P.forward(cfg, w, toks, pairing="adjacent")
     r = Replay(TraceSession(path, dtype, 64))
     r.step([("a", toks[:41], "all")])
     r.step([("a", toks[41:], "all")])
     assert_close(r.logits("a", 60), ref, dtype, "gguf")
-    assert np.abs(ref - P.forward(TINY_B, w, toks, pairing="half")).max() > 1e-3     # the pairing matters
+    assert np.abs(ref - P.forward(cfg, w, toks, pairing="half")).max() > 1e-3     # the pairing matters
+    # portions of changing size, down to two tokens
+    r = Replay(TraceSession(path, dtype, 64))
+    sizes, i, k = [5, 2, 7, 3, 2, 16, 17, 2], 0, 0
+    while i < len(toks):
+        n = min(sizes[k % len(sizes)], len(toks) - i)
+        r.step([("a", toks[i:i + n], "all")])
+        i, k = i + n, k + 1
+    assert_close(r.logits("a", 60), ref, dtype, "gguf portions")
+    # mixed, with pages used again
+    s, mtoks, schedule = mixed_case(None, "B", dtype, model_path=path)
+    r, owners = run_mixed(s, mtoks, schedule)
+    assert pages_were_reused(owners)
+    for name, t in mtoks.items():
+        assert_close(r.logits(name, len(t)), P.forward(cfg, w, t, pairing="adjacent"), dtype, f"gguf mixed {name}")

@@ -297,7 +297,7 @@ def test_attention_finds_one_far_key(ops, dtype, far_key):
 def run_flash(ops, q, lens, qlens, table, plane, ps, Hq, Hkv, D, window, use_tc=False, counts=None, comb_warps=1):
     """Drive the tensor-core attention the way the attention part does: plan, launch per
     row-tile class (the tcgen05 kernel for its class when use_tc), merge splits."""
-    from ferrum_b200.engine.attn_plan import build_host
+    from ferrum_b200.parts.attention_plan import build_host
     T = sum(qlens)
     out = torch.full((T, Hq * D), float("nan"), device="cuda", dtype=torch.bfloat16)
     pos0 = [n - ql for n, ql in zip(lens, qlens)]

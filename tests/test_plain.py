@@ -69,6 +69,38 @@ def test_llama3_scaling_takes_all_three_branches():
     assert np.allclose(f[3:], base[3:] / 8)
 
 
+def test_llama3_scaling_against_numbers_worked_by_hand():
+    """The blended branch, worked on paper (40-digit decimal arithmetic, independent of both
+    implementations).  Rule: f = theta^(-2i/R); wavelength = 2 pi / f; between original/high and
+    original/low, s = (original / wavelength - low) / (high - low) and f' = ((1 - s) / factor + s) f.
+
+    Second tiny configuration (theta 5e5, R 32, original 64, factor 8, low 1, high 4), pair 2:
+      f = 5e5^(-4/32) = 0.19392274474868577...; wavelength = 32.400455734691059... (between 16 and 64)
+      s = (64 / 32.4004557... - 1) / 3 = 0.32509361930029289...
+      f' = ((1 - s) / 8 + s) f = 0.079403009179208206...
+    Pair 1 (wavelength 14.268 < 16) keeps f = 0.44036660267178047...; pair 3 (73.576 > 64) gives f / 8 =
+    0.08539710028576561... / 8 = 0.010674637535720701...
+    Fourth tiny configuration (theta 1e5, R 64, original 32, factor 4, low 1, high 2), pair 3:
+      f = 1e5^(-6/64) = 0.33982083289425593...; wavelength = 18.489700156596233... (between 16 and 32)
+      s = (32 / 18.4897001... - 1) / 1 = 0.73069329026322490...
+      f' = ((1 - s) / 4 + s) f = 0.27118381008918403...
+    and pair 4: f = 0.23713737056616552..., s = 0.20773071095743265..., f' = 0.096229878578255677...
+    The product's table is checked against the same numbers."""
+    from conftest import TINY_D
+    from ferrum_b200.config import LlamaConfig
+    from ferrum_b200.parts.rope import inverse_frequencies
+    want_b = {1: 0.4403666026717804735919833, 2: 0.07940300917920820642694930, 3: 0.08539710028576561128014966 / 8}
+    want_d = {2: 0.4869675251658631149352974, 3: 0.2711838100891840334453061, 4: 0.09622987857825567756248523,
+              5: 0.1654817099943181422945613 / 4}
+    for cfg, want in ((TINY_B, want_b), (TINY_D, want_d)):
+        plain = P.rope_inv_freq(cfg)
+        c = LlamaConfig.from_dict(cfg)
+        product = inverse_frequencies(c.rope_dim, c.rope_freq_base, c.rope_scaling)
+        for i, v in want.items():
+            assert plain[i] == pytest.approx(v, rel=1e-12), (i, plain[i], v)
+            assert product[i] == pytest.approx(v, rel=1e-12), (i, product[i], v)
+
+
 def test_argmax_anchor():
     """crates/core-types/src/model.rs:304-309."""
     assert P.argmax([1.0, 3.0, 3.0, float("nan")]) == 1

@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from helpers import Replay, assert_close, plain_logits, random_tokens
+from helpers import Replay, assert_close, mixed_case, pages_were_reused, plain_logits, random_tokens, run_mixed
 from conftest import TINY
 
 pytestmark = pytest.mark.gpu
@@ -65,51 +65,76 @@ def test_portions_of_changing_size(cuda, model_dirs, name, dtype):
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_mixed_batches_with_page_reuse(cuda, model_dirs, name, dtype):
     """Up to four live requests, portions of some beside decoded tokens of others, in a pool
-    so small that pages freed by finished requests are used again by later ones."""
-    vocab = TINY[name][0]["vocab_size"]
-    lens = {"a": 70, "b": 45, "c": 33, "d": 90, "e": 50, "f": 21}
-    toks = {k: random_tokens(n, vocab, 20 + i) for i, (k, n) in enumerate(lens.items())}
-    ref = {k: plain_logits(model_dirs[name], dtype, v) for k, v in toks.items()}
-    # a+b+c+d rounded up to 64 each = 128+64+64+128 = 384 tokens live at most
-    s = session(model_dirs, name, dtype, 384)
-    r = Replay(s)
-    cur = {k: 0 for k in toks}
-
-    def take(k, n):
-        out = toks[k][cur[k]:cur[k] + n]
-        cur[k] += len(out)
-        return out
-
-    def done(k):
-        return cur[k] >= len(toks[k])
-
-    live, waiting, step = ["a", "b", "c", "d"], ["e", "f"], 0
-    pattern = {0: [7, 1, 2, 13], 1: [1, 5, 1, 2], 2: [16, 1, 3, 1], 3: [2, 2, 1, 30]}
-    seen_pages = set()
-    while live:
-        sizes = pattern[step % 4]
-        entries, ended = [], []
-        for j, k in enumerate(list(live)):
-            if step % 5 == 4 and j == 1:
-                continue                      # a request may sit out a step and go on later
-            part = take(k, sizes[j % 4])
-            if part:
-                entries.append((k, part, "all"))
-            if done(k):
-                ended.append(k)
-        r.step(entries, end=ended)
-        for k in live:
-            if k in s.slots:
-                seen_pages.update(p for p in s.cache.manager.table(0, s.slots[k]) if p >= 0)
-        for k in ended:
-            live.remove(k)
-            if waiting:
-                live.append(waiting.pop(0))
-        step += 1
-        assert s.cache.manager.check() == ""
+    smaller than the requests need together: a page freed by a finished request is held by a later one."""
+    s, toks, schedule = mixed_case(model_dirs, name, dtype)
+    r, owners = run_mixed(s, toks, schedule)
+    assert pages_were_reused(owners), "no page was ever held by two requests"
+    # the held pages were the whole pool at the peak (the sequence of tokens after a wait sees a reused page)
+    assert len(owners) == s.cache.manager.free_pages(0)
     for k in toks:
-        assert_close(r.logits(k, len(toks[k])), ref[k], dtype, f"{name} mixed {k}")
+        assert_close(r.logits(k, len(toks[k])), plain_logits(model_dirs[name], dtype, toks[k]), dtype, f"{name} mixed {k}")
     assert s.cache.manager.used_pages(0) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("page_size", [8, 32])
+def test_other_page_sizes_through_a_whole_model(cuda, model_dirs, dtype, page_size):
+    """Pages of 8 and of 32 positions (the tensor-core kernels' gather, the rotary kernel's
+    page arithmetic) under the mixed workload and under portions, on the configuration that runs
+    the tensor-core kernels."""
+    s, toks, schedule = mixed_case(model_dirs, "D", dtype, page_size=page_size)
+    r, owners = run_mixed(s, toks, schedule)
+    assert pages_were_reused(owners)
+    for k in toks:
+        assert_close(r.logits(k, len(toks[k])), plain_logits(model_dirs["D"], dtype, toks[k]), dtype, f"page {page_size} {k}")
+    long = random_tokens(330, TINY["D"][0]["vocab_size"], 77)
+    r = Replay(session(model_dirs, "D", dtype, 352, page_size=page_size))
+    r.step([("a", long[:290], "all")])
+    for i in range(290, 330, 3):
+        r.step([("a", long[i:i + 3], "all")])
+    assert_close(r.logits("a", 330), plain_logits(model_dirs["D"], dtype, long), dtype, f"page {page_size} portions")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wrong_page_index_is_caught(cuda, model_dirs, dtype, monkeypatch):
+    """The comparisons above can fail: with one entry of one block table off by one on the host
+    (still a page of the pool, so nothing faults) for the second half of the run, a request
+    reads another page's keys and its logits leave the tolerance."""
+    import ctypes
+    from ferrum_b200 import host
+    s, toks, schedule = mixed_case(model_dirs, "D", dtype)
+    n_pages = s.cache.manager.free_pages(0)
+    real = host.module().copy_tables
+    calls = {"n": 0}
+
+    def off_by_one(cache, group, slots, dst, row_stride):
+        real(cache, group, slots, dst, row_stride)
+        calls["n"] += 1
+        row = (ctypes.c_int32 * row_stride).from_address(dst)          # the first request's table row
+        if calls["n"] > len(schedule) // 2 and row[0] >= 0 and cache.seq_len(slots[0]) >= 16:
+            row[0] = (row[0] + 1) % n_pages
+
+    monkeypatch.setattr(host.module(), "copy_tables", off_by_one)
+    r, _ = run_mixed(s, toks, schedule)
+    with pytest.raises(AssertionError):
+        for k in toks:
+            assert_close(r.logits(k, len(toks[k])), plain_logits(model_dirs["D"], dtype, toks[k]), dtype, f"mutated {k}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_query_heads_on_one_kv_head(cuda, model_dirs, dtype):
+    """32 query heads share one KV head: a decoded token brings 32 rows, twice what the 16-row
+    tile of the tensor-core kernel takes, so decoding runs on the 64-row class and without a
+    CUDA graph.  Decodes well past the step at which a graph would have been captured."""
+    from conftest import TINY_G
+    toks = random_tokens(100, TINY_G["vocab_size"], 78)
+    s = session(model_dirs, "G", dtype, 128)
+    assert not s.runner.use_graphs or dtype == "float32"
+    r = Replay(s)
+    r.step([("a", toks[:70], "all")])
+    for t in toks[70:]:
+        r.step([("a", [t], "all")])
+    assert_close(r.logits("a", 100), plain_logits(model_dirs["G"], dtype, toks), dtype, "32 heads per kv head")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

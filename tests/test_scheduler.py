@@ -17,7 +17,8 @@ def make(pages=64, page_size=4, max_requests=4, budget=16, chunk=0, eos=-1, voca
     h = host.module()
     cache = h.CacheManager([h.GroupSpec(page_size, window, pages, width)], max_requests)
     cfg = h.SchedulerConfig()
-    cfg.max_batch_tokens, cfg.chunk_size, cfg.eos_token_id, cfg.n_vocab = budget, chunk, eos, vocab
+    cfg.max_batch_tokens, cfg.chunk_size, cfg.n_vocab = budget, chunk, vocab
+    cfg.eos_token_ids = list(eos) if isinstance(eos, (list, tuple)) else ([] if eos < 0 else [eos])
     cfg.max_model_len, cfg.max_batch_seqs = max_model_len, max_seqs
     return h.Scheduler(cache, cfg), cache
 
@@ -86,6 +87,17 @@ def test_eos_and_stop_tokens_are_emitted_then_finish_with_stop():
     assert out == {1: [5, 9], 2: [33]}
     assert reasons == {1: host.module().FINISH_STOP, 2: host.module().FINISH_STOP}
     assert c.free_slots() == 4 and c.free_pages(0) == 64
+
+
+def test_any_of_several_end_tokens_stops_a_sequence():
+    """A model may name several ids that end a sequence (an end-of-text and an end-of-turn id):
+    whichever is drawn first is emitted and finishes the request with reason stop."""
+    s, c = make(eos=[9, 17])
+    s.submit(1, [1, 2], 10)
+    s.submit(2, [1, 2], 10)
+    out, reasons = run(s, c, lambda rid, pos: {1: {1: 5, 2: 17}, 2: {1: 6, 2: 7, 3: 9}}[rid].get(pos, 0))
+    assert out == {1: [5, 17], 2: [6, 7, 9]}
+    assert reasons == {1: host.module().FINISH_STOP, 2: host.module().FINISH_STOP}
 
 
 def test_max_new_tokens_zero_finishes_with_length_and_no_token():
