@@ -8,7 +8,7 @@ errors, exit code 2 for usage errors and 1 for runtime errors, messages prefixed
 `SubmitRequest` and `SamplingParams` (crates/core-types/src/schedule.rs:16-49).
 
     ferrum generate --model DIR|FILE.gguf --prompt-tokens 1,2,3 [--prompt-tokens ...]
-                    [--dtype bfloat16|float32] [--max-new-tokens N] [--temperature T] [--top-p 1]
+                    [--dtype bfloat16|float16|float32] [--max-new-tokens N] [--temperature T] [--top-p 1]
                     [--seed S] [--stop-tokens a,b] [--max-batch-tokens N] [--max-batch-seqs N]
                     [--chunk-size N] [--page-size N] [--num-pages N] [--max-model-len N]
                     [--random-weights] [--weights-seed S] [--stats]

@@ -1,4 +1,4 @@
-// Paged causal GQA attention on the tensor cores (bfloat16), for prompt portions and for
+// Paged causal GQA attention on the tensor cores (bfloat16 or float16), for prompt portions and for
 // decoded tokens, with an optional split of the key range across CTAs.
 //
 // One CTA handles one work item x one KV head.  A work item is a tile of BM "packed rows"
@@ -26,10 +26,12 @@
 
 namespace {
 
+typedef uint16_t elem16;   // a bfloat16 or float16 element: the kernels move them and the template says which they are
+
 struct FlashParams {
-  const __nv_bfloat16* q;
-  __nv_bfloat16* out;
-  const __nv_bfloat16* kv_plane;
+  const elem16* q;
+  elem16* out;
+  const elem16* kv_plane;
   const int* block_table;
   const int* q_start;   // [R + 1] first token of each request in this batch
   const int* pos0;      // [R] cached positions before this step
@@ -37,6 +39,7 @@ struct FlashParams {
   const int* cta_items; // null: CTA (x, y) runs item x for KV head y; else CTA x runs items [cta_items[x], cta_items[x+1])
   float* part_o;        // [slot][BM][D]
   float* part_ml;       // [slot][BM][2]
+  int* err;             // raised to 5 when a key's page is missing from the block table
   long long page_stride;
   int ldq, ldo, page_size, page_shift, table_width;
   int Hq, Hkv, G, window;
@@ -64,33 +67,39 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* 
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+template <bool HALF>
+__device__ __forceinline__ void mma16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  if (HALF)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
+template <bool HALF>
+__device__ __forceinline__ unsigned pack16(float lo, float hi) {
+  return HALF ? pack2<__half>(lo, hi) : pack2<__nv_bfloat16>(lo, hi);
 }
 
-// element (row, col) of a [rows][D] bfloat16 tile whose 16-byte chunks are XOR-swizzled by row
+// element (row, col) of a [rows][D] 16-bit tile whose 16-byte chunks are XOR-swizzled by row
 template <int D>
-__device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row, int col) {
+__device__ __forceinline__ elem16* tile_ptr(elem16* base, int row, int col) {
   const int chunk = (col >> 3) ^ (row & 7);
   return base + row * D + (chunk << 3) + (col & 7);
 }
 
-template <int D, int WM, int WN>
+template <int D, int WM, int WN, bool HALF>
 __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, int kvh, uint8_t* smem_raw) {
   constexpr int BM = 16 * WM;
   constexpr int NT = WM * WN * 32;
   constexpr int KW = BN / WN;   // keys of a tile that one warp handles
   constexpr int CH = D / 8;     // 16-byte chunks per row
   static_assert(KW % 16 == 0, "a warp needs at least 16 keys per tile");
-  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BM][D]
-  __nv_bfloat16* sK = sQ + BM * D;                                  // [2][BN][D]
-  __nv_bfloat16* sV = sK + 2 * BN * D;                              // [2][BN][D]
+  elem16* sQ = reinterpret_cast<elem16*>(smem_raw);  // [BM][D]
+  elem16* sK = sQ + BM * D;                           // [2][BN][D]
+  elem16* sV = sK + 2 * BN * D;                       // [2][BN][D]
 
   const int req = wk[0], row0 = wk[1], kv_begin = wk[2], kv_end = wk[3], n_splits = wk[4], part = wk[5];
   if (n_splits == 0) return;  // padding of a fixed-size work list
@@ -109,9 +118,9 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
   for (int idx = tid; idx < BM * CH; idx += NT) {
     const int r = idx / CH, c = idx % CH;
     const int pr = row0 + r;
-    __nv_bfloat16* dst = sQ + r * D + ((c ^ (r & 7)) << 3);
+    elem16* dst = sQ + r * D + ((c ^ (r & 7)) << 3);
     if (pr < n_rows) {
-      const __nv_bfloat16* src = p.q + (size_t)(qs + pr / G) * p.ldq + (size_t)(kvh * G + pr % G) * D + c * 8;
+      const elem16* src = p.q + (size_t)(qs + pr / G) * p.ldq + (size_t)(kvh * G + pr % G) * D + c * 8;
       cp_async16(dst, src, 16);
     } else {
       *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
@@ -124,20 +133,26 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
   static_assert(NT % CH == 0 && RPP % 8 == 0 && BN % RPP == 0, "load pattern");
   const int ld_c = tid % CH, ld_r = tid / CH;
   const int ld_off = ld_r * D + ((ld_c ^ (ld_r & 7)) << 3);
-  const __nv_bfloat16* kv_head = p.kv_plane + (size_t)kvh * ps * D + ld_c * 8;
+  const elem16* kv_head = p.kv_plane + (size_t)kvh * ps * D + ld_c * 8;
   const int ps_shift = p.page_shift;  // log2(page_size), or -1 when it is no power of two
   auto load_tile = [&](int buf, int key0) {
-    __nv_bfloat16* dk = sK + buf * BN * D + ld_off;
-    __nv_bfloat16* dv = sV + buf * BN * D + ld_off;
+    elem16* dk = sK + buf * BN * D + ld_off;
+    elem16* dv = sV + buf * BN * D + ld_off;
 #pragma unroll
     for (int i = 0; i < PASSES; ++i) {
       const int key = key0 + ld_r + i * RPP;
-      const bool valid = key < kv_end;
-      const __nv_bfloat16* src = p.kv_plane;
+      bool valid = key < kv_end;
+      const elem16* src = p.kv_plane;
       if (valid) {
         const int lp = ps_shift >= 0 ? key >> ps_shift : key / ps;
         const int in_page = ps_shift >= 0 ? key & (ps - 1) : key - lp * ps;
-        src = kv_head + (size_t)bt[lp] * p.page_stride + in_page * D;
+        const int page = lp < p.table_width ? bt[lp] : -1;
+        if (page < 0) {   // a key without a page: nothing is read (the rows arrive as zeros), the step fails
+          valid = false;
+          atomicExch(p.err, 5);
+        } else {
+          src = kv_head + (size_t)page * p.page_stride + in_page * D;
+        }
       }
       cp_async16(dk + i * RPP * D, src, valid ? 16 : 0);
       cp_async16(dv + i * RPP * D, valid ? src + v_off : src, valid ? 16 : 0);
@@ -183,8 +198,8 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
         ldmatrix_x4(qf[kk], tile_ptr<D>(sQ, r, kk * 16 + (lane >> 4) * 8));
       }
     }
-    __nv_bfloat16* tK = sK + buf * BN * D;
-    __nv_bfloat16* tV = sV + buf * BN * D;
+    elem16* tK = sK + buf * BN * D;
+    elem16* tV = sV + buf * BN * D;
     const int key0 = kv_begin + it * BN + wn * KW;
 
     // ---- S = Q K^T for this warp's 16 rows x KW keys
@@ -200,8 +215,8 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
         unsigned b[4];
         const int r = wn * KW + nb * 16 + (lane & 7) + (lane >> 4) * 8;
         ldmatrix_x4(b, tile_ptr<D>(tK, r, kk * 16 + ((lane >> 3) & 1) * 8));
-        mma_bf16(s[2 * nb], qf[kk], b[0], b[1]);
-        mma_bf16(s[2 * nb + 1], qf[kk], b[2], b[3]);
+        mma16<HALF>(s[2 * nb], qf[kk], b[0], b[1]);
+        mma16<HALF>(s[2 * nb + 1], qf[kk], b[2], b[3]);
       }
     }
     // ---- mask, scale, online softmax.  A tile that every row of the warp sees in full
@@ -260,17 +275,17 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
 #pragma unroll
     for (int ks = 0; ks < KW / 16; ++ks) {
       unsigned a[4];
-      a[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
-      a[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
-      a[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-      a[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+      a[0] = pack16<HALF>(s[2 * ks][0], s[2 * ks][1]);
+      a[1] = pack16<HALF>(s[2 * ks][2], s[2 * ks][3]);
+      a[2] = pack16<HALF>(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+      a[3] = pack16<HALF>(s[2 * ks + 1][2], s[2 * ks + 1][3]);
 #pragma unroll
       for (int db = 0; db < D / 16; ++db) {
         unsigned b[4];
         const int r = wn * KW + ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         ldmatrix_x4_trans(b, tile_ptr<D>(tV, r, db * 16 + (lane >> 4) * 8));
-        mma_bf16(o[2 * db], a, b[0], b[1]);
-        mma_bf16(o[2 * db + 1], a, b[2], b[3]);
+        mma16<HALF>(o[2 * db], a, b[0], b[1]);
+        mma16<HALF>(o[2 * db + 1], a, b[2], b[3]);
       }
     }
     __syncthreads();  // everyone is done with this buffer before the next load overwrites it
@@ -319,10 +334,10 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
     }
     if (n_splits == 1) {
       const float inv = L > 0.f ? 1.0f / L : 0.f;
-      __nv_bfloat16* dst = p.out + (size_t)(qs + pr / G) * p.ldo + (size_t)(kvh * G + pr % G) * D + d;
+      elem16* dst = p.out + (size_t)(qs + pr / G) * p.ldo + (size_t)(kvh * G + pr % G) * D + d;
       uint2 packed;
-      packed.x = pack_bf16(acc.x * inv, acc.y * inv);
-      packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+      packed.x = pack16<HALF>(acc.x * inv, acc.y * inv);
+      packed.y = pack16<HALF>(acc.z * inv, acc.w * inv);
       *reinterpret_cast<uint2*>(dst) = packed;
     } else {
       const size_t slot = (size_t)part * BM + r;
@@ -335,7 +350,7 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
   }
 }
 
-template <int D, int WM, int WN>
+template <int D, int WM, int WN, bool HALF>
 __global__ void __launch_bounds__(WM * WN * 32)
 flash_kernel(const FlashParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -355,14 +370,14 @@ flash_kernel(const FlashParams p) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) item[i] = wk[i];
     item[5] = item[5] * p.Hkv + blockIdx.y;
-    flash_item<D, WM, WN>(p, item, blockIdx.y, smem_raw);
+    flash_item<D, WM, WN, HALF>(p, item, blockIdx.y, smem_raw);
     TRACE_MARK(TRACE_EXIT);
     return;
   }
   const int begin = p.cta_items[blockIdx.x], end = p.cta_items[blockIdx.x + 1];
   for (int w = begin; w < end; ++w) {
     const int* wk = p.work + (size_t)w * 8;
-    flash_item<D, WM, WN>(p, wk, wk[6], smem_raw);
+    flash_item<D, WM, WN, HALF>(p, wk, wk[6], smem_raw);
     __syncthreads();  // the next item's loads reuse the shared memory the merge just read
   }
   TRACE_MARK(TRACE_EXIT);
@@ -378,9 +393,9 @@ flash_kernel(const FlashParams p) {
 constexpr int COMBINE_MAX_WARPS = 8;
 template <int D>
 __global__ void __launch_bounds__(32 * COMBINE_MAX_WARPS)
-combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* part_ml, const int* q_start,
+combine_kernel(elem16* out, int ldo, const float* part_o, const float* part_ml, const int* q_start,
                const int* req_of_token, const int* req_tile0, const int* tile_info, const int* token_list, int G,
-               int Hkv, int BM) {
+               int Hkv, int BM, int half) {
   TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0, TRACE_COMBINE);
   pdl_launch();
   // The index arrays were copied to the device before the step's first kernel ran: they are
@@ -459,12 +474,12 @@ combine_kernel(__nv_bfloat16* out, int ldo, const float* part_o, const float* pa
   if (!active) return;
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   uint2 packed;
-  packed.x = pack_bf16(acc.x * inv, acc.y * inv);
-  packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+  packed.x = pack2_bits(acc.x * inv, acc.y * inv, half != 0);
+  packed.y = pack2_bits(acc.z * inv, acc.w * inv, half != 0);
   *reinterpret_cast<uint2*>(out + (size_t)t * ldo + (size_t)head * D + d) = packed;
 }
 
-template <int D, int WM, int WN>
+template <int D, int WM, int WN, bool HALF>
 int launch_flash(const FlashParams& p, int n_work, int n_ctas, cudaStream_t stream) {
   constexpr int BM = 16 * WM;
   constexpr int kv_bytes = 4 * BN * D * 2 + BM * D * 2;
@@ -472,12 +487,12 @@ int launch_flash(const FlashParams& p, int n_work, int n_ctas, cudaStream_t stre
   constexpr int smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_kernel<D, WM, WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(flash_kernel<D, WM, WN, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     FERRUM_CHECK_ARG(e == cudaSuccess, "attention_flash: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   dim3 grid = p.cta_items ? dim3(n_ctas, 1) : dim3(n_work, p.Hkv);
-  launch_kernel(flash_kernel<D, WM, WN>, grid, dim3(WM * WN * 32), smem, stream, p);
+  launch_kernel(flash_kernel<D, WM, WN, HALF>, grid, dim3(WM * WN * 32), smem, stream, p);
   FERRUM_CHECK_LAUNCH("attention_flash");
   return 0;
 }
@@ -491,12 +506,15 @@ FERRUM_API int ferrum_attention_flash_supported(int D, int bm) { return (D == 64
 // work: [n_work][8] int32 on the device (see FlashParams).  bm: 16 (a few rows per request,
 // key range split between four warps) or 64.  cta_items (n_ctas + 1 ints) selects the
 // balanced-list mode; null runs a grid of (n_work, Hkv).
-FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo, const void* kv_plane,
+FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo, int dtype, const void* kv_plane,
                                       long long page_stride, int page_size, const int* block_table, int table_width,
                                       const int* q_start, const int* pos0, const int* work, int n_work,
                                       const int* cta_items, int n_ctas, float* part_o, float* part_ml, int Hq, int Hkv,
-                                      int D, float scale, int window, int bm, int trigger_early, cudaStream_t stream) {
+                                      int D, float scale, int window, int bm, int trigger_early, int* err_flag,
+                                      cudaStream_t stream) {
   FERRUM_CHECK_ARG(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_flash: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
+  FERRUM_CHECK_ARG(ferrum_is_16bit(dtype), "attention_flash: dtype code %d is not a 16-bit type", dtype);
+  FERRUM_CHECK_ARG(err_flag != nullptr, "attention_flash: the error flag is required");
   FERRUM_CHECK_ARG(ferrum_attention_flash_supported(D, bm), "attention_flash: head size %d with row tile %d is not built; "
                    "use the generic kernel", D, bm);
   FERRUM_CHECK_ARG(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
@@ -506,7 +524,8 @@ FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo
   FERRUM_CHECK_ARG(cta_items == nullptr || n_ctas > 0, "attention_flash: an item list needs a CTA count");
   FlashParams p;
   p.cta_items = cta_items;
-  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.kv_plane = (const __nv_bfloat16*)kv_plane;
+  p.q = (const elem16*)q; p.out = (elem16*)out; p.kv_plane = (const elem16*)kv_plane;
+  p.err = err_flag;
   p.block_table = block_table; p.q_start = q_start; p.pos0 = pos0; p.work = work;
   p.part_o = part_o; p.part_ml = part_ml; p.page_stride = page_stride;
   p.ldq = ldq; p.ldo = ldo; p.page_size = page_size; p.table_width = table_width;
@@ -516,17 +535,25 @@ FERRUM_API int ferrum_attention_flash(const void* q, int ldq, void* out, int ldo
   p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.window = window;
   p.trigger_early = trigger_early;
   p.scale_log2 = scale * 1.4426950408889634f;
-  if (D == 64 && bm == 16) return launch_flash<64, 1, 4>(p, n_work, n_ctas, stream);
-  if (D == 64 && bm == 64) return launch_flash<64, 4, 1>(p, n_work, n_ctas, stream);
-  if (D == 128 && bm == 16) return launch_flash<128, 1, 4>(p, n_work, n_ctas, stream);
-  return launch_flash<128, 4, 1>(p, n_work, n_ctas, stream);
+  if (dtype == FERRUM_F16) {
+    if (D == 64 && bm == 16) return launch_flash<64, 1, 4, true>(p, n_work, n_ctas, stream);
+    if (D == 64 && bm == 64) return launch_flash<64, 4, 1, true>(p, n_work, n_ctas, stream);
+    if (D == 128 && bm == 16) return launch_flash<128, 1, 4, true>(p, n_work, n_ctas, stream);
+    return launch_flash<128, 4, 1, true>(p, n_work, n_ctas, stream);
+  }
+  if (D == 64 && bm == 16) return launch_flash<64, 1, 4, false>(p, n_work, n_ctas, stream);
+  if (D == 64 && bm == 64) return launch_flash<64, 4, 1, false>(p, n_work, n_ctas, stream);
+  if (D == 128 && bm == 16) return launch_flash<128, 1, 4, false>(p, n_work, n_ctas, stream);
+  return launch_flash<128, 4, 1, false>(p, n_work, n_ctas, stream);
 }
 
-FERRUM_API int ferrum_attention_combine(void* out, int ldo, const float* part_o, const float* part_ml,
+FERRUM_API int ferrum_attention_combine(void* out, int ldo, int dtype, const float* part_o, const float* part_ml,
                                         const int* q_start, const int* req_of_token, const int* req_tile0,
                                         const int* tile_info, const int* token_list, int n_tokens, int Hq, int Hkv,
                                         int D, int bm, int n_warps, cudaStream_t stream) {
   FERRUM_CHECK_ARG(D == 64 || D == 128, "attention_combine: head size %d is not built", D);
+  FERRUM_CHECK_ARG(ferrum_is_16bit(dtype), "attention_combine: dtype code %d is not a 16-bit type", dtype);
+  const int half = dtype == FERRUM_F16;
   FERRUM_CHECK_ARG(n_warps >= 1 && n_warps <= COMBINE_MAX_WARPS, "attention_combine: %d warps per block (1..%d)", n_warps,
                    COMBINE_MAX_WARPS);
   if (n_tokens == 0) return 0;
@@ -534,11 +561,11 @@ FERRUM_API int ferrum_attention_combine(void* out, int ldo, const float* part_o,
   FERRUM_CHECK_ARG(grid.y <= 65535, "attention_combine: too many heads");
   const int smem = n_warps > 1 ? n_warps * 32 * (int)(sizeof(float4) + sizeof(float2)) : 0;
   if (D == 64)
-    launch_kernel(combine_kernel<64>, grid, dim3(32 * n_warps), smem, stream, (__nv_bfloat16*)out, ldo, part_o, part_ml, q_start,
-                  req_of_token, req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
+    launch_kernel(combine_kernel<64>, grid, dim3(32 * n_warps), smem, stream, (elem16*)out, ldo, part_o, part_ml, q_start,
+                  req_of_token, req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm, half);
   else
-    launch_kernel(combine_kernel<128>, grid, dim3(32 * n_warps), smem, stream, (__nv_bfloat16*)out, ldo, part_o, part_ml, q_start,
-                  req_of_token, req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm);
+    launch_kernel(combine_kernel<128>, grid, dim3(32 * n_warps), smem, stream, (elem16*)out, ldo, part_o, part_ml, q_start,
+                  req_of_token, req_tile0, tile_info, token_list, Hq / Hkv, Hkv, bm, half);
   FERRUM_CHECK_LAUNCH("attention_combine");
   return 0;
 }

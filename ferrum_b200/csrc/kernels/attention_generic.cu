@@ -101,15 +101,9 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
   if (n_tokens == 0) return 0;
   dim3 grid(n_tokens, (Hq + ATT_WARPS - 1) / ATT_WARPS);
   FERRUM_CHECK_ARG(grid.y <= 65535, "attention: too many heads");
-  if (dtype == FERRUM_F32)
-    attention_generic_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>((const float*)q, ldq, (float*)out, ldo, positions,
-        req_of_token, block_table, table_width, (const float*)kv_plane, page_stride, page_size, Hq, Hkv, D, scale, window, err_flag);
-  else if (dtype == FERRUM_BF16)
-    attention_generic_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, stream>>>((const __nv_bfloat16*)q, ldq,
-        (__nv_bfloat16*)out, ldo, positions, req_of_token, block_table, table_width, (const __nv_bfloat16*)kv_plane,
-        page_stride, page_size, Hq, Hkv, D, scale, window, err_flag);
-  else
-    FERRUM_CHECK_ARG(false, "attention: unknown dtype code %d", dtype);
+  FERRUM_DISPATCH_DTYPE(dtype, T, (attention_generic_kernel<T><<<grid, ATT_WARPS * 32, 0, stream>>>(
+      (const T*)q, ldq, (T*)out, ldo, positions, req_of_token, block_table, table_width, (const T*)kv_plane, page_stride,
+      page_size, Hq, Hkv, D, scale, window, err_flag)));
   FERRUM_CHECK_LAUNCH("attention_generic");
   return 0;
 }

@@ -1,4 +1,4 @@
-// Paged causal GQA attention for prompt portions on the tcgen05 matrix unit (bfloat16).
+// Paged causal GQA attention for prompt portions on the tcgen05 matrix unit (bfloat16 or float16).
 //
 // One CTA handles one work item x one KV head.  An item is a pair of row tiles of one request
 // and a key range [kv_begin, kv_end).  A row tile is `tok` consecutive tokens x the G query
@@ -42,7 +42,7 @@ namespace {
 constexpr float TC_LAZY = 8.0f;  // the running maximum moves when it grows by more than this (log2 units)
 
 struct AttnTcParams {
-  __nv_bfloat16* out;
+  uint16_t* out;        // bfloat16 or float16 elements, as the template says
   const int* block_table;
   const int* q_start;   // [R + 1] first token of each request in this batch
   const int* pos0;      // [R] cached positions before this step
@@ -148,12 +148,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
+template <bool HALF>
+__device__ __forceinline__ uint32_t pack2_16(float lo, float hi) {
+  return HALF ? pack2<__half>(lo, hi) : pack2<__nv_bfloat16>(lo, hi);
 }
 
-template <int D, int NT, int BN, int NS>
+template <int D, int NT, int BN, int NS, bool HALF>
 __global__ void __launch_bounds__(AttnTcConfig<D, NT, BN, NS>::THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const AttnTcParams p) {
   using Cfg = AttnTcConfig<D, NT, BN, NS>;
@@ -245,9 +245,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int ps = p.page_size;
     const int pages_per_stage = BN / ps;
     const int* bt = p.block_table + (size_t)req * p.table_width;
-    auto page_of = [&](int j) {  // this lane's page of stage j; a missing page reads as zeros (masked keys)
+    auto page_of = [&](int j) {  // this lane's page of stage j; a page past the key range reads as zeros (masked keys)
       const int lp = ((kv0 + j * BN) >> p.page_shift) + lane;
-      return (lane < pages_per_stage && j >= 0 && j < n_j && lp < p.table_width) ? bt[lp] : -1;
+      if (!(lane < pages_per_stage && j >= 0 && j < n_j)) return -1;
+      const int page = lp < p.table_width ? bt[lp] : -1;
+      // a key of the item's range without a page: the keys arrive as zeros and the step fails
+      if (page < 0 && lp * ps < kv_end && (lp + 1) * ps > kv_begin) atomicExch(p.err, 5);
+      return page;
     };
     // one stage of keys (kv = 0) or values (kv = 1); false on a timeout
     auto load_stage = [&](int j, int kv, int page) {
@@ -285,8 +289,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ------------------------------------------------------------ MMA issuer of one row tile
     if (lane == 0) {
       const int t = warp - 1;
-      const uint32_t idesc_qk = umma_idesc_bf16(128, BN);
-      const uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B (values) is MN-major
+      const uint32_t idesc_qk = umma_idesc_16bit(128, BN, HALF);
+      const uint32_t idesc_pv = umma_idesc_16bit(128, D, HALF) | (1u << 16);  // B (values) is MN-major
       const uint32_t q_addr = smem_base + Cfg::OFF_Q + t * Cfg::Q_TILE_BYTES;
       const uint32_t o_tmem = tmem_base + Cfg::O_COL + t * D;
       auto issue_qk = [&](int s, int buf) {
@@ -443,8 +447,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         l1 += e1;
         l2 += e2;
         l3 += e3;
-        pk[c / 2] = pack2_bf16(e0, e1);
-        pk[c / 2 + 1] = pack2_bf16(e2, e3);
+        pk[c / 2] = pack2_16<HALF>(e0, e1);
+        pk[c / 2 + 1] = pack2_16<HALF>(e2, e3);
       }
       l_run += (l0 + l1) + (l2 + l3);
       if (j + 1 == n_j && kv_end - key0 < BN) {
@@ -488,7 +492,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc_fence_after();
       const bool whole = n_splits == 1;
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      __nv_bfloat16* orow = p.out + (size_t)(qs + tok_in_req) * p.ldo + (size_t)(kvh * G + r % G) * D;
+      uint16_t* orow = p.out + (size_t)(qs + tok_in_req) * p.ldo + (size_t)(kvh * G + r % G) * D;
       const size_t prow = (size_t)part * (NT * tok * G) + t * tok * G + r;
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) {
@@ -499,10 +503,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             uint4 v;
-            v.x = pack2_bf16(o[c] * inv, o[c + 1] * inv);
-            v.y = pack2_bf16(o[c + 2] * inv, o[c + 3] * inv);
-            v.z = pack2_bf16(o[c + 4] * inv, o[c + 5] * inv);
-            v.w = pack2_bf16(o[c + 6] * inv, o[c + 7] * inv);
+            v.x = pack2_16<HALF>(o[c] * inv, o[c + 1] * inv);
+            v.y = pack2_16<HALF>(o[c + 2] * inv, o[c + 3] * inv);
+            v.z = pack2_16<HALF>(o[c + 4] * inv, o[c + 5] * inv);
+            v.w = pack2_16<HALF>(o[c + 6] * inv, o[c + 7] * inv);
             *reinterpret_cast<uint4*>(orow + c0 + c) = v;
           }
         } else {
@@ -618,16 +622,16 @@ int cache_map(const void* plane, long long n_pages, int Hkv, int page_size, int 
   return 0;
 }
 
-template <int D, int NT, int BN, int NS>
+template <int D, int NT, int BN, int NS, bool HALF>
 int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const AttnTcParams& p, int n_work, cudaStream_t stream) {
   using Cfg = AttnTcConfig<D, NT, BN, NS>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<D, NT, BN, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<D, NT, BN, NS, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     FERRUM_CHECK_ARG(e == cudaSuccess, "attention_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
-  launch_kernel(attention_tc_kernel<D, NT, BN, NS>, dim3(p.Hkv, n_work), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, mq, mkv, p);
+  launch_kernel(attention_tc_kernel<D, NT, BN, NS, HALF>, dim3(p.Hkv, n_work), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, mq, mkv, p);
   FERRUM_CHECK_LAUNCH("attention_tc");
   return 0;
 }
@@ -652,7 +656,7 @@ FERRUM_API int ferrum_attention_tc_tokens(int D, int G, int page_size) {
 // Items of ferrum_attention_tc_tokens * G rows in the work-list format of ferrum_attention_flash;
 // grid (Hkv, n_work).  q has q_rows rows of ldq elements (the buffer's capacity, of which the
 // batch may use fewer); the plane has n_pages pages.
-FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, void* out, int ldo, const void* kv_plane,
+FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, void* out, int ldo, int dtype, const void* kv_plane,
                                    long long page_stride, long long n_pages, int page_size, const int* block_table,
                                    int table_width, const int* q_start, const int* pos0, const int* work, int n_work,
                                    float* part_o, float* part_ml, int Hq, int Hkv, int D, float scale, int window,
@@ -662,6 +666,7 @@ FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, voi
   const int tok = ferrum_attention_tc_tokens(D, G, page_size) / TC_TILES;
   FERRUM_CHECK_ARG(tok > 0, "attention_tc: head size %d, group %d, page size %d is not built; use attention_flash", D, G, page_size);
   FERRUM_CHECK_ARG(err_flag != nullptr, "attention_tc: the error flag is required");
+  FERRUM_CHECK_ARG(ferrum_is_16bit(dtype), "attention_tc: dtype code %d is not a 16-bit type", dtype);
   FERRUM_CHECK_ARG(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
                    ((uintptr_t)kv_plane & 15) == 0, "attention_tc: operands must be 16-byte aligned");
   FERRUM_CHECK_ARG(page_stride == 2LL * Hkv * page_size * D, "attention_tc: the plane's pages must be dense "
@@ -672,7 +677,7 @@ FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, voi
   if (n_work == 0) return 0;
   FERRUM_CHECK_ARG(n_work <= 65535, "attention_tc: %d work items are more than one launch takes", n_work);
   AttnTcParams p;
-  p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.q_start = q_start; p.pos0 = pos0; p.work = work;
+  p.out = (uint16_t*)out; p.block_table = block_table; p.q_start = q_start; p.pos0 = pos0; p.work = work;
   p.part_o = part_o; p.part_ml = part_ml; p.err = err_flag;
   p.ldo = ldo; p.page_size = page_size; p.table_width = table_width;
   p.page_shift = 0;
@@ -682,6 +687,10 @@ FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, voi
   CUtensorMap mq, mkv;
   if (int r = query_map(q, q_rows, ldq, Hq, D, G, tok, &mq)) return r;
   if (int r = cache_map(kv_plane, n_pages, Hkv, page_size, D, &mkv)) return r;
-  if (D == 64) return launch_attention_tc<64, TC_TILES, TC_BN, TC_STAGES>(mq, mkv, p, n_work, stream);
-  return launch_attention_tc<128, TC_TILES, TC_BN, TC_STAGES>(mq, mkv, p, n_work, stream);
+  if (dtype == FERRUM_F16) {
+    if (D == 64) return launch_attention_tc<64, TC_TILES, TC_BN, TC_STAGES, true>(mq, mkv, p, n_work, stream);
+    return launch_attention_tc<128, TC_TILES, TC_BN, TC_STAGES, true>(mq, mkv, p, n_work, stream);
+  }
+  if (D == 64) return launch_attention_tc<64, TC_TILES, TC_BN, TC_STAGES, false>(mq, mkv, p, n_work, stream);
+  return launch_attention_tc<128, TC_TILES, TC_BN, TC_STAGES, false>(mq, mkv, p, n_work, stream);
 }

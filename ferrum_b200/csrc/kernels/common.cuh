@@ -2,13 +2,15 @@
 // fixed tree shape, error reporting of the C entry points.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #define FERRUM_API extern "C" __attribute__((visibility("default")))
 
 // dtype codes shared with the Python side
-enum FerrumDType : int { FERRUM_F32 = 0, FERRUM_BF16 = 1 };
+enum FerrumDType : int { FERRUM_F32 = 0, FERRUM_BF16 = 1, FERRUM_F16 = 2 };
+inline bool ferrum_is_16bit(int dtype) { return dtype == FERRUM_BF16 || dtype == FERRUM_F16; }
 
 // Error text of the last failed entry point on this thread (see ferrum_last_error).
 void ferrum_set_error(const char* fmt, ...);
@@ -108,9 +110,46 @@ template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Two float32 values rounded to the 16-bit type T and packed, the first in the low half.
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// The bits of one float32 value rounded to bfloat16 (half = false) or to float16 (half = true),
+// for epilogues whose 16-bit type is a run-time parameter.
+__device__ __forceinline__ uint16_t bits16(float v, bool half) {
+  return half ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ uint32_t pack2_bits(float lo, float hi, bool half) {
+  return half ? pack2<__half>(lo, hi) : pack2<__nv_bfloat16>(lo, hi);
+}
+
+// Run `body` with T bound to the storage type of a dtype code (float, __nv_bfloat16, __half).
+#define FERRUM_DISPATCH_DTYPE(dtype, T, ...)                      \
+  do {                                                            \
+    if ((dtype) == FERRUM_F32) { using T = float; __VA_ARGS__; }  \
+    else if ((dtype) == FERRUM_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else if ((dtype) == FERRUM_F16) { using T = __half; __VA_ARGS__; }         \
+    else FERRUM_CHECK_ARG(false, "unknown dtype code %d", (int)(dtype));      \
+  } while (0)
+#define FERRUM_DISPATCH_16BIT(dtype, T, ...)                      \
+  do {                                                            \
+    if ((dtype) == FERRUM_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else if ((dtype) == FERRUM_F16) { using T = __half; __VA_ARGS__; }    \
+    else FERRUM_CHECK_ARG(false, "dtype code %d is not a 16-bit type", (int)(dtype)); \
+  } while (0)
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -1,6 +1,6 @@
 // Memory-bound kernels of the step: embedding gather, RMSNorm, rotary encoding fused
-// with the paged cache write, SwiGLU.  All arithmetic is float32; storage is float32
-// or bfloat16.  Formulas follow the reference's scalar kernels
+// with the paged cache write, SwiGLU.  All arithmetic is float32; storage is float32,
+// bfloat16 or float16.  Formulas follow the reference's scalar kernels
 // (crates/kernels/src/scalar.rs:143-156 rms, :167-189 rope; crates/kernels/src/math.rs:8-10 silu).
 #include "common.cuh"
 #include "partials.cuh"
@@ -27,12 +27,7 @@ FERRUM_API int ferrum_embedding(const void* table, int dtype, const int* ids, fl
   FERRUM_CHECK_ARG(n_tokens >= 0 && E > 0 && V > 0, "embedding: bad sizes T=%d E=%d V=%d", n_tokens, E, V);
   if (n_tokens == 0) return 0;
   const int threads = E >= 1024 ? 256 : 128;
-  if (dtype == FERRUM_F32)
-    launch_kernel(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, E, V, err_flag);
-  else if (dtype == FERRUM_BF16)
-    launch_kernel(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, E, V, err_flag);
-  else
-    FERRUM_CHECK_ARG(false, "embedding: unknown dtype code %d", dtype);
+  FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(embedding_kernel<T>, n_tokens, threads, 0, stream, (const T*)table, ids, out, E, V, err_flag));
   FERRUM_CHECK_LAUNCH("embedding");
   return 0;
 }
@@ -62,6 +57,9 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 // Many rows of a width that is a multiple of 4: one block per row, float4 loads, the row kept
 // in registers between the sum of squares and the scaling (read once, written once).
 constexpr int NORM_VEC_MAX = 4;  // float4 per thread
+// pack2 for an output type that may also be float (a branch the compiler removes for float)
+template <typename TOut> __device__ __forceinline__ uint32_t pack2_out(float lo, float hi) { return pack2<TOut>(lo, hi); }
+template <> __device__ __forceinline__ uint32_t pack2_out<float>(float, float) { return 0u; }
 template <typename TOut>
 __global__ void __launch_bounds__(512)
 rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ out,
@@ -96,10 +94,9 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TOu
     if (sizeof(TOut) == 4) {
       reinterpret_cast<float4*>(o)[i] = make_float4(a, b, c, d);
     } else {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
       uint2 pk;
-      pk.x = *reinterpret_cast<uint32_t*>(&lo);
-      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      pk.x = pack2_out<TOut>(a, b);
+      pk.y = pack2_out<TOut>(c, d);
       reinterpret_cast<uint2*>(o)[i] = pk;
     }
   }
@@ -217,32 +214,23 @@ FERRUM_API int ferrum_rmsnorm(const float* x, const float* w, void* out, int out
   FERRUM_CHECK_ARG(n_rows >= 0 && E > 0, "rmsnorm: bad sizes rows=%d E=%d", n_rows, E);
   FERRUM_CHECK_ARG(eps > 0.f, "rmsnorm: eps must be positive");
   if (n_rows == 0) return 0;
-  if (n_rows <= NORM_CLUSTER_MAX_ROWS && E >= 128 && (out_dtype == FERRUM_F32 || out_dtype == FERRUM_BF16)) {
+  if (n_rows <= NORM_CLUSTER_MAX_ROWS && E >= 128) {
     const PartialLayout none{nullptr, 0, 0, 0, 0};
-    cudaError_t e = out_dtype == FERRUM_F32
-        ? launch_norm_cluster<float>(const_cast<float*>(x), w, (float*)out, rows, n_rows, E, eps, none, stream)
-        : launch_norm_cluster<__nv_bfloat16>(const_cast<float*>(x), w, (__nv_bfloat16*)out, rows, n_rows, E, eps, none, stream);
+    cudaError_t e = cudaErrorInvalidValue;
+    FERRUM_DISPATCH_DTYPE(out_dtype, T, e = launch_norm_cluster<T>(const_cast<float*>(x), w, (T*)out, rows, n_rows, E, eps, none, stream));
     FERRUM_CHECK_ARG(e == cudaSuccess, "rmsnorm: cluster launch failed: %s", cudaGetErrorString(e));
     return 0;
   }
   if (E % 4 == 0 && E >= 512 && E <= 4 * NORM_VEC_MAX * 512 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
-      ((uintptr_t)out & 15) == 0 && (out_dtype == FERRUM_F32 || out_dtype == FERRUM_BF16)) {
+      ((uintptr_t)out & 15) == 0) {
     const int n4 = E / 4;
     const int vthreads = n4 >= 2048 ? 512 : (n4 >= 512 ? 256 : 128);
-    if (out_dtype == FERRUM_F32)
-      launch_kernel(rmsnorm_vec_kernel<float>, n_rows, vthreads, 0, stream, x, w, (float*)out, rows, E, eps);
-    else
-      launch_kernel(rmsnorm_vec_kernel<__nv_bfloat16>, n_rows, vthreads, 0, stream, x, w, (__nv_bfloat16*)out, rows, E, eps);
+    FERRUM_DISPATCH_DTYPE(out_dtype, T, launch_kernel(rmsnorm_vec_kernel<T>, n_rows, vthreads, 0, stream, x, w, (T*)out, rows, E, eps));
     FERRUM_CHECK_LAUNCH("rmsnorm");
     return 0;
   }
   const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
-  if (out_dtype == FERRUM_F32)
-    launch_kernel(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)out, rows, E, eps);
-  else if (out_dtype == FERRUM_BF16)
-    launch_kernel(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, (__nv_bfloat16*)out, rows, E, eps);
-  else
-    FERRUM_CHECK_ARG(false, "rmsnorm: unknown dtype code %d", out_dtype);
+  FERRUM_DISPATCH_DTYPE(out_dtype, T, launch_kernel(rmsnorm_kernel<T>, n_rows, threads, 0, stream, x, w, (T*)out, rows, E, eps));
   FERRUM_CHECK_LAUNCH("rmsnorm");
   return 0;
 }
@@ -306,20 +294,14 @@ FERRUM_API int ferrum_rmsnorm_reduce(float* h, const float* w, void* out, int ou
   PartialLayout L;
   if (int r = make_layout(partials, layout, &L)) return r;
   FERRUM_CHECK_ARG(E <= L.tiles * 128, "rmsnorm_reduce: the partials cover %d features, the rows have %d", L.tiles * 128, E);
-  if (n_rows <= NORM_CLUSTER_MAX_ROWS && E >= 128 && (out_dtype == FERRUM_F32 || out_dtype == FERRUM_BF16)) {
-    cudaError_t e = out_dtype == FERRUM_F32
-        ? launch_norm_cluster<float>(h, w, (float*)out, rows, n_rows, E, eps, L, stream)
-        : launch_norm_cluster<__nv_bfloat16>(h, w, (__nv_bfloat16*)out, rows, n_rows, E, eps, L, stream);
+  if (n_rows <= NORM_CLUSTER_MAX_ROWS && E >= 128) {
+    cudaError_t e = cudaErrorInvalidValue;
+    FERRUM_DISPATCH_DTYPE(out_dtype, T, e = launch_norm_cluster<T>(h, w, (T*)out, rows, n_rows, E, eps, L, stream));
     FERRUM_CHECK_ARG(e == cudaSuccess, "rmsnorm_reduce: cluster launch failed: %s", cudaGetErrorString(e));
     return 0;
   }
   const int threads = E >= 2048 ? 1024 : (E >= 512 ? 256 : 128);  // many loads per element: many threads
-  if (out_dtype == FERRUM_F32)
-    launch_kernel(rmsnorm_reduce_kernel<float>, n_rows, threads, 0, stream, h, w, (float*)out, rows, E, eps, L);
-  else if (out_dtype == FERRUM_BF16)
-    launch_kernel(rmsnorm_reduce_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, h, w, (__nv_bfloat16*)out, rows, E, eps, L);
-  else
-    FERRUM_CHECK_ARG(false, "rmsnorm_reduce: unknown dtype code %d", out_dtype);
+  FERRUM_DISPATCH_DTYPE(out_dtype, T, launch_kernel(rmsnorm_reduce_kernel<T>, n_rows, threads, 0, stream, h, w, (T*)out, rows, E, eps, L));
   FERRUM_CHECK_LAUNCH("rmsnorm_reduce");
   return 0;
 }
@@ -438,13 +420,14 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int ld, const int* __rest
   TRACE_MARK(TRACE_EXIT);
 }
 
-// Many tokens, bfloat16, the whole head rotated (R == D, D a multiple of 16): a thread rotates
+// Many tokens, a 16-bit type, the whole head rotated (R == D, D a multiple of 16): a thread rotates
 // eight pairs with 16-byte loads and stores, or copies eight value elements.  Same formulas and
 // the same error codes as the kernel above.
+template <typename T>
 __global__ void __launch_bounds__(128)
-rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ positions,
+rope_cache_vec_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
                       const int* __restrict__ req_of_token, const int* __restrict__ block_table, int table_width,
-                      const float* __restrict__ cos_sin, int n_pos, __nv_bfloat16* __restrict__ kv_plane,
+                      const float* __restrict__ cos_sin, int n_pos, T* __restrict__ kv_plane,
                       long long page_stride, int page_size, int Hq, int Hkv, int D, int pairing, int write_kv,
                       int n_tokens, int* __restrict__ err) {
   pdl_launch();
@@ -460,8 +443,8 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __rest
     if (item == 0) atomicExch(err, 2);
     return;
   }
-  __nv_bfloat16* row = qkv + (size_t)t * ld;
-  __nv_bfloat16* kdst = nullptr;
+  T* row = qkv + (size_t)t * ld;
+  T* kdst = nullptr;
   if (write_kv) {
     const int lp = pos / page_size;
     if (lp >= table_width) {
@@ -483,15 +466,15 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __rest
   }
   const int h = item / chunks, c = item % chunks;
   if (h >= Hq && !write_kv) return;
-  __nv_bfloat16* src = row + (size_t)h * D;
+  T* src = row + (size_t)h * D;
   const int o0 = pairing == 0 ? c * 16 : c * 8, o1 = pairing == 0 ? c * 16 + 8 : half + c * 8;
   uint4 r0 = *reinterpret_cast<const uint4*>(src + o0), r1 = *reinterpret_cast<const uint4*>(src + o1);
-  const __nv_bfloat16* e0 = reinterpret_cast<const __nv_bfloat16*>(&r0);
-  const __nv_bfloat16* e1 = reinterpret_cast<const __nv_bfloat16*>(&r1);
+  const T* e0 = reinterpret_cast<const T*>(&r0);
+  const T* e1 = reinterpret_cast<const T*>(&r1);
   const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + ((size_t)pos * half + c * 8) * 2);
   uint4 w0, w1;
-  __nv_bfloat16* f0 = reinterpret_cast<__nv_bfloat16*>(&w0);
-  __nv_bfloat16* f1 = reinterpret_cast<__nv_bfloat16*>(&w1);
+  T* f0 = reinterpret_cast<T*>(&w0);
+  T* f1 = reinterpret_cast<T*>(&w1);
 #pragma unroll
   for (int k = 0; k < 4; ++k) {  // pairs 2k and 2k+1 of this chunk
     const float4 cs = cs4[k];  // cos, sin, cos, sin
@@ -501,13 +484,13 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __rest
       const float cv = q == 0 ? cs.x : cs.z, sv = q == 0 ? cs.y : cs.w;
       float x0, x1;
       if (pairing == 0) {  // elements 2i and 2i+1 of the 16 loaded
-        x0 = __bfloat162float(i < 4 ? e0[2 * i] : e1[2 * i - 8]);
-        x1 = __bfloat162float(i < 4 ? e0[2 * i + 1] : e1[2 * i - 7]);
+        x0 = to_f32<T>(i < 4 ? e0[2 * i] : e1[2 * i - 8]);
+        x1 = to_f32<T>(i < 4 ? e0[2 * i + 1] : e1[2 * i - 7]);
       } else {
-        x0 = __bfloat162float(e0[i]);
-        x1 = __bfloat162float(e1[i]);
+        x0 = to_f32<T>(e0[i]);
+        x1 = to_f32<T>(e1[i]);
       }
-      const __nv_bfloat16 a = __float2bfloat16_rn(x0 * cv - x1 * sv), b = __float2bfloat16_rn(x0 * sv + x1 * cv);
+      const T a = from_f32<T>(x0 * cv - x1 * sv), b = from_f32<T>(x0 * sv + x1 * cv);
       if (pairing == 0) {
         if (i < 4) {
           f0[2 * i] = a;
@@ -522,7 +505,7 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __rest
       }
     }
   }
-  __nv_bfloat16* dst = h < Hq ? src : kdst + (size_t)(h - Hq) * page_size * D;
+  T* dst = h < Hq ? src : kdst + (size_t)(h - Hq) * page_size * D;
   *reinterpret_cast<uint4*>(dst + o0) = w0;
   *reinterpret_cast<uint4*>(dst + o1) = w1;
 }
@@ -545,13 +528,13 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
     FERRUM_CHECK_ARG((write_kv ? Hq + 2 * Hkv : Hq) * D <= L.tiles * 128 && n_tokens <= L.acc_cols,
                      "rope: the partials do not cover the rows");
   }
-  if (dtype == FERRUM_BF16 && n_tokens > 64 && n_tokens <= 65535 && partials == nullptr && R == D && D % 16 == 0 && ld % 8 == 0 &&
+  if (ferrum_is_16bit(dtype) && n_tokens > 64 && n_tokens <= 65535 && partials == nullptr && R == D && D % 16 == 0 && ld % 8 == 0 &&
       ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)cos_sin & 15) == 0 &&
       (!write_kv || (((uintptr_t)kv_plane & 15) == 0 && page_stride % 8 == 0))) {
     const int per_token = (Hq + Hkv) * (D / 16) + (write_kv ? Hkv * (D / 8) : 0);
-    launch_kernel(rope_cache_vec_kernel, dim3((per_token + 127) / 128, n_tokens), dim3(128), 0, stream, (__nv_bfloat16*)qkv, ld,
-                  positions, req_of_token, block_table, table_width, cos_sin, n_pos, (__nv_bfloat16*)kv_plane, page_stride,
-                  page_size, Hq, Hkv, D, pairing, write_kv, n_tokens, err_flag);
+    FERRUM_DISPATCH_16BIT(dtype, T, launch_kernel(rope_cache_vec_kernel<T>, dim3((per_token + 127) / 128, n_tokens), dim3(128), 0, stream,
+                                                  (T*)qkv, ld, positions, req_of_token, block_table, table_width, cos_sin, n_pos,
+                                                  (T*)kv_plane, page_stride, page_size, Hq, Hkv, D, pairing, write_kv, n_tokens, err_flag));
     FERRUM_CHECK_LAUNCH("rope_cache_write");
     return 0;
   }
@@ -559,15 +542,9 @@ FERRUM_API int ferrum_rope_cache_write(void* qkv, int dtype, int n_tokens, int l
   // few tokens, or a product still in partials (several loads per element): several blocks per
   // token, four head slots each, so that a row is read by many SMs at once
   const dim3 grid(n_tokens, (n_tokens <= 64 || partials != nullptr) ? (Hq + 2 * Hkv + 3) / 4 : 1);
-  if (dtype == FERRUM_F32)
-    launch_kernel(rope_cache_kernel<float>, grid, threads, 0, stream, (float*)qkv, ld, positions, req_of_token, block_table,
-        table_width, cos_sin, n_pos, (float*)kv_plane, page_stride, page_size, Hq, Hkv, D, R, pairing, write_kv, err_flag, L);
-  else if (dtype == FERRUM_BF16)
-    launch_kernel(rope_cache_kernel<__nv_bfloat16>, grid, threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions, req_of_token,
-        block_table, table_width, cos_sin, n_pos, (__nv_bfloat16*)kv_plane, page_stride, page_size, Hq, Hkv, D, R,
-        pairing, write_kv, err_flag, L);
-  else
-    FERRUM_CHECK_ARG(false, "rope: unknown dtype code %d", dtype);
+  FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(rope_cache_kernel<T>, grid, threads, 0, stream, (T*)qkv, ld, positions, req_of_token,
+                                                block_table, table_width, cos_sin, n_pos, (T*)kv_plane, page_stride, page_size, Hq,
+                                                Hkv, D, R, pairing, write_kv, err_flag, L));
   FERRUM_CHECK_LAUNCH("rope_cache_write");
   return 0;
 }
@@ -588,17 +565,18 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
   }
 }
 
-// bfloat16 rows of 16-byte multiples: 16-byte loads and stores, SWIGLU_VEC groups of eight features
+// 16-bit rows of 16-byte multiples: 16-byte loads and stores, SWIGLU_VEC groups of eight features
 // per thread with all their loads issued before the arithmetic.
 constexpr int SWIGLU_VEC = 4;
+template <typename T>
 __global__ void __launch_bounds__(256)
-swiglu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int F, int ld_in, int ld_out) {
+swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int F, int ld_in, int ld_out) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.y;
   const int groups = F >> 3;
   const int i0 = blockIdx.x * (blockDim.x * SWIGLU_VEC) + threadIdx.x;  // this thread's groups: i0 + k * blockDim.x
-  const __nv_bfloat16* row = gu + (size_t)t * ld_in;
+  const T* row = gu + (size_t)t * ld_in;
   uint4 g[SWIGLU_VEC], u[SWIGLU_VEC];
 #pragma unroll
   for (int k = 0; k < SWIGLU_VEC; ++k) {
@@ -612,16 +590,16 @@ swiglu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restric
   for (int k = 0; k < SWIGLU_VEC; ++k) {
     const int i = i0 + k * blockDim.x;
     if (i >= groups) continue;
-    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g[k]);
-    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u[k]);
+    const T* ge = reinterpret_cast<const T*>(&g[k]);
+    const T* ue = reinterpret_cast<const T*>(&u[k]);
     uint4 o;
-    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+    uint32_t* o2 = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float2 gv = __bfloat1622float2(g2[j]), uv = __bfloat1622float2(u2[j]);
+      const float gx = to_f32<T>(ge[2 * j]), gy = to_f32<T>(ge[2 * j + 1]), ux = to_f32<T>(ue[2 * j]), uy = to_f32<T>(ue[2 * j + 1]);
       // fast exponential and division, as in the products' own SwiGLU epilogues: the result is
-      // rounded to bfloat16, and the arithmetic, not the memory, set this kernel's time
-      o2[j] = __floats2bfloat162_rn(__fdividef(gv.x, 1.0f + __expf(-gv.x)) * uv.x, __fdividef(gv.y, 1.0f + __expf(-gv.y)) * uv.y);
+      // rounded to 16 bits, and the arithmetic, not the memory, set this kernel's time
+      o2[j] = pack2<T>(__fdividef(gx, 1.0f + __expf(-gx)) * ux, __fdividef(gy, 1.0f + __expf(-gy)) * uy);
     }
     *reinterpret_cast<uint4*>(act + (size_t)t * ld_out + i * 8) = o;
   }
@@ -629,7 +607,8 @@ swiglu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restric
 
 // act[t, f] = silu(gate) * up where gate and up are still partials of a two-product launch
 // (columns t and acc_cols / 2 + t of the partial tiles).
-__global__ void swiglu_reduce_kernel(__nv_bfloat16* __restrict__ act, int F, int ld_out, const PartialLayout L) {
+template <typename T>
+__global__ void swiglu_reduce_kernel(T* __restrict__ act, int F, int ld_out, const PartialLayout L) {
   __shared__ PartialTable tab;
   TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0, TRACE_SWIGLU_REDUCE);
   build_partial_table(L, tab);
@@ -637,10 +616,10 @@ __global__ void swiglu_reduce_kernel(__nv_bfloat16* __restrict__ act, int F, int
   pdl_wait();
   TRACE_MARK(TRACE_WAITED);
   const int t = blockIdx.y;
-  __nv_bfloat16* o = act + (size_t)t * ld_out;
+  T* o = act + (size_t)t * ld_out;
   for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F; f += gridDim.x * blockDim.x) {
     const float g = partial_sum(L, tab, t, f), u = partial_sum(L, tab, L.acc_cols / 2 + t, f);
-    o[f] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+    o[f] = from_f32<T>(g / (1.0f + __expf(-g)) * u);
   }
   TRACE_MARK(TRACE_EXIT);
 }
@@ -650,8 +629,9 @@ __global__ void swiglu_reduce_kernel(__nv_bfloat16* __restrict__ act, int F, int
 // tokens with the slot addresses it worked out once.  One load and one table lookup per
 // feature and token made this kernel, not memory, the limit at 64 tokens.
 constexpr int SWIGLU_REDUCE_TOKENS = 2;
+template <typename T>
 __global__ void __launch_bounds__(256)
-swiglu_reduce_vec_kernel(__nv_bfloat16* __restrict__ act, int n_tokens, int F, int ld_out, const PartialLayout L) {
+swiglu_reduce_vec_kernel(T* __restrict__ act, int n_tokens, int F, int ld_out, const PartialLayout L) {
   __shared__ PartialTable tab;
   TRACE_BEGIN(threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1, TRACE_SWIGLU_REDUCE);
   build_partial_table(L, tab);
@@ -687,17 +667,15 @@ swiglu_reduce_vec_kernel(__nv_bfloat16* __restrict__ act, int n_tokens, int F, i
       gs.x += g[s].x; gs.y += g[s].y; gs.z += g[s].z; gs.w += g[s].w;
       us.x += u[s].x; us.y += u[s].y; us.z += u[s].z; us.w += u[s].w;
     }
-    __nv_bfloat162 lo = __floats2bfloat162_rn(gs.x / (1.0f + __expf(-gs.x)) * us.x, gs.y / (1.0f + __expf(-gs.y)) * us.y);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(gs.z / (1.0f + __expf(-gs.z)) * us.z, gs.w / (1.0f + __expf(-gs.w)) * us.w);
     uint2 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&lo);
-    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    pk.x = pack2<T>(gs.x / (1.0f + __expf(-gs.x)) * us.x, gs.y / (1.0f + __expf(-gs.y)) * us.y);
+    pk.y = pack2<T>(gs.z / (1.0f + __expf(-gs.z)) * us.z, gs.w / (1.0f + __expf(-gs.w)) * us.w);
     *reinterpret_cast<uint2*>(act + (size_t)t * ld_out + f) = pk;
   }
   TRACE_MARK(TRACE_EXIT);
 }
 
-FERRUM_API int ferrum_swiglu_reduce(void* act, int n_tokens, int F, int ld_out, const float* partials, const int* layout,
+FERRUM_API int ferrum_swiglu_reduce(void* act, int dtype, int n_tokens, int F, int ld_out, const float* partials, const int* layout,
                                     cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && F > 0 && ld_out >= F, "swiglu_reduce: bad sizes");
   if (n_tokens == 0) return 0;
@@ -706,12 +684,12 @@ FERRUM_API int ferrum_swiglu_reduce(void* act, int n_tokens, int F, int ld_out, 
   FERRUM_CHECK_ARG(F <= L.tiles * 128 && n_tokens <= L.acc_cols / 2, "swiglu_reduce: the partials do not cover the rows");
   if (n_tokens > 16 && F % 4 == 0 && ld_out % 4 == 0 && ((uintptr_t)act & 7) == 0) {
     dim3 vgrid((F / 4 + 255) / 256, (n_tokens + SWIGLU_REDUCE_TOKENS - 1) / SWIGLU_REDUCE_TOKENS);
-    launch_kernel(swiglu_reduce_vec_kernel, vgrid, dim3(256), 0, stream, (__nv_bfloat16*)act, n_tokens, F, ld_out, L);
+    FERRUM_DISPATCH_16BIT(dtype, T, launch_kernel(swiglu_reduce_vec_kernel<T>, vgrid, dim3(256), 0, stream, (T*)act, n_tokens, F, ld_out, L));
     FERRUM_CHECK_LAUNCH("swiglu_reduce");
     return 0;
   }
   dim3 grid((F + 255) / 256 > 32 ? 32 : (F + 255) / 256, n_tokens);
-  launch_kernel(swiglu_reduce_kernel, grid, dim3(256), 0, stream, (__nv_bfloat16*)act, F, ld_out, L);
+  FERRUM_DISPATCH_16BIT(dtype, T, launch_kernel(swiglu_reduce_kernel<T>, grid, dim3(256), 0, stream, (T*)act, F, ld_out, L));
   FERRUM_CHECK_LAUNCH("swiglu_reduce");
   return 0;
 }
@@ -721,20 +699,15 @@ FERRUM_API int ferrum_swiglu(const void* gu, void* act, int dtype, int n_tokens,
   FERRUM_CHECK_ARG(n_tokens >= 0 && F > 0 && ld_in >= 2 * F && ld_out >= F, "swiglu: bad sizes T=%d F=%d", n_tokens, F);
   if (n_tokens == 0) return 0;
   FERRUM_CHECK_ARG(n_tokens <= 65535, "swiglu: more than 65535 tokens in one call");
-  if (dtype == FERRUM_BF16 && F % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && ((uintptr_t)gu & 15) == 0 &&
+  if (ferrum_is_16bit(dtype) && F % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && ((uintptr_t)gu & 15) == 0 &&
       ((uintptr_t)act & 15) == 0) {
     dim3 vgrid((F / 8 + 256 * SWIGLU_VEC - 1) / (256 * SWIGLU_VEC), n_tokens);
-    launch_kernel(swiglu_vec_kernel, vgrid, dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, F, ld_in, ld_out);
+    FERRUM_DISPATCH_16BIT(dtype, T, launch_kernel(swiglu_vec_kernel<T>, vgrid, dim3(256), 0, stream, (const T*)gu, (T*)act, F, ld_in, ld_out));
     FERRUM_CHECK_LAUNCH("swiglu");
     return 0;
   }
   dim3 grid((F + 255) / 256 > 64 ? 64 : (F + 255) / 256, n_tokens);
-  if (dtype == FERRUM_F32)
-    launch_kernel(swiglu_kernel<float>, grid, 256, 0, stream, (const float*)gu, (float*)act, F, ld_in, ld_out);
-  else if (dtype == FERRUM_BF16)
-    launch_kernel(swiglu_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, F, ld_in, ld_out);
-  else
-    FERRUM_CHECK_ARG(false, "swiglu: unknown dtype code %d", dtype);
+  FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(swiglu_kernel<T>, grid, 256, 0, stream, (const T*)gu, (T*)act, F, ld_in, ld_out));
   FERRUM_CHECK_LAUNCH("swiglu");
   return 0;
 }

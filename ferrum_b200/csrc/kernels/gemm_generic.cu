@@ -1,11 +1,25 @@
 // out[t, n] = sum_k x[t, k] * w[n, k] on the CUDA cores, float32 accumulation with FFMA.
 //
-// This is the true 32-bit matrix product of the engine (the tensor cores have no
-// float32 input type; TF32 is not 32-bit), and the bfloat16 product for shapes the
-// tcgen05 kernel refuses (rows that are not 16-byte multiples).  Every output element
-// is one accumulator that walks k = 0..K-1 in order, so a token's result does not
-// depend on how many other tokens are in the call.  The reference's product is the same
-// left-to-right dot per output (crates/kernels/src/scalar.rs:221-241).
+// This is the true 32-bit matrix product of the engine (the tensor cores have no float32
+// input type; TF32 is not 32-bit), and the 16-bit product for shapes the tcgen05 kernel
+// refuses (rows that are not 16-byte multiples).  The reference's product is a left-to-right
+// dot per output (crates/kernels/src/scalar.rs:221-241).  Two kernels:
+//
+// Tiled (more than 16 tokens): a CTA computes BM tokens x 128 features; both operands are
+// K-major, so a thread fetches 16 bytes along K of one row, and the 8-wide k-slices go into
+// shared memory transposed ([k][row]), double buffered: the loads of slice i + 1 are in flight
+// while slice i is multiplied.  A thread owns BM/16 x 8 outputs in registers.  Every output is
+// ONE accumulator that walks k = 0..K-1 in order.
+//
+// Skinny (up to 16 tokens: decoding): the product is a stream of the weights.  A CTA owns 8
+// features; its 8 warps cut K into 8 contiguous ranges of whole 128-element blocks (a function
+// of K alone); a lane walks its 4 elements of every block of its warp's range in order; the
+// 32 lanes meet in a fixed shuffle tree and the 8 warps are added in warp order.
+//
+// In both kernels the order of the sum of an output is a function of K only, so a token's
+// result does not depend on how many other tokens are in the call or where it stands among
+// them.  (Between the two kernels the orders differ: a token decoded alone and the same token
+// inside a larger batch agree to rounding, not bitwise.)
 #include "common.cuh"
 
 enum GemmEpilogue : int {
@@ -14,83 +28,220 @@ enum GemmEpilogue : int {
   EPI_RESIDUAL = 2,   // out (float32) += acc        (the residual sum stays float32)
 };
 
-constexpr int BM = 64, BN = 64, BK = 16;
+template <typename T>
+__device__ __forceinline__ void epilogue_store(void* out, size_t o, float v, int epi) {
+  if (epi == EPI_STORE) ((T*)out)[o] = from_f32<T>(v);
+  else if (epi == EPI_STORE_F32) ((float*)out)[o] = v;
+  else ((float*)out)[o] += v;
+}
 
-template <typename T, int EPI>
+// ------------------------------------------------------------------ tiled kernel
+constexpr int TBN = 128, TBK = 8;
+
+// VEC: float32 operands whose rows start on 16-byte boundaries and K a multiple of 4.
+template <typename T, int BM, bool VEC>
 __global__ void __launch_bounds__(256)
-gemm_generic_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ out, int M, int N, int K,
-                    int ldx, int ldw, int ldo) {
-  __shared__ float xs[BK][BM + 1];
-  __shared__ float ws[BK][BN + 1];
+gemm_tiled_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ out, int M, int N, int K, int ldx,
+                  int ldw, int ldo, int epi) {
+  constexpr int TM = BM / 16;               // outputs per thread along the tokens
+  constexpr int A_VECS = BM * TBK / 4;      // 16-byte pieces of a token slice (at most 256)
+  __shared__ __align__(16) float xs[2][TBK][BM];
+  __shared__ __align__(16) float ws[2][TBK][TBN];
   const int tid = threadIdx.x;
-  const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, 4 x 4 outputs each
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  float acc[4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * TBN;
+  // this thread's piece of a slice: row lr, k offset lk (0 or 4)
+  const int lr = tid >> 1, lk = (tid & 1) * 4;
+  const bool a_loader = tid < A_VECS;
+  const T* xrow = x + (size_t)min(m0 + lr, M - 1) * ldx;
+  const T* wrow = w + (size_t)min(n0 + lr, N - 1) * ldw;
+  const bool a_ok = a_loader && m0 + lr < M, b_ok = n0 + lr < N;
 
-  for (int k0 = 0; k0 < K; k0 += BK) {
-    // 64 rows x 16 k per operand = 1024 elements, 4 per thread
+  float acc[TM][8];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int idx = tid + e * 256;
-      const int r = idx >> 4, kk = idx & 15;
-      const int k = k0 + kk;
-      const int m = m0 + r, n = n0 + r;
-      xs[kk][r] = (m < M && k < K) ? to_f32<T>(x[(size_t)m * ldx + k]) : 0.f;
-      ws[kk][r] = (n < N && k < K) ? to_f32<T>(w[(size_t)n * ldw + k]) : 0.f;
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  float ra[4], rb[4];
+  auto fetch = [&](int k0) {
+    const int k = k0 + lk;
+    if (VEC) {
+      const float4 za = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 a = (a_ok && k < K) ? *reinterpret_cast<const float4*>((const float*)xrow + k) : za;
+      const float4 b = (b_ok && k < K) ? *reinterpret_cast<const float4*>((const float*)wrow + k) : za;
+      ra[0] = a.x; ra[1] = a.y; ra[2] = a.z; ra[3] = a.w;
+      rb[0] = b.x; rb[1] = b.y; rb[2] = b.z; rb[3] = b.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ra[i] = (a_ok && k + i < K) ? to_f32<T>(xrow[k + i]) : 0.f;
+        rb[i] = (b_ok && k + i < K) ? to_f32<T>(wrow[k + i]) : 0.f;
+      }
     }
-    __syncthreads();
+  };
+  auto stash = [&](int buf) {
 #pragma unroll
-    for (int kk = 0; kk < BK; ++kk) {
-      float a[4], b[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = xs[kk][ty * 4 + i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = ws[kk][tx * 4 + j];
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    for (int i = 0; i < 4; ++i) {
+      if (a_loader) xs[buf][lk + i][lr] = ra[i];
+      ws[buf][lk + i][lr] = rb[i];
     }
-    __syncthreads();
+  };
+
+  const int n_slices = (K + TBK - 1) / TBK;
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  for (int s = 0; s < n_slices; ++s) {
+    const int buf = s & 1;
+    if (s + 1 < n_slices) fetch((s + 1) * TBK);   // in flight during the arithmetic below
+#pragma unroll
+    for (int kk = 0; kk < TBK; ++kk) {
+      float a[TM], b[8];
+      if (TM >= 4) {
+#pragma unroll
+        for (int g = 0; g < TM / 4; ++g) {
+          const float4 v = *reinterpret_cast<const float4*>(&xs[buf][kk][g * 64 + ty * 4]);
+          a[g * 4] = v.x; a[g * 4 + 1] = v.y; a[g * 4 + 2] = v.z; a[g * 4 + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < TM; ++i) a[i] = xs[buf][kk][ty * TM + i];
+      }
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const float4 v = *reinterpret_cast<const float4*>(&ws[buf][kk][g * 64 + tx * 4]);
+        b[g * 4] = v.x; b[g * 4 + 1] = v.y; b[g * 4 + 2] = v.z; b[g * 4 + 3] = v.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (s + 1 < n_slices) {
+      stash(buf ^ 1);      // the other buffer: nobody reads it during this slice
+      __syncthreads();
+    }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int m = m0 + ty * 4 + i;
+  for (int i = 0; i < TM; ++i) {
+    const int m = m0 + (TM >= 4 ? (i / 4) * 64 + ty * 4 + (i & 3) : ty * TM + i);
     if (m >= M) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = n0 + tx * 4 + j;
-      if (n >= N) continue;
-      const size_t o = (size_t)m * ldo + n;
-      if (EPI == EPI_STORE) ((T*)out)[o] = from_f32<T>(acc[i][j]);
-      else if (EPI == EPI_STORE_F32) ((float*)out)[o] = acc[i][j];
-      else ((float*)out)[o] += acc[i][j];
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 + (j / 4) * 64 + tx * 4 + (j & 3);
+      if (n < N) epilogue_store<T>(out, (size_t)m * ldo + n, acc[i][j], epi);
     }
+  }
+}
+
+// ------------------------------------------------------------------ skinny kernel
+constexpr int SK_FEAT = 8;     // features per CTA
+constexpr int SK_WARPS = 8;    // warps per CTA: K ranges
+constexpr int SK_TOK = 8;      // tokens per pass
+constexpr int SK_MAX_TOKENS = 16;
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(SK_WARPS * 32, 2)
+gemm_skinny_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ out, int M, int N, int K, int ldx,
+                   int ldw, int ldo, int epi) {
+  __shared__ float part[SK_WARPS][SK_FEAT][SK_TOK];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * SK_FEAT;
+  const int n_blocks = (K + 127) / 128;
+  const int b_begin = n_blocks * warp / SK_WARPS, b_end = n_blocks * (warp + 1) / SK_WARPS;
+  const T* wr[SK_FEAT];
+#pragma unroll
+  for (int f = 0; f < SK_FEAT; ++f) wr[f] = w + (size_t)min(n0 + f, N - 1) * ldw;
+
+  for (int m0 = 0; m0 < M; m0 += SK_TOK) {
+    float acc[SK_FEAT][SK_TOK];
+#pragma unroll
+    for (int f = 0; f < SK_FEAT; ++f)
+#pragma unroll
+      for (int m = 0; m < SK_TOK; ++m) acc[f][m] = 0.f;
+#pragma unroll 1
+    for (int b = b_begin; b < b_end; ++b) {
+      const int k = b * 128 + lane * 4;
+      float wv[SK_FEAT][4];
+      if (VEC) {
+#pragma unroll
+        for (int f = 0; f < SK_FEAT; ++f) {
+          const float4 v = k < K ? __ldcs(reinterpret_cast<const float4*>((const float*)wr[f] + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          wv[f][0] = v.x; wv[f][1] = v.y; wv[f][2] = v.z; wv[f][3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int f = 0; f < SK_FEAT; ++f)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) wv[f][i] = k + i < K ? to_f32<T>(wr[f][k + i]) : 0.f;
+      }
+#pragma unroll
+      for (int m = 0; m < SK_TOK; ++m) {
+        float xv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (m0 + m < M) {
+          const T* xr = x + (size_t)(m0 + m) * ldx;
+          if (VEC) {
+            if (k < K) {
+              const float4 v = *reinterpret_cast<const float4*>((const float*)xr + k);
+              xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = k + i < K ? to_f32<T>(xr[k + i]) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int f = 0; f < SK_FEAT; ++f)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[f][m] = fmaf(wv[f][i], xv[i], acc[f][m]);
+      }
+    }
+#pragma unroll
+    for (int f = 0; f < SK_FEAT; ++f)
+#pragma unroll
+      for (int m = 0; m < SK_TOK; ++m) {
+        const float v = warp_sum(acc[f][m]);
+        if (lane == 0) part[warp][f][m] = v;
+      }
+    __syncthreads();
+    if (threadIdx.x < SK_FEAT * SK_TOK) {
+      const int f = threadIdx.x % SK_FEAT, m = threadIdx.x / SK_FEAT;
+      float v = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < SK_WARPS; ++wi) v += part[wi][f][m];
+      if (n0 + f < N && m0 + m < M) epilogue_store<T>(out, (size_t)(m0 + m) * ldo + n0 + f, v, epi);
+    }
+    __syncthreads();
   }
 }
 
 template <typename T>
 static int launch_generic(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo,
                           int epilogue, cudaStream_t stream) {
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  FERRUM_CHECK_ARG(grid.y <= 65535, "gemm: too many row tiles (%u)", grid.y);
-  switch (epilogue) {
-    case EPI_STORE:
-      gemm_generic_kernel<T, EPI_STORE><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, out, M, N, K, ldx, ldw, ldo);
-      break;
-    case EPI_STORE_F32:
-      gemm_generic_kernel<T, EPI_STORE_F32><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, out, M, N, K, ldx, ldw, ldo);
-      break;
-    case EPI_RESIDUAL:
-      gemm_generic_kernel<T, EPI_RESIDUAL><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, out, M, N, K, ldx, ldw, ldo);
-      break;
-    default:
-      FERRUM_CHECK_ARG(false, "gemm: unknown epilogue %d", epilogue);
+  FERRUM_CHECK_ARG(epilogue >= EPI_STORE && epilogue <= EPI_RESIDUAL, "gemm: unknown epilogue %d", epilogue);
+  const bool vec = sizeof(T) == 4 && K % 4 == 0 && ldx % 4 == 0 && ldw % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+  const T* xp = (const T*)x;
+  const T* wp = (const T*)w;
+  if (M <= SK_MAX_TOKENS) {
+    const dim3 grid((N + SK_FEAT - 1) / SK_FEAT);
+    if (vec) gemm_skinny_kernel<T, true><<<grid, SK_WARPS * 32, 0, stream>>>(xp, wp, out, M, N, K, ldx, ldw, ldo, epilogue);
+    else gemm_skinny_kernel<T, false><<<grid, SK_WARPS * 32, 0, stream>>>(xp, wp, out, M, N, K, ldx, ldw, ldo, epilogue);
+    FERRUM_CHECK_LAUNCH("gemm_generic");
+    return 0;
   }
+  const int bm = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  const dim3 grid((N + TBN - 1) / TBN, (M + bm - 1) / bm);
+  FERRUM_CHECK_ARG(grid.y <= 65535, "gemm: too many row tiles (%u)", grid.y);
+#define TILED(BM_)                                                                                                        \
+  do {                                                                                                                    \
+    if (vec) gemm_tiled_kernel<T, BM_, true><<<grid, 256, 0, stream>>>(xp, wp, out, M, N, K, ldx, ldw, ldo, epilogue);   \
+    else gemm_tiled_kernel<T, BM_, false><<<grid, 256, 0, stream>>>(xp, wp, out, M, N, K, ldx, ldw, ldo, epilogue);      \
+  } while (0)
+  if (bm == 32) TILED(32);
+  else if (bm == 64) TILED(64);
+  else TILED(128);
+#undef TILED
   FERRUM_CHECK_LAUNCH("gemm_generic");
   return 0;
 }
@@ -100,7 +251,6 @@ FERRUM_API int ferrum_gemm_generic(const void* x, const void* w, void* out, int 
   FERRUM_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   FERRUM_CHECK_ARG(ldx >= K && ldw >= K && ldo >= N, "gemm: a row stride is shorter than its row");
   if (M == 0) return 0;
-  if (dtype == FERRUM_F32) return launch_generic<float>(x, w, out, M, N, K, ldx, ldw, ldo, epilogue, stream);
-  if (dtype == FERRUM_BF16) return launch_generic<__nv_bfloat16>(x, w, out, M, N, K, ldx, ldw, ldo, epilogue, stream);
-  FERRUM_CHECK_ARG(false, "gemm: unknown dtype code %d", dtype);
+  FERRUM_DISPATCH_DTYPE(dtype, T, return launch_generic<T>(x, w, out, M, N, K, ldx, ldw, ldo, epilogue, stream));
+  return 0;
 }

@@ -1,4 +1,6 @@
-// bfloat16 matrix product on the tcgen05 tensor cores: out[t, n] = sum_k x[t, k] * w[n, k].
+// 16-bit (bfloat16 or float16) matrix product on the tcgen05 tensor cores: out[t, n] = sum_k x[t, k] * w[n, k],
+// float32 accumulation.  The two types differ in the instruction descriptor's operand format and in
+// how the epilogue rounds; everything else (tensor maps, tiles, schedules) moves 16-bit elements.
 //
 // Orientation: the weight rows are the M side of the instruction (128 rows of W per tile,
 // one row per TMEM lane) and the tokens are the N side (BT columns, 16..256).  The same
@@ -35,10 +37,10 @@
 using namespace sm100;
 
 enum TcEpilogue : int {
-  TC_STORE_BF16 = 0,  // out bf16 [M, ldo] = acc
+  TC_STORE_BF16 = 0,  // out 16-bit [M, ldo] = acc   (the operands' type)
   TC_STORE_F32 = 1,   // out f32  [M, ldo] = acc
   TC_RESIDUAL = 2,    // out f32  [M, ldo] += acc
-  TC_SWIGLU = 3,      // out bf16 [M, ldo] = silu(acc0) * acc1   (DUAL only)
+  TC_SWIGLU = 3,      // out 16-bit [M, ldo] = silu(acc0) * acc1   (DUAL only)
 };
 
 struct TcParams {
@@ -54,6 +56,9 @@ struct TcParams {
   int stream_weights;  // 1: every weight tile is read once in this launch: its L2 lines are the first to go
   int gated;           // 1 (pair kernel): weight rows come interleaved (gate i, up i, gate i + 1, ...), N counts these
                        // rows, and the epilogue writes silu(gate) * up for N / 2 features
+  int half;            // 0: operands and 16-bit outputs are bfloat16; 1: float16
+  long long wait_cycles;  // limit of every mbarrier wait (0: the default of about a second); tests shorten it
+  int drop_loads;      // test hook: the producer requests no tile at all, so that the waits for them run out
 };
 
 constexpr int TILE_N = 128;  // weight rows per tile (the instruction's M)
@@ -87,10 +92,11 @@ __device__ __forceinline__ void tc_apply16(const TcParams& p, int t_base, int n,
   const size_t ld = (size_t)p.ldo;
   switch (p.epilogue) {
     case TC_STORE_BF16: {
-      __nv_bfloat16* out = (__nv_bfloat16*)p.out + o;
+      uint16_t* out = (uint16_t*)p.out + o;
+      const bool half = p.half != 0;
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (j < valid) out[j * ld] = __float2bfloat16_rn(a0[j]);
+        if (j < valid) out[j * ld] = bits16(a0[j], half);
       break;
     }
     case TC_STORE_F32: {
@@ -111,10 +117,11 @@ __device__ __forceinline__ void tc_apply16(const TcParams& p, int t_base, int n,
       break;
     }
     case TC_SWIGLU: {
-      __nv_bfloat16* out = (__nv_bfloat16*)p.out + o;
+      uint16_t* out = (uint16_t*)p.out + o;
+      const bool half = p.half != 0;
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (j < valid) out[j * ld] = __float2bfloat16_rn(a0[j] / (1.0f + __expf(-a0[j])) * a1[j]);
+        if (j < valid) out[j * ld] = bits16(a0[j] / (1.0f + __expf(-a0[j])) * a1[j], half);
       break;
     }
   }
@@ -177,10 +184,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abort_p = &abort_flag;
+  const long long wait_limit = p.wait_cycles > 0 ? p.wait_cycles : WAIT_LIMIT_CYCLES;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (lane == 0 && p.drop_loads) {
+      // (test hook) nothing is requested, nothing will be in flight: the other roles' waits run out
+      pdl_wait();
+      pdl_launch();
+    } else if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
       long long tile = u_begin / nkb;
@@ -222,7 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       s = pre % STAGES;
       phase = pre == STAGES ? 1 : 0;
       for (long long u = u_begin + pre; u < u_end; ++u) {
-        if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p)) {
+        if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p, wait_limit)) {
           abort_flag = 1;
           atomicExch(p.err, 10);
           break;
@@ -246,7 +258,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(TILE_N, BT);
+      const uint32_t idesc = umma_idesc_16bit(TILE_N, BT, p.half != 0);
       int s = 0;
       uint32_t phase = 0;
       int seg = 0;
@@ -256,7 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const long long tile = u / nkb;
         const long long seg_end = min(u_end, (tile + 1) * (long long)nkb);
         const int buf = seg & 1, use = seg >> 1;
-        if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, abort_p)) {
+        if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, abort_p, wait_limit)) {
           abort_flag = 1;
           atomicExch(p.err, 13);
           break;
@@ -265,7 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint32_t d0 = tmem_base + buf * Cfg::ACC_COLS;
         bool first = true;
         for (; u < seg_end; ++u) {
-          if (!mbar_wait(full_bar(s), phase, abort_p)) {
+          if (!mbar_wait(full_bar(s), phase, abort_p, wait_limit)) {
             abort_flag = 1;
             atomicExch(p.err, 11);
             ok = false;
@@ -310,7 +322,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       const long long seg_end = min(u_end, (tile + 1) * (long long)nkb);
       const bool whole = kb0 == 0 && seg_end == (tile + 1) * (long long)nkb;
       const int buf = seg & 1, use = seg >> 1;
-      bool ok = mbar_wait(acc_full_bar(buf), use & 1, abort_p);
+      bool ok = mbar_wait(acc_full_bar(buf), use & 1, abort_p, wait_limit);
       if (!ok) abort_flag = 1;
       asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps agree on going on
       if (abort_flag) {
@@ -565,6 +577,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abort_p = &abort_flag;
+  const long long wait_limit = p.wait_cycles > 0 ? p.wait_cycles : WAIT_LIMIT_CYCLES;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -582,7 +595,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const int n0 = n_idx * 2 * TILE_N + (int)rank * TILE_N;
         const int t0 = t_idx * PAIR_BT + (int)rank * (PAIR_BT / 2);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p)) {
+          if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p, wait_limit)) {
             abort_flag = 1;
             atomicExch(p.err, 10);
             ok = false;
@@ -604,7 +617,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = umma_idesc_bf16(2 * TILE_N, PAIR_BT);
+      const uint32_t idesc = umma_idesc_16bit(2 * TILE_N, PAIR_BT, p.half != 0);
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -612,7 +625,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       int kb0, kb1;
       for (int seg = 0; ok && sched.segment(seg, tile, kb0, kb1); ++seg) {
         const int buf = seg & 1, use = seg >> 1;
-        if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, abort_p)) {
+        if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, abort_p, wait_limit)) {
           abort_flag = 1;
           atomicExch(p.err, 13);
           break;
@@ -621,7 +634,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const uint32_t d0 = tmem_base + buf * ACC_COLS;
         bool first = true;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(full_bar(s), phase, abort_p)) {
+          if (!mbar_wait(full_bar(s), phase, abort_p, wait_limit)) {
             abort_flag = 1;
             atomicExch(p.err, 11);
             ok = false;
@@ -685,9 +698,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 #pragma unroll
           for (int j = 0; j < 32; ++j) st[j * TILE_N + n_local] = v[j];
         } else {
-          __nv_bfloat16* st = (__nv_bfloat16*)stage;
+          uint16_t* st = (uint16_t*)stage;
+          const bool half = p.half != 0;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) st[j * TILE_N + n_local] = __float2bfloat16_rn(v[j]);
+          for (int j = 0; j < 32; ++j) st[j * TILE_N + n_local] = bits16(v[j], half);
         }
         stage_send(stage, &tmap_out, p.epilogue == TC_RESIDUAL, n0_cta, t0 + c0);
       } else if (n0_cta + n_local < p.N) {
@@ -707,12 +721,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     auto emit32_gated = [&](int t0, int c0, int n0_cta, const float (&v)[32]) {
       const int odd = lane & 1;
       uint8_t* stage = stage_acquire();
-      __nv_bfloat16* st = (__nv_bfloat16*)stage + (odd * 16) * (TILE_N / 2) + (n_local >> 1);
+      uint16_t* st = (uint16_t*)stage + (odd * 16) * (TILE_N / 2) + (n_local >> 1);
+      const bool half = p.half != 0;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float theirs = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[16 + j], 1);
         const float g = odd ? theirs : v[j], up = odd ? v[16 + j] : theirs;
-        st[j * (TILE_N / 2)] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * up);
+        st[j * (TILE_N / 2)] = bits16(g / (1.0f + __expf(-g)) * up, half);
       }
       stage_send(stage, &tmap_out, false, n0_cta >> 1, t0 + c0);
     };
@@ -722,7 +737,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     for (int seg = 0; sched.segment(seg, tile, kb0, kb1); ++seg) {
       const bool whole = kb0 == 0 && kb1 == nkb;
       const int buf = seg & 1, use = seg >> 1;
-      bool ok = mbar_wait(acc_full_bar(buf), use & 1, abort_p);
+      bool ok = mbar_wait(acc_full_bar(buf), use & 1, abort_p, wait_limit);
       if (!ok) abort_flag = 1;
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (abort_flag) {
@@ -824,7 +839,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     bulk_load(dst + c * TILE_N * 4, src + (size_t)c * TILE_N, 32 * TILE_N * 4, fetch_bar);
                 }
               }
-              fine = mbar_wait(fetch_bar, fetch_phase, abort_p);
+              fine = mbar_wait(fetch_bar, fetch_phase, abort_p, wait_limit);
               fetch_phase ^= 1;
               if (!fine) abort_flag = 1;
               asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -923,9 +938,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             if (p.gated) {  // four neighbouring rows are two (gate, up) pairs
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
-                const __nv_bfloat162 o2 = __floats2bfloat162_rn(acc[k].x / (1.0f + __expf(-acc[k].x)) * acc[k].y,
-                                                                acc[k].z / (1.0f + __expf(-acc[k].z)) * acc[k].w);
-                *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)stage + (cg + k) * (TILE_N / 2) + (q4 >> 1)) = o2;
+                const uint32_t o2 = pack2_bits(acc[k].x / (1.0f + __expf(-acc[k].x)) * acc[k].y,
+                                               acc[k].z / (1.0f + __expf(-acc[k].z)) * acc[k].w, p.half != 0);
+                *reinterpret_cast<uint32_t*>((uint16_t*)stage + (cg + k) * (TILE_N / 2) + (q4 >> 1)) = o2;
               }
               stage_send(stage, &tmap_out, false, n0 >> 1, t0 + c0);
               continue;
@@ -936,11 +951,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             } else {
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
-                __nv_bfloat162 lo = __floats2bfloat162_rn(acc[k].x, acc[k].y), hi = __floats2bfloat162_rn(acc[k].z, acc[k].w);
                 uint2 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&lo);
-                pk.y = *reinterpret_cast<uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>((__nv_bfloat16*)stage + (cg + k) * TILE_N + q4) = pk;
+                pk.x = pack2_bits(acc[k].x, acc[k].y, p.half != 0);
+                pk.y = pack2_bits(acc[k].z, acc[k].w, p.half != 0);
+                *reinterpret_cast<uint2*>((uint16_t*)stage + (cg + k) * TILE_N + q4) = pk;
               }
             }
             stage_send(stage, &tmap_out, p.epilogue == TC_RESIDUAL, n0, t0 + c0);
@@ -1080,6 +1094,20 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
   return 0;
 }
 
+// Test hooks (see ferrum_gemm_tc_test_hooks): a shorter limit for every wait of the kernels, and a
+// producer that requests nothing.
+static long long g_wait_cycles = 0;
+static int g_drop_loads = 0;
+// wait_cycles > 0 shortens every bounded wait of the tensor-core product kernels to that many
+// clock cycles (0: the default, about a second).  drop_loads = 1 makes the single-CTA kernel's
+// producer request no tile, so that the waits for them run out: the kernel then raises an error
+// code (10 to 13), frees its tensor memory and returns, and the context stays usable.  For
+// tests of that path only; both settings stay until they are set back.
+FERRUM_API void ferrum_gemm_tc_test_hooks(long long wait_cycles, int drop_loads) {
+  g_wait_cycles = wait_cycles > 0 ? wait_cycles : 0;
+  g_drop_loads = drop_loads != 0;
+}
+
 static bool g_pair_kernel = true;
 // The CTA-pair kernel can be switched off (every shape then runs on the single-CTA kernel).
 FERRUM_API void ferrum_set_gemm_pair_kernel(int on) { g_pair_kernel = on != 0; }
@@ -1148,14 +1176,16 @@ FERRUM_API long long ferrum_gemm_tc_workspace(int M, int N, int K, int dual, int
   return 2LL * n_ctas * (long long)(bt * (dual ? 2 : 1)) * TILE_N;
 }
 
-// x [M, K] bf16 (row stride ldx), w [w_rows, K] bf16 (row stride ldw), N output features.
+// x [M, K] (row stride ldx) and w [w_rows, K] (row stride ldw) of the 16-bit type `dtype`
+// (FERRUM_BF16 or FERRUM_F16), N output features.
 // dual_offset > 0 selects the two-product kernel with the SwiGLU epilogue: the second weight
 // tile starts at row dual_offset + n.  n_ctas = 0 means one CTA per SM.
-FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo,
+FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int dtype, int M, int N, int K, int ldx, int ldw, int ldo,
                               int w_rows, int epilogue, int dual_offset, int n_ctas, float* workspace,
                               long long workspace_floats, int* counters, int n_counters, int* err_flag,
                               cudaStream_t stream) {
   FERRUM_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+  FERRUM_CHECK_ARG(ferrum_is_16bit(dtype), "gemm_tc: dtype code %d is not a 16-bit type", dtype);
   FERRUM_CHECK_ARG(err_flag != nullptr, "gemm_tc: the error flag is required");
   if (M == 0) return 0;
   FERRUM_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tc: K=%d and the row strides (%d, %d) must be multiples of 8 "
@@ -1178,6 +1208,9 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int M, in
     if (n_ctas > units) n_ctas = (int)units;
   }
   TcParams p{out, workspace, counters, err_flag, M, N, K, ldo, epilogue, dual_offset, 0};
+  p.half = dtype == FERRUM_F16;
+  p.wait_cycles = g_wait_cycles;
+  p.drop_loads = g_drop_loads;
   p.stream_weights = (M + bt - 1) / bt == 1;  // one token tile: no weight tile is read twice
   CUtensorMap mw, mx;
   if (dual && M > TILE_N && g_pair_kernel && n_ctas >= 2 && ((uintptr_t)out & 15) == 0 && ldo % 8 == 0) {
@@ -1283,10 +1316,11 @@ FERRUM_API int ferrum_gemm_tc_can_defer(int M, int N, int K, int dual, int n_cta
 }
 
 // layout[0..3] = k-blocks per tile, tiles, CTAs, columns per partial: what partial_sum() needs.
-FERRUM_API int ferrum_gemm_tc_deferred(const void* x, const void* w, int M, int N, int K, int ldx, int ldw, int w_rows,
+FERRUM_API int ferrum_gemm_tc_deferred(const void* x, const void* w, int dtype, int M, int N, int K, int ldx, int ldw, int w_rows,
                                        int dual_offset, int n_ctas, float* workspace, long long workspace_floats,
                                        int* layout, int* err_flag, cudaStream_t stream) {
   FERRUM_CHECK_ARG(M > 0 && N > 0 && K > 0 && err_flag && layout, "gemm_tc_deferred: bad arguments");
+  FERRUM_CHECK_ARG(ferrum_is_16bit(dtype), "gemm_tc_deferred: dtype code %d is not a 16-bit type", dtype);
   FERRUM_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0,
                    "gemm_tc_deferred: operands must have 16-byte rows and alignment");
   FERRUM_CHECK_ARG(ldx >= K && ldw >= K, "gemm_tc_deferred: a row stride is shorter than its row");
@@ -1310,6 +1344,8 @@ FERRUM_API int ferrum_gemm_tc_deferred(const void* x, const void* w, int M, int 
   if (int r = get_tensor_map(w, w_rows, K, ldw, TILE_N, &mw)) return r;
   if (int r = get_tensor_map(x, M, K, ldx, bt, &mx)) return r;
   TcParams p{nullptr, workspace, nullptr, err_flag, M, N, K, 0, dual ? TC_SWIGLU : TC_STORE_F32, dual_offset, 1};
+  p.half = dtype == FERRUM_F16;
+  p.wait_cycles = g_wait_cycles;
   p.stream_weights = 1;  // deferred mode has one token tile: no weight tile is read twice
   switch (bt) {
     case 16: return dual ? launch_tc<16, true>(mw, mx, p, n_ctas, stream) : launch_tc<16, false>(mw, mx, p, n_ctas, stream);

@@ -43,14 +43,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Waits for the phase with the given parity to complete; false after ~1.5e9 cycles
 // (about a second), or at once when *abort is already set by another role.
 constexpr long long WAIT_LIMIT_CYCLES = 1500000000LL;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, long long limit = WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    if (clock64() - t0 > limit) return false;
   }
 }
 
@@ -128,16 +128,20 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                       // layout: SWIZZLE_128B
   return d;
 }
-// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M x N tile.
-__device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N) {
+// Instruction descriptor of kind::f16: 16-bit x 16-bit -> float32, both operands K-major, M x N
+// tile.  The operand format field is 0 for float16 and 1 for bfloat16.
+__device__ __forceinline__ uint32_t umma_idesc_16bit(int M, int N, bool half) {
   uint32_t d = 0;
   d |= 1u << 4;                     // D format: F32
-  d |= 1u << 7;                     // A format: BF16
-  d |= 1u << 10;                    // B format: BF16
+  if (!half) {
+    d |= 1u << 7;                   // A format: BF16
+    d |= 1u << 10;                  // B format: BF16
+  }
   d |= (uint32_t)(N >> 3) << 17;    // N / 8
   d |= (uint32_t)(M >> 4) << 24;    // M / 16
   return d;
 }
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N) { return umma_idesc_16bit(M, N, false); }
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"

@@ -25,7 +25,8 @@ from ..weights import init_random, load_weights
 from .batch import StepEntry
 from .runner import ModelRunner
 
-DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16, "fp16": torch.float16,
+          "f16": torch.float16, "half": torch.float16, "float32": torch.float32, "fp32": torch.float32,
           "f32": torch.float32}
 FINISH_REASONS = {0: "stop", 1: "length", 2: "cancelled"}
 
@@ -34,7 +35,7 @@ def parse_dtype(name):
     try:
         return DTYPES[str(name).lower()]
     except KeyError:
-        raise ConfigError(f"unsupported dtype {name!r}; choose bfloat16 or float32") from None
+        raise ConfigError(f"unsupported dtype {name!r}; choose bfloat16, float16 or float32") from None
 
 
 def load_model(path, dtype="bfloat16", device="cuda", max_positions=None, random_seed=None):

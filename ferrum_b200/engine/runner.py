@@ -22,7 +22,12 @@ _DEVICE_ERRORS = {
     3: "a position is beyond the block table", 4: "a token's page is missing from the block table",
     5: "attention reached a position whose page is missing", 6: "a row of logits is all NaN",
     10: "tensor-core product: the producer timed out", 11: "tensor-core product: the matrix unit timed out",
-    12: "tensor-core product: the epilogue timed out",
+    12: "tensor-core product: the epilogue timed out", 13: "tensor-core product: the accumulator was not released in time",
+    14: "tensor-core product: partial tiles did not arrive in time",
+    20: "tensor-core attention: the producer timed out", 22: "tensor-core attention: the queries did not arrive in time",
+    23: "tensor-core attention: keys or values did not arrive in time", 24: "tensor-core attention: the weights were not ready in time",
+    25: "tensor-core attention: the scores were not ready in time", 26: "tensor-core attention: the output was not ready in time",
+    27: "tensor-core attention: a product did not finish in time", 28: "tensor-core attention: the last values did not arrive in time",
 }
 
 
@@ -85,11 +90,11 @@ class ModelRunner:
             raise InvalidRequest("tokens on the device stand for one token per entry")
         self.ctx.fill(entries, mgr if self.cache.n_groups else [], keep_token_ids=bool(tokens_on_device))
         logits = self._run_decode() if decode_only else self.model.forward(self.ctx, self.cache)
+        if check:
+            self.check_device_errors()       # raises before anything is committed: the lengths stay as they were
         if commit:
             for e in entries:
                 mgr.commit(e.slot, e.pos0 + len(e.tokens))
-        if check:
-            self.check_device_errors()
         return logits[:self.ctx.n_want] if logits is not None else None
 
     def _generation(self):

@@ -16,15 +16,16 @@ import torch
 from ..errors import KernelError
 from . import build
 
-F32, BF16 = 0, 1
-_DT = {torch.float32: F32, torch.bfloat16: BF16}
+F32, BF16, F16 = 0, 1, 2
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+SIXTEEN_BIT = (torch.bfloat16, torch.float16)       # the tensor-core kernels take either
 
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL = 0, 1, 2                       # generic product
 TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05 product
 
 _lib = None
 _lock = threading.Lock()
-ABI = 5
+ABI = 6
 
 
 def lib():
@@ -56,6 +57,14 @@ def require_cuda(device=None):
 def sm_count():
     """Multiprocessors of the current CUDA device, as the kernels' own grids count them."""
     return int(lib().ferrum_gemm_tc_default_ctas())
+
+
+def gemm_tc_test_hooks(wait_cycles=0, drop_loads=False):
+    """For tests of the failure path only: shorten every bounded wait of the tensor-core product
+    kernels to `wait_cycles` clock cycles (0: the default of about a second), and make the
+    producer of the single-CTA kernel request nothing, so that the waits run out and the kernel
+    leaves with an error code.  Call again without arguments to restore."""
+    lib().ferrum_gemm_tc_test_hooks(c_longlong(int(wait_cycles)), c_int(1 if drop_loads else 0))
 
 
 def set_dependent_launch(on: bool):
@@ -97,6 +106,13 @@ def _need(t, dtype, name, ndim=None):
         raise KernelError(f"{name} must have {ndim} dimensions, found {t.dim()}")
     if t.dim() and t.stride(-1) != 1 and t.shape[-1] > 1:
         raise KernelError(f"{name} must be contiguous in its last dimension")
+
+
+def _need16(t, name, ndim=None, like=None):
+    """A CUDA tensor of a 16-bit float type (the same as `like`'s when given)."""
+    _need(t, like.dtype if like is not None else None, name, ndim)
+    if t.dtype not in SIXTEEN_BIT:
+        raise KernelError(f"{name} must be bfloat16 or float16, found {t.dtype}")
 
 
 def dtype_code(dtype):
@@ -157,8 +173,8 @@ def residual_reduce(h, n_rows, partials):
 
 def swiglu_reduce(act, n_tokens, F, partials):
     """act[t, f] = silu(gate) * up from a deferred two-product launch."""
-    _need(act, torch.bfloat16, "act", 2)
-    _check(lib().ferrum_swiglu_reduce(_ptr(act), c_int(n_tokens), c_int(F), c_int(act.stride(0)), _ptr(partials.workspace),
+    _need16(act, "act", 2)
+    _check(lib().ferrum_swiglu_reduce(_ptr(act), dtype_code(act.dtype), c_int(n_tokens), c_int(F), c_int(act.stride(0)), _ptr(partials.workspace),
                                       partials._c, _stream()), "swiglu_reduce")
 
 
@@ -169,14 +185,14 @@ def gemm_tc_can_defer(M, N, K, dual):
 def gemm_tc_deferred(x, w, err, workspace, M=None, N=None, dual_offset=0, n_ctas=0):
     """The tensor-core product without its final reduction: returns `Partials` for the kernel
     that consumes the product.  Only for shapes that `gemm_tc_can_defer` accepts."""
-    _need(x, torch.bfloat16, "x", 2); _need(w, torch.bfloat16, "w", 2); _need(workspace, torch.float32, "workspace")
+    _need16(x, "x", 2); _need16(w, "w", 2, like=x); _need(workspace, torch.float32, "workspace")
     M = x.shape[0] if M is None else M
     K = w.shape[1]
     N = (w.shape[0] - dual_offset) if N is None else N
     if x.shape[1] != K or x.shape[0] < M:
         raise KernelError(f"gemm_tc_deferred: shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)}")
     layout = (c_int * 4)()
-    _check(lib().ferrum_gemm_tc_deferred(_ptr(x), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
+    _check(lib().ferrum_gemm_tc_deferred(_ptr(x), _ptr(w), dtype_code(x.dtype), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
                                          c_int(w.stride(0)), c_int(w.shape[0]), c_int(dual_offset), c_int(n_ctas),
                                          _ptr(workspace), c_longlong(workspace.numel()), layout, _ptr(err), _stream()),
            "gemm_tc_deferred")
@@ -199,8 +215,8 @@ def gemm_generic(x, w, out, epilogue, M=None):
 
 
 def gemm_tc_supported(x, w):
-    """True when the tcgen05 kernel takes these operands (bfloat16, 16-byte rows)."""
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+    """True when the tcgen05 kernel takes these operands (one 16-bit type, 16-byte rows)."""
+    return (x.dtype in SIXTEEN_BIT and w.dtype == x.dtype and x.shape[1] % 8 == 0
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
@@ -217,23 +233,23 @@ def gemm_tc_workspace(M, N, K, dual, n_ctas=0):
 
 
 def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_offset=0, n_ctas=0):
-    """bfloat16 tensor-core product; see csrc/kernels/gemm_tc.cu.  `N` is the number of
+    """16-bit (bfloat16 or float16) tensor-core product; see csrc/kernels/gemm_tc.cu.  `N` is the number of
     output features (rows of w used per product); with dual_offset > 0 rows dual_offset + n
     feed the second product of the SwiGLU epilogue.  `workspace` (float32) and `counters`
     (int32, all zero) are scratch for tiles that several CTAs share; n_ctas = 0 means one CTA
     per SM."""
-    _need(x, torch.bfloat16, "x", 2); _need(w, torch.bfloat16, "w", 2); _need(out, None, "out", 2)
+    _need16(x, "x", 2); _need16(w, "w", 2, like=x); _need(out, None, "out", 2)
     M = x.shape[0] if M is None else M
     K = w.shape[1]
     N = (w.shape[0] - dual_offset) if N is None else N
     if x.shape[1] != K or out.shape[1] < N or out.shape[0] < M or x.shape[0] < M:
         raise KernelError(f"gemm_tc: shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
-    want = torch.bfloat16 if epilogue in (TC_STORE_BF16, TC_SWIGLU) else torch.float32
+    want = x.dtype if epilogue in (TC_STORE_BF16, TC_SWIGLU) else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm_tc: out must be {want} for epilogue {epilogue}")
     _need(workspace, torch.float32, "workspace")
     _need(counters, torch.int32, "counters")
-    _check(lib().ferrum_gemm_tc(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
+    _check(lib().ferrum_gemm_tc(_ptr(x), _ptr(w), _ptr(out), dtype_code(x.dtype), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
                                 c_int(w.stride(0)), c_int(out.stride(0)), c_int(w.shape[0]), c_int(epilogue),
                                 c_int(dual_offset), c_int(n_ctas), _ptr(workspace), c_longlong(workspace.numel()),
                                 _ptr(counters), c_int(counters.numel()), _ptr(err), _stream()), "gemm_tc")
@@ -281,29 +297,30 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
 
 def attention_flash_supported(dtype, D, page_stride=0):
     """True when the tensor-core attention kernel is built for this dtype and head size."""
-    return dtype == torch.bfloat16 and bool(lib().ferrum_attention_flash_supported(c_int(D), c_int(16)))
+    return dtype in SIXTEEN_BIT and bool(lib().ferrum_attention_flash_supported(c_int(D), c_int(16)))
 
 
 def attention_flash(q, out, kv_plane, page_stride, page_size, block_table, q_start, pos0, work, n_work, part_o,
-                    part_ml, Hq, Hkv, D, scale, window, bm, cta_items=None, n_ctas=0, trigger_early=False):
+                    part_ml, Hq, Hkv, D, scale, window, bm, err, cta_items=None, n_ctas=0, trigger_early=False):
     """Tensor-core attention over the work items of one row-tile class (bm 16 or 64).
     trigger_early: the kernels that follow in the stream may start while this one runs."""
-    _need(q, torch.bfloat16, "q", 2); _need(out, torch.bfloat16, "out", 2); _need(kv_plane, torch.bfloat16, "kv_plane")
+    _need16(q, "q", 2); _need16(out, "out", 2, like=q); _need16(kv_plane, "kv_plane", like=q)
     _need(block_table, torch.int32, "block_table", 2); _need(work, torch.int32, "work", 1)
-    _check(lib().ferrum_attention_flash(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(kv_plane),
+    _check(lib().ferrum_attention_flash(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), dtype_code(q.dtype),
+                                        _ptr(kv_plane),
                                         c_longlong(page_stride), c_int(page_size), _ptr(block_table),
                                         c_int(block_table.shape[1]), _ptr(q_start), _ptr(pos0), _ptr(work),
                                         c_int(n_work), _ptr(cta_items), c_int(n_ctas), _ptr(part_o), _ptr(part_ml),
                                         c_int(Hq), c_int(Hkv), c_int(D),
                                         c_float(scale), c_int(window), c_int(bm), c_int(1 if trigger_early else 0),
-                                        _stream()), "attention_flash")
+                                        _ptr(err), _stream()), "attention_flash")
 
 
 def attention_tc_tokens(D, G, page_size, kv_plane=None, page_stride=0):
     """Tokens per work item of the tcgen05 attention kernel for this head size, group size and
     page size (an item has that many tokens x G rows); 0 where the kernel does not apply (other
     sizes, float32, pages that are not dense in the plane)."""
-    if kv_plane is not None and (kv_plane.dtype != torch.bfloat16 or kv_plane.dim() != 5 or
+    if kv_plane is not None and (kv_plane.dtype not in SIXTEEN_BIT or kv_plane.dim() != 5 or
                                  page_stride != kv_plane[0].numel()):
         return 0
     return int(lib().ferrum_attention_tc_tokens(c_int(D), c_int(G), c_int(page_size)))
@@ -312,10 +329,10 @@ def attention_tc_tokens(D, G, page_size, kv_plane=None, page_stride=0):
 def attention_tc(q, out, kv_plane, page_stride, page_size, block_table, q_start, pos0, work, n_work, part_o, part_ml,
                  Hq, Hkv, D, scale, window, err):
     """tcgen05 attention over work items of attention_tc_tokens * G rows (prompt portions)."""
-    _need(q, torch.bfloat16, "q", 2); _need(out, torch.bfloat16, "out", 2); _need(kv_plane, torch.bfloat16, "kv_plane")
+    _need16(q, "q", 2); _need16(out, "out", 2, like=q); _need16(kv_plane, "kv_plane", like=q)
     _need(block_table, torch.int32, "block_table", 2); _need(work, torch.int32, "work", 1)
     _check(lib().ferrum_attention_tc(_ptr(q), c_int(q.stride(0)), c_longlong(q.shape[0]), _ptr(out), c_int(out.stride(0)),
-                                     _ptr(kv_plane), c_longlong(page_stride), c_longlong(kv_plane.shape[0]),
+                                     dtype_code(q.dtype), _ptr(kv_plane), c_longlong(page_stride), c_longlong(kv_plane.shape[0]),
                                      c_int(page_size), _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),
                                      _ptr(pos0), _ptr(work), c_int(n_work), _ptr(part_o), _ptr(part_ml), c_int(Hq),
                                      c_int(Hkv), c_int(D), c_float(scale), c_int(window), _ptr(err), _stream()),
@@ -326,7 +343,8 @@ def attention_combine(out, part_o, part_ml, q_start, req_of_token, req_tile0, ti
                       D, bm, n_warps=1):
     """Merges the key-range splits written by attention_flash into `out`.  n_warps (1..8): warps
     per (token, head) that share its splits; more than one pays from about 16 splits on."""
-    _check(lib().ferrum_attention_combine(_ptr(out), c_int(out.stride(0)), _ptr(part_o), _ptr(part_ml), _ptr(q_start),
+    _need16(out, "out", 2)
+    _check(lib().ferrum_attention_combine(_ptr(out), c_int(out.stride(0)), dtype_code(out.dtype), _ptr(part_o), _ptr(part_ml), _ptr(q_start),
                                           _ptr(req_of_token), _ptr(req_tile0), _ptr(tile_info), _ptr(token_list),
                                           c_int(n_tokens), c_int(Hq), c_int(Hkv), c_int(D), c_int(bm), c_int(n_warps), _stream()),
            "attention_combine")

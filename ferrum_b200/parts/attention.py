@@ -108,7 +108,7 @@ class PagedAttention(Mixer):
             else:
                 ops.attention_flash(qkv, out, cache.plane, cache.page_stride, cache.page_size, table, ctx.q_start,
                                     ctx.pos0, plan.work, plan.n_work, part_o, part_ml, Hq, Hkv, D, self.scale,
-                                    self.window, plan.bm, plan.cta_items, plan.n_ctas,
+                                    self.window, plan.bm, ctx.err, plan.cta_items, plan.n_ctas,
                                     trigger_early=ctx.n_tokens <= EARLY_TRIGGER_MAX_TOKENS)
             if plan.n_comb:
                 ops.attention_combine(out, part_o, part_ml, ctx.q_start, ctx.req_of_token, plan.req_tile0,

@@ -6,8 +6,10 @@ a missing `output.weight` means the output shares the embedding (crates/model/sr
 103-111).  Same rules here, except that all problems are collected into a single
 `WeightsError` instead of stopping at the first.
 
-Storage policy: matrices are kept in the compute dtype (bfloat16 or float32; float16 and
-bfloat16 files upcast exactly for the float32 path), vectors such as norm weights stay
+Storage policy: matrices are kept in the compute dtype (bfloat16, float16 or float32: a
+float16 file computed in float16 is used as stored, as the reference does with F16 weights,
+crates/core-types/src/dtype.rs:24-45; float16 and bfloat16 files upcast exactly for the
+float32 path; a file of the other 16-bit type is rounded), vectors such as norm weights stay
 float32, integer tables become int32.
 """
 from __future__ import annotations

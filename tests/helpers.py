@@ -9,11 +9,11 @@ REL_F32 = 1e-4
 # 16-bit compute: every activation between kernels is rounded to 8 (bfloat16) or 11 (float16) bits
 # of mantissa, so the bound is relative to the spread of the logits it perturbs: per row,
 # max |x - ref| <= C * std(ref row).  C is three times the worst ratio seen over the whole suite
-# on a B200 (bfloat16: 0.029, in the wide model at 400 tokens a step), far below the third of a standard deviation that
+# on a B200 (bfloat16 0.029, float16 0.0040, both in the wide model at 400 tokens a step), far below the third of a standard deviation that
 # a fixed absolute bound would let pass.  With it goes the reference's second acceptance rule
 # (docs/ARCHITECTURE.md:215-222; tests/accept/tests/m4_forward.rs:45-62,168-187): the top-1 token
 # agrees on at least 99 % of the rows whose top-2 margin exceeds the bound.
-C_16BIT = {"bfloat16": 0.09, "float16": 0.1}
+C_16BIT = {"bfloat16": 0.09, "float16": 0.012}
 TOP1_AGREEMENT = 0.99
 STATS = {}        # what -> worst ratio seen (written out at the end of a session, see conftest.py)
 

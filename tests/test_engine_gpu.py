@@ -41,7 +41,7 @@ def check_against_plain(folder, dtype, prompt, got, temperature=0.0, seed=0):
 
 
 @pytest.mark.parametrize("name", ["A", "B", "D"])
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
 def test_greedy_generation(cuda, model_dirs, name, dtype):
     vocab = TINY[name][0]["vocab_size"]
     prompt = random_tokens(16, vocab, 40)
@@ -130,7 +130,7 @@ def test_missing_extension_or_device_fails_loudly(cuda, monkeypatch):
         lib.require_cuda()
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
 def test_steps_queued_ahead_change_nothing(cuda, model_dirs, dtype):
     """The engine queues the next decode step before it has read the current one's tokens (the
     ids go from the sampling kernel to the next step on the device).  Same tokens, same finish

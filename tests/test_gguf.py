@@ -97,7 +97,7 @@ def test_config_from_a_gguf_file(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
 def test_model_from_gguf_rotates_adjacent_pairs(cuda, tmp_path, dtype):
     """The second tiny configuration as an F16 GGUF file: the engine's logits equal the plain
     implementation's with the reference's adjacent-pair rotation on the same (unpermuted) rows.

@@ -7,7 +7,7 @@ from conftest import TINY
 
 pytestmark = pytest.mark.gpu
 
-CASES = [(m, d) for m in ("A", "B", "C", "D") for d in ("float32", "bfloat16")]
+CASES = [(m, d) for m in ("A", "B", "C", "D") for d in ("float32", "bfloat16", "float16")]
 
 
 def session(model_dirs, name, dtype, max_tokens, **kw):
@@ -76,7 +76,7 @@ def test_mixed_batches_with_page_reuse(cuda, model_dirs, name, dtype):
     assert s.cache.manager.used_pages(0) == 0
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
 @pytest.mark.parametrize("page_size", [8, 32])
 def test_other_page_sizes_through_a_whole_model(cuda, model_dirs, dtype, page_size):
     """Pages of 8 and of 32 positions (the tensor-core kernels' gather, the rotary kernel's
@@ -121,7 +121,7 @@ def test_a_wrong_page_index_is_caught(cuda, model_dirs, dtype, monkeypatch):
             assert_close(r.logits(k, len(toks[k])), plain_logits(model_dirs["D"], dtype, toks[k]), dtype, f"mutated {k}")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
 def test_many_query_heads_on_one_kv_head(cuda, model_dirs, dtype):
     """32 query heads share one KV head: a decoded token brings 32 rows, twice what the 16-row
     tile of the tensor-core kernel takes, so decoding runs on the 64-row class and without a
@@ -137,7 +137,7 @@ def test_many_query_heads_on_one_kv_head(cuda, model_dirs, dtype):
     assert_close(r.logits("a", 100), plain_logits(model_dirs["G"], dtype, toks), dtype, "32 heads per kv head")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
 def test_wide_model_with_many_tokens_per_step(cuda, model_dirs, dtype):
     """A model wide enough (1024 features, head size 128) and steps long enough for the kernels
     that the tiny configurations never reach: products of 300 to 400 tokens on CTA pairs, cut
@@ -158,7 +158,7 @@ def test_wide_model_with_many_tokens_per_step(cuda, model_dirs, dtype):
     assert_close(r.logits("b", len(b)), plain_logits(model_dirs["E"], dtype, b), dtype, "wide b")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
 def test_long_decoding(cuda, model_dirs, dtype):
     """Several hundred tokens one by one: many pages, many page edges."""
     vocab = TINY["C"][0]["vocab_size"]
@@ -205,15 +205,16 @@ def test_trace_run_program(cuda, model_dirs, tmp_path):
     assert not (out / "1.f32").exists()
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 @pytest.mark.parametrize("name", ["B", "D"])
-def test_decode_graph_replay_matches_kernel_launches(cuda, model_dirs, name):
+def test_decode_graph_replay_matches_kernel_launches(cuda, model_dirs, name, dtype):
     """Decode steps replayed from a captured CUDA graph give the logits that the same steps
     give when launched kernel by kernel, while requests grow across page and split edges."""
     vocab = TINY[name][0]["vocab_size"]
     toks = {k: random_tokens(170, vocab, 30 + i) for i, k in enumerate("abc")}
     outs = []
     for graphs in (False, True):
-        s = session(model_dirs, name, "bfloat16", 3 * 192)
+        s = session(model_dirs, name, dtype, 3 * 192)
         s.runner.use_graphs = graphs
         r = Replay(s)
         r.step([(k, toks[k][:40 + 7 * i], []) for i, k in enumerate("abc")])
@@ -225,6 +226,6 @@ def test_decode_graph_replay_matches_kernel_launches(cuda, model_dirs, name):
         assert (s.runner.graph_replays > 90) == graphs
         outs.append(np.stack([r.rows[(k, p)] for k in "abc" for p in range(40 + 7 * "abc".index(k), 140)]))
     assert np.abs(outs[0] - outs[1]).max() <= 1e-6
-    ref = plain_logits(model_dirs[name], "bfloat16", toks["a"][:140])
+    ref = plain_logits(model_dirs[name], dtype, toks["a"][:140])
     got = np.stack([r.rows[("a", p)] for p in range(40, 140)])
-    assert_close(got, ref[40:140], "bfloat16", "graph decode")
+    assert_close(got, ref[40:140], dtype, "graph decode")
