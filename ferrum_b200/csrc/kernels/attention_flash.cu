@@ -135,27 +135,22 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
   const int ld_off = ld_r * D + ((ld_c ^ (ld_r & 7)) << 3);
   const elem16* kv_head = p.kv_plane + (size_t)kvh * ps * D + ld_c * 8;
   const int ps_shift = p.page_shift;  // log2(page_size), or -1 when it is no power of two
+  bool page_missing = false;   // a key of the range had no page (checked without a branch in the copy loop)
   auto load_tile = [&](int buf, int key0) {
     elem16* dk = sK + buf * BN * D + ld_off;
     elem16* dv = sV + buf * BN * D + ld_off;
 #pragma unroll
     for (int i = 0; i < PASSES; ++i) {
       const int key = key0 + ld_r + i * RPP;
-      bool valid = key < kv_end;
-      const elem16* src = p.kv_plane;
-      if (valid) {
-        const int lp = ps_shift >= 0 ? key >> ps_shift : key / ps;
-        const int in_page = ps_shift >= 0 ? key & (ps - 1) : key - lp * ps;
-        const int page = lp < p.table_width ? bt[lp] : -1;
-        if (page < 0) {   // a key without a page: nothing is read (the rows arrive as zeros), the step fails
-          valid = false;
-          atomicExch(p.err, 5);
-        } else {
-          src = kv_head + (size_t)page * p.page_stride + in_page * D;
-        }
-      }
+      const bool in_range = key < kv_end;
+      const int lp = ps_shift >= 0 ? key >> ps_shift : key / ps;
+      const int in_page = ps_shift >= 0 ? key & (ps - 1) : key - lp * ps;
+      const int page = (in_range && lp < p.table_width) ? bt[lp] : -1;
+      const bool valid = page >= 0;      // a key without a page: nothing is read, the rows arrive as zeros
+      page_missing |= in_range && !valid;
+      const elem16* src = kv_head + (size_t)max(page, 0) * p.page_stride + in_page * D;
       cp_async16(dk + i * RPP * D, src, valid ? 16 : 0);
-      cp_async16(dv + i * RPP * D, valid ? src + v_off : src, valid ? 16 : 0);
+      cp_async16(dv + i * RPP * D, src + v_off, valid ? 16 : 0);
     }
   };
   const int n_tiles = (kv_end - kv_begin + BN - 1) / BN;
@@ -292,6 +287,7 @@ __device__ __forceinline__ void flash_item(const FlashParams& p, const int* wk, 
   }
   cp_async_wait<0>();
   __syncthreads();
+  if (page_missing) atomicExch(p.err, 5);   // the step fails; what this item writes is discarded by the host
 
   // ---- each warp leaves (m, l, O) in shared memory; the WN partial results are merged
 #pragma unroll

@@ -280,19 +280,33 @@ def rope_cache_write(qkv, n_tokens, positions, req_of_token, block_table, cos_si
            "rope_cache_write")
 
 
+def attention_generic_split():
+    """Keys per split of the generic attention kernel's split mode."""
+    return int(lib().ferrum_attention_generic_split())
+
+
 def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv_plane, page_stride, page_size, Hq,
-                      Hkv, D, scale, window, err):
-    """Causal GQA attention of every token over its request's pages (one warp per token and head)."""
+                      Hkv, D, scale, window, err, part=None, split_slots=0):
+    """Causal GQA attention of every token over its request's pages on the CUDA cores, float32
+    arithmetic.  part=None: one CTA per (token, group of heads) walks the whole key range (many
+    tokens).  With `part` (float32, n_tokens * Hq * split_slots * (D + 2) elements) every row's keys
+    are cut at multiples of `attention_generic_split()` among split_slots CTAs and folded by a
+    second launch (few tokens); split_slots must cover the longest row."""
     _need(q, None, "q", 2); _need(out, q.dtype, "out", 2); _need(kv_plane, q.dtype, "kv_plane")
     _need(positions, torch.int32, "positions", 1); _need(req_of_token, torch.int32, "req_of_token", 1)
     _need(block_table, torch.int32, "block_table", 2)
     if not block_table.is_contiguous():
         raise KernelError("attention: block_table must be contiguous")
+    if part is not None:
+        _need(part, torch.float32, "part")
+        if part.numel() < n_tokens * Hq * split_slots * (D + 2):
+            raise KernelError("attention: the partials buffer is too small")
     _check(lib().ferrum_attention_generic(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)),
                                           dtype_code(q.dtype), c_int(n_tokens), _ptr(positions), _ptr(req_of_token),
                                           _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_plane),
                                           c_longlong(page_stride), c_int(page_size), c_int(Hq), c_int(Hkv), c_int(D),
-                                          c_float(scale), c_int(window), _ptr(err), _stream()), "attention_generic")
+                                          c_float(scale), c_int(window), _ptr(err), _ptr(part), c_int(split_slots),
+                                          _stream()), "attention_generic")
 
 
 def attention_flash_supported(dtype, D, page_stride=0):

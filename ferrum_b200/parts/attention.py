@@ -74,9 +74,27 @@ class PagedAttention(Mixer):
         if ops.attention_flash_supported(self.dtype, D):
             self._flash(qkv, out, ctx, cache, table)
         else:
-            ops.attention_generic(qkv, out, T, ctx.positions, ctx.req_of_token, table, cache.plane, cache.page_stride,
-                                  cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err)
+            self._generic(qkv, out, ctx, cache, table)
         linear(out, self.w_output_weight, residual, RESIDUAL, ctx, M=T)
+
+    def _generic(self, qkv, out, ctx, cache, table):
+        """CUDA-core path.  With enough rows to fill the GPU (a prompt portion) every row walks its
+        keys alone; with few (decoding) the keys of a row are cut into splits among CTAs.  Which of
+        the two runs depends on the number of tokens only, and so does the number of split slots
+        while a CUDA graph is being captured or replayed (then it covers the longest context the
+        cache can hold)."""
+        T, Hq, Hkv, D = ctx.n_tokens, self.Hq, self.Hkv, self.D
+        rows = T * Hkv * -(-(Hq // Hkv) // 4)
+        part, slots = None, 0
+        if rows < 2 * attention_plan.sm_count():
+            split = ops.attention_generic_split()
+            longest = table.shape[1] * cache.page_size if ctx.fixed_shapes else ctx.max_kv_len
+            if self.window > 0:
+                longest = min(longest, self.window + split)       # a window of w keys touches at most w / split + 2 splits
+            slots = longest // split + 2
+            part = ctx.buf("attn_generic_part", (T * Hq * slots * (D + 2),), torch.float32)
+        ops.attention_generic(qkv, out, T, ctx.positions, ctx.req_of_token, table, cache.plane, cache.page_stride,
+                              cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err, part, slots)
 
     def plan(self, ctx, cache):
         """The step's work lists of the tensor-core kernels for this layer's shape (None on the

@@ -6,6 +6,7 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py attn_decode [--batch 8] [--context 8192] [--layers 4]
     python kernel_bench.py attn_prefill [--tokens 2048]
     python kernel_bench.py gemm --tokens 8 --n 6144 --k 4096 [--epilogue store|residual|swiglu] [--copies 8]
+    python kernel_bench.py gemm|attn_decode|attn_prefill ... --dtype fp32    (the CUDA-core kernels of the 32-bit path)
     python kernel_bench.py rmsnorm|rope --tokens 8
     FERRUM_KERNEL_TRACE=1 python kernel_bench.py timeline [--batch 8] [--context 8192] [--layers 4]
 `timeline` runs decode steps of a model with `--layers` layers on the library built with the
@@ -43,6 +44,8 @@ def main():
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--deferred", action="store_true", help="gemm: leave the partials to the consumer (as decoding does)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"],
+                    help="fp32 times the CUDA-core kernels of the true 32-bit path (its fraction is of the FFMA peak)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--no-dependent-launch", action="store_true", help="plain stream order between the launches")
     args = ap.parse_args()
@@ -57,6 +60,8 @@ def main():
     ops.set_dependent_launch(not args.no_dependent_launch)
     pk = peaks()
     dev = "cuda"
+    td = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    esize = 4 if args.dtype == "fp32" else 2
     Hq, Hkv, D, ps = args.hq, args.hkv, args.head_dim, args.page_size
     gen = torch.Generator(device=dev).manual_seed(0)
     runs = []
@@ -72,15 +77,15 @@ def main():
         ctx_len = args.context if decode else args.tokens
         n_pages = R * ((ctx_len + ps - 1) // ps)
         width = (ctx_len + ps - 1) // ps
-        planes = [torch.randn(n_pages, 2, Hkv, ps, D, device=dev, generator=gen).mul_(0.5).bfloat16() for _ in range(args.layers)]
+        planes = [torch.randn(n_pages, 2, Hkv, ps, D, device=dev, generator=gen).mul_(0.5).to(td) for _ in range(args.layers)]
         perm = torch.randperm(n_pages).view(R, width).tolist()
         ctx = StepContext(dev, max(16, R * qlen), R, [width])
         ctx.fixed_shapes = False
         ctx.fill([StepEntry(r, ctx_len - qlen, [1] * qlen) for r in range(R)], [perm])
         T = R * qlen
-        q = torch.randn(T, Hq * D, device=dev, generator=gen).bfloat16()
-        out = torch.empty(T, Hq * D, device=dev, dtype=torch.bfloat16)
-        att = PagedAttention(Hq * D, Hq, Hkv, D, None, torch.bfloat16)
+        q = torch.randn(T, Hq * D, device=dev, generator=gen).to(td)
+        out = torch.empty(T, Hq * D, device=dev, dtype=td)
+        att = PagedAttention(Hq * D, Hq, Hkv, D, None, td)
 
         class Cache:
             pass
@@ -90,10 +95,11 @@ def main():
             c.plane, c.page_stride, c.page_size, c.group, c.writes = pl, pl.stride(0), ps, 0, True
             caches.append(c)
         table = ctx.block_tables[0]
-        runs = [lambda c=c: att._flash(q, out, ctx, c, table) for c in caches]
-        kv_bytes = R * ctx_len * 2 * Hkv * D * 2
+        run_attention = att._flash if ops.attention_flash_supported(td, D) else att._generic
+        runs = [lambda c=c: run_attention(q, out, ctx, c, table) for c in caches]
+        kv_bytes = R * ctx_len * 2 * Hkv * D * esize
         flops = 4.0 * Hq * D * (ctx_len * qlen if decode else qlen * qlen / 2) * R
-        work = {"bytes": kv_bytes + 2 * T * Hq * D * 2, "flops": flops, "bound": "hbm" if decode else "tensor"}
+        work = {"bytes": kv_bytes + 2 * T * Hq * D * esize, "flops": flops, "bound": "hbm" if decode else "tensor"}
     elif args.kernel == "gemm":
         M, N, K = args.tokens, args.n, args.k
         dual = args.epilogue == "swiglu"
@@ -101,21 +107,25 @@ def main():
         ws = torch.empty(ws_f, device=dev)
         cnt = torch.zeros(max(tiles, 1), dtype=torch.int32, device=dev)
         err = torch.zeros(1, dtype=torch.int32, device=dev)
-        x = torch.randn(M, K, device=dev, generator=gen).bfloat16()
-        weights = [torch.randn(N * (2 if dual else 1), K, device=dev, generator=gen).mul_(0.02).bfloat16() for _ in range(args.copies)]
+        x = torch.randn(M, K, device=dev, generator=gen).to(td)
+        weights = [torch.randn(N * (2 if dual else 1), K, device=dev, generator=gen).mul_(0.02).to(td) for _ in range(args.copies)]
         if args.epilogue == "residual":
             o = torch.zeros(M, N, device=dev)
             epi = ops.TC_RESIDUAL
         else:
-            o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            o = torch.empty(M, N * (2 if dual and args.dtype == "fp32" else 1), device=dev, dtype=td)
             epi = ops.TC_SWIGLU if dual else ops.TC_STORE_BF16
-        runs = [lambda w=w: ops.gemm_tc(x, w, o, epi, err, ws, cnt, N=N, dual_offset=N if dual else 0, n_ctas=args.ctas) for w in weights]
-        if args.deferred:
+        if args.dtype == "fp32":     # the CUDA-core product (gate and up as one product of 2N rows; the activation is a kernel of its own)
+            gepi = ops.EPI_RESIDUAL if args.epilogue == "residual" else ops.EPI_STORE
+            runs = [lambda w=w: ops.gemm_generic(x, w, o, gepi) for w in weights]
+        else:
+            runs = [lambda w=w: ops.gemm_tc(x, w, o, epi, err, ws, cnt, N=N, dual_offset=N if dual else 0, n_ctas=args.ctas) for w in weights]
+        if args.deferred and args.dtype != "fp32":
             if not ops.gemm_tc_can_defer(M, N, K, dual):
                 sys.exit("this shape cannot defer its reduction")
             runs = [lambda w=w: ops.gemm_tc_deferred(x, w, err, ws, N=N, dual_offset=N if dual else 0) for w in weights]
-        wb = N * K * 2 * (2 if dual else 1)
-        work = {"bytes": wb + M * K * 2 + M * N * (4 if args.epilogue == "residual" else 2),
+        wb = N * K * esize * (2 if dual else 1)
+        work = {"bytes": wb + M * K * esize + M * N * (4 if args.epilogue == "residual" else esize),
                 "flops": 2.0 * M * N * K * (2 if dual else 1), "bound": "hbm" if M <= 128 else "tensor"}
     elif args.kernel == "rmsnorm":
         T, E = args.tokens, args.k
@@ -164,7 +174,13 @@ def main():
     us = ev0.elapsed_time(ev1) / args.iters * 1e3
     gbs = work["bytes"] / (us * 1e-6) / 1e9
     tf = work["flops"] / (us * 1e-6) / 1e12
-    frac = gbs / pk["hbm_gbs"] if work["bound"] == "hbm" else tf / pk["bf16_tflops"]
+    if work["bound"] == "hbm":
+        frac = gbs / pk["hbm_gbs"]
+    elif args.dtype == "fp32":       # the CUDA cores' own peak: SMs x 128 lanes x 2 flops x the maximum clock
+        frac = tf / (ops.sm_count() * 128 * 2 * 1.965e9 / 1e12)
+        work["bound"] = "ffma"
+    else:
+        frac = tf / pk["bf16_tflops"]
     print(json.dumps({"kernel": args.kernel, "us": round(us, 2), "GBps": round(gbs, 1), "TFLOPs": round(tf, 2),
                       "bound": work["bound"], "frac_of_peak": round(frac, 4), "peaks": pk["source"],
                       "args": {k: v for k, v in vars(args).items() if k != "kernel"}}))

@@ -112,7 +112,7 @@ def test_gemm_generic_anchor(ops):
 @pytest.mark.parametrize("K", [333, 4096])
 def test_gemm_generic_row_independent_of_batch(ops, K):
     """A token's product is bit-identical whatever else is in the call, within each of the two
-    kernels (up to 16 tokens: the weight-streaming kernel; more: the tiled kernel), and the two
+    kernels (up to 64 tokens: the weight-streaming kernel; more: the tiled kernel), and the two
     agree to float32 rounding."""
     g = torch.Generator(device="cuda").manual_seed(4)
     x = torch.randn(70, K, device="cuda", generator=g)
@@ -123,12 +123,14 @@ def test_gemm_generic_row_independent_of_batch(ops, K):
         ops.gemm_generic(x[rows].contiguous(), w, out, ops.EPI_STORE)
         return out
 
-    full = run(list(range(70)))                                  # tiled, 128-token tiles
-    assert torch.equal(run(list(range(20, 60)))[17], full[37])   # tiled, 64-token tile, another place in the tile
-    assert torch.equal(run(list(range(30, 50)))[7], full[37])    # tiled, 32-token tile
+    x = torch.cat([x, torch.randn(130, K, device="cuda", generator=g)])
+    full = run(list(range(200)))                                 # tiled, 128-token tiles
+    assert torch.equal(run(list(range(100)))[37], full[37])      # tiled, another grid
+    assert torch.equal(run(list(range(30, 110)))[7], full[37])   # tiled, another place in the tile
     one = run([37])                                              # streaming
     assert torch.equal(run([3, 37, 5, 9, 11, 2, 1, 0, 8, 37])[1], one[0])
     assert torch.equal(run(list(range(37, 53)))[0], one[0])
+    assert torch.equal(run(list(range(0, 64)))[37], one[0])      # streaming, several passes
     assert (one[0] - full[37]).abs().max() <= 2.5e-7 * K * full[37].abs().max()
 
 
@@ -269,7 +271,7 @@ def paged_setup(lens, Hkv, D, page_size, dtype, seed, extra_pages=3):
                                                 (3, 3, 80, 32, 0), (4, 2, 32, 16, 21), (2, 1, 256, 16, 0)])
 def test_attention_generic(ops, dtype, Hq, Hkv, D, ps, window):
     """Mixed batch: a whole prompt, a late portion, two single decoded tokens."""
-    lens = [37, 130, 65, 1]
+    lens = [37, 1300, 65, 1]
     qlens = [37, 9, 1, 1]
     plane, table, ks, vs = paged_setup(lens, Hkv, D, ps, dtype, 7)
     g = torch.Generator(device="cuda").manual_seed(8)
@@ -280,27 +282,33 @@ def test_attention_generic(ops, dtype, Hq, Hkv, D, ps, window):
         pos += list(range(n - ql, n)); req += [r] * ql
     out = torch.empty(T, Hq * D, device="cuda", dtype=dtype)
     e = err_flag()
-    ops.attention_generic(q, out, T, torch.tensor(pos, dtype=torch.int32, device="cuda"),
-                          torch.tensor(req, dtype=torch.int32, device="cuda"), table, plane, plane.stride(0), ps,
-                          Hq, Hkv, D, 1.0 / math.sqrt(D), window, e)
+    posd, reqd = torch.tensor(pos, dtype=torch.int32, device="cuda"), torch.tensor(req, dtype=torch.int32, device="cuda")
+    ops.attention_generic(q, out, T, posd, reqd, table, plane, plane.stride(0), ps, Hq, Hkv, D, 1.0 / math.sqrt(D), window, e)
+    # the same rows with their keys cut into splits of 512 among CTAs (what a batch of few tokens runs)
+    slots = max(lens) // ops.attention_generic_split() + 2
+    part = torch.full((T * Hq * slots * (D + 2),), float("nan"), device="cuda")
+    out2 = torch.empty_like(out)
+    ops.attention_generic(q, out2, T, posd, reqd, table, plane, plane.stride(0), ps, Hq, Hkv, D, 1.0 / math.sqrt(D), window, e,
+                          part, slots)
     assert e.item() == 0
-    t0 = 0
-    for r, (n, ql) in enumerate(zip(lens, qlens)):
-        qfull = np.zeros((n, Hq, D))
-        qfull[n - ql:] = q[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
-        ref = P.attention(qfull, ks[r].double().cpu().numpy(), vs[r].double().cpu().numpy(), window)[n - ql:]
-        got = out[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
-        tol = 1e-4 if dtype == torch.float32 else 1.5e-2
-        assert np.abs(got - ref).max() <= tol, (r, np.abs(got - ref).max())
-        t0 += ql
+    for res in (out, out2):
+        t0 = 0
+        for r, (n, ql) in enumerate(zip(lens, qlens)):
+            qfull = np.zeros((n, Hq, D))
+            qfull[n - ql:] = q[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
+            ref = P.attention(qfull, ks[r].double().cpu().numpy(), vs[r].double().cpu().numpy(), window)[n - ql:]
+            got = res[t0:t0 + ql].double().cpu().numpy().reshape(ql, Hq, D)
+            tol = 1e-5 if dtype == torch.float32 else (1.5e-2 if dtype == torch.bfloat16 else 2e-3)
+            assert np.abs(got - ref).max() <= tol, (r, np.abs(got - ref).max())
+            t0 += ql
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("far_key", [0, 15, 16, 17, 255, 256, 499])
+@pytest.mark.parametrize("far_key", [0, 15, 16, 17, 255, 256, 511, 512, 1023, 1024, 1099])
 def test_attention_finds_one_far_key(ops, dtype, far_key):
-    """One key among 500 matches the query strongly; its value must come through.  A kernel
+    """One key among 1100 matches the query strongly; its value must come through.  A kernel
     that skips a page edge or the first or last key shows at once."""
-    Hq = Hkv = 2; D = 32; ps = 16; n = 500
+    Hq = Hkv = 2; D = 32; ps = 16; n = 1100
     plane, table, ks, vs = paged_setup([n], Hkv, D, ps, dtype, 9)
     kq = ks[0][far_key].float()                       # [Hkv, D]; Hq == Hkv here
     # score of the far key = 40, of every other key ~ N(0, 7)
@@ -308,9 +316,11 @@ def test_attention_finds_one_far_key(ops, dtype, far_key):
     q = q.to(dtype)
     out = torch.empty(1, Hq * D, device="cuda", dtype=dtype)
     e = err_flag()
+    slots = n // ops.attention_generic_split() + 2
+    part = torch.full((Hq * slots * (D + 2),), float("nan"), device="cuda")
     ops.attention_generic(q, out, 1, torch.tensor([n - 1], dtype=torch.int32, device="cuda"),
                           torch.zeros(1, dtype=torch.int32, device="cuda"), table, plane, plane.stride(0), ps, Hq, Hkv,
-                          D, 1.0 / math.sqrt(D), 0, e)
+                          D, 1.0 / math.sqrt(D), 0, e, part, slots)
     qfull = np.zeros((n, Hq, D)); qfull[-1] = q.double().cpu().numpy().reshape(Hq, D)
     ref = P.attention(qfull, ks[0].double().cpu().numpy(), vs[0].double().cpu().numpy())[-1]
     got = out.double().cpu().numpy().reshape(Hq, D)
