@@ -314,11 +314,21 @@ def make_toy_architecture():
             self.n_vocab, self.n_embd, self.n_layer = d["vocab_size"], d["hidden_size"], d["num_hidden_layers"]
             self.hidden, self.decay, self.eps, self.n_pos = d["expert_hidden"], d["decay"], d["eps"], d["positions"]
             self.eos_token_id = None
+            # layers named here mix by the framework's own paged attention instead: (heads, kv heads, head size)
+            self.attention_layers = {int(k): tuple(v) for k, v in d.get("attention_layers", {}).items()}
 
     def build(cfg, dtype, device, max_positions=None):
-        blocks = [PreNormBlock(RMSNorm(cfg.n_embd, cfg.eps, dtype), EmaMixer(cfg.n_embd, cfg.decay),
-                               RMSNorm(cfg.n_embd, cfg.eps, dtype), RoutedFFN(cfg.n_embd, cfg.hidden),
-                               names=("norm_a.", "ema_", "norm_b.", "moe_")) for _ in range(cfg.n_layer)]
+        from ferrum_b200.parts import PagedAttention, RotaryEmbedding
+        blocks = []
+        for i in range(cfg.n_layer):
+            if i in cfg.attention_layers:      # the mixer is chosen layer by layer
+                hq, hkv, hd = cfg.attention_layers[i]
+                rope = RotaryEmbedding(hd, hd, 10000.0, None, "adjacent", cfg.n_pos, device)
+                mixer, name = PagedAttention(cfg.n_embd, hq, hkv, hd, rope, dtype), "attn_"
+            else:
+                mixer, name = EmaMixer(cfg.n_embd, cfg.decay), "ema_"
+            blocks.append(PreNormBlock(RMSNorm(cfg.n_embd, cfg.eps, dtype), mixer, RMSNorm(cfg.n_embd, cfg.eps, dtype),
+                                       RoutedFFN(cfg.n_embd, cfg.hidden), names=("norm_a.", name, "norm_b.", "moe_")))
         emb = TokenEmbedding(cfg.n_vocab, cfg.n_embd)
         return DecoderModel(cfg, dtype, emb, LearnedPositions(cfg.n_pos, cfg.n_embd), blocks,
                             RMSNorm(cfg.n_embd, cfg.eps, dtype), OutputHead(cfg.n_vocab, cfg.n_embd, emb, tied=True))
@@ -383,5 +393,45 @@ def test_toy_architecture_is_registered_built_and_stepped(cuda, dtype, tmp_path)
         # a slot that is used again starts from a zero state
         again = h.run([[("c", ta)]])["c"]
         assert np.abs(again - got["a"]).max() <= tol
+    finally:
+        registry.unregister("ToyForCausalLM")
+
+
+def test_engine_over_state_and_pages_with_preemption(cuda):
+    """The Python entry point over a model the framework has never seen: layer 0 mixes by the toy
+    EMA recurrence (a state per request), layer 1 by the framework's paged attention (pages), the
+    feed-forwards are routed.  With so few pages that two decoding requests cannot both stay, one
+    is preempted: its pages AND its state are dropped, it is recomputed from its first token, and
+    both requests still generate exactly what they generate alone."""
+    from ferrum_b200 import Engine
+    from ferrum_b200.weights import init_random
+    registry = make_toy_architecture()
+    try:
+        d = {"architectures": ["ToyForCausalLM"], "vocab_size": 97, "hidden_size": 48, "num_hidden_layers": 2,
+             "expert_hidden": 56, "decay": 0.75, "eps": 1e-5, "positions": 128, "attention_layers": {"1": [3, 1, 16]}}
+        arch = registry.lookup("ToyForCausalLM")
+        cfg = arch.read_config(d)
+        model = arch.build(cfg, torch.float32, "cuda")
+        assert "blk.0.ema_in.weight" in model.weight_specs() and "blk.1.attn_q.weight" in model.weight_specs()
+        init_random(model, 17)
+        rng = np.random.default_rng(8)
+        prompts = [rng.integers(0, 97, 20).tolist(), rng.integers(0, 97, 20).tolist()]
+
+        def engine(**kw):
+            args = dict(model=model, page_size=16, num_pages=64, max_batch_tokens=64, max_batch_seqs=4, max_model_len=64)
+            args.update(kw)
+            return Engine(**args)
+
+        roomy = engine()
+        assert len(roomy.cache.states) == 1 and roomy.cache.n_groups == 1
+        alone = [roomy.generate([p], max_new_tokens=40)[0] for p in prompts]
+        assert all(len(a) == 40 for a in alone) and alone[0] != alone[1]
+        tight = engine(num_pages=6)                       # 96 positions of cache, 120 needed
+        assert tight.generate(prompts, max_new_tokens=40) == alone
+        st = tight.stats()
+        assert st["preemptions"] >= 1 and st["pages_used"] == [0] and st["active"] == 0
+        # in portions of 8 tokens with a budget of 12 a step, prompts and decoded tokens share steps
+        chunked = engine(chunk_size=8, max_batch_tokens=12)
+        assert chunked.generate(prompts, max_new_tokens=40) == alone
     finally:
         registry.unregister("ToyForCausalLM")

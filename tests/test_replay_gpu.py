@@ -229,3 +229,44 @@ def test_decode_graph_replay_matches_kernel_launches(cuda, model_dirs, name, dty
     ref = plain_logits(model_dirs[name], dtype, toks["a"][:140])
     got = np.stack([r.rows[("a", p)] for p in range(40, 140)])
     assert_close(got, ref[40:140], dtype, "graph decode")
+
+
+@pytest.fixture(scope="module")
+def wide_layer(tmp_path_factory):
+    """One layer at the widths of Llama-3.1-8B (4096 features, 32 query heads on 8 KV heads of 128,
+    14336 hidden features), a small vocabulary; stored in bfloat16."""
+    from ferrum_b200.weights import write_random_model
+    cfg = {"architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 1, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 257, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192},
+           "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
+    d = tmp_path_factory.mktemp("wide_layer")
+    write_random_model(cfg, str(d), 9, dtype="bfloat16")
+    toks = random_tokens(64, cfg["vocab_size"], 80)
+    import plain_llama as P
+    cfg_p, w = P.read_model(str(d))                    # bfloat16 values, exact in every compute dtype but float16
+    return str(d), toks, P.forward(cfg_p, w, toks)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_layer_at_the_widths_of_the_8b_model(cuda, wide_layer, dtype):
+    """The products at their real sizes (reductions over 4096 and 14336 elements) against the plain
+    implementation: 64 tokens, the first 40 in one step, then portions and single tokens.  In
+    float32 the bound is the reference's for reductions longer than 4096 (relative 1e-3,
+    docs/ARCHITECTURE.md:142-153); the engine is in fact far inside it."""
+    from ferrum_b200.engine.trace import TraceSession
+    folder, toks, ref = wide_layer
+    r = Replay(TraceSession(folder, dtype, 64))
+    r.step([("a", toks[:40], "all")])
+    r.step([("a", toks[40:57], "all")])
+    for t in toks[57:]:
+        r.step([("a", [t], "all")])
+    got = r.logits("a", 64)
+    if dtype == "float32":
+        lim = np.maximum(1e-6, 1e-3 * np.maximum(1.0, np.abs(ref)))
+        assert np.isfinite(got).all() and (np.abs(got - ref) <= lim).all(), np.abs(got - ref).max()
+        assert np.abs(got - ref).max() <= 2e-5, np.abs(got - ref).max()        # what float32 sums of this length give
+        assert (got.argmax(-1) == ref.argmax(-1)).mean() >= 0.99
+    else:
+        assert_close(got, ref, dtype, "8b widths")
