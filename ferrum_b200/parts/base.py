@@ -39,7 +39,8 @@ import torch
 class ParamSpec:
     shape: Tuple[int, ...]
     kind: str = "matrix"          # "matrix": compute dtype; "vector": float32; "table": int32
-    init: str = "normal"          # random-weights mode: "normal" N(0, .02); "ones_normal" 1 + N(0, .02)
+    init: object = "normal"       # random-weights mode: "normal" N(0, .02), "ones_normal" 1 + N(0, .02), another name
+                                  # registered in weights/random_init.py, or a function (shape, generator, device, std)
     optional: bool = False        # may be absent from the file (e.g. a tied output matrix)
 
 

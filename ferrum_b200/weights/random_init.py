@@ -19,16 +19,29 @@ from .safetensors_io import write_safetensors
 
 _DT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
 
+# How a parameter is drawn, by the `init` of its ParamSpec: a name registered here, or a function
+# (shape, generator, device, std) -> float32 tensor given in the spec itself.  A part that needs
+# another distribution brings it along; nothing here has to change.
+INITS = {
+    "normal": lambda shape, g, device, std: torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std,
+    "ones_normal": lambda shape, g, device, std: 1.0 + torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std,
+    "zeros": lambda shape, g, device, std: torch.zeros(shape, device=device, dtype=torch.float32),
+}
+
+
+def register_init(name, fn):
+    INITS[name] = fn
+
 
 def _tensor(name, spec, seed, device, std):
     g = torch.Generator(device=device)
     g.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (2 ** 63))
     if spec.kind == "table":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
-    t = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32) * std
-    if spec.init == "ones_normal":
-        t += 1.0
-    return t
+    draw = spec.init if callable(spec.init) else INITS.get(spec.init)
+    if draw is None:
+        raise ValueError(f"{name}: unknown initialisation {spec.init!r} (registered: {', '.join(sorted(INITS))})")
+    return draw(tuple(spec.shape), g, device, std)
 
 
 def init_random(model, seed, device="cuda", std=0.02):

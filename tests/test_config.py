@@ -91,3 +91,22 @@ def test_gguf_metadata_reader_uses_the_reference_keys():
         LlamaConfig.from_gguf_metadata({**meta, "llama.use_parallel_residual": True})
     with pytest.raises(ConfigError, match="rope scaling"):
         LlamaConfig.from_gguf_metadata({**meta, "llama.rope.scaling.type": "linear"})
+
+
+def test_another_rope_scaling_rule_is_one_registration():
+    """The rotary part looks its scaling rule up by name; a rule it has never seen is registered
+    from outside, and the part also takes ready-made frequencies."""
+    from types import SimpleNamespace
+    from ferrum_b200.parts import rope
+    rope.register_scaling("halve_all", lambda f, block: [x / block.factor for x in f])
+    try:
+        block = SimpleNamespace(rope_type="halve_all", factor=2.0)
+        base = rope.inverse_frequencies(8, 100.0)
+        assert rope.inverse_frequencies(8, 100.0, block) == [x / 2.0 for x in base]
+        rot = rope.RotaryEmbedding(8, 8, 100.0, block, "adjacent", 4, "cpu")
+        given = rope.RotaryEmbedding(8, 8, 0.0, None, "adjacent", 4, "cpu", frequencies=[x / 2.0 for x in base])
+        assert (rot.cos_sin == given.cos_sin).all()
+    finally:
+        rope.SCALINGS.pop("halve_all")
+    with pytest.raises(ValueError, match="unsupported rope scaling halve_all"):
+        rope.inverse_frequencies(8, 100.0, SimpleNamespace(rope_type="halve_all", factor=2.0))

@@ -136,3 +136,20 @@ def test_random_bytes_never_crash_the_reader(tmp_path):
                 SafetensorsFile(str(p))
             except FileFormatError:
                 pass
+
+
+def test_a_part_brings_its_own_initialisation(tmp_path):
+    """The random-weights mode draws a parameter as its ParamSpec says: a registered name or a
+    function of the part's own; an unknown name is an error that lists the known ones."""
+    import torch
+    from ferrum_b200.parts.base import ParamSpec
+    from ferrum_b200.weights import random_init
+    spec = ParamSpec((3, 5), init=lambda shape, g, device, std: torch.full(shape, 7.0, device=device))
+    assert torch.equal(random_init._tensor("x", spec, 0, "cpu", 0.02), torch.full((3, 5), 7.0))
+    random_init.register_init("halves", lambda shape, g, device, std: torch.full(shape, 0.5, device=device))
+    try:
+        assert random_init._tensor("x", ParamSpec((2,), kind="vector", init="halves"), 0, "cpu", 0.02).tolist() == [0.5, 0.5]
+    finally:
+        random_init.INITS.pop("halves")
+    with pytest.raises(ValueError, match="unknown initialisation 'nope'.*normal"):
+        random_init._tensor("x", ParamSpec((2,), init="nope"), 0, "cpu", 0.02)
