@@ -29,6 +29,7 @@ Weights are random N(0, 0.02); token ids are uniform random from a seed.  No L2 
 between steps: a step reads gigabytes of weights, far more than the 126 MB L2 holds.
 """
 import argparse
+import gc
 import json
 import os
 import random
@@ -451,7 +452,9 @@ def serve(args):
                          "non_graph_steps": len(launch_ms),
                          "host_ms_per_non_graph_step": round(statistics.median(launch_ms), 3) if launch_ms else None,
                          "gpu_launches": int(ops.launches - l0)})
-            del eng
+            eng._launch = None            # (the timing wrapper holds the engine: break the cycle so that its cache is freed)
+            del eng, inner, timed_launch
+            gc.collect()
             torch.cuda.empty_cache()
     best = runs[-1]
     line = {

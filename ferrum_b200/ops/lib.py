@@ -7,6 +7,7 @@ memory (pointer, shape, stride); no torch operator runs on the product path.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 import threading
 from ctypes import c_float, c_int, c_longlong, c_void_p
@@ -178,7 +179,9 @@ def swiglu_reduce(act, n_tokens, F, partials):
                                       partials._c, _stream()), "swiglu_reduce")
 
 
+@functools.lru_cache(maxsize=4096)
 def gemm_tc_can_defer(M, N, K, dual):
+    """(A pure function of the shape, asked for every product of every step: remembered.)"""
     return bool(lib().ferrum_gemm_tc_can_defer(c_int(M), c_int(N), c_int(K), c_int(1 if dual else 0), c_int(0)))
 
 
@@ -224,6 +227,7 @@ def gemm_tc_token_tile(M, dual):
     return lib().ferrum_gemm_tc_token_tile(c_int(M), c_int(1 if dual else 0))
 
 
+@functools.lru_cache(maxsize=4096)
 def gemm_tc_workspace(M, N, K, dual, n_ctas=0):
     """(workspace floats, tile counters) that a launch needs."""
     tiles = c_int(0)
