@@ -17,7 +17,7 @@ static void raise_as(const char* cls, const char* what) {
 
 PYBIND11_MODULE(_host, m) {
   m.doc() = "native cache manager and scheduler of ferrum_b200";
-  m.attr("ABI") = 4;
+  m.attr("ABI") = 5;
 
   py::register_exception_translator([](std::exception_ptr p) {
     try {
@@ -89,7 +89,8 @@ PYBIND11_MODULE(_host, m) {
       .def_readonly("sample", &PlanEntry::sample)
       .def_readonly("temperature", &PlanEntry::temperature)
       .def_readonly("seed", &PlanEntry::seed)
-      .def_readonly("counter", &PlanEntry::counter);
+      .def_readonly("counter", &PlanEntry::counter)
+      .def_readonly("from_device", &PlanEntry::from_device);
 
   py::class_<Event>(m, "Event")
       .def_readonly("kind", &Event::kind)

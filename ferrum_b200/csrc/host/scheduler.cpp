@@ -186,31 +186,70 @@ void Scheduler::abandon() {
 
 std::vector<PlanEntry> Scheduler::plan_ahead() {
   if (!planned_ || !ahead_.empty() || !pending_.empty() || !queue_.empty()) return {};
-  if (plan_.size() != active_.size() || (int)plan_.size() > cfg_.max_batch_tokens) return {};
-  std::vector<int> need(cache_->n_groups(), 0);
-  std::vector<size_t> seq_of;
+  // where every active sequence stands once the current plan is committed, if nothing stops
+  struct After {
+    int cursor;
+    bool decoding, samples_now;
+  };
+  std::vector<After> after(active_.size());
+  for (size_t i = 0; i < active_.size(); ++i) after[i] = After{active_[i].cursor, active_[i].decoding, false};
+  std::vector<size_t> sampled_seq;   // the sequences of this step's sampled rows, in its order
   for (auto& e : plan_) {
-    if (!e.sample || e.slot < 0) return {};
+    if (e.slot < 0) return {};
     size_t idx = active_.size();
     for (size_t i = 0; i < active_.size(); ++i)
       if (active_[i].id == e.id) idx = i;
     if (idx == active_.size()) return {};
     const Seq& s = active_[idx];
-    if (s.generated + 1 >= s.max_new) return {};  // this step's token is its last: the batch changes
     const int len_after = e.pos0 + (int)e.tokens.size();
-    if (len_after + 1 > cfg_.max_model_len) return {};
-    const auto miss = cache_->pages_missing(s.slot, len_after + 1);
+    after[idx].cursor = len_after;
+    if (e.sample) {
+      if (s.generated + 1 >= s.max_new) return {};  // this step's token is its last: the batch changes
+      if (len_after + 1 > cfg_.max_model_len) return {};
+      after[idx].decoding = true;
+      after[idx].samples_now = true;
+      sampled_seq.push_back(idx);
+    } else if (len_after >= s.prompt_len) {
+      return {};  // a prompt ends without a token (nothing to generate): the sequence finishes at commit
+    }
+  }
+  // a decoding sequence that sits this step out knows its token already: the ordinary plan takes it
+  for (size_t i = 0; i < active_.size(); ++i)
+    if (active_[i].decoding && !after[i].samples_now) return {};
+  int budget = cfg_.max_batch_tokens;
+  if ((int)sampled_seq.size() > budget) return {};
+  // pages: one more position for every sampled row, without preemption
+  std::vector<int> need(cache_->n_groups(), 0);
+  for (size_t idx : sampled_seq) {
+    const auto miss = cache_->pages_missing(active_[idx].slot, after[idx].cursor + 1);
     for (size_t g = 0; g < miss.size(); ++g) need[g] += miss[g];
-    seq_of.push_back(idx);
   }
   for (size_t g = 0; g < need.size(); ++g)
     if (need[g] > cache_->free_pages((int)g)) return {};  // the ordinary plan decides who is preempted
-  for (size_t k = 0; k < plan_.size(); ++k) {
-    const PlanEntry& e = plan_[k];
-    const Seq& s = active_[seq_of[k]];
-    const int len_after = e.pos0 + (int)e.tokens.size();
-    cache_->grow(s.slot, len_after + 1);
-    ahead_.push_back(PlanEntry{s.id, s.slot, len_after, {-1}, true, s.temperature, s.seed, s.generated + 1});
+  for (size_t idx : sampled_seq) {
+    const Seq& s = active_[idx];
+    cache_->grow(s.slot, after[idx].cursor + 1);
+    PlanEntry e{s.id, s.slot, after[idx].cursor, {-1}, true, s.temperature, s.seed, s.generated + 1};
+    e.from_device = true;
+    ahead_.push_back(std::move(e));
+    --budget;
+  }
+  // portions of the prompts that are not done, oldest first, as plan() hands them out
+  for (size_t i = 0; i < active_.size() && budget > 0; ++i) {
+    const Seq& s = active_[i];
+    if (after[i].decoding) continue;
+    const int remaining = s.prompt_len - after[i].cursor;
+    if (remaining <= 0) continue;
+    int take = std::min(budget, remaining);
+    if (cfg_.chunk_size > 0) take = std::min(take, cfg_.chunk_size);
+    take = cache_->max_growable(s.slot, after[i].cursor + take) - after[i].cursor;
+    if (take <= 0) break;  // no page for it now; later prompts do not overtake it
+    cache_->grow(s.slot, after[i].cursor + take);
+    PlanEntry e{s.id, s.slot, after[i].cursor, {}, false, s.temperature, s.seed, s.generated};
+    e.tokens.assign(s.tokens.begin() + after[i].cursor, s.tokens.begin() + after[i].cursor + take);
+    e.sample = (after[i].cursor + take == s.prompt_len) && s.max_new > 0;
+    ahead_.push_back(std::move(e));
+    budget -= take;
   }
   return ahead_;
 }
@@ -273,7 +312,7 @@ std::vector<Event> Scheduler::commit(const std::vector<int32_t>& sampled) {
       for (size_t i = 0; i < active_.size(); ++i)
         if (active_[i].id == a.id) idx = i;
       if (idx == active_.size()) a.slot = -1;
-      else a.tokens[0] = active_[idx].tokens.back();
+      else if (a.from_device) a.tokens[0] = active_[idx].tokens.back();
     }
     plan_.swap(ahead_);
     ahead_.clear();

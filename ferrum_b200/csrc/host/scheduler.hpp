@@ -11,10 +11,12 @@
 // temperature sampling is accepted.
 //
 // A step may be planned one ahead: between plan() and commit(), plan_ahead() gives the batch that
-// follows if no sampled row draws a stopping token, with token ids still unknown, so that the
-// engine can put it on the GPU's queue before it has read the current step's tokens.  commit()
-// then turns it into the current plan; a row whose sequence did stop (or was cancelled) is void:
-// its slot is -1, the GPU computes it for nothing and its sampled id is ignored.
+// follows if no sampled row draws a stopping token, so that the engine can put it on the GPU's
+// queue before it has read the current step's tokens.  Its rows: first one token for every row
+// that samples in the current step, in that step's order (their ids are not known yet: the GPU
+// hands them from one step to the next), then the next portions of prompts that are not done.
+// commit() then turns it into the current plan; a row whose sequence did stop (or was cancelled)
+// is void: its slot is -1, the GPU computes it for nothing and its sampled id is ignored.
 //
 // When pages run out: a decoding sequence that needs a page takes it from the most recently
 // admitted running sequence, which is preempted: its pages and slot are freed and it goes
@@ -57,6 +59,7 @@ struct PlanEntry {
   float temperature;
   uint64_t seed;
   int counter;                   // tokens generated before this one (keys the random draw)
+  bool from_device = false;      // plan_ahead: the one token is the id the step before draws for this row (-1 here)
 };
 
 struct Event {
@@ -86,10 +89,12 @@ class Scheduler {
   // The batch did not run: forget the plan, every sequence is as before the step.
   void abandon();
   // Between plan() and commit(): the next step's batch, if it is decided already whatever tokens
-  // this step draws short of a stopping token (every planned row samples and has tokens left to
-  // generate, nothing is queued, every active sequence is in the plan, pages suffice without
-  // preemption).  Its pages are reserved; each entry carries the one token id -1 (the id this
-  // step draws for its row, same order).  Empty when the next batch cannot be told yet.
+  // this step draws short of a stopping token: every row that samples has tokens left to
+  // generate, nothing is queued, every decoding sequence is in the plan, no prompt ends without
+  // a token, and pages suffice without preemption.  Its pages are reserved.  The entries with
+  // from_device come first, one per sampled row of this step in the same order, each with the
+  // one token id -1; portions of unfinished prompts follow.  Empty when the next batch cannot be
+  // told yet.
   std::vector<PlanEntry> plan_ahead();
   bool planned() const { return planned_; }
 

@@ -136,10 +136,10 @@ class Engine:
         """Plan a batch, run it, sample on the device, read the ids back, commit.
 
         While the GPU runs the batch the scheduler is asked for the one after it
-        (`plan_ahead`); if that is decided already, it is queued behind the running one (its
-        token ids are on the device already: this step's sampling kernel writes them where the
-        next step reads its tokens), and the next call finds it in flight.  The events returned
-        are always those of one step."""
+        (`plan_ahead`); if that is decided already, it is queued behind the running one (the ids
+        that this step draws are on the device already: its sampling kernel writes them where the
+        next step reads its first tokens; portions of prompts that follow come from the host),
+        and the next call finds it in flight.  The events returned are always those of one step."""
         if self._in_flight is None:
             plan = self.scheduler.plan()
             if not plan:
@@ -176,8 +176,9 @@ class Engine:
             entries.append(StepEntry(p.slot, p.pos0, p.tokens, [n - 1] if p.sample else []))
             if p.sample:
                 rows.append(p)
+        # (a batch planned ahead starts with the rows whose token the step before it is still drawing)
         logits = self.runner.step(entries, commit=False, check=False, ahead_of_commit=ahead_of_commit,
-                                  tokens_on_device=ahead_of_commit)
+                                  tokens_on_device=sum(1 for p in plan if p.from_device))
         # the ids also go where a step queued behind this one looks for its tokens
         return self.sampler.launch(logits, rows, also_to=self.runner.ctx.token_store) if rows else _NOTHING_SAMPLED
 

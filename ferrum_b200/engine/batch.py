@@ -135,8 +135,9 @@ class StepContext:
     def fill(self, entries: List[StepEntry], tables, token_capacity=None, keep_token_ids=False):
         """tables: the native CacheManager whose block tables the entries' slots index, or
         explicit rows, tables[g][r] being the row of entry r in group g.  keep_token_ids: the
-        device already holds this step's token ids (`token_store`, written by an earlier kernel
-        of the stream); the entries' own ids are placeholders and are not uploaded."""
+        device already holds the first so many token ids of this step (`token_store`, written by an
+        earlier kernel of the stream); the entries' own ids are placeholders there and are not
+        uploaded."""
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         if R > self.max_requests or T > self.max_tokens:
@@ -182,7 +183,7 @@ class StepContext:
                 t += n
         qstart[R] = T
         total = o + 3 * R + 1
-        first = T if keep_token_ids else 0
+        first = min(int(keep_token_ids), T)
         self._dev[first:total].copy_(host[first:total], non_blocking=True)
         self._host.sent()
         self.h2d_bytes = (total - first) * 4

@@ -63,9 +63,9 @@ class ModelRunner:
 
         ahead_of_commit: the step is queued before the one ahead of it has been committed, so an
         entry starts past its request's committed length, where that step ends (the caller
-        vouches for it).  tokens_on_device: the token ids of the batch, one per entry, are already in
-        `ctx.token_store` (an earlier kernel of the stream leaves them there); the entries carry
-        placeholders."""
+        vouches for it).  tokens_on_device: the first so many entries bring one token each whose id
+        is already in `ctx.token_store` (an earlier kernel of the stream leaves them there, in this
+        order); those entries carry placeholders.  True stands for every entry."""
         mgr = self.cache.manager
         if not entries:
             return None
@@ -85,10 +85,10 @@ class ModelRunner:
                     s[e.slot].zero_()                      # a request starts from an all-zero state
         decode_only = self.use_graphs and all(len(e.tokens) == 1 for e in entries)
         self.ctx.fixed_shapes = decode_only
-        n_tok = sum(len(e.tokens) for e in entries)
-        if tokens_on_device and n_tok != len(entries):
-            raise InvalidRequest("tokens on the device stand for one token per entry")
-        self.ctx.fill(entries, mgr if self.cache.n_groups else [], keep_token_ids=bool(tokens_on_device))
+        n_dev = len(entries) if tokens_on_device is True else int(tokens_on_device)
+        if n_dev > len(entries) or any(len(e.tokens) != 1 for e in entries[:n_dev]):
+            raise InvalidRequest("tokens on the device stand for one token per entry, first in the batch")
+        self.ctx.fill(entries, mgr if self.cache.n_groups else [], keep_token_ids=n_dev)
         logits = self._run_decode() if decode_only else self.model.forward(self.ctx, self.cache)
         if check:
             self.check_device_errors()       # raises before anything is committed: the lengths stay as they were

@@ -9,7 +9,7 @@ from .ops import build
 
 _mod = None
 _lock = threading.Lock()
-ABI = 4
+ABI = 5
 
 
 def module():

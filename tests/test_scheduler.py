@@ -238,10 +238,11 @@ def test_random_workloads_finish_with_the_tokens_each_request_would_get_alone(se
 # ---------------------------------------------------------------- a step planned ahead
 def run_ahead(sched, cache, next_token, max_steps=5000, log=None):
     """The engine's loop with one step planned ahead: the batch that follows is asked for before
-    the current one's tokens are known, and is 'launched' with unknown token ids."""
+    the current one's tokens are known, and is 'launched' with the ids of its first rows unknown."""
     out, reasons = {}, {}
-    in_flight = None       # rows (request ids) of a batch that was launched ahead
+    in_flight = None       # sampled rows (request id, position) of a batch that was launched ahead
     aheads = 0
+    end = {}               # request id -> one past the last position of every batch launched so far
     for _ in range(max_steps):
         if sched.idle() and in_flight is None:
             break
@@ -252,19 +253,28 @@ def run_ahead(sched, cache, next_token, max_steps=5000, log=None):
                     assert ev.kind == 1
                     reasons[ev.id] = ev.reason
                 continue
+            end = {}                   # (an ordinary plan may have preempted: everything starts from the committed lengths)
             for p in plan:
-                assert cache.seq_len(p.slot) == p.pos0
+                assert cache.seq_len(p.slot) == p.pos0 and not p.from_device
+                end[p.id] = p.pos0 + len(p.tokens)
             in_flight = [(p.id, p.pos0 + len(p.tokens) - 1) for p in plan if p.sample]
         rows, in_flight = in_flight, None
         ahead = sched.plan_ahead()
         if ahead:
             aheads += 1
-            assert [a.id for a in ahead] == [r[0] for r in rows]            # same rows, same order
-            for a, (_, last_pos) in zip(ahead, rows):
+            dev = [a for a in ahead if a.from_device]
+            assert ahead[:len(dev)] == dev or [a.id for a in ahead[:len(dev)]] == [a.id for a in dev]   # they come first
+            assert [a.id for a in dev] == [r[0] for r in rows]              # this step's sampled rows, same order
+            for a, (_, last_pos) in zip(dev, rows):
                 assert list(a.tokens) == [-1] and a.sample
                 assert a.pos0 == last_pos + 1 > cache.seq_len(a.slot)         # right after the uncommitted step
-                assert cache.pages_missing(a.slot, a.pos0 + 1) == [0]        # its page is reserved
-            in_flight = [(a.id, a.pos0) for a in ahead]
+            for a in ahead:
+                assert a.pos0 == end.get(a.id, cache.seq_len(a.slot))          # every batch goes on where the last ended
+                assert a.from_device or all(t >= 0 for t in a.tokens)         # a prompt's tokens are known
+                assert cache.pages_missing(a.slot, a.pos0 + len(a.tokens)) == [0]        # its pages are reserved
+                end[a.id] = a.pos0 + len(a.tokens)
+            assert sum(len(a.tokens) for a in ahead) <= 33
+            in_flight = [(a.id, a.pos0 + len(a.tokens) - 1) for a in ahead if a.sample]
             if log is not None:
                 log.append([a.id for a in ahead])
         # the GPU computes every launched row, also rows that turn out void; ids are passed for all
@@ -274,6 +284,7 @@ def run_ahead(sched, cache, next_token, max_steps=5000, log=None):
                 out.setdefault(ev.id, []).append(ev.token)
             else:
                 reasons[ev.id] = ev.reason
+                end.pop(ev.id, None)
         assert cache.check() == ""
     assert sched.idle() and in_flight is None
     return out, reasons, aheads
@@ -299,9 +310,10 @@ def test_plan_ahead_declines_when_the_next_batch_is_not_decided():
     s.submit(1, [1, 2, 3, 4, 5, 6], 3)              # six prompt tokens, four per step
     assert s.plan_ahead() == []                      # nothing planned
     plan = s.plan()
-    assert not plan[0].sample and s.plan_ahead() == []      # a prompt portion: the next step is known, but not sampled
+    ahead = s.plan_ahead()                           # a prompt portion: the rest of the prompt follows, and samples
+    assert not plan[0].sample and [(a.pos0, list(a.tokens), a.sample, a.from_device) for a in ahead] == [(4, [5, 6], True, False)]
     s.commit([])
-    s.plan()
+    assert s.planned()
     s.submit(2, [9], 2)
     assert s.plan_ahead() == []                      # someone is queued: the next batch admits them
     s.abandon()
@@ -369,3 +381,32 @@ def test_random_workloads_with_steps_planned_ahead(seed):
         assert out.get(rid, []) == exp, rid
     assert set(reasons) == set(want)
     assert c.free_pages(0) == c.group(0).num_pages and c.check() == ""
+
+
+def test_plan_ahead_mixes_the_rows_that_sample_with_the_next_portions():
+    """Request 1 is decoding, request 2 has a long prompt cut into portions of 4: every step that
+    is planned ahead brings request 1's next token (its id still on the GPU) first and request 2's
+    next portion after it; the step in which the prompt ends samples for both."""
+    s, c = make(budget=8, chunk=4)
+    s.submit(1, [1, 2], 20)
+    s.submit(2, list(range(10, 23)), 5)              # 13 prompt tokens
+    plan = s.plan()
+    assert [(p.id, len(p.tokens), p.sample) for p in plan] == [(1, 2, True), (2, 4, False)]
+    ahead = s.plan_ahead()
+    assert [(a.id, a.pos0, list(a.tokens), a.sample, a.from_device) for a in ahead] == \
+        [(1, 2, [-1], True, True), (2, 4, [14, 15, 16, 17], False, False)]
+    s.commit([7])
+    ahead = s.plan_ahead()
+    assert [(a.id, a.pos0, len(a.tokens), a.sample, a.from_device) for a in ahead] == [(1, 3, 1, True, True), (2, 8, 4, False, False)]
+    s.commit([7])
+    ahead = s.plan_ahead()                           # the last portion: one token, and it samples
+    assert [(a.id, a.pos0, list(a.tokens), a.sample, a.from_device) for a in ahead] == \
+        [(1, 4, [-1], True, True), (2, 12, [22], True, False)]
+    s.commit([7])
+    ahead = s.plan_ahead()                           # both decode now, in the order in which they sampled
+    assert [(a.id, a.pos0, a.from_device) for a in ahead] == [(1, 5, True), (2, 13, True)]
+    evs = s.commit([7, 8])
+    assert [(e.id, e.token) for e in evs] == [(1, 7), (2, 8)]
+    s.abandon()                                      # (the batch planned ahead never ran; the loop below plans afresh)
+    out, reasons, _ = run_ahead(s, c, lambda rid, pos: 9)
+    assert len(out[1]) + 4 == 20 and len(out[2]) + 1 == 5 and c.check() == ""
