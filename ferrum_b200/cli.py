@@ -11,7 +11,7 @@ errors, exit code 2 for usage errors and 1 for runtime errors, messages prefixed
                     [--dtype bfloat16|float16|float32] [--max-new-tokens N] [--temperature T] [--top-p 1]
                     [--seed S] [--stop-tokens a,b] [--max-batch-tokens N] [--max-batch-seqs N]
                     [--chunk-size N] [--page-size N] [--num-pages N] [--max-model-len N]
-                    [--random-weights] [--weights-seed S] [--stats]
+                    [--random-weights] [--weights-seed S] [--stats] [--profile]
     ferrum random-weights --config CONFIG.json --out DIR [--seed S] [--dtype float32|bfloat16|float16] [--gguf]
     ferrum replay --model DIR --dtype D --out DIR --max-tokens N        (steps on standard input)
     ferrum dump FILE.gguf|FILE.safetensors|DIR
@@ -31,7 +31,7 @@ OPTIONS = {
                  "--max-new-tokens": "int", "--temperature": "float", "--top-p": "float", "--seed": "int",
                  "--stop-tokens": "tokens", "--max-batch-tokens": "int", "--max-batch-seqs": "int",
                  "--chunk-size": "int", "--page-size": "int", "--num-pages": "int", "--max-model-len": "int",
-                 "--random-weights": "flag", "--weights-seed": "int", "--stats": "flag"},
+                 "--random-weights": "flag", "--weights-seed": "int", "--stats": "flag", "--profile": "flag"},
     "random-weights": {"--config": "str", "--out": "str", "--seed": "int", "--dtype": "str", "--gguf": "flag"},
     "replay": {"--model": "str", "--dtype": "str", "--out": "str", "--max-tokens": "int", "--page-size": "int",
                "--max-requests": "int"},
@@ -126,7 +126,7 @@ def cmd_generate(opts):
         if flag in opts:
             kw[name] = opts[flag]
     eng = Engine(model, dtype=opts.get("--dtype", "bfloat16"), random_weights=bool(opts.get("--random-weights")),
-                 seed=opts.get("--weights-seed", 0), **kw)
+                 seed=opts.get("--weights-seed", 0), profile=bool(opts.get("--profile")), **kw)
     sp = SamplingParams(opts.get("--temperature", 0.0), opts.get("--top-p", 1.0), opts.get("--seed", 0))
     ids = [eng.submit(p, opts.get("--max-new-tokens", 16), sp, opts.get("--stop-tokens", [])) for p in prompts]
     out, reasons = {i: [] for i in ids}, {}
@@ -140,6 +140,14 @@ def cmd_generate(opts):
         print(json.dumps({"id": i, "tokens": out[i], "finish_reason": reasons[i]}))
     if opts.get("--stats"):
         print(json.dumps(eng.stats()), file=sys.stderr)
+    if opts.get("--profile"):
+        # per kernel: launches, milliseconds, share of the GPU time; products also GB/s, TFLOP/s, fraction of the roofline
+        rows = eng.profile_report()
+        print(f"{'kernel':24s} {'launches':>8s} {'ms':>10s} {'share':>7s} {'us/launch':>10s} {'GB/s':>9s} {'TFLOP/s':>9s} {'roofline':>9s}",
+              file=sys.stderr)
+        for r in rows:
+            print(f"{r['kernel']:24s} {r['launches']:8d} {r['ms']:10.3f} {r['share'] * 100:6.1f}% {r['us_per_launch']:10.2f} "
+                  f"{r.get('GBps', ''):>9} {r.get('TFLOPs', ''):>9} {r.get('frac_of_roofline', ''):>9}", file=sys.stderr)
     return 0
 
 

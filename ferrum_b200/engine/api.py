@@ -80,7 +80,7 @@ _NOTHING_SAMPLED = object()      # stands for the ticket of a batch without samp
 class Engine:
     def __init__(self, model_path=None, dtype="bfloat16", random_weights=False, seed=0, page_size=16,
                  num_pages=None, max_batch_tokens=2048, max_batch_seqs=64, chunk_size=0, max_model_len=None,
-                 gpu_memory_fraction=0.85, device="cuda", model=None, plan_ahead=True):
+                 gpu_memory_fraction=0.85, device="cuda", model=None, plan_ahead=True, profile=False):
         ops.require_cuda()
         if model is None:
             model, td = load_model(model_path, dtype, device, max_positions=max_model_len,
@@ -113,6 +113,11 @@ class Engine:
         self._next_id = 0
         self.plan_ahead = bool(plan_ahead)
         self._in_flight = None       # the sampling ticket of a batch that is on the GPU's queue
+        if profile:
+            # every launch is timed on its own: no CUDA graphs, one step at a time
+            self.runner.use_graphs = False
+            self.plan_ahead = False
+            ops.profile_begin()
 
     # ------------------------------------------------------------------ requests
     def submit(self, prompt_tokens: Sequence[int], max_new_tokens: int, sampling: SamplingParams = None,
@@ -203,6 +208,22 @@ class Engine:
                 else:
                     live.discard(ev.id)
         return [out[i] for i in ids]
+
+    def profile_report(self):
+        """Rows of `ops.profile_report` for everything launched since the engine was made with
+        profile=True: per kernel its launches, milliseconds, share and, for the products, GB/s and
+        TFLOP/s against the measured peaks of this machine where a MEASURED_PEAKS.json gives them."""
+        import json
+        peaks = None
+        for folder in (os.getcwd(), os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))):
+            try:
+                with open(os.path.join(folder, "MEASURED_PEAKS.json")) as f:
+                    d = json.load(f)
+                peaks = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"])}
+                break
+            except (OSError, ValueError, KeyError, TypeError):
+                continue
+        return ops.profile_report(peaks)
 
     def stats(self) -> dict:
         s = self.scheduler.stats()

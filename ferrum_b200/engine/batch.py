@@ -10,6 +10,7 @@ and one host-to-device copy per step (plus one per cache group for the block tab
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Sequence
 
@@ -25,25 +26,50 @@ class StepEntry:
     want: Sequence[int] = ()       # indices into `tokens` whose logits are wanted
 
 
+CANARY = 0x7FC0BEEF      # bit pattern of the guard words (a quiet NaN when read as float32)
+
+
 class Scratch:
     """Named device buffers that live across steps and only ever grow, so that a buffer
-    keeps its address from step to step."""
+    keeps its address from step to step.
 
-    def __init__(self, device):
+    guard > 0 (FERRUM_CANARY=1 sets 64): debugging mode.  Every buffer is allocated to the exact
+    size asked for plus `guard` 4-byte words behind it that hold a fixed pattern; `check()` names
+    the buffers whose guard words a kernel has overwritten.  A buffer is then reallocated whenever
+    its size changes, so steps run without CUDA graphs in this mode."""
+
+    def __init__(self, device, guard=None):
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
+        self._guards: Dict[str, torch.Tensor] = {}
         self.generation = 0      # bumped whenever a buffer is (re)allocated and so may have moved
+        self.guard = int(os.environ.get("FERRUM_CANARY", "0") == "1") * 64 if guard is None else int(guard)
 
     def get(self, name, shape, dtype):
         n = 1
         for s in shape:
             n *= int(s)
         t = self._bufs.get(name)
+        if self.guard:
+            if t is None or t.dtype != dtype or t.numel() != max(n, 1):
+                esize = torch.empty((), dtype=dtype).element_size()
+                nbytes = (max(n, 1) * esize + 3) // 4 * 4
+                raw = torch.empty(nbytes + 4 * self.guard, dtype=torch.uint8, device=self.device)
+                words = raw[nbytes:].view(torch.int32)
+                words.fill_(CANARY)
+                t = raw[:max(n, 1) * esize].view(dtype)
+                self._bufs[name], self._guards[name] = t, words
+                self.generation += 1
+            return t[:n].view(*shape)
         if t is None or t.dtype != dtype or t.numel() < n:
             t = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[name] = t
             self.generation += 1
         return t[:n].view(*shape)
+
+    def check(self):
+        """Names of the buffers whose guard words no longer hold the pattern (guard mode only)."""
+        return [name for name, words in self._guards.items() if not bool((words == CANARY).all())]
 
     def bytes(self):
         return sum(t.numel() * t.element_size() for t in self._bufs.values())

@@ -15,6 +15,7 @@ import torch
 from ..cache import CacheStorage
 from ..errors import CacheError, FerrumError, InvalidRequest, KernelError
 from ..ops import lib as ops
+from ..models.decoder import NVTX
 from .batch import StepContext, StepEntry
 
 _DEVICE_ERRORS = {
@@ -51,7 +52,8 @@ class ModelRunner:
         widths = [cache.table_width] * cache.n_groups
         self.ctx = StepContext(self.device, self.max_batch_tokens, self.max_batch_requests, widths, err=err)
         self.ctx.cache = cache
-        self.use_graphs = bool(use_graphs) and model.all_graph_safe()
+        # (guarded scratch buffers move whenever their size changes: no graphs then)
+        self.use_graphs = bool(use_graphs) and model.all_graph_safe() and not self.ctx.scratch.guard
         self._graphs = {}
         self._seen = {}
         self.graph_replays = 0
@@ -89,7 +91,11 @@ class ModelRunner:
         if n_dev > len(entries) or any(len(e.tokens) != 1 for e in entries[:n_dev]):
             raise InvalidRequest("tokens on the device stand for one token per entry, first in the batch")
         self.ctx.fill(entries, mgr if self.cache.n_groups else [], keep_token_ids=n_dev)
+        if NVTX:
+            torch.cuda.nvtx.range_push(f"step tokens={self.ctx.n_tokens} requests={self.ctx.n_reqs}")
         logits = self._run_decode() if decode_only else self.model.forward(self.ctx, self.cache)
+        if NVTX:
+            torch.cuda.nvtx.range_pop()
         if check:
             self.check_device_errors()       # raises before anything is committed: the lengths stay as they were
         if commit:
@@ -128,8 +134,13 @@ class ModelRunner:
         return logits
 
     def check_device_errors(self):
-        """Synchronises and raises if a kernel raised the error flag."""
+        """Synchronises and raises if a kernel raised the error flag, or (in the debugging mode with
+        guarded scratch buffers) wrote past the end of one."""
         code = int(self.ctx.err.item())
         if code:
             self.ctx.err.zero_()
             raise KernelError(f"device error {code}: {_DEVICE_ERRORS.get(code, 'unknown')}")
+        if self.ctx.scratch.guard:
+            bad = self.ctx.scratch.check()
+            if bad:
+                raise KernelError("a kernel wrote past the end of: " + ", ".join(bad))

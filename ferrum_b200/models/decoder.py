@@ -11,7 +11,14 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Optional
 
+import os
+
+import torch
+
 from ..parts.base import Part
+
+# FERRUM_NVTX=1: every step and every run of a block is an NVTX range (for a system profiler's timeline)
+NVTX = os.environ.get("FERRUM_NVTX", "0") == "1"
 
 
 @dataclass(frozen=True)
@@ -70,7 +77,11 @@ class DecoderModel(Part):
         if self.position is not None:
             self.position.on_embedding(h, ctx)
         for k, run in enumerate(self.schedule):
+            if NVTX:
+                torch.cuda.nvtx.range_push(f"run {k} block {run.block}")
             self.blocks[run.block].forward(h, ctx, cache.layer_cache(k))
+            if NVTX:
+                torch.cuda.nvtx.range_pop()
         if ctx.n_want == 0:
             ctx.pending_residual = None      # nobody reads the residual stream any more
             return None

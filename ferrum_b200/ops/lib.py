@@ -77,11 +77,85 @@ def set_dependent_launch(on: bool):
 launches = 0          # kernel launches made through this module (every entry point launches one kernel)
 
 
+class _Profile:
+    """Per-kernel timing for `profile_begin` / `profile_report`: one CUDA event after every launch;
+    a launch's time is the span from the event before it to its own (its wait for the kernel ahead
+    of it included).  `work` is (bytes it must move, flops) where the wrapper knows them."""
+
+    def __init__(self):
+        self.rows = []        # (name, event after, work)
+        self.start = torch.cuda.Event(enable_timing=True)
+        self.start.record()
+
+    def mark(self, name, work):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.rows.append((name, ev, work))
+
+
+_profile = None
+_work = None          # set by a wrapper just before its launch: (bytes, flops)
+
+
+def profile_begin():
+    """Start timing every kernel launched through this module (steps must run without CUDA graphs:
+    `Engine(profile=True)` sees to it)."""
+    global _profile
+    require_cuda()
+    _profile = _Profile()
+
+
+def profile_report(peaks=None):
+    """Stops the timing and returns one row per kernel name, largest total first: launches, total
+    milliseconds, share of the total, microseconds per launch and, where the wrapper knows the
+    kernel's work, GB/s and TFLOP/s (with `peaks` = {"hbm_gbs", "bf16_tflops"} also the fraction of
+    whichever bound is nearer)."""
+    global _profile
+    prof, _profile = _profile, None
+    if prof is None:
+        return []
+    torch.cuda.synchronize()
+    acc, prev = {}, prof.start
+    for name, ev, work in prof.rows:
+        r = acc.setdefault(name, {"kernel": name, "launches": 0, "ms": 0.0, "bytes": 0, "flops": 0.0, "known": 0})
+        r["launches"] += 1
+        r["ms"] += prev.elapsed_time(ev)
+        if work is not None:
+            r["bytes"] += work[0]
+            r["flops"] += work[1]
+            r["known"] += 1
+        prev = ev
+    total = sum(r["ms"] for r in acc.values()) or 1.0
+    out = []
+    for r in sorted(acc.values(), key=lambda r: -r["ms"]):
+        row = {"kernel": r["kernel"], "launches": r["launches"], "ms": round(r["ms"], 3), "share": round(r["ms"] / total, 4),
+               "us_per_launch": round(r["ms"] * 1e3 / r["launches"], 2)}
+        if r["known"] == r["launches"] and r["ms"] > 0:
+            row["GBps"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9, 1)
+            row["TFLOPs"] = round(r["flops"] / (r["ms"] * 1e-3) / 1e12, 2)
+            if peaks:
+                row["frac_of_roofline"] = round(max(row["GBps"] / peaks["hbm_gbs"], row["TFLOPs"] / peaks["bf16_tflops"]), 4)
+        out.append(row)
+    return out
+
+
 def _check(rc, name):
-    global launches
+    global launches, _work
     if rc != 0:
+        _work = None
         raise KernelError(f"{name}: {lib().ferrum_last_error().decode()}")
     launches += 1
+    if _profile is not None:
+        _profile.mark(name, _work)
+    _work = None
+
+
+def _gemm_work(x, w, out, M, N, K, products=1):
+    """(bytes, flops) of a product for the profile: every weight once, the tokens and the result."""
+    global _work
+    if _profile is not None:
+        _work = (products * N * K * w.element_size() + M * K * x.element_size() + M * N * out.element_size(),
+                 2.0 * products * M * N * K)
 
 
 def _ptr(t):
@@ -195,6 +269,7 @@ def gemm_tc_deferred(x, w, err, workspace, M=None, N=None, dual_offset=0, n_ctas
     if x.shape[1] != K or x.shape[0] < M:
         raise KernelError(f"gemm_tc_deferred: shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)}")
     layout = (c_int * 4)()
+    _gemm_work(x, w, workspace, M, N, K, 2 if dual_offset else 1)
     _check(lib().ferrum_gemm_tc_deferred(_ptr(x), _ptr(w), dtype_code(x.dtype), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
                                          c_int(w.stride(0)), c_int(w.shape[0]), c_int(dual_offset), c_int(n_ctas),
                                          _ptr(workspace), c_longlong(workspace.numel()), layout, _ptr(err), _stream()),
@@ -212,6 +287,7 @@ def gemm_generic(x, w, out, epilogue, M=None):
     want = x.dtype if epilogue == EPI_STORE else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm: out must be {want} for epilogue {epilogue}")
+    _gemm_work(x, w, out, M, N, K)
     _check(lib().ferrum_gemm_generic(_ptr(x), _ptr(w), _ptr(out), dtype_code(x.dtype), c_int(M), c_int(N), c_int(K),
                                      c_int(x.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue),
                                      _stream()), "gemm_generic")
@@ -253,6 +329,7 @@ def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_
         raise KernelError(f"gemm_tc: out must be {want} for epilogue {epilogue}")
     _need(workspace, torch.float32, "workspace")
     _need(counters, torch.int32, "counters")
+    _gemm_work(x, w, out, M, N, K, 2 if dual_offset else 1)
     _check(lib().ferrum_gemm_tc(_ptr(x), _ptr(w), _ptr(out), dtype_code(x.dtype), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
                                 c_int(w.stride(0)), c_int(out.stride(0)), c_int(w.shape[0]), c_int(epilogue),
                                 c_int(dual_offset), c_int(n_ctas), _ptr(workspace), c_longlong(workspace.numel()),

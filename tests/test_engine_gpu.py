@@ -165,3 +165,21 @@ def test_steps_queued_ahead_change_nothing(cuda, model_dirs, dtype):
     queued, r1 = run(True)
     assert queued == one_by_one and r0 == r1
     assert one_by_one[2] == probe[:probe.index(probe[5]) + 1] and r0[2] == "stop"
+
+
+def test_profile_mode_times_every_kernel(cuda, model_dirs):
+    """Engine(profile=True): every launch is timed on its own (no CUDA graphs, one step at a time);
+    the report has one row per kernel, the shares add up, the products report their rates, and the
+    tokens are those of an ordinary engine."""
+    vocab = TINY["D"][0]["vocab_size"]
+    prompt = random_tokens(40, vocab, 95)
+    want = engine(model_dirs, "D", "bfloat16").generate([prompt], max_new_tokens=6)[0]
+    eng = engine(model_dirs, "D", "bfloat16", profile=True)
+    assert eng.generate([prompt], max_new_tokens=6) == [want]
+    rows = eng.profile_report()
+    names = {r["kernel"] for r in rows}
+    assert {"rmsnorm", "rope_cache_write", "sample"} <= names and any(n.startswith("gemm_tc") for n in names), names
+    assert abs(sum(r["share"] for r in rows) - 1.0) < 0.01 and all(r["ms"] >= 0 and r["launches"] > 0 for r in rows)
+    gemm = next(r for r in rows if r["kernel"].startswith("gemm_tc"))
+    assert gemm["GBps"] > 0 and gemm["TFLOPs"] > 0
+    assert eng.runner.graph_replays == 0 and eng.profile_report() == []

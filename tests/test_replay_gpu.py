@@ -270,3 +270,23 @@ def test_one_layer_at_the_widths_of_the_8b_model(cuda, wide_layer, dtype):
         assert (got.argmax(-1) == ref.argmax(-1)).mean() >= 0.99
     else:
         assert_close(got, ref, dtype, "8b widths")
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "bfloat16"), ("D", "bfloat16"), ("D", "float16"), ("D", "float32")])
+def test_no_kernel_writes_past_its_scratch_buffers(cuda, model_dirs, name, dtype, monkeypatch):
+    """The debugging mode with guarded scratch buffers: every buffer of a step is allocated to its
+    exact size with guard words behind it, and after every step of the mixed workload (portions,
+    single tokens, tails of every tile shape) the guard words are intact.  That the check can fail
+    is shown by overwriting one guard word by hand."""
+    from ferrum_b200 import KernelError
+    monkeypatch.setenv("FERRUM_CANARY", "1")
+    s, toks, schedule = mixed_case(model_dirs, name, dtype)
+    assert s.runner.ctx.scratch.guard == 64 and not s.runner.use_graphs
+    r, _ = run_mixed(s, toks, schedule)              # (every step ends with the check: runner.check_device_errors)
+    assert s.runner.ctx.scratch.check() == [] and len(s.runner.ctx.scratch._guards) >= 5
+    for k in toks:
+        assert_close(r.logits(k, len(toks[k])), plain_logits(model_dirs[name], dtype, toks[k]), dtype, f"guarded {k}")
+    first = next(iter(s.runner.ctx.scratch._guards))
+    s.runner.ctx.scratch._guards[first][3] = 0
+    with pytest.raises(KernelError, match="wrote past the end of: " + first):
+        s.runner.check_device_errors()
