@@ -472,7 +472,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         fence_proxy_async();   // the matrix unit reads these rows
       }
       // P replaces the first half of the scores' columns (every score of the row is in registers
-      // by now); the scores of stage j + 2 come to these columns only after P V of this stage
+      // by now); the scores of stage j + 2 come to these columns only after P V of this stage.
+      // (Storing it 32 keys at a time behind the exponentials, with one wait at the end, was
+      // measured slower: the wait is not what a stage spends its time on.)
 #pragma unroll
       for (int c0 = 0; c0 < BN / 2; c0 += 32) tmem_st32u(lane_addr + Cfg::S_COL + (2 * t + buf) * BN + c0, &pk[c0]);
       tc_fence_before();     // this thread's tensor-memory accesses precede the products that follow
@@ -534,6 +536,443 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ the CTA-pair kernel (head size 128)
+// Two CTAs of a cluster take the two row tiles of an item, one each, and every product is ONE
+// tcgen05.mma.cta_group::2 over both (M = 256):
+//   S = Q K^T   Q sits in tensor memory (each CTA's own 128 rows, written there once per item),
+//               and the 128 keys of a stage are split between the CTAs' shared memories (64 each)
+//   O += P V    P in tensor memory as before, V split by columns: each CTA stages all 128 keys
+//               of its 64 of the 128 value columns
+// so an instruction fetches 2 KB per CTA from shared memory for 512 KFLOP of that CTA's rows
+// (6 KB for 262 KFLOP above), each CTA loads half of every stage's keys and values by TMA (no
+// multicast: the halves are different data), and a stage is 128 keys.  Tensor memory per CTA:
+// two score buffers of 128 columns, O in 128, Q in 64.  The leader issues all products and commits
+// to both CTAs' barriers; the peers' threads announce P on the leader's barriers.
+//
+// Measured on a B200 (32 query heads on 8, 2,048 / 8,192 tokens of one request): 82 / 913 us
+// against 45 / 520 us of the kernel above, so the launch below takes this kernel only on request
+// (ferrum_set_attention_pair_kernel).  Per-thread clocks showed why: the matrix unit is idle for
+// most of a stage in both kernels; a stage's time goes to its softmax (64 exponentials a thread at
+// the special-function unit's rate, the row maximum, the P store and its wait), and here the two
+// row tiles' softmax runs on two SMs in lock-step with one product stream instead of overlapping
+// on one SM, while both SMs pay the per-item start (Q through registers into tensor memory).
+// Halving the shared-memory operand traffic does not touch what binds.
+template <int NS>
+struct AttnPairConfig {
+  static constexpr int D = 128, BN = 128;
+  static constexpr int K_HALF_BYTES = (BN / 2) * 128;          // this CTA's 64 keys x 64 columns
+  static constexpr int K_STAGE_BYTES = 2 * K_HALF_BYTES;      // ... x 128 columns
+  static constexpr int V_STAGE_BYTES = BN * 128;               // all 128 keys x this CTA's 64 columns
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + NS * K_STAGE_BYTES;
+  static constexpr int OFF_BARS = OFF_V + NS * V_STAGE_BYTES;
+  static constexpr int N_BARS = 1 + 5 * NS + 6;
+  static constexpr int SMEM_BYTES = OFF_BARS + N_BARS * 8 + 1024;
+  static constexpr int S_COL = 0, O_COL = 2 * BN, Q_COL = 2 * BN + D;   // 256 + 128 + 64 columns
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int THREADS = 32 * 10;                      // producer, issuer, eight softmax warps (two threads per row)
+  static_assert(SMEM_BYTES <= 232448, "stages do not fit shared memory");
+};
+
+template <int NS, bool HALF>
+__global__ void __launch_bounds__(AttnPairConfig<NS>::THREADS, 1)
+attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map_kv, const uint16_t* __restrict__ q, int ldq,
+                         const AttnTcParams p) {
+  using Cfg = AttnPairConfig<NS>;
+  constexpr int D = Cfg::D, BN = Cfg::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ float row_max[2][2][128];          // [stage parity][key half][row]: what the two threads of a row tell each other
+  __shared__ float row_sum[2][128];             // [key half][row]: their sums, at the end
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();      // 0: leader (row tile 0), 1: its peer (row tile 1)
+  const int kvh = blockIdx.x >> 1;
+  const int* wk = p.work + (size_t)blockIdx.y * 8;
+  const int req = wk[0], row0 = wk[1], kv_begin = wk[2], kv_end = wk[3], n_splits = wk[4];
+  if (n_splits == 0 || kv_end <= kv_begin) return;  // padding of a fixed-size work list (the same for both CTAs)
+  const int part = wk[5] * p.Hkv + kvh;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + Cfg::OFF_BARS;
+  const uint32_t q_ready = bar_base;                                       // leader: every softmax thread of the pair has put its part of Q in place
+  auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };            // leader: bytes of both CTAs
+  auto k_empty = [&](int s) { return bar_base + 8u * (1 + NS + s); };      // every CTA: the leader's commit
+  auto v_full = [&](int s) { return bar_base + 8u * (1 + 2 * NS + s); };
+  auto v_empty = [&](int s) { return bar_base + 8u * (1 + 3 * NS + s); };
+  auto v_landed = [&](int s) { return bar_base + 8u * (1 + 4 * NS + s); }; // every CTA: the last stage's values are there
+  auto s_ready = [&](int b) { return bar_base + 8u * (1 + 5 * NS + b); };  // every CTA
+  auto p_ready = [&](int b) { return bar_base + 8u * (1 + 5 * NS + 2 + b); };  // leader: every softmax thread of the pair
+  const uint32_t pv_done = bar_base + 8u * (1 + 5 * NS + 4);               // every CTA
+  const uint32_t o_done = bar_base + 8u * (1 + 5 * NS + 5);                // every CTA
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    prefetch_tensormap(&map_kv);
+    mbar_init(q_ready, 16);       // one arrival per softmax warp of the pair (8 warps in each CTA)
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
+      mbar_init(v_landed(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_ready(b), 1);
+      mbar_init(p_ready(b), 16);
+    }
+    mbar_init(pv_done, 1);
+    mbar_init(o_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_p = &abort_flag;
+  auto wait_all = [&](uint32_t bar, uint32_t parity) {
+    const bool got = mbar_wait(bar, parity, abort_p);
+    return __all_sync(0xffffffffu, got) != 0;
+  };
+  pdl_wait();
+
+  const int G = p.G, tok = p.tok;
+  const int qs = p.q_start[req];
+  const int q_len = p.q_start[req + 1] - qs;
+  const int pos0 = p.pos0[req];
+  const int tok0 = row0 / G;
+  const int kv0 = kv_begin & ~(BN - 1);       // stages start on 128-key borders: whole pages
+  const int n_j = (kv_end - kv0 + BN - 1) / BN;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    // Keys: this CTA's 64 of the stage's 128, all columns.  Values: all 128 keys, this CTA's 64
+    // columns.  Lane i looks up page i of a stage's 128 keys one stage ahead (the lookups overlap the
+    // waits instead of standing in front of every copy); the keys' pages are a part of the same list.
+    const int ps = p.page_size;
+    const int k_pages = (BN / 2) / ps, v_pages = BN / ps;
+    const int* bt = p.block_table + (size_t)req * p.table_width;
+    auto pages_of = [&](int j) {  // this lane's page of stage j; -1 (the box reads as zeros) where there is none
+      if (lane >= v_pages || j >= n_j) return -1;
+      const int lp = ((kv0 + j * BN) >> p.page_shift) + lane;
+      const int page = lp < p.table_width ? bt[lp] : -1;
+      if (page < 0 && lp * ps < kv_end && (lp + 1) * ps > kv_begin) atomicExch(p.err, 5);
+      return page;
+    };
+    auto load_stage = [&](int j, int kv, int page) {   // page: this lane's page of the stage's values (lane < v_pages)
+      const int s = j % NS;
+      const uint32_t parity = ((j / NS) & 1) ^ 1;
+      const uint32_t full = kv ? v_full(s) : k_full(s);
+      bool ok = true;
+      if (lane == 0) {
+        ok = mbar_wait(kv ? v_empty(s) : k_empty(s), parity, abort_p);
+        if (ok && rank == 0) mbar_expect_tx(full, 2 * (kv ? Cfg::V_STAGE_BYTES : Cfg::K_STAGE_BYTES));
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return false;
+      const uint32_t leader_full = map_to_cta(full, 0);
+      if (kv) {
+        if (lane < v_pages) {
+          const int y = page < 0 ? -ps : ((page * 2 + 1) * p.Hkv + kvh) * ps;   // a negative row: the box reads as zeros
+          tma_load_2d_pair(smem_base + Cfg::OFF_V + s * Cfg::V_STAGE_BYTES + lane * ps * 128, &map_kv, leader_full,
+                           (int)rank * 64, y);
+        }
+      } else {
+        const int mine = __shfl_sync(0xffffffffu, page, ((int)rank * k_pages + lane) & 31);   // the keys' pages: this CTA's half of the list
+        if (lane < k_pages) {
+          const int y = mine < 0 ? -ps : ((mine * 2) * p.Hkv + kvh) * ps;
+          const uint32_t dst = smem_base + Cfg::OFF_K + s * Cfg::K_STAGE_BYTES + lane * ps * 128;
+          tma_load_2d_pair(dst, &map_kv, leader_full, 0, y);
+          tma_load_2d_pair(dst + Cfg::K_HALF_BYTES, &map_kv, leader_full, 64, y);
+        }
+      }
+      return true;
+    };
+    bool ok = true;
+    int page_prev = -1, page_cur = pages_of(0);
+    for (int j = 0; ok && j <= n_j; ++j) {   // keys of stage j, then values of stage j - 1
+      const int page_next = pages_of(j + 1);
+      if (j < n_j) ok = load_stage(j, 0, page_cur);
+      if (ok && j > 0) ok = load_stage(j - 1, 1, page_prev);
+      page_prev = page_cur;
+      page_cur = page_next;
+    }
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0) atomicExch(p.err, 30);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (the leader's, for both CTAs)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc_qk = umma_idesc_16bit(256, BN, HALF);
+      const uint32_t idesc_pv = umma_idesc_16bit(256, D, HALF) | (1u << 16);  // B (values) is MN-major
+      const uint32_t q_tmem = tmem_base + Cfg::Q_COL, o_tmem = tmem_base + Cfg::O_COL;
+      auto issue_qk = [&](int s, int buf) {
+        const uint32_t k_addr = smem_base + Cfg::OFF_K + s * Cfg::K_STAGE_BYTES;
+        const uint32_t s_tmem = tmem_base + Cfg::S_COL + buf * BN;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {  // 16 elements of the head on: 8 columns of Q, 32 bytes of a key row
+          const int h = kk >> 2, in = kk & 3;
+          umma_16bit_pair_ts(s_tmem, q_tmem + kk * 8, umma_desc_k_sw128(k_addr + h * Cfg::K_HALF_BYTES) + (uint64_t)(in * 2),
+                             idesc_qk, kk > 0);
+        }
+      };
+      auto issue_pv = [&](int s, int buf, bool accumulate) {
+        const uint32_t v_addr = smem_base + Cfg::OFF_V + s * Cfg::V_STAGE_BYTES;
+        const uint32_t p_tmem = tmem_base + Cfg::S_COL + buf * BN;  // P lies over the scores it came from
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)  // 16 keys on: 8 columns of P, 16 rows of V
+          umma_16bit_pair_ts(o_tmem, p_tmem + kk * 8, umma_desc_mn_sw128(v_addr + kk * 16 * 128, Cfg::V_STAGE_BYTES, 1024),
+                             idesc_pv, accumulate || kk > 0);
+      };
+      bool ok = mbar_wait_cluster(q_ready, 0, abort_p);
+      int code = 32;
+      for (int jj = 0; ok && jj < 2 && jj < n_j; ++jj) {
+        ok = mbar_wait(k_full(jj % NS), (jj / NS) & 1, abort_p);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(jj % NS, jj);
+        umma_commit_pair(s_ready(jj), 3);
+        umma_commit_pair(k_empty(jj % NS), 3);
+      }
+      for (int j = 0; ok && j < n_j; ++j) {
+        const int s = j % NS;
+        const int jn = j + 2;
+        const bool more = jn < n_j;
+        const int s2 = jn % NS;
+        ok = mbar_wait(v_full(s), (j / NS) & 1, abort_p);
+        if (!ok) {
+          code = 33;
+          break;
+        }
+        if (j + 1 == n_j) umma_commit_pair(v_landed(s), 3);   // the CTAs may clear the rows past the last key
+        ok = mbar_wait_cluster(p_ready(j & 1), (j >> 1) & 1, abort_p);
+        if (!ok) {
+          code = 34;
+          break;
+        }
+        tc_fence_after();
+        issue_pv(s, j & 1, j > 0);
+        umma_commit_pair(pv_done, 3);
+        if (j + 1 == n_j) umma_commit_pair(o_done, 3);
+        umma_commit_pair(v_empty(s), 3);
+        if (more) {
+          ok = mbar_wait(k_full(s2), (jn / NS) & 1, abort_p);
+          if (!ok) {
+            code = 33;
+            break;
+          }
+          tc_fence_after();
+          issue_qk(s2, j & 1);
+          umma_commit_pair(s_ready(j & 1), 3);
+          umma_commit_pair(k_empty(s2), 3);
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicExch(p.err, code);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax and output: two threads per row of this CTA's tile
+    // Warps 2..5 take the first 64 keys of every stage, warps 6..9 the other 64 (a warp reaches the
+    // 32 lanes of tensor memory that its number modulo 4 names, so warps w and w + 4 share rows).
+    // The two threads of a row agree on the row's maximum through shared memory once per stage;
+    // each keeps the sum of its own keys, and they split the columns of O between them.
+    const int t = (int)rank;
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;             // which 64 keys of a stage, which 64 columns of O
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int tok_in_req = tok0 + t * tok + r / G;
+    const bool row_valid = r < tok * G && tok_in_req < q_len;
+    const int qpos = pos0 + tok_in_req;
+    const int tile_first = tok0 + t * tok;
+    const int qpos_min = pos0 + tile_first;
+    const int qpos_max = pos0 + min(q_len - 1, tile_first + tok - 1);
+    const bool tile_full = tok * G == 128 && tile_first + tok <= q_len;
+    const uint32_t leader_q_ready = map_to_cta(q_ready, 0);
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };  // the two warps of these rows
+    constexpr int HB = BN / 2;                    // keys of a stage per thread
+    // ---- this row of Q into tensor memory: this thread's 64 of the 128 elements = 32 columns of two
+    {
+      uint32_t qw[32];
+      const uint4* src = reinterpret_cast<const uint4*>(q + (size_t)(qs + (row_valid ? tok_in_req : 0)) * ldq +
+                                                        (size_t)(kvh * G + r % G) * D + half * 64);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 v = row_valid ? src[i] : make_uint4(0, 0, 0, 0);
+        qw[4 * i] = v.x; qw[4 * i + 1] = v.y; qw[4 * i + 2] = v.z; qw[4 * i + 3] = v.w;
+      }
+      tmem_st32u(lane_addr + Cfg::Q_COL + half * 32, qw);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_q_ready);   // (one arrival a warp: a peer's arrivals cross to the leader's SM)
+    }
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_j; ++j) {
+      const int buf = j & 1;
+      ok = wait_all(s_ready(buf), (j >> 1) & 1);
+      if (!ok) {
+        abort_flag = 1;
+        if (lane == 0) atomicExch(p.err, 35);
+        break;
+      }
+      tc_fence_after();
+      float s[HB];
+#pragma unroll
+      for (int c0 = 0; c0 < HB; c0 += 32) tmem_ld32(lane_addr + Cfg::S_COL + buf * BN + half * HB + c0, &s[c0]);
+      const int key0 = kv0 + j * BN;
+      const bool unmasked = tile_full && key0 + BN - 1 <= qpos_min && key0 >= kv_begin && key0 + BN <= kv_end &&
+                            (p.window == 0 || key0 > qpos_max - p.window);
+      if (!unmasked) {
+        const int hi = row_valid ? min(qpos, kv_end - 1) : -1;
+        const int lo = max(kv_begin, p.window > 0 ? qpos - p.window + 1 : 0);
+#pragma unroll
+        for (int c = 0; c < HB; ++c) {
+          const int key = key0 + half * HB + c;
+          if (key > hi || key < lo) s[c] = -INFINITY;
+        }
+      }
+      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+#pragma unroll
+      for (int c = 4; c < HB; c += 4) {
+        mx0 = fmaxf(mx0, s[c]);
+        mx1 = fmaxf(mx1, s[c + 1]);
+        mx2 = fmaxf(mx2, s[c + 2]);
+        mx3 = fmaxf(mx3, s[c + 3]);
+      }
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      row_max[buf][half][r] = mx;
+      pair_sync();
+      mx = fmaxf(mx, row_max[buf][half ^ 1][r]);
+      const float cand = fmaxf(m_run, mx * p.scale_log2);
+      const bool grow = cand > m_run + TC_LAZY;     // the same in both threads of the row: they share mx and m_run
+      if (__any_sync(0xffffffffu, grow)) {
+        const float f = m_run == -INFINITY ? 0.f : fast_exp2(m_run - cand);
+        l_run *= f;
+        if (j > 0) {
+          ok = wait_all(pv_done, (j - 1) & 1);
+          if (!ok) {
+            abort_flag = 1;
+            if (lane == 0) atomicExch(p.err, 37);
+            break;
+          }
+          tc_fence_after();
+#pragma unroll 1
+          for (int c0 = 0; c0 < D / 2; c0 += 32) {
+            float o[32];
+            tmem_ld32(lane_addr + Cfg::O_COL + half * (D / 2) + c0, o);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] *= f;
+            tmem_st32(lane_addr + Cfg::O_COL + half * (D / 2) + c0, o);
+          }
+        }
+        m_run = cand;
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      uint32_t pk[HB / 2];
+#pragma unroll
+      for (int c = 0; c < HB; c += 4) {
+        const float e0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_use)), e1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_use));
+        const float e2 = fast_exp2(fmaf(s[c + 2], p.scale_log2, -m_use)), e3 = fast_exp2(fmaf(s[c + 3], p.scale_log2, -m_use));
+        l0 += e0;
+        l1 += e1;
+        l2 += e2;
+        l3 += e3;
+        pk[c / 2] = pack2_16<HALF>(e0, e1);
+        pk[c / 2 + 1] = pack2_16<HALF>(e2, e3);
+      }
+      l_run += (l0 + l1) + (l2 + l3);
+      if (j + 1 == n_j && kv_end - key0 < BN) {
+        // rows of the last stage past the key range may hold anything: cleared in this CTA's half of
+        // the values once the stage has landed (the leader says so), before P is announced
+        const int s_last = j % NS;
+        ok = wait_all(v_landed(s_last), 0);
+        if (!ok) {
+          abort_flag = 1;
+          if (lane == 0) atomicExch(p.err, 38);
+          break;
+        }
+        const int first_bad = kv_end - key0;
+        uint8_t* v = smem + Cfg::OFF_V + s_last * Cfg::V_STAGE_BYTES;
+        const int n16 = (BN - first_bad) * 8;
+        for (int i = half * 128 + r; i < n16; i += 256) *reinterpret_cast<uint4*>(v + first_bad * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+        fence_proxy_async();
+      }
+      // P (two values a column) over the first half of the stage's score columns: this thread's 32 of the 64
+      tmem_st32u(lane_addr + Cfg::S_COL + buf * BN + half * (HB / 2), pk);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(p_ready(buf), 0));
+    }
+    if (ok) ok = wait_all(o_done, 0);
+    if (!ok) {
+      abort_flag = 1;
+      if (lane == 0) atomicExch(p.err, 36);
+    } else {
+      tc_fence_after();
+      // the row's sum is the two threads' sums
+      row_sum[half][r] = l_run;
+      pair_sync();
+      const float l_row = l_run + row_sum[half ^ 1][r];
+      const bool whole = n_splits == 1;
+      const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+      uint16_t* orow = p.out + (size_t)(qs + tok_in_req) * p.ldo + (size_t)(kvh * G + r % G) * D + half * (D / 2);
+      const size_t prow = (size_t)part * (2 * tok * G) + t * tok * G + r;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        float o[32];
+        tmem_ld32(lane_addr + Cfg::O_COL + half * (D / 2) + c0, o);
+        if (!row_valid) continue;
+        if (whole) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 v;
+            v.x = pack2_16<HALF>(o[c] * inv, o[c + 1] * inv);
+            v.y = pack2_16<HALF>(o[c + 2] * inv, o[c + 3] * inv);
+            v.z = pack2_16<HALF>(o[c + 4] * inv, o[c + 5] * inv);
+            v.w = pack2_16<HALF>(o[c + 6] * inv, o[c + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            *reinterpret_cast<float4*>(p.part_o + prow * D + half * (D / 2) + c0 + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+        }
+      }
+      if (!whole && row_valid && half == 0) {
+        p.part_ml[prow * 2] = m_run;
+        p.part_ml[prow * 2 + 1] = l_row;
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) {
+    const long long t0c = clock64();
+    while (clock64() - t0c < 2000000LL) {
+    }
+  }
+  // neither CTA may leave while the other can still signal its barriers or read its tensor memory
+  tc_fence_before();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -636,12 +1075,47 @@ int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const Att
   return 0;
 }
 
+template <int NS, bool HALF>
+int launch_attention_tc_pair(const CUtensorMap& mkv, const void* q, int ldq, const AttnTcParams& p, int n_work, cudaStream_t stream) {
+  using Cfg = AttnPairConfig<NS>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_pair_kernel<NS, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    FERRUM_CHECK_ARG(e == cudaSuccess, "attention_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * p.Hkv, n_work);      // the two CTAs of a pair are neighbours in x
+  cfg.blockDim = dim3(Cfg::THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ferrum_dependent_launch_enabled() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tc_pair_kernel<NS, HALF>, mkv, (const uint16_t*)q, ldq, p);
+  FERRUM_CHECK_ARG(e == cudaSuccess, "attention_tc: pair kernel launch failed: %s", cudaGetErrorString(e));
+  FERRUM_CHECK_LAUNCH("attention_tc_pair");
+  return 0;
+}
+
+bool g_attention_pair = false;
+
 // The shape in use: two row tiles per CTA that share three stages of 64 keys.  One tile with
 // stages of 128 keys (half the waits and fences per key, no second tile to fill the matrix unit
 // while the first computes P) was measured slower: 67.8 against 51.8 us for a 2048-token prompt.
 constexpr int TC_TILES = 2, TC_BN = 64, TC_STAGES = 3;
 
 }  // namespace
+
+// Head size 128 runs on CTA pairs (one row tile per CTA, see attention_tc_pair_kernel) unless this is
+// switched off; the single-CTA kernel takes the same work items.
+FERRUM_API void ferrum_set_attention_pair_kernel(int on) { g_attention_pair = on != 0; }
 
 // Tokens per work item for a group of G query heads per KV head (an item is TC_TILES tiles of
 // 128 / G tokens), or 0 when this kernel does not take the shape: head sizes 64 and 128; pages
@@ -685,8 +1159,12 @@ FERRUM_API int ferrum_attention_tc(const void* q, int ldq, long long q_rows, voi
   p.Hkv = Hkv; p.G = G; p.tok = tok; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   CUtensorMap mq, mkv;
-  if (int r = query_map(q, q_rows, ldq, Hq, D, G, tok, &mq)) return r;
   if (int r = cache_map(kv_plane, n_pages, Hkv, page_size, D, &mkv)) return r;
+  if (D == 128 && g_attention_pair) {
+    if (dtype == FERRUM_F16) return launch_attention_tc_pair<3, true>(mkv, q, ldq, p, n_work, stream);
+    return launch_attention_tc_pair<3, false>(mkv, q, ldq, p, n_work, stream);
+  }
+  if (int r = query_map(q, q_rows, ldq, Hq, D, G, tok, &mq)) return r;
   if (dtype == FERRUM_F16) {
     if (D == 64) return launch_attention_tc<64, TC_TILES, TC_BN, TC_STAGES, true>(mq, mkv, p, n_work, stream);
     return launch_attention_tc<128, TC_TILES, TC_BN, TC_STAGES, true>(mq, mkv, p, n_work, stream);

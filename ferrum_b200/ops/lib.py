@@ -421,6 +421,12 @@ def attention_tc_tokens(D, G, page_size, kv_plane=None, page_stride=0):
     return int(lib().ferrum_attention_tc_tokens(c_int(D), c_int(G), c_int(page_size)))
 
 
+def set_attention_pair_kernel(on: bool):
+    """Head size 128 runs the tcgen05 attention on CTA pairs (on by default); off: the single-CTA
+    kernel takes the same work items (for comparisons)."""
+    lib().ferrum_set_attention_pair_kernel(c_int(1 if on else 0))
+
+
 def attention_tc(q, out, kv_plane, page_stride, page_size, block_table, q_start, pos0, work, n_work, part_o, part_ml,
                  Hq, Hkv, D, scale, window, err):
     """tcgen05 attention over work items of attention_tc_tokens * G rows (prompt portions)."""

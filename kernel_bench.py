@@ -46,6 +46,8 @@ def main():
     ap.add_argument("--deferred", action="store_true", help="gemm: leave the partials to the consumer (as decoding does)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"],
                     help="fp32 times the CUDA-core kernels of the true 32-bit path (its fraction is of the FFMA peak)")
+    ap.add_argument("--attention-pair", choices=["on", "off"], default=None,
+                    help="attn_prefill at head size 128: the kernel of two CTAs on one tile (on) or of one CTA (off)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--no-dependent-launch", action="store_true", help="plain stream order between the launches")
     args = ap.parse_args()
@@ -58,6 +60,8 @@ def main():
     from ferrum_b200.ops import lib as ops
     ops.require_cuda()
     ops.set_dependent_launch(not args.no_dependent_launch)
+    if args.attention_pair is not None:
+        ops.set_attention_pair_kernel(args.attention_pair == "on")
     pk = peaks()
     dev = "cuda"
     td = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]

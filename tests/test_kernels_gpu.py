@@ -391,11 +391,19 @@ def test_attention_flash(ops, Hq, Hkv, D, ps, window, h16):
         t0 += ql
 
 
+@pytest.fixture(params=[True, False], ids=["pair", "single"])
+def pair(request, ops):
+    """Head size 128 runs on CTA pairs by default; the single-CTA kernel is tested too."""
+    ops.set_attention_pair_kernel(request.param)
+    yield request.param
+    ops.set_attention_pair_kernel(True)
+
+
 @pytest.mark.parametrize("h16", H16)
 @pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(4, 2, 64, 16, 0), (6, 2, 64, 8, 0), (8, 1, 128, 16, 0), (32, 8, 128, 16, 0),
                                                 (3, 3, 128, 32, 0), (4, 2, 64, 64, 21), (8, 2, 128, 16, 300),
-                                                (10, 2, 128, 16, 0), (14, 2, 64, 16, 90)])
-def test_attention_tc(ops, Hq, Hkv, D, ps, window, h16):
+                                                (10, 2, 128, 16, 0), (14, 2, 64, 16, 90), (4, 1, 128, 8, 700)])
+def test_attention_tc(ops, Hq, Hkv, D, ps, window, h16, pair):
     """The tcgen05 kernel on prompt portions: a whole prompt, a late portion of a long request
     (its key range is split), a portion that ends inside a tile, beside decoded tokens that
     stay on the other kernel.  Groups that do not divide 128 leave padding rows in the tiles."""
