@@ -5,10 +5,14 @@
 // The same code runs a prompt portion and a decoded token: a row is one token and up to four
 // query heads of one KV head, and reads keys lo..pos from the cache (the rotary kernel has
 // already stored this step's keys).  A CTA of four warps handles a row, or one 128-key split of
-// it.  A warp takes every fourth key of the CTA's range; its 32 lanes read one key row
-// together (lane i reads elements i, i + 32, ... : whole 128-byte lines), so a K/V row read
-// once serves the row's heads.  Per head the warp keeps an online softmax (max, sum and the
-// weighted values) in float32 with expf; the four warps are then merged in warp order.
+// it, in tiles of 32 keys (16 for head sizes above 128): the four warps bring the tile's key and
+// value rows into shared memory together (16-byte loads where the rows allow, converted to
+// float32), then warp g works for head g alone: lane j forms the score of key j from shared
+// memory (no reduction across lanes: a lane walks the head size in order), the warp takes the
+// tile's maximum and sum by shuffles, leaves the weights in shared memory, and lane i adds the
+// weighted values of elements i, i + 32, ... in key order.  Max, sum and the weighted values stay
+// in float32 registers with expf.  (Before, a warp read one key row together and reduced every
+// score across its lanes: some 90 instructions per key and head against about 15 here.)
 //
 // Two ways to hand out the work, chosen by the number of rows alone.  Many rows (a prompt
 // portion): one CTA per row walks its whole key range and writes the output.  Few rows
@@ -21,33 +25,82 @@
 #include "common.cuh"
 
 constexpr int AG_WARPS = 4;
-constexpr int AG_HEADS = 4;      // query heads of one KV head that share a CTA's key reads
+constexpr int AG_HEADS = 4;      // query heads of one KV head that share a CTA's key reads: one warp each
 constexpr int AG_SPLIT = 128;    // keys per split (absolute positions s * 128 .. s * 128 + 127)
 constexpr int AG_MAX_D = 256;
 constexpr int AG_DI = AG_MAX_D / 32;
-constexpr int AG_KEYS = 4;       // keys a warp fetches together
+static_assert(AG_HEADS == AG_WARPS, "warp g works for head g");
 
-// (m, l, o) of b folded into a: the softmax of the union of two key sets.
-__device__ __forceinline__ void ag_fold(float& m, float& l, float& o, float mb, float lb, float ob) {
-  const float m_new = fmaxf(m, mb);
-  const float fa = m == -INFINITY ? 0.f : expf(m - m_new);
-  const float fb = mb == -INFINITY ? 0.f : expf(mb - m_new);
-  l = l * fa + lb * fb;
-  o = o * fa + ob * fb;
-  m = m_new;
+// Shared memory of a CTA for head sizes up to 32 * DI, two tiles deep: keys [2][TK][32 DI + 4]
+// (the 4 floats of padding make a quarter warp's 16-byte reads of one column of eight rows hit
+// different banks), values [2][TK][32 DI], queries [4][32 DI], weights [4][TK], row offsets
+// [2][TK]; keys, values and queries are zero past the head size.
+template <int DI>
+struct AgTile {
+  static constexpr int TK = DI <= 4 ? 32 : 16;
+  static constexpr int DP = 32 * DI;
+  static constexpr int KS = DP + 4;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + 2 * TK * KS;
+  static constexpr int OFF_Q = OFF_V + 2 * TK * DP;
+  static constexpr int OFF_P = OFF_Q + AG_HEADS * DP;
+  static constexpr int OFF_ROW = OFF_P + AG_HEADS * TK;       // (an even number of floats: the offsets are 8-byte aligned)
+  static constexpr int SMEM_BYTES = (OFF_ROW + 2 * TK * 2) * 4;
+};
+
+__device__ __forceinline__ void ag_cp_async16(void* smem, const void* gmem, int src_bytes) {   // src_bytes 0: sixteen zero bytes
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void ag_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void ag_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Four consecutive elements of a cache or query row as float32: one 16-byte (float) or 8-byte
+// (16-bit types) load where `vec` says the rows are aligned for it, else element by element
+// with a bound.
+template <typename T>
+__device__ __forceinline__ float4 ag_load4(const T* row, int d, int D, bool vec) {
+  float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (vec) {
+    if (d < D) {   // (D is a multiple of 4 here)
+      if constexpr (sizeof(T) == 4) {
+        r = *reinterpret_cast<const float4*>(row + d);
+      } else {
+        const uint2 u = *reinterpret_cast<const uint2*>(row + d);
+        const T* e = reinterpret_cast<const T*>(&u);
+        r = make_float4(to_f32<T>(e[0]), to_f32<T>(e[1]), to_f32<T>(e[2]), to_f32<T>(e[3]));
+      }
+    }
+  } else {
+    if (d < D) r.x = to_f32<T>(row[d]);
+    if (d + 1 < D) r.y = to_f32<T>(row[d + 1]);
+    if (d + 2 < D) r.z = to_f32<T>(row[d + 2]);
+    if (d + 3 < D) r.w = to_f32<T>(row[d + 3]);
+  }
+  return r;
 }
 
 // part: null (the CTA covers the row's whole key range and writes `out`), or the partials
 // [token][head][split slot][D + 2] of the split that blockIdx.y names.
+// The tile after the one being worked on is on its way meanwhile: float32 rows that are 16-byte
+// aligned go from the cache to shared memory by cp.async (nothing passes through registers,
+// absent rows arrive as zeros); other rows are loaded and converted by the threads.
 template <typename T, int DI>
 __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
                          const int* __restrict__ positions, const int* __restrict__ req_of_token,
                          const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
                          long long page_stride, int page_size, int Hq, int Hkv, int D, float scale, int window,
-                         int* __restrict__ err, float* __restrict__ part, int split_slots) {
-  __shared__ float sm_ml[AG_WARPS][AG_HEADS][2];
-  __shared__ float sm_o[AG_WARPS][AG_HEADS][DI * 32];
+                         int* __restrict__ err, float* __restrict__ part, int split_slots, int vec) {
+  using Tile = AgTile<DI>;
+  constexpr int TK = Tile::TK, DP = Tile::DP, KS = Tile::KS;
+  extern __shared__ __align__(16) float ag_smem[];
+  float* const sm_k = ag_smem + Tile::OFF_K;
+  float* const sm_v = ag_smem + Tile::OFF_V;
+  float* const sm_q = ag_smem + Tile::OFF_Q;
+  float* const sm_p = ag_smem + Tile::OFF_P;
+  long long* const sm_row = reinterpret_cast<long long*>(ag_smem + Tile::OFF_ROW);   // [2][TK]: element offset of a key's row; -1: no such key
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = Hq / Hkv;
   const int chunks = (G + AG_HEADS - 1) / AG_HEADS;
@@ -66,93 +119,146 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
     k_end = min(pos + 1, (s + 1) * AG_SPLIT);
   }
   const int* bt = block_table + (size_t)req_of_token[t] * table_width;
+  const size_t v_off = (size_t)Hkv * page_size * D;
+  const bool vec_ok = vec != 0;
+  const bool async_rows = vec_ok && sizeof(T) == 4;
+  const int n_tiles = (k_end - k_begin + TK - 1) / TK;
 
-  float qr[AG_HEADS][DI];
+  // where the rows of tile n lie (threads 0 .. TK-1)
+  auto find_rows = [&](int n) {
+    if (threadIdx.x < TK) {
+      const int key = k_begin + n * TK + threadIdx.x;
+      long long off = -1;
+      if (key < k_end) {
+        const int lp = key / page_size;
+        const int page = lp < table_width ? bt[lp] : -1;
+        if (page < 0) atomicExch(err, 5);      // a key of the row's range without a page: read as absent, and the step fails
+        else off = (long long)page * page_stride + ((long long)kvh * page_size + key % page_size) * D;
+      }
+      sm_row[(n & 1) * TK + threadIdx.x] = off;
+    }
+  };
+  // tile n on its way into its buffer (the caller commits the group)
+  auto load_tile = [&](int n) {
+    const int b = n & 1;
+    float* const kb = sm_k + b * TK * KS;
+    float* const vb = sm_v + b * TK * DP;
+    for (int idx = threadIdx.x; idx < TK * (DP / 4); idx += AG_WARPS * 32) {
+      const int j = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+      const long long off = sm_row[b * TK + j];
+      if (async_rows) {
+        const bool there = off >= 0 && d < D;
+        const T* src = kv_plane + (there ? off + d : 0);
+        ag_cp_async16(&kb[j * KS + d], src, there ? 16 : 0);
+        ag_cp_async16(&vb[j * DP + d], src + (there ? v_off : 0), there ? 16 : 0);
+      } else {
+        float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+        if (off >= 0) {
+          kk = ag_load4<T>(kv_plane + off, d, D, vec_ok);
+          vv = ag_load4<T>(kv_plane + off + v_off, d, D, vec_ok);
+        }
+        *reinterpret_cast<float4*>(&kb[j * KS + d]) = kk;
+        *reinterpret_cast<float4*>(&vb[j * DP + d]) = vv;
+      }
+    }
+  };
+
+  // the row's queries, zero past the head size and for heads the chunk does not have
+  for (int idx = threadIdx.x; idx < AG_HEADS * (DP / 4); idx += AG_WARPS * 32) {
+    const int g = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (g < nh) v = ag_load4<T>(q + (size_t)t * ldq + (size_t)(h0 + g) * D, d, D, vec_ok && ldq % 4 == 0);
+    *reinterpret_cast<float4*>(&sm_q[g * DP + d]) = v;
+  }
+  find_rows(0);
+  __syncthreads();
+  load_tile(0);
+  ag_cp_async_commit();
+
+  float m = -INFINITY, l = 0.f, acc[DI];      // of head `warp` (the same in all its lanes; acc: elements lane + 32 i)
 #pragma unroll
-  for (int g = 0; g < AG_HEADS; ++g)
+  for (int i = 0; i < DI; ++i) acc[i] = 0.f;
+
+  for (int n = 0; n < n_tiles; ++n) {
+    const int b = n & 1;
+    const bool more = n + 1 < n_tiles;
+    if (more) find_rows(n + 1);                // (its buffer was last read for tile n - 1, before the barrier that ended it)
+    __syncthreads();
+    if (more) load_tile(n + 1);
+    ag_cp_async_commit();
+    ag_cp_async_wait<1>();                     // everything but the newest group: tile n is there
+    const bool have = lane < TK && sm_row[b * TK + lane] >= 0;
+    __syncthreads();
+    if (warp < nh) {
+      const float* const kb = sm_k + b * TK * KS;
+      const float* const vb = sm_v + b * TK * DP;
+      // ---- lane j: the score of key j for this warp's head, the head size walked in order
+      float s = -INFINITY;
+      if (have) {
+        const float4* kr = reinterpret_cast<const float4*>(&kb[lane * KS]);
+        const float4* qr = reinterpret_cast<const float4*>(&sm_q[warp * DP]);
+        float dot = 0.f;
+#pragma unroll 8
+        for (int c = 0; c < DP / 4; ++c) {
+          const float4 a = qr[c], k4 = kr[c];
+          dot = fmaf(a.x, k4.x, dot);
+          dot = fmaf(a.y, k4.y, dot);
+          dot = fmaf(a.z, k4.z, dot);
+          dot = fmaf(a.w, k4.w, dot);
+        }
+        s = dot * scale;
+      }
+      const float m_new = fmaxf(m, warp_max(s));
+      float corr = 1.f, pj = 0.f;
+      if (m_new != -INFINITY) {                 // (else no key of the tile exists: nothing changes)
+        corr = m == -INFINITY ? 0.f : expf(m - m_new);
+        pj = s == -INFINITY ? 0.f : expf(s - m_new);
+      }
+      l = l * corr + warp_sum(pj);
+      m = m_new;
+      __syncwarp();                             // the weights of the tile before have been read
+      if (lane < TK) sm_p[warp * TK + lane] = pj;
+      __syncwarp();
+      // ---- lane i: elements i, i + 32, ... of the weighted values, keys in ascending order
+      float a[DI];
+#pragma unroll
+      for (int i = 0; i < DI; ++i) a[i] = acc[i] * corr;
+      const float4* pr = reinterpret_cast<const float4*>(&sm_p[warp * TK]);
+#pragma unroll 2
+      for (int j4 = 0; j4 < TK / 4; ++j4) {
+        const float4 pw = pr[j4];
+        const float* vr = &vb[(j4 * 4) * DP + lane];
+#pragma unroll
+        for (int i = 0; i < DI; ++i) {
+          a[i] = fmaf(pw.x, vr[32 * i], a[i]);
+          a[i] = fmaf(pw.y, vr[DP + 32 * i], a[i]);
+          a[i] = fmaf(pw.z, vr[2 * DP + 32 * i], a[i]);
+          a[i] = fmaf(pw.w, vr[3 * DP + 32 * i], a[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < DI; ++i) acc[i] = a[i];
+    }
+  }
+  ag_cp_async_wait<0>();
+  if (warp >= nh) return;
+  const int h = h0 + warp;
+  if (part == nullptr) {
 #pragma unroll
     for (int i = 0; i < DI; ++i) {
       const int d = lane + 32 * i;
-      qr[g][i] = (g < nh && d < D) ? to_f32<T>(q[(size_t)t * ldq + (size_t)(h0 + g) * D + d]) : 0.f;
+      if (d < D) out[(size_t)t * ldo + (size_t)h * D + d] = from_f32<T>(l > 0.f ? acc[i] / l : 0.f);
     }
-  float m[AG_HEADS], l[AG_HEADS], acc[AG_HEADS][DI];
-#pragma unroll
-  for (int g = 0; g < AG_HEADS; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < DI; ++i) acc[g][i] = 0.f;
-  }
-  const size_t v_off = (size_t)Hkv * page_size * D;
-  // This warp's keys: every fourth key of the range, counted in absolute positions.  AG_KEYS keys
-  // are fetched together (their loads are in flight at once: a warp that handled one key at a
-  // time was a chain of memory latencies) and then folded into the softmax one after the other.
-  int key0 = k_begin + ((warp - k_begin) & (AG_WARPS - 1));
-  for (; key0 < k_end; key0 += AG_WARPS * AG_KEYS) {
-    float kd[AG_KEYS][DI], vd[AG_KEYS][DI];
-    bool have[AG_KEYS];
-#pragma unroll
-    for (int j = 0; j < AG_KEYS; ++j) {
-      const int key = key0 + j * AG_WARPS;
-      const int lp = key / page_size;
-      const int page = (key < k_end && lp < table_width) ? bt[lp] : -1;
-      have[j] = page >= 0;
-      if (key < k_end && page < 0 && lane == 0) atomicExch(err, 5);
-      const T* kr = kv_plane + (size_t)max(page, 0) * page_stride + ((size_t)kvh * page_size + key % page_size) * D;
-      const T* vr = kr + v_off;
-#pragma unroll
-      for (int i = 0; i < DI; ++i) {
-        const int d = lane + 32 * i;
-        kd[j][i] = (have[j] && d < D) ? to_f32<T>(kr[d]) : 0.f;
-        vd[j][i] = (have[j] && d < D) ? to_f32<T>(vr[d]) : 0.f;
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < AG_KEYS; ++j) {
-      if (!have[j]) continue;          // (uniform over the warp)
-#pragma unroll
-      for (int g = 0; g < AG_HEADS; ++g) {
-        if (g >= nh) break;
-        float dot = 0.f;
-#pragma unroll
-        for (int i = 0; i < DI; ++i) dot = fmaf(qr[g][i], kd[j][i], dot);
-        const float s = warp_sum(dot) * scale;
-        const float m_new = fmaxf(m[g], s);
-        const float corr = m[g] == -INFINITY ? 0.f : expf(m[g] - m_new);
-        const float p = expf(s - m_new);
-        l[g] = l[g] * corr + p;
-#pragma unroll
-        for (int i = 0; i < DI; ++i) acc[g][i] = fmaf(p, vd[j][i], acc[g][i] * corr);
-        m[g] = m_new;
-      }
-    }
-  }
-  // ---- the four warps meet in warp order
-#pragma unroll
-  for (int g = 0; g < AG_HEADS; ++g) {
+  } else {
+    float* p = part + (((size_t)t * Hq + h) * split_slots + blockIdx.y) * (D + 2);
     if (lane == 0) {
-      sm_ml[warp][g][0] = m[g];
-      sm_ml[warp][g][1] = l[g];
+      p[0] = m;
+      p[1] = l;
     }
 #pragma unroll
-    for (int i = 0; i < DI; ++i) sm_o[warp][g][lane + 32 * i] = acc[g][i];
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < nh * DI * 32; idx += AG_WARPS * 32) {
-    const int g = idx / (DI * 32), d = idx % (DI * 32);
-    if (d >= D) continue;
-    float M = -INFINITY, L = 0.f, O = 0.f;
-#pragma unroll
-    for (int w = 0; w < AG_WARPS; ++w) ag_fold(M, L, O, sm_ml[w][g][0], sm_ml[w][g][1], sm_o[w][g][d]);
-    if (part == nullptr) {
-      out[(size_t)t * ldo + (size_t)(h0 + g) * D + d] = from_f32<T>(L > 0.f ? O / L : 0.f);
-    } else {
-      float* p = part + (((size_t)t * Hq + h0 + g) * split_slots + blockIdx.y) * (D + 2);
-      p[2 + d] = O;
-      if (d == 0) {
-        p[0] = M;
-        p[1] = L;
-      }
+    for (int i = 0; i < DI; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) p[2 + d] = acc[i];
     }
   }
 }
@@ -227,10 +333,22 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
   const long long rows = (long long)n_tokens * Hkv * ((G + AG_HEADS - 1) / AG_HEADS);
   FERRUM_CHECK_ARG(rows < (1LL << 31), "attention: too many rows");
   const dim3 grid((unsigned)rows, part ? split_slots : 1);
+  // rows of D elements start on 16-byte (float32) or 8-byte (16-bit) borders: vector loads
+  const int vec = D % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)kv_plane & 15) == 0 && page_stride % 4 == 0;
 #define AG_LAUNCH(DI_)                                                                                                  \
-  FERRUM_DISPATCH_DTYPE(dtype, T, (attention_generic_kernel<T, DI_><<<grid, AG_WARPS * 32, 0, stream>>>(              \
+  FERRUM_DISPATCH_DTYPE(dtype, T, {                                                                                     \
+    static bool configured = false;                                                                                     \
+    if (!configured) {                                                                                                  \
+      cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<T, DI_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           AgTile<DI_>::SMEM_BYTES);                                                    \
+      FERRUM_CHECK_ARG(e == cudaSuccess, "attention: cannot reserve %d bytes of shared memory: %s", AgTile<DI_>::SMEM_BYTES, \
+                       cudaGetErrorString(e));                                                                          \
+      configured = true;                                                                                                \
+    }                                                                                                                   \
+    attention_generic_kernel<T, DI_><<<grid, AG_WARPS * 32, AgTile<DI_>::SMEM_BYTES, stream>>>(                        \
       (const T*)q, ldq, (T*)out, ldo, positions, req_of_token, block_table, table_width, (const T*)kv_plane, page_stride, \
-      page_size, Hq, Hkv, D, scale, window, err_flag, part, split_slots)))
+      page_size, Hq, Hkv, D, scale, window, err_flag, part, split_slots, vec);                                          \
+  })
   if (D <= 32) AG_LAUNCH(1);
   else if (D <= 64) AG_LAUNCH(2);
   else if (D <= 128) AG_LAUNCH(4);

@@ -86,7 +86,7 @@ class PagedAttention(Mixer):
         T, Hq, Hkv, D = ctx.n_tokens, self.Hq, self.Hkv, self.D
         rows = T * Hkv * -(-(Hq // Hkv) // 4)
         part, slots = None, 0
-        if rows < 2 * attention_plan.sm_count():
+        if rows < 8 * attention_plan.sm_count():     # (a CTA slot is a third of an SM: under some 2.7 waves of whole rows the last wave idles too much)
             split = ops.attention_generic_split()
             longest = table.shape[1] * cache.page_size if ctx.fixed_shapes else ctx.max_kv_len
             if self.window > 0:
