@@ -18,9 +18,20 @@
 // Llama-3.1-8B shapes with 8 tokens: 43 to 60 % of the copy bandwidth, 65 % with one token; four
 // features per CTA with the next block's weights requested ahead was no faster.)
 //
-// In both kernels the order of the sum of an output is a function of K only, so a token's
+// Stream (float32 with 16-byte aligned rows, up to 64 tokens in passes of 8: the decode steps of
+// the 32-bit path; the skinny kernel remains for 16-bit types and unaligned rows):
+// the skinny kernel keeps too few bytes on their way (its loads wait in registers for the
+// multiplications before them: 22 % of the warp slots busy, 46 % of the copy bandwidth at 8
+// tokens).  Here a CTA of 8 features brings 512-element slices of its weight rows and of the
+// tokens' rows into a ring of three shared-memory stages with cp.async, two stages ahead of the
+// arithmetic, and nothing passes through registers on the way.  A thread owns four consecutive k
+// of every slice for 8 features x 4 tokens; at the end the 32 sums of a lane meet the other
+// lanes' in a butterfly that halves the values at every step (31 shuffles), and the four warps
+// of a token group are added in warp order.
+//
+// In all kernels the order of the sum of an output is a function of K only, so a token's
 // result does not depend on how many other tokens are in the call or where it stands among
-// them.  (Between the two kernels the orders differ: a token decoded alone and the same token
+// them.  (Between the kernels the orders differ: a token decoded alone and the same token
 // inside a larger batch agree to rounding, not bitwise.)
 #include "common.cuh"
 
@@ -218,6 +229,112 @@ gemm_skinny_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __res
   }
 }
 
+// ------------------------------------------------------------------ stream kernel (float32, a few tokens)
+constexpr int ST_FEAT = 8;       // features per CTA
+constexpr int ST_TOK = 8;        // tokens at most
+constexpr int ST_KT = 512;       // elements of K per stage
+constexpr int ST_STAGES = 3;
+constexpr int ST_THREADS = 256;
+constexpr int ST_STAGE_FLOATS = (ST_FEAT + ST_TOK) * ST_KT;
+constexpr int ST_SMEM_BYTES = ST_STAGES * ST_STAGE_FLOATS * 4;
+
+__device__ __forceinline__ void st_cp_async16(void* smem, const void* gmem, int src_bytes) {   // src_bytes 0: sixteen zero bytes
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+}
+
+__global__ void __launch_bounds__(ST_THREADS, 2)
+gemm_stream_kernel(const float* __restrict__ x, const float* __restrict__ w, void* __restrict__ out, int M, int N, int K,
+                   int ldx, int ldw, int ldo, int epi) {
+  extern __shared__ __align__(16) float st_smem[];
+  __shared__ float red[ST_THREADS / 32][32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n0 = blockIdx.x * ST_FEAT;
+  const int n_stages = (K + ST_KT - 1) / ST_KT;
+  const int kq = tid & 127, tg = tid >> 7;   // this thread: elements kq * 4 .. + 3 of every stage, tokens tg * 4 .. + 3 of the pass
+  static_assert(ST_FEAT == ST_TOK, "one loop brings a stage's weight rows and token rows");
+  // More than 8 tokens go in passes of 8; the later passes find the CTA's weight rows in the L2.
+  for (int m0 = 0; m0 < M; m0 += ST_TOK) {
+    // stage s of K into its place in the ring: rows past N or M and elements past K arrive as zeros
+    auto load_stage = [&](int s) {
+      float* const ws = st_smem + (s % ST_STAGES) * ST_STAGE_FLOATS;
+      float* const xs = ws + ST_FEAT * ST_KT;
+      const int k0 = s * ST_KT;
+#pragma unroll
+      for (int i = tid; i < ST_FEAT * (ST_KT / 4); i += ST_THREADS) {
+        const int r = i / (ST_KT / 4), c = (i % (ST_KT / 4)) * 4;
+        const bool wt = n0 + r < N && k0 + c < K;
+        st_cp_async16(&ws[r * ST_KT + c], w + (wt ? (size_t)(n0 + r) * ldw + k0 + c : 0), wt ? 16 : 0);
+        const bool xt = m0 + r < M && k0 + c < K;
+        st_cp_async16(&xs[r * ST_KT + c], x + (xt ? (size_t)(m0 + r) * ldx + k0 + c : 0), xt ? 16 : 0);
+      }
+    };
+#pragma unroll
+    for (int s = 0; s < ST_STAGES - 1; ++s) {
+      if (s < n_stages) load_stage(s);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    float acc[ST_FEAT][4];
+#pragma unroll
+    for (int f = 0; f < ST_FEAT; ++f)
+#pragma unroll
+      for (int m = 0; m < 4; ++m) acc[f][m] = 0.f;
+    for (int s = 0; s < n_stages; ++s) {
+      // (the stage this load overwrites was read in the iteration before, which ended with a barrier)
+      if (s + ST_STAGES - 1 < n_stages) load_stage(s + ST_STAGES - 1);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group %0;" ::"n"(ST_STAGES - 1) : "memory");   // all but the newest two groups: stage s is there
+      __syncthreads();
+      const float* const ws = st_smem + (s % ST_STAGES) * ST_STAGE_FLOATS;
+      const float* const xs = ws + ST_FEAT * ST_KT;
+      float4 xv[4];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) xv[m] = *reinterpret_cast<const float4*>(&xs[(tg * 4 + m) * ST_KT + kq * 4]);
+#pragma unroll
+      for (int f = 0; f < ST_FEAT; ++f) {
+        const float4 wv = *reinterpret_cast<const float4*>(&ws[f * ST_KT + kq * 4]);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          acc[f][m] = fmaf(wv.x, xv[m].x, acc[f][m]);
+          acc[f][m] = fmaf(wv.y, xv[m].y, acc[f][m]);
+          acc[f][m] = fmaf(wv.z, xv[m].z, acc[f][m]);
+          acc[f][m] = fmaf(wv.w, xv[m].w, acc[f][m]);
+        }
+      }
+      __syncthreads();
+    }
+    // ---- the 32 lanes meet: at every step a lane keeps the half of its values that its partner
+    // sends the other half of; after five steps lane i holds the warp's sum of value i = f * 4 + m
+    float v[32];
+#pragma unroll
+    for (int f = 0; f < ST_FEAT; ++f)
+#pragma unroll
+      for (int m = 0; m < 4; ++m) v[f * 4 + m] = acc[f][m];
+#pragma unroll
+    for (int step = 0; step < 5; ++step) {
+      const int off = 16 >> step, half = 16 >> step;     // values kept after this step
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < half; ++i) {
+        const float mine = upper ? v[i + half] : v[i];
+        const float theirs = upper ? v[i] : v[i + half];
+        v[i] = mine + __shfl_xor_sync(0xffffffffu, theirs, off);
+      }
+    }
+    red[warp][lane] = v[0];
+    __syncthreads();
+    if (tid < 2 * 32) {
+      const int g = tid >> 5, i = tid & 31;        // token group, value index
+      float sum = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) sum += red[g * 4 + wi][i];
+      const int m = m0 + g * 4 + (i & 3), n = n0 + (i >> 2);
+      if (m < M && n < N) epilogue_store<float>(out, (size_t)m * ldo + n, sum, epi);
+    }
+    __syncthreads();     // `red` and the ring are free for the next pass
+  }
+}
+
 template <typename T>
 static int launch_generic(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo,
                           int epilogue, cudaStream_t stream) {
@@ -225,6 +342,20 @@ static int launch_generic(const void* x, const void* w, void* out, int M, int N,
   const bool vec = sizeof(T) == 4 && K % 4 == 0 && ldx % 4 == 0 && ldw % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
   const T* xp = (const T*)x;
   const T* wp = (const T*)w;
+  if constexpr (sizeof(T) == 4) {
+    if (vec && M <= SK_MAX_TOKENS) {
+      static bool configured = false;
+      if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM_BYTES);
+        FERRUM_CHECK_ARG(e == cudaSuccess, "gemm: cannot reserve %d bytes of shared memory: %s", ST_SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+      }
+      gemm_stream_kernel<<<(N + ST_FEAT - 1) / ST_FEAT, ST_THREADS, ST_SMEM_BYTES, stream>>>((const float*)x, (const float*)w, out, M, N, K,
+                                                                                           ldx, ldw, ldo, epilogue);
+      FERRUM_CHECK_LAUNCH("gemm_generic");
+      return 0;
+    }
+  }
   if (M <= SK_MAX_TOKENS) {
     const dim3 grid((N + SK_FEAT - 1) / SK_FEAT);
     if (vec) gemm_skinny_kernel<T, true><<<grid, SK_WARPS * 32, 0, stream>>>(xp, wp, out, M, N, K, ldx, ldw, ldo, epilogue);
