@@ -263,6 +263,244 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
   }
 }
 
+// ------------------------------------------------------------------ prompt portions: tiles of tokens
+// With many tokens the kernel above reads every key row once per token.  Here a CTA takes up to
+// AG_TQ consecutive tokens of ONE request (and up to four heads of one KV head): the tile of keys
+// and values in shared memory serves all of them, the score loop reads a key element once for the
+// AG_TQ queries of a head, and the value loop reads a value element once for AG_TQ weighted sums.
+// Warp g still works for head g alone; it keeps max, sum and the weighted values of its AG_TQ
+// rows.  The arithmetic of a row is the same as above (tiles of 32 keys from the first key that
+// any of the CTA's rows sees), so a row's result depends on its chunk's first key only through
+// where the tile borders fall: rounding.
+// A CTA finds its chunk from q_start (tokens of request r are q_start[r] .. q_start[r+1]-1, in
+// ascending positions): chunk c of the grid is the c-th chunk of AG_TQ tokens counted request by
+// request; the grid has an upper bound of chunks and the CTAs past the last chunk leave.
+constexpr int AG_TQ = 8;
+
+template <int DI>
+struct AgTokenTile {
+  using Tile = AgTile<DI>;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + 2 * Tile::TK * Tile::KS;
+  static constexpr int OFF_Q = OFF_V + 2 * Tile::TK * Tile::DP;                 // [AG_TQ][4][DP]
+  static constexpr int OFF_P = OFF_Q + AG_TQ * AG_HEADS * Tile::DP;             // [4][AG_TQ][TK]
+  static constexpr int OFF_ROW = OFF_P + AG_HEADS * AG_TQ * Tile::TK;
+  static constexpr int SMEM_BYTES = (OFF_ROW + 2 * Tile::TK * 2) * 4;
+};
+
+template <typename T, int DI>
+__global__ void __launch_bounds__(AG_WARPS * 32)
+attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
+                                const int* __restrict__ positions, const int* __restrict__ q_start, int n_reqs,
+                                const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
+                                long long page_stride, int page_size, int Hq, int Hkv, int D, float scale, int window,
+                                int* __restrict__ err, int vec) {
+  using Tile = AgTile<DI>;
+  using TT = AgTokenTile<DI>;
+  constexpr int TK = Tile::TK, DP = Tile::DP, KS = Tile::KS;
+  extern __shared__ __align__(16) float ag_smem[];
+  float* const sm_k = ag_smem + TT::OFF_K;
+  float* const sm_v = ag_smem + TT::OFF_V;
+  float* const sm_q = ag_smem + TT::OFF_Q;
+  float* const sm_p = ag_smem + TT::OFF_P;
+  long long* const sm_row = reinterpret_cast<long long*>(ag_smem + TT::OFF_ROW);
+  __shared__ int chunk_req, chunk_t0, chunk_nt;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = Hq / Hkv;
+  const int hchunks = (G + AG_HEADS - 1) / AG_HEADS;
+  const int c = blockIdx.x / (Hkv * hchunks);
+  const int kvh = (blockIdx.x / hchunks) % Hkv;
+  const int hchunk = blockIdx.x % hchunks;
+  if (threadIdx.x == 0) {
+    int left = c, r = 0, t0 = 0, nt = 0;
+    for (; r < n_reqs; ++r) {
+      const int a = q_start[r], len = q_start[r + 1] - a;
+      const int n = (len + AG_TQ - 1) / AG_TQ;
+      if (left < n) {
+        t0 = a + left * AG_TQ;
+        nt = min(AG_TQ, a + len - t0);
+        break;
+      }
+      left -= n;
+    }
+    chunk_req = r;
+    chunk_t0 = t0;
+    chunk_nt = nt;     // 0: past the last chunk
+  }
+  __syncthreads();
+  const int req = chunk_req, t0 = chunk_t0, nt = chunk_nt;
+  if (nt == 0) return;
+  const int h0 = kvh * G + hchunk * AG_HEADS;
+  const int nh = min(AG_HEADS, G - hchunk * AG_HEADS);
+  // rows: token t0 + i at position pos[i], seeing keys lo[i] .. pos[i]
+  int pos[AG_TQ], lo[AG_TQ];
+  int k_begin = 0x7fffffff, k_end = 0;
+#pragma unroll
+  for (int i = 0; i < AG_TQ; ++i) {
+    pos[i] = i < nt ? positions[t0 + i] : -1;
+    lo[i] = i < nt ? (window > 0 ? max(0, pos[i] - window + 1) : 0) : 0x7fffffff;
+    if (i < nt) {
+      k_begin = min(k_begin, lo[i]);
+      k_end = max(k_end, pos[i] + 1);
+    }
+  }
+  const int* bt = block_table + (size_t)req * table_width;
+  const size_t v_off = (size_t)Hkv * page_size * D;
+  const bool vec_ok = vec != 0;
+  const bool async_rows = vec_ok && sizeof(T) == 4;
+  const int n_tiles = (k_end - k_begin + TK - 1) / TK;
+
+  auto find_rows = [&](int n) {
+    if (threadIdx.x < TK) {
+      const int key = k_begin + n * TK + threadIdx.x;
+      long long off = -1;
+      if (key < k_end) {
+        const int lp = key / page_size;
+        const int page = lp < table_width ? bt[lp] : -1;
+        if (page < 0) atomicExch(err, 5);
+        else off = (long long)page * page_stride + ((long long)kvh * page_size + key % page_size) * D;
+      }
+      sm_row[(n & 1) * TK + threadIdx.x] = off;
+    }
+  };
+  auto load_tile = [&](int n) {
+    const int b = n & 1;
+    float* const kb = sm_k + b * TK * KS;
+    float* const vb = sm_v + b * TK * DP;
+    for (int idx = threadIdx.x; idx < TK * (DP / 4); idx += AG_WARPS * 32) {
+      const int j = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+      const long long off = sm_row[b * TK + j];
+      if (async_rows) {
+        const bool there = off >= 0 && d < D;
+        const T* src = kv_plane + (there ? off + d : 0);
+        ag_cp_async16(&kb[j * KS + d], src, there ? 16 : 0);
+        ag_cp_async16(&vb[j * DP + d], src + (there ? v_off : 0), there ? 16 : 0);
+      } else {
+        float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+        if (off >= 0) {
+          kk = ag_load4<T>(kv_plane + off, d, D, vec_ok);
+          vv = ag_load4<T>(kv_plane + off + v_off, d, D, vec_ok);
+        }
+        *reinterpret_cast<float4*>(&kb[j * KS + d]) = kk;
+        *reinterpret_cast<float4*>(&vb[j * DP + d]) = vv;
+      }
+    }
+  };
+
+  // the chunk's queries [token][head][DP], zero past the head size and for rows that do not exist
+  for (int idx = threadIdx.x; idx < AG_TQ * AG_HEADS * (DP / 4); idx += AG_WARPS * 32) {
+    const int i = idx / (AG_HEADS * (DP / 4)), g = (idx / (DP / 4)) % AG_HEADS, d = (idx % (DP / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < nt && g < nh) v = ag_load4<T>(q + (size_t)(t0 + i) * ldq + (size_t)(h0 + g) * D, d, D, vec_ok && ldq % 4 == 0);
+    *reinterpret_cast<float4*>(&sm_q[(i * AG_HEADS + g) * DP + d]) = v;
+  }
+  find_rows(0);
+  __syncthreads();
+  load_tile(0);
+  ag_cp_async_commit();
+
+  float m[AG_TQ], l[AG_TQ], acc[AG_TQ][DI];
+#pragma unroll
+  for (int i = 0; i < AG_TQ; ++i) {
+    m[i] = -INFINITY;
+    l[i] = 0.f;
+#pragma unroll
+    for (int e = 0; e < DI; ++e) acc[i][e] = 0.f;
+  }
+
+  for (int n = 0; n < n_tiles; ++n) {
+    const int b = n & 1;
+    const bool more = n + 1 < n_tiles;
+    if (more) find_rows(n + 1);
+    __syncthreads();
+    if (more) load_tile(n + 1);
+    ag_cp_async_commit();
+    ag_cp_async_wait<1>();
+    const bool have = lane < TK && sm_row[b * TK + lane] >= 0;
+    __syncthreads();
+    if (warp < nh) {
+      const float* const kb = sm_k + b * TK * KS;
+      const float* const vb = sm_v + b * TK * DP;
+      const int key = k_begin + n * TK + lane;
+      // ---- lane j: the scores of key j for this warp's head and the chunk's tokens
+      float sc[AG_TQ];
+#pragma unroll
+      for (int i = 0; i < AG_TQ; ++i) sc[i] = 0.f;
+      {
+        const float4* kr = reinterpret_cast<const float4*>(&kb[(lane < TK ? lane : 0) * KS]);
+#pragma unroll 4
+        for (int cc = 0; cc < DP / 4; ++cc) {
+          const float4 k4 = kr[cc];
+#pragma unroll
+          for (int i = 0; i < AG_TQ; ++i) {
+            const float4 a = *reinterpret_cast<const float4*>(&sm_q[(i * AG_HEADS + warp) * DP + cc * 4]);
+            sc[i] = fmaf(a.x, k4.x, sc[i]);
+            sc[i] = fmaf(a.y, k4.y, sc[i]);
+            sc[i] = fmaf(a.z, k4.z, sc[i]);
+            sc[i] = fmaf(a.w, k4.w, sc[i]);
+          }
+        }
+      }
+      float corr[AG_TQ];
+      __syncwarp();                             // the weights of the tile before have been read
+#pragma unroll
+      for (int i = 0; i < AG_TQ; ++i) {
+        const bool seen = have && key <= pos[i] && key >= lo[i];
+        const float sv = seen ? sc[i] * scale : -INFINITY;
+        const float m_new = fmaxf(m[i], warp_max(sv));
+        float cr = 1.f, pj = 0.f;
+        if (m_new != -INFINITY) {
+          cr = m[i] == -INFINITY ? 0.f : expf(m[i] - m_new);
+          pj = sv == -INFINITY ? 0.f : expf(sv - m_new);
+        }
+        l[i] = l[i] * cr + warp_sum(pj);
+        m[i] = m_new;
+        corr[i] = cr;
+        if (lane < TK) sm_p[(warp * AG_TQ + i) * TK + lane] = pj;
+      }
+      __syncwarp();
+      // ---- lane e: elements e, e + 32, ... of the weighted values of every row, keys in ascending order
+#pragma unroll
+      for (int i = 0; i < AG_TQ; ++i)
+#pragma unroll
+        for (int e = 0; e < DI; ++e) acc[i][e] *= corr[i];
+#pragma unroll 1
+      for (int j4 = 0; j4 < TK / 4; ++j4) {
+        float vv[4][DI];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+          for (int e = 0; e < DI; ++e) vv[jj][e] = vb[(j4 * 4 + jj) * DP + lane + 32 * e];
+#pragma unroll
+        for (int i = 0; i < AG_TQ; ++i) {
+          const float4 pw = *reinterpret_cast<const float4*>(&sm_p[(warp * AG_TQ + i) * TK + j4 * 4]);
+#pragma unroll
+          for (int e = 0; e < DI; ++e) {
+            float a = acc[i][e];
+            a = fmaf(pw.x, vv[0][e], a);
+            a = fmaf(pw.y, vv[1][e], a);
+            a = fmaf(pw.z, vv[2][e], a);
+            a = fmaf(pw.w, vv[3][e], a);
+            acc[i][e] = a;
+          }
+        }
+      }
+    }
+  }
+  ag_cp_async_wait<0>();
+  if (warp >= nh) return;
+  const int h = h0 + warp;
+#pragma unroll
+  for (int i = 0; i < AG_TQ; ++i) {
+    if (i >= nt) break;
+#pragma unroll
+    for (int e = 0; e < DI; ++e) {
+      const int d = lane + 32 * e;
+      if (d < D) out[(size_t)(t0 + i) * ldo + (size_t)h * D + d] = from_f32<T>(l[i] > 0.f ? acc[i][e] / l[i] : 0.f);
+    }
+  }
+}
+
 // Folds the splits of every (token, head) in ascending key order: one warp each.
 template <typename T>
 __global__ void __launch_bounds__(32)
@@ -318,11 +556,13 @@ FERRUM_API int ferrum_attention_generic_split() { return AG_SPLIT; }
 // Otherwise `part` holds n_tokens * Hq * split_slots * (D + 2) floats, every row's key range is
 // cut at multiples of 128 keys among split_slots CTAs (split_slots must cover the longest row),
 // and a second launch folds the partials into `out`.
+// q_start (n_reqs + 1 entries on the device; may be null): with it and without `part`, tokens of a
+// request that follow each other in the batch share their key tiles (the kernel for prompt portions).
 FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int ldo, int dtype, int n_tokens,
                                         const int* positions, const int* req_of_token, const int* block_table,
                                         int table_width, const void* kv_plane, long long page_stride, int page_size,
                                         int Hq, int Hkv, int D, float scale, int window, int* err_flag, float* part,
-                                        int split_slots, cudaStream_t stream) {
+                                        int split_slots, const int* q_start, int n_reqs, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
   FERRUM_CHECK_ARG(D > 0 && D <= AG_MAX_D, "attention: head size %d is outside (0, %d]", D, AG_MAX_D);
   FERRUM_CHECK_ARG(page_size > 0 && table_width > 0 && window >= 0, "attention: bad cache arguments");
@@ -332,9 +572,36 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
   const int G = Hq / Hkv;
   const long long rows = (long long)n_tokens * Hkv * ((G + AG_HEADS - 1) / AG_HEADS);
   FERRUM_CHECK_ARG(rows < (1LL << 31), "attention: too many rows");
-  const dim3 grid((unsigned)rows, part ? split_slots : 1);
   // rows of D elements start on 16-byte (float32) or 8-byte (16-bit) borders: vector loads
   const int vec = D % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)kv_plane & 15) == 0 && page_stride % 4 == 0;
+  if (part == nullptr && q_start != nullptr && n_reqs > 0) {
+    // an upper bound of the chunks of AG_TQ tokens, request by request
+    const long long chunks = (n_tokens + AG_TQ - 1) / AG_TQ + n_reqs;
+    const long long ctas = chunks * Hkv * ((G + AG_HEADS - 1) / AG_HEADS);
+    FERRUM_CHECK_ARG(ctas < (1LL << 31), "attention: too many rows");
+#define AG_LAUNCH_TOKENS(DI_)                                                                                           \
+  FERRUM_DISPATCH_DTYPE(dtype, T, {                                                                                     \
+    static bool configured = false;                                                                                     \
+    if (!configured) {                                                                                                  \
+      cudaError_t e = cudaFuncSetAttribute(attention_generic_tokens_kernel<T, DI_>,                                     \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, AgTokenTile<DI_>::SMEM_BYTES);  \
+      FERRUM_CHECK_ARG(e == cudaSuccess, "attention: cannot reserve %d bytes of shared memory: %s",                     \
+                       AgTokenTile<DI_>::SMEM_BYTES, cudaGetErrorString(e));                                            \
+      configured = true;                                                                                                \
+    }                                                                                                                   \
+    attention_generic_tokens_kernel<T, DI_><<<(unsigned)ctas, AG_WARPS * 32, AgTokenTile<DI_>::SMEM_BYTES, stream>>>(   \
+      (const T*)q, ldq, (T*)out, ldo, positions, q_start, n_reqs, block_table, table_width, (const T*)kv_plane,         \
+      page_stride, page_size, Hq, Hkv, D, scale, window, err_flag, vec);                                                \
+  })
+    if (D <= 32) AG_LAUNCH_TOKENS(1);
+    else if (D <= 64) AG_LAUNCH_TOKENS(2);
+    else if (D <= 128) AG_LAUNCH_TOKENS(4);
+    else AG_LAUNCH_TOKENS(8);
+#undef AG_LAUNCH_TOKENS
+    FERRUM_CHECK_LAUNCH("attention_generic_tokens");
+    return 0;
+  }
+  const dim3 grid((unsigned)rows, part ? split_slots : 1);
 #define AG_LAUNCH(DI_)                                                                                                  \
   FERRUM_DISPATCH_DTYPE(dtype, T, {                                                                                     \
     static bool configured = false;                                                                                     \

@@ -18,7 +18,7 @@ void ferrum_set_error(const char* fmt, ...) {
 FERRUM_API const char* ferrum_last_error() { return g_error; }
 
 // Version of the kernel library's C interface; the Python side refuses a stale build.
-FERRUM_API int ferrum_kernels_abi() { return 6; }
+FERRUM_API int ferrum_kernels_abi() { return 7; }
 
 // Dependent launch (see common.cuh) can be switched off, e.g. to compare timings.
 static bool g_dependent_launch = true;

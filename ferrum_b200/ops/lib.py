@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 6
+ABI = 7
 
 
 def lib():
@@ -367,12 +367,14 @@ def attention_generic_split():
 
 
 def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv_plane, page_stride, page_size, Hq,
-                      Hkv, D, scale, window, err, part=None, split_slots=0):
+                      Hkv, D, scale, window, err, part=None, split_slots=0, q_start=None, n_reqs=0):
     """Causal GQA attention of every token over its request's pages on the CUDA cores, float32
     arithmetic.  part=None: one CTA per (token, group of heads) walks the whole key range (many
     tokens).  With `part` (float32, n_tokens * Hq * split_slots * (D + 2) elements) every row's keys
     are cut at multiples of `attention_generic_split()` among split_slots CTAs and folded by a
-    second launch (few tokens); split_slots must cover the longest row."""
+    second launch (few tokens); split_slots must cover the longest row.  With q_start (the device's
+    n_reqs + 1 token offsets of the requests, tokens of a request in ascending positions) and no
+    `part`, up to eight tokens of a request that follow each other share every tile of keys."""
     _need(q, None, "q", 2); _need(out, q.dtype, "out", 2); _need(kv_plane, q.dtype, "kv_plane")
     _need(positions, torch.int32, "positions", 1); _need(req_of_token, torch.int32, "req_of_token", 1)
     _need(block_table, torch.int32, "block_table", 2)
@@ -387,7 +389,8 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
                                           _ptr(block_table), c_int(block_table.shape[1]), _ptr(kv_plane),
                                           c_longlong(page_stride), c_int(page_size), c_int(Hq), c_int(Hkv), c_int(D),
                                           c_float(scale), c_int(window), _ptr(err), _ptr(part), c_int(split_slots),
-                                          _stream()), "attention_generic")
+                                          _ptr(q_start) if part is None else None, c_int(n_reqs), _stream()),
+           "attention_generic")
 
 
 def attention_flash_supported(dtype, D, page_stride=0):

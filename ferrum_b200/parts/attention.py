@@ -94,7 +94,8 @@ class PagedAttention(Mixer):
             slots = longest // split + 2
             part = ctx.buf("attn_generic_part", (T * Hq * slots * (D + 2),), torch.float32)
         ops.attention_generic(qkv, out, T, ctx.positions, ctx.req_of_token, table, cache.plane, cache.page_stride,
-                              cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err, part, slots)
+                              cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err, part, slots,
+                              q_start=ctx.q_start, n_reqs=ctx.n_reqs)
 
     def plan(self, ctx, cache):
         """The step's work lists of the tensor-core kernels for this layer's shape (None on the

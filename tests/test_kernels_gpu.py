@@ -290,8 +290,13 @@ def test_attention_generic(ops, dtype, Hq, Hkv, D, ps, window):
     out2 = torch.empty_like(out)
     ops.attention_generic(q, out2, T, posd, reqd, table, plane, plane.stride(0), ps, Hq, Hkv, D, 1.0 / math.sqrt(D), window, e,
                           part, slots)
+    # and with up to eight tokens of a request sharing every tile of keys (what a batch of many tokens runs)
+    out3 = torch.full_like(out, float("nan"))
+    qstart = torch.tensor(np.concatenate([[0], np.cumsum(qlens)]), dtype=torch.int32, device="cuda")
+    ops.attention_generic(q, out3, T, posd, reqd, table, plane, plane.stride(0), ps, Hq, Hkv, D, 1.0 / math.sqrt(D), window, e,
+                          q_start=qstart, n_reqs=len(lens))
     assert e.item() == 0
-    for res in (out, out2):
+    for res in (out, out2, out3):
         t0 = 0
         for r, (n, ql) in enumerate(zip(lens, qlens)):
             qfull = np.zeros((n, Hq, D))
