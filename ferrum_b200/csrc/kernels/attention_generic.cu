@@ -268,14 +268,16 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
 // AG_TQ consecutive tokens of ONE request (and up to four heads of one KV head): the tile of keys
 // and values in shared memory serves all of them, the score loop reads a key element once for the
 // AG_TQ queries of a head, and the value loop reads a value element once for AG_TQ weighted sums.
-// Warp g still works for head g alone; it keeps max, sum and the weighted values of its AG_TQ
-// rows.  The arithmetic of a row is the same as above (tiles of 32 keys from the first key that
+// A warp still works for one head alone; it keeps max, sum and the weighted values of four of the
+// chunk's tokens (eight warps: four heads x two halves of the tokens).  The arithmetic of a row is the same as above (tiles of 32 keys from the first key that
 // any of the CTA's rows sees), so a row's result depends on its chunk's first key only through
 // where the tile borders fall: rounding.
 // A CTA finds its chunk from q_start (tokens of request r are q_start[r] .. q_start[r+1]-1, in
 // ascending positions): chunk c of the grid is the c-th chunk of AG_TQ tokens counted request by
 // request; the grid has an upper bound of chunks and the CTAs past the last chunk leave.
 constexpr int AG_TQ = 8;
+constexpr int AG_TWARPS = 8;                 // warp w: head w % 4, tokens (w / 4) * 4 .. + 3 of the chunk
+constexpr int AG_TH = AG_TQ / (AG_TWARPS / AG_HEADS);
 
 template <int DI>
 struct AgTokenTile {
@@ -289,7 +291,7 @@ struct AgTokenTile {
 };
 
 template <typename T, int DI>
-__global__ void __launch_bounds__(AG_WARPS * 32)
+__global__ void __launch_bounds__(AG_TWARPS * 32)
 attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
                                 const int* __restrict__ positions, const int* __restrict__ q_start, int n_reqs,
                                 const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
@@ -305,7 +307,8 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
   float* const sm_p = ag_smem + TT::OFF_P;
   long long* const sm_row = reinterpret_cast<long long*>(ag_smem + TT::OFF_ROW);
   __shared__ int chunk_req, chunk_t0, chunk_nt;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = (threadIdx.x >> 5) & (AG_HEADS - 1), lane = threadIdx.x & 31;   // the head this warp works for
+  const int i0 = (threadIdx.x >> 7) * AG_TH;                                      // ... and the first of its AG_TH tokens
   const int G = Hq / Hkv;
   const int hchunks = (G + AG_HEADS - 1) / AG_HEADS;
   const int c = blockIdx.x / (Hkv * hchunks);
@@ -333,16 +336,20 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
   const int h0 = kvh * G + hchunk * AG_HEADS;
   const int nh = min(AG_HEADS, G - hchunk * AG_HEADS);
   // rows: token t0 + i at position pos[i], seeing keys lo[i] .. pos[i]
-  int pos[AG_TQ], lo[AG_TQ];
-  int k_begin = 0x7fffffff, k_end = 0;
+  int k_begin = 0x7fffffff, k_end = 0;     // the keys that any row of the chunk sees
 #pragma unroll
   for (int i = 0; i < AG_TQ; ++i) {
-    pos[i] = i < nt ? positions[t0 + i] : -1;
-    lo[i] = i < nt ? (window > 0 ? max(0, pos[i] - window + 1) : 0) : 0x7fffffff;
     if (i < nt) {
-      k_begin = min(k_begin, lo[i]);
-      k_end = max(k_end, pos[i] + 1);
+      const int p = positions[t0 + i];
+      k_begin = min(k_begin, window > 0 ? max(0, p - window + 1) : 0);
+      k_end = max(k_end, p + 1);
     }
+  }
+  int pos[AG_TH], lo[AG_TH];               // of this warp's rows
+#pragma unroll
+  for (int i = 0; i < AG_TH; ++i) {
+    pos[i] = i0 + i < nt ? positions[t0 + i0 + i] : -1;
+    lo[i] = i0 + i < nt ? (window > 0 ? max(0, pos[i] - window + 1) : 0) : 0x7fffffff;
   }
   const int* bt = block_table + (size_t)req * table_width;
   const size_t v_off = (size_t)Hkv * page_size * D;
@@ -367,7 +374,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
     const int b = n & 1;
     float* const kb = sm_k + b * TK * KS;
     float* const vb = sm_v + b * TK * DP;
-    for (int idx = threadIdx.x; idx < TK * (DP / 4); idx += AG_WARPS * 32) {
+    for (int idx = threadIdx.x; idx < TK * (DP / 4); idx += AG_TWARPS * 32) {
       const int j = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
       const long long off = sm_row[b * TK + j];
       if (async_rows) {
@@ -388,7 +395,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
   };
 
   // the chunk's queries [token][head][DP], zero past the head size and for rows that do not exist
-  for (int idx = threadIdx.x; idx < AG_TQ * AG_HEADS * (DP / 4); idx += AG_WARPS * 32) {
+  for (int idx = threadIdx.x; idx < AG_TQ * AG_HEADS * (DP / 4); idx += AG_TWARPS * 32) {
     const int i = idx / (AG_HEADS * (DP / 4)), g = (idx / (DP / 4)) % AG_HEADS, d = (idx % (DP / 4)) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < nt && g < nh) v = ag_load4<T>(q + (size_t)(t0 + i) * ldq + (size_t)(h0 + g) * D, d, D, vec_ok && ldq % 4 == 0);
@@ -399,9 +406,9 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
   load_tile(0);
   ag_cp_async_commit();
 
-  float m[AG_TQ], l[AG_TQ], acc[AG_TQ][DI];
+  float m[AG_TH], l[AG_TH], acc[AG_TH][DI];     // of this warp's rows: tokens i0 .. i0 + AG_TH - 1 of the chunk
 #pragma unroll
-  for (int i = 0; i < AG_TQ; ++i) {
+  for (int i = 0; i < AG_TH; ++i) {
     m[i] = -INFINITY;
     l[i] = 0.f;
 #pragma unroll
@@ -423,17 +430,17 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
       const float* const vb = sm_v + b * TK * DP;
       const int key = k_begin + n * TK + lane;
       // ---- lane j: the scores of key j for this warp's head and the chunk's tokens
-      float sc[AG_TQ];
+      float sc[AG_TH];
 #pragma unroll
-      for (int i = 0; i < AG_TQ; ++i) sc[i] = 0.f;
+      for (int i = 0; i < AG_TH; ++i) sc[i] = 0.f;
       {
         const float4* kr = reinterpret_cast<const float4*>(&kb[(lane < TK ? lane : 0) * KS]);
 #pragma unroll 4
         for (int cc = 0; cc < DP / 4; ++cc) {
           const float4 k4 = kr[cc];
 #pragma unroll
-          for (int i = 0; i < AG_TQ; ++i) {
-            const float4 a = *reinterpret_cast<const float4*>(&sm_q[(i * AG_HEADS + warp) * DP + cc * 4]);
+          for (int i = 0; i < AG_TH; ++i) {
+            const float4 a = *reinterpret_cast<const float4*>(&sm_q[((i0 + i) * AG_HEADS + warp) * DP + cc * 4]);
             sc[i] = fmaf(a.x, k4.x, sc[i]);
             sc[i] = fmaf(a.y, k4.y, sc[i]);
             sc[i] = fmaf(a.z, k4.z, sc[i]);
@@ -441,10 +448,10 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
           }
         }
       }
-      float corr[AG_TQ];
+      float corr[AG_TH];
       __syncwarp();                             // the weights of the tile before have been read
 #pragma unroll
-      for (int i = 0; i < AG_TQ; ++i) {
+      for (int i = 0; i < AG_TH; ++i) {
         const bool seen = have && key <= pos[i] && key >= lo[i];
         const float sv = seen ? sc[i] * scale : -INFINITY;
         const float m_new = fmaxf(m[i], warp_max(sv));
@@ -456,12 +463,12 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
         l[i] = l[i] * cr + warp_sum(pj);
         m[i] = m_new;
         corr[i] = cr;
-        if (lane < TK) sm_p[(warp * AG_TQ + i) * TK + lane] = pj;
+        if (lane < TK) sm_p[(warp * AG_TQ + i0 + i) * TK + lane] = pj;
       }
       __syncwarp();
       // ---- lane e: elements e, e + 32, ... of the weighted values of every row, keys in ascending order
 #pragma unroll
-      for (int i = 0; i < AG_TQ; ++i)
+      for (int i = 0; i < AG_TH; ++i)
 #pragma unroll
         for (int e = 0; e < DI; ++e) acc[i][e] *= corr[i];
 #pragma unroll 1
@@ -472,8 +479,8 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 #pragma unroll
           for (int e = 0; e < DI; ++e) vv[jj][e] = vb[(j4 * 4 + jj) * DP + lane + 32 * e];
 #pragma unroll
-        for (int i = 0; i < AG_TQ; ++i) {
-          const float4 pw = *reinterpret_cast<const float4*>(&sm_p[(warp * AG_TQ + i) * TK + j4 * 4]);
+        for (int i = 0; i < AG_TH; ++i) {
+          const float4 pw = *reinterpret_cast<const float4*>(&sm_p[(warp * AG_TQ + i0 + i) * TK + j4 * 4]);
 #pragma unroll
           for (int e = 0; e < DI; ++e) {
             float a = acc[i][e];
@@ -491,12 +498,12 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
   if (warp >= nh) return;
   const int h = h0 + warp;
 #pragma unroll
-  for (int i = 0; i < AG_TQ; ++i) {
-    if (i >= nt) break;
+  for (int i = 0; i < AG_TH; ++i) {
+    if (i0 + i >= nt) break;
 #pragma unroll
     for (int e = 0; e < DI; ++e) {
       const int d = lane + 32 * e;
-      if (d < D) out[(size_t)(t0 + i) * ldo + (size_t)h * D + d] = from_f32<T>(l[i] > 0.f ? acc[i][e] / l[i] : 0.f);
+      if (d < D) out[(size_t)(t0 + i0 + i) * ldo + (size_t)h * D + d] = from_f32<T>(l[i] > 0.f ? acc[i][e] / l[i] : 0.f);
     }
   }
 }
@@ -589,7 +596,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
                        AgTokenTile<DI_>::SMEM_BYTES, cudaGetErrorString(e));                                            \
       configured = true;                                                                                                \
     }                                                                                                                   \
-    attention_generic_tokens_kernel<T, DI_><<<(unsigned)ctas, AG_WARPS * 32, AgTokenTile<DI_>::SMEM_BYTES, stream>>>(   \
+    attention_generic_tokens_kernel<T, DI_><<<(unsigned)ctas, AG_TWARPS * 32, AgTokenTile<DI_>::SMEM_BYTES, stream>>>(   \
       (const T*)q, ldq, (T*)out, ldo, positions, q_start, n_reqs, block_table, table_width, (const T*)kv_plane,         \
       page_stride, page_size, Hq, Hkv, D, scale, window, err_flag, vec);                                                \
   })
