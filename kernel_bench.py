@@ -8,7 +8,11 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py gemm --tokens 8 --n 6144 --k 4096 [--epilogue store|residual|swiglu] [--copies 8]
     python kernel_bench.py gemm|attn_decode|attn_prefill ... --dtype fp32    (the CUDA-core kernels of the 32-bit path)
     python kernel_bench.py rmsnorm|rope --tokens 8
+    python kernel_bench.py step --tokens 2048 [--layers 2] [--dtype bf16|fp16|fp32]   (one prompt portion through the model)
     FERRUM_KERNEL_TRACE=1 python kernel_bench.py timeline [--batch 8] [--context 8192] [--layers 4]
+`step` runs whole steps of one request's prompt portion of `--tokens` tokens through a model of
+`--layers` layers (the step function, cache and kernels that generation uses) and prints the
+step's time; under `ncu --metrics gpu__time_duration.sum` it is the list of the step's launches.
 `timeline` runs decode steps of a model with `--layers` layers on the library built with the
 kernel trace (block 0 of every instrumented kernel records the GPU's global timer at entry,
 after its dependency wait and at exit) and prints one line per launch of the last step: what
@@ -27,7 +31,7 @@ sys.path.insert(0, ROOT)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemm", "rmsnorm", "rope", "timeline"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemm", "rmsnorm", "rope", "step", "timeline"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=8)
@@ -54,6 +58,8 @@ def main():
 
     if args.kernel == "timeline":
         return timeline(args)
+    if args.kernel == "step":
+        return prompt_step(args)
     import torch
     from bench import peaks
     from ferrum_b200.engine.batch import StepContext, StepEntry
@@ -188,6 +194,48 @@ def main():
     print(json.dumps({"kernel": args.kernel, "us": round(us, 2), "GBps": round(gbs, 1), "TFLOPs": round(tf, 2),
                       "bound": work["bound"], "frac_of_peak": round(frac, 4), "peaks": pk["source"],
                       "args": {k: v for k, v in vars(args).items() if k != "kernel"}}))
+    return 0
+
+
+def prompt_step(args):
+    import torch
+    from bench import LLAMA31_8B
+    from ferrum_b200.cache.storage import CacheStorage
+    from ferrum_b200.config import registry
+    from ferrum_b200.engine.batch import StepEntry
+    from ferrum_b200.engine.runner import ModelRunner
+    from ferrum_b200.ops import lib as ops
+    from ferrum_b200.weights import init_random
+    ops.require_cuda()
+    td = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    T = args.tokens
+    cfgd = dict(LLAMA31_8B)
+    cfgd["num_hidden_layers"] = args.layers
+    arch = registry.lookup("LlamaForCausalLM")
+    cfg = arch.read_config(cfgd)
+    model = arch.build(cfg, td, "cuda", max_positions=T + 64)
+    init_random(model, 0)
+    cache = CacheStorage(model, td, "cuda", page_size=args.page_size, max_tokens=2 * (T + 64), max_requests=4, max_model_len=T + 64)
+    runner = ModelRunner(model, cache, max_batch_tokens=T, max_batch_requests=2)
+    gen = torch.Generator().manual_seed(1)
+    times = []
+    for rep in range(args.warmup + args.iters):
+        slot = cache.open()
+        toks = torch.randint(0, cfg.n_vocab, (T,), generator=gen).tolist()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        l0 = ops.launches
+        ev0.record()
+        runner.step([StepEntry(slot, 0, toks, [T - 1])], check=True)
+        ev1.record()
+        torch.cuda.synchronize()
+        if rep >= args.warmup:
+            times.append(ev0.elapsed_time(ev1))
+        launches = ops.launches - l0
+        cache.close(slot)
+    times.sort()
+    print(json.dumps({"kernel": "step", "tokens": T, "layers": args.layers, "dtype": args.dtype, "launches": int(launches),
+                      "ms_median": round(times[len(times) // 2], 3), "ms_min": round(times[0], 3), "ms_max": round(times[-1], 3)}))
     return 0
 
 
