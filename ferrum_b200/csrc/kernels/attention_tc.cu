@@ -21,6 +21,18 @@
 // memory, by the row's own thread) when it grows by more than 2^8; until then P is computed
 // against the older maximum, which changes nothing in the quotient O / l.
 //
+// What sets the pace (clocks taken per role on a 2,048-token prompt): a 64-key stage of both tiles
+// takes about 2,300 cycles, and the chain that closes every two stages is softmax of stage j
+// (1,800 cycles for its 64 exponentials at the special-function unit's rate with the other tile's
+// warp on the same scheduler, the maximum, P) -> P V of stage j (its P lies over the scores'
+// buffer) -> Q K^T of stage j + 2 into that buffer (eight dependent steps: 1,600 cycles from the
+// first instruction to the scores being seen) -> softmax of stage j + 2.  A thread gets one
+// tcgen05.mma, and a warp one TMA copy, off about every 120 cycles whatever the instruction's
+// size (one, two and four issuing threads: 121, 60 and 30 + cycles an instruction overall), which
+// is why the steps of a product cost what they do.  Giving keys and values a producer warp each
+// and Q K^T and P V an issuing thread each per tile left the time unchanged (47.8 against 47.7 us):
+// the chain above stays.  One issuing thread for both tiles, step by step in turn, was slower (54 us).
+//
 // Roles (352 threads): warp 0 = TMA producer, warps 1 and 2 = MMA issuers of tile 0 and 1 (one
 // issuing thread each: while one does its waits and commits, the other's products run; warp 1
 // also owns the tensor memory), warps 3..6 = rows of tile 0, warps 7..10 = rows of tile 1.  Every wait is bounded; on a
