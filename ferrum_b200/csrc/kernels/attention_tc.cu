@@ -29,9 +29,16 @@
 // first instruction to the scores being seen) -> softmax of stage j + 2.  A thread gets one
 // tcgen05.mma, and a warp one TMA copy, off about every 120 cycles whatever the instruction's
 // size (one, two and four issuing threads: 121, 60 and 30 + cycles an instruction overall), which
-// is why the steps of a product cost what they do.  Giving keys and values a producer warp each
-// and Q K^T and P V an issuing thread each per tile left the time unchanged (47.8 against 47.7 us):
-// the chain above stays.  One issuing thread for both tiles, step by step in turn, was slower (54 us).
+// is why the steps of a product cost what they do.  Built, verified and measured without a gain
+// (47.7 to 49.4 us against 47.7 us; 553 to 581 against 556 us at 8,192 tokens), each removing one
+// of the three 2,100-to-2,300-cycle limits and meeting the next: a producer warp each for keys and
+// values (one warp's sixteen copies of a stage take 2,300 cycles); an issuing thread each for
+// Q K^T and P V of a tile (one thread's twelve steps and six commits take 2,100); P in columns of
+// its own with one score buffer, so that the next scores are issued as soon as the current ones
+// have been read (their eight dependent steps then end about when the softmax does, 1,900
+// cycles); and all three together.  One issuing thread for both tiles, step by step in turn, was
+// slower (54 us).  At 2,048 tokens a third of the time is outside this loop: 256 items of 1 to 32
+// stages on 148 CTAs, each with some 3.5 us of start and end (Q, first keys, output).
 //
 // Roles (352 threads): warp 0 = TMA producer, warps 1 and 2 = MMA issuers of tile 0 and 1 (one
 // issuing thread each: while one does its waits and commits, the other's products run; warp 1
