@@ -23,6 +23,12 @@ from .linear import RESIDUAL, STORE, linear, linear_deferred
 EARLY_TRIGGER_MAX_TOKENS = 16
 
 
+# The CUDA-core attention cuts a row's keys among CTAs while the step has fewer rows than this many
+# per SM (a CTA slot is a third of an SM: under some 2.7 waves of whole rows the last wave idles
+# too much); with more rows, tokens of a request that follow each other share their key tiles.
+GENERIC_SPLIT_BELOW = 8
+
+
 class PagedAttention(Mixer):
     @property
     def graph_safe(self):
@@ -86,7 +92,7 @@ class PagedAttention(Mixer):
         T, Hq, Hkv, D = ctx.n_tokens, self.Hq, self.Hkv, self.D
         rows = T * Hkv * -(-(Hq // Hkv) // 4)
         part, slots = None, 0
-        if rows < 8 * attention_plan.sm_count():     # (a CTA slot is a third of an SM: under some 2.7 waves of whole rows the last wave idles too much)
+        if rows < GENERIC_SPLIT_BELOW * attention_plan.sm_count():
             split = ops.attention_generic_split()
             longest = table.shape[1] * cache.page_size if ctx.fixed_shapes else ctx.max_kv_len
             if self.window > 0:

@@ -170,8 +170,8 @@ def run_mixed(s, toks, schedule):
 def mixed_case(model_dirs, name, dtype, page_size=16, model_path=None, **kw):
     """The mixed workload in a pool of exactly the pages its live requests need at their peak,
     fewer than all requests need together: pages of finished requests must be handed out again."""
-    from conftest import TINY
-    vocab = TINY[name][0]["vocab_size"]
+    import conftest
+    vocab = getattr(conftest, "TINY_" + name)["vocab_size"]
     toks = {k: random_tokens(n, vocab, 20 + i) for i, (k, n) in enumerate(MIXED_LENS.items())}
     schedule = mixed_schedule(MIXED_LENS)
     pool = peak_pages(schedule, page_size)

@@ -76,6 +76,31 @@ def test_mixed_batches_with_page_reuse(cuda, model_dirs, name, dtype):
     assert s.cache.manager.used_pages(0) == 0
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "float32"), ("A", "bfloat16"), ("G", "float32")])
+def test_tokens_of_a_request_share_key_tiles(cuda, model_dirs, name, dtype, monkeypatch):
+    """The CUDA-core attention's kernel for steps of many tokens (up to eight tokens of a request
+    per CTA, found on the device from the requests' token offsets), forced on every step of the
+    mixed workload and of portions of changing size: chunks that end inside a request, requests of
+    one decoded token beside portions, windows."""
+    from ferrum_b200.parts import attention
+    monkeypatch.setattr(attention, "GENERIC_SPLIT_BELOW", 0)
+    s, toks, schedule = mixed_case(model_dirs, name, dtype)
+    r, owners = run_mixed(s, toks, schedule)
+    for k in toks:
+        assert_close(r.logits(k, len(toks[k])), plain_logits(model_dirs[name], dtype, toks[k]), dtype, f"{name} token tiles {k}")
+    import conftest
+    vocab = getattr(conftest, "TINY_" + name)["vocab_size"]
+    long = random_tokens(150, vocab, 21)
+    r = Replay(session(model_dirs, name, dtype, 192))
+    sizes, i, k = [9, 8, 17, 1, 2, 31, 16, 7, 40, 3], 0, 0
+    while i < len(long):
+        n = min(sizes[k % len(sizes)], len(long) - i)
+        r.step([("a", long[i:i + n], "all")])
+        i += n
+        k += 1
+    assert_close(r.logits("a", len(long)), plain_logits(model_dirs[name], dtype, long), dtype, f"{name} token tiles, portions")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
 @pytest.mark.parametrize("page_size", [8, 32])
 def test_other_page_sizes_through_a_whole_model(cuda, model_dirs, dtype, page_size):
