@@ -6,7 +6,7 @@
 // dot per output (crates/kernels/src/scalar.rs:221-241).  Two kernels:
 //
 // Tiled (more than 64 tokens): a CTA computes BM tokens x 128 features; both operands are
-// K-major, so a thread fetches 16 bytes along K of one row, and the 8-wide k-slices go into
+// K-major, so a thread fetches 16 bytes along K of one row, and the 16-wide k-slices go into
 // shared memory transposed ([k][row]), double buffered: the loads of slice i + 1 are in flight
 // while slice i is multiplied.  A thread owns BM/16 x 8 outputs in registers.  Every output is
 // ONE accumulator that walks k = 0..K-1 in order.
@@ -49,7 +49,8 @@ __device__ __forceinline__ void epilogue_store(void* out, size_t o, float v, int
 }
 
 // ------------------------------------------------------------------ tiled kernel
-constexpr int TBN = 128, TBK = 8;
+constexpr int TBN = 128, TBK = 16;
+constexpr int TLV = TBK / 8;      // 16-byte pieces of a slice that a thread brings per operand
 
 // VEC: float32 operands whose rows start on 16-byte boundaries and K a multiple of 4.
 template <typename T, int BM, bool VEC>
@@ -57,13 +58,13 @@ __global__ void __launch_bounds__(256)
 gemm_tiled_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ out, int M, int N, int K, int ldx,
                   int ldw, int ldo, int epi) {
   constexpr int TM = BM / 16;               // outputs per thread along the tokens
-  constexpr int A_VECS = BM * TBK / 4;      // 16-byte pieces of a token slice (at most 256)
+  constexpr int A_VECS = BM * 8 / 4;        // 16-byte pieces of eight k of a token slice (at most 256)
   __shared__ __align__(16) float xs[2][TBK][BM];
   __shared__ __align__(16) float ws[2][TBK][TBN];
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * TBN;
-  // this thread's piece of a slice: row lr, k offset lk (0 or 4)
+  // this thread's pieces of a slice: row lr, k offsets lk (0 or 4) + 8 q
   const int lr = tid >> 1, lk = (tid & 1) * 4;
   const bool a_loader = tid < A_VECS;
   const T* xrow = x + (size_t)min(m0 + lr, M - 1) * ldx;
@@ -76,29 +77,34 @@ gemm_tiled_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __rest
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
-  float ra[4], rb[4];
+  float ra[TLV][4], rb[TLV][4];
   auto fetch = [&](int k0) {
-    const int k = k0 + lk;
-    if (VEC) {
-      const float4 za = make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4 a = (a_ok && k < K) ? *reinterpret_cast<const float4*>((const float*)xrow + k) : za;
-      const float4 b = (b_ok && k < K) ? *reinterpret_cast<const float4*>((const float*)wrow + k) : za;
-      ra[0] = a.x; ra[1] = a.y; ra[2] = a.z; ra[3] = a.w;
-      rb[0] = b.x; rb[1] = b.y; rb[2] = b.z; rb[3] = b.w;
-    } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        ra[i] = (a_ok && k + i < K) ? to_f32<T>(xrow[k + i]) : 0.f;
-        rb[i] = (b_ok && k + i < K) ? to_f32<T>(wrow[k + i]) : 0.f;
+    for (int q = 0; q < TLV; ++q) {
+      const int k = k0 + q * 8 + lk;
+      if (VEC) {
+        const float4 za = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 a = (a_ok && k < K) ? *reinterpret_cast<const float4*>((const float*)xrow + k) : za;
+        const float4 b = (b_ok && k < K) ? *reinterpret_cast<const float4*>((const float*)wrow + k) : za;
+        ra[q][0] = a.x; ra[q][1] = a.y; ra[q][2] = a.z; ra[q][3] = a.w;
+        rb[q][0] = b.x; rb[q][1] = b.y; rb[q][2] = b.z; rb[q][3] = b.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          ra[q][i] = (a_ok && k + i < K) ? to_f32<T>(xrow[k + i]) : 0.f;
+          rb[q][i] = (b_ok && k + i < K) ? to_f32<T>(wrow[k + i]) : 0.f;
+        }
       }
     }
   };
   auto stash = [&](int buf) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (a_loader) xs[buf][lk + i][lr] = ra[i];
-      ws[buf][lk + i][lr] = rb[i];
-    }
+    for (int q = 0; q < TLV; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (a_loader) xs[buf][q * 8 + lk + i][lr] = ra[q][i];
+        ws[buf][q * 8 + lk + i][lr] = rb[q][i];
+      }
   };
 
   const int n_slices = (K + TBK - 1) / TBK;
