@@ -13,6 +13,8 @@ errors, exit code 2 for usage errors and 1 for runtime errors, messages prefixed
                     [--chunk-size N] [--page-size N] [--num-pages N] [--max-model-len N]
                     [--random-weights] [--weights-seed S] [--stats] [--profile]
     ferrum random-weights --config CONFIG.json --out DIR [--seed S] [--dtype float32|bfloat16|float16] [--gguf]
+    ferrum bench --model DIR|CONFIG.json [--random-weights] [--dtype D] [--batch B] [--prompt-len P] [--new-tokens N]
+                 [--layers L] [--page-size N] [--chunk-size N] [--seed S]
     ferrum replay --model DIR --dtype D --out DIR --max-tokens N        (steps on standard input)
     ferrum dump FILE.gguf|FILE.safetensors|DIR
     ferrum serve                                                          (not part of this engine)
@@ -23,7 +25,7 @@ import json
 import os
 import sys
 
-USAGE = "usage: ferrum generate|random-weights|replay|dump|serve [options]  (ferrum --help lists them)"
+USAGE = "usage: ferrum generate|random-weights|bench|replay|dump|serve [options]  (ferrum --help lists them)"
 
 # option -> (kind, repeatable)
 OPTIONS = {
@@ -33,6 +35,8 @@ OPTIONS = {
                  "--chunk-size": "int", "--page-size": "int", "--num-pages": "int", "--max-model-len": "int",
                  "--random-weights": "flag", "--weights-seed": "int", "--stats": "flag", "--profile": "flag"},
     "random-weights": {"--config": "str", "--out": "str", "--seed": "int", "--dtype": "str", "--gguf": "flag"},
+    "bench": {"--model": "str", "--random-weights": "flag", "--dtype": "str", "--batch": "int", "--prompt-len": "int",
+              "--new-tokens": "int", "--layers": "int", "--page-size": "int", "--chunk-size": "int", "--seed": "int"},
     "replay": {"--model": "str", "--dtype": "str", "--out": "str", "--max-tokens": "int", "--page-size": "int",
                "--max-requests": "int"},
     "dump": {},
@@ -164,6 +168,64 @@ def cmd_random_weights(opts):
     return 0
 
 
+def cmd_bench(opts):
+    """B random prompts of P tokens, N new tokens each, greedy, through the engine's own entry
+    point: one JSON line with the time of the prompts (until every request has its first token)
+    and the decoded tokens a second after that.  `--model` names a model folder, or with
+    `--random-weights` a config.json whose sizes are built with random weights (`--layers`
+    overrides its layer count, for shapes that would not fit otherwise)."""
+    import random
+    import time
+    import torch
+    from .config import registry
+    from .engine.api import Engine, load_model, parse_dtype
+    from .weights import init_random
+    model_arg = _need(opts, "--model")
+    dtype = opts.get("--dtype", "bfloat16")
+    B, P, N = opts.get("--batch", 8), opts.get("--prompt-len", 128), opts.get("--new-tokens", 64)
+    if min(B, P, N) < 1:
+        raise CliError("--batch, --prompt-len and --new-tokens must be positive")
+    page = opts.get("--page-size", 16)
+    max_len = P + N + page
+    if opts.get("--random-weights"):
+        path = os.path.join(model_arg, "config.json") if os.path.isdir(model_arg) else model_arg
+        with open(path) as f:
+            cfgd = json.load(f)
+        if "--layers" in opts:
+            cfgd["num_hidden_layers"] = opts["--layers"]
+        arch = registry.lookup(cfgd["architectures"][0])
+        model = arch.build(arch.read_config(cfgd), parse_dtype(dtype), "cuda", max_positions=max_len)
+        init_random(model, opts.get("--seed", 0))
+    else:
+        model, _ = load_model(model_arg, dtype, max_positions=max_len)
+    eng = Engine(model=model, page_size=page, num_pages=B * (-(-max_len // page)), max_batch_tokens=max(2048, B),
+                 max_batch_seqs=B, chunk_size=opts.get("--chunk-size", 0), max_model_len=max_len)
+    rng = random.Random(opts.get("--seed", 0))
+    vocab = model.n_vocab
+    for rep in range(2):                       # the first run captures the decode graphs
+        ids = [eng.submit([rng.randrange(vocab) for _ in range(P)], N) for _ in range(B)]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        first, done, t_first, tokens = set(), 0, None, 0
+        while done < B:
+            for ev in eng.step():
+                if ev.kind == "token":
+                    tokens += 1
+                    first.add(ev.id)
+                else:
+                    done += 1
+            if t_first is None and len(first) == B:
+                t_first = time.perf_counter()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+    decoded = tokens - B
+    print(json.dumps({"batch": B, "prompt_len": P, "new_tokens": N, "dtype": dtype, "layers": len(model.blocks),
+                      "prompt_ms": round((t_first - t0) * 1e3, 3), "prompt_tok_s": round(B * P / (t_first - t0), 1),
+                      "decode_tok_s": round(decoded / (t1 - t_first), 1) if decoded and t1 > t_first else None,
+                      "total_s": round(t1 - t0, 4)}))
+    return 0
+
+
 def cmd_replay(opts):
     from .engine.trace import TraceSession
     s = TraceSession(_need(opts, "--model"), _need(opts, "--dtype"), _need(opts, "--max-tokens"),
@@ -208,6 +270,8 @@ def main(argv=None):
             return cmd_generate(opts)
         if command == "random-weights":
             return cmd_random_weights(opts)
+        if command == "bench":
+            return cmd_bench(opts)
         if command == "replay":
             return cmd_replay(opts)
         return cmd_dump(positional)

@@ -209,6 +209,16 @@ class Engine:
                     live.discard(ev.id)
         return [out[i] for i in ids]
 
+    def step_raw(self, entries, commit=True):
+        """The step function itself, below the scheduler: `entries` is a list of
+        `StepEntry(slot, pos0, tokens, want)` on slots taken with `self.cache.open()` (given back with
+        `self.cache.close(slot)`); returns the float32 logits [wanted, vocab] on the device, or None.
+        For replay and tests.  It shares the cache with `submit()` / `step()` but not their
+        bookkeeping: use it on an engine that has no requests in flight."""
+        if self._in_flight is not None or not self.scheduler.idle():
+            raise RuntimeError("step_raw: the engine has requests in flight")
+        return self.runner.step(list(entries), commit=commit)
+
     def profile_report(self):
         """Rows of `ops.profile_report` for everything launched since the engine was made with
         profile=True: per kernel its launches, milliseconds, share and, for the products, GB/s and

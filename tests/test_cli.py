@@ -44,6 +44,18 @@ def test_value_errors():
                                           "--stats": True}
 
 
+def test_bench_options_parse():
+    from ferrum_b200.cli import CliError, parse_args
+    cmd, opts, _ = parse_args(["bench", "--model", "cfg.json", "--random-weights", "--batch=4", "--prompt-len", "32",
+                               "--new-tokens", "8", "--layers", "2"])
+    assert cmd == "bench" and opts == {"--model": "cfg.json", "--random-weights": True, "--batch": 4, "--prompt-len": 32,
+                                       "--new-tokens": 8, "--layers": 2}
+    with pytest.raises(CliError, match="unknown argument: --prompt-tokens"):
+        parse_args(["bench", "--model", "m", "--prompt-tokens", "1,2"])
+    p = ferrum("bench")
+    assert p.returncode == 2 and "--model is required" in p.stderr
+
+
 def test_serve_names_the_missing_server():
     p = ferrum("serve")
     assert p.returncode == 1 and "not part of this engine" in p.stderr

@@ -183,3 +183,39 @@ def test_profile_mode_times_every_kernel(cuda, model_dirs):
     gemm = next(r for r in rows if r["kernel"].startswith("gemm_tc"))
     assert gemm["GBps"] > 0 and gemm["TFLOPs"] > 0
     assert eng.runner.graph_replays == 0 and eng.profile_report() == []
+
+
+def test_step_raw_is_the_step_function_below_the_scheduler(cuda, model_dirs):
+    """Engine.step_raw runs given entries on slots of the engine's own cache and returns logits;
+    it refuses while requests are in flight."""
+    import torch
+    from ferrum_b200.engine import StepEntry
+    vocab = TINY["A"][0]["vocab_size"]
+    toks = random_tokens(20, vocab, 90)
+    eng = engine(model_dirs, "A", "float32")
+    slot = eng.cache.open()
+    a = eng.step_raw([StepEntry(slot, 0, toks[:13], [12])])
+    b = eng.step_raw([StepEntry(slot, 13, toks[13:], list(range(7)))])
+    eng.cache.close(slot)
+    got = torch.cat([a[:1], b[:7]]).cpu().numpy()
+    cfg, w = P.read_model(model_dirs["A"])
+    ref = P.forward(cfg, w, toks)[12:]
+    from helpers import assert_close
+    assert_close(got, ref, "float32", "step_raw")
+    eng.submit(toks, 2)
+    with pytest.raises(RuntimeError, match="in flight"):
+        eng.step_raw([])
+    assert eng.generate([toks], max_new_tokens=2)
+
+
+def test_bench_command(cuda, tmp_path):
+    import json, os, subprocess, sys
+    from conftest import ROOT, TINY_D
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(TINY_D))
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "ferrum"), "bench", "--model", str(cfg), "--random-weights",
+                        "--batch", "3", "--prompt-len", "40", "--new-tokens", "6", "--dtype", "bfloat16"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr
+    line = json.loads(p.stdout.strip().splitlines()[-1])
+    assert line["batch"] == 3 and line["decode_tok_s"] > 0 and line["prompt_tok_s"] > 0
