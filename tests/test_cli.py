@@ -95,3 +95,24 @@ def test_generate_command(cuda, model_dirs):
     assert json.loads(p.stderr.strip().splitlines()[-1])["finished"] == 2
     p = ferrum("generate", "--model", model_dirs["A"], "--prompt-tokens", "999")
     assert p.returncode == 1 and "vocabulary" in p.stderr
+
+
+def test_interface_revision_names_this_surface():
+    """The public surface that INTERFACE_REVISION stands for: a change here is a change of the number."""
+    import inspect
+    import ferrum_b200
+    from ferrum_b200 import cli
+    from ferrum_b200.engine import api
+    from ferrum_b200.parts import base
+    assert ferrum_b200.INTERFACE_REVISION == 2
+    methods = sorted(n for n, _ in inspect.getmembers(api.Engine, inspect.isfunction) if not n.startswith("_"))
+    assert methods == ["cancel", "generate", "profile_report", "stats", "step", "step_raw", "submit"]
+    assert list(inspect.signature(api.Engine.submit).parameters)[1:6] == ["prompt_tokens", "max_new_tokens", "sampling",
+                                                                           "stop_tokens", "request_id"]
+    assert sorted(cli.OPTIONS) == ["bench", "dump", "generate", "random-weights", "replay", "serve"]
+    assert {"--model", "--prompt-tokens", "--dtype", "--max-new-tokens", "--temperature", "--seed", "--stop-tokens",
+            "--max-batch-tokens", "--chunk-size", "--page-size", "--num-pages", "--max-model-len"} <= set(cli.OPTIONS["generate"])
+    for cls, names in ((base.Mixer, ["param_specs", "cache_need", "forward", "plan"]), (base.FeedForward, ["param_specs", "forward"]),
+                       (base.Norm, ["param_specs", "forward"]), (base.PositionEncoding, ["param_specs", "rotary", "on_embedding"])):
+        for n in names:
+            assert hasattr(cls, n), (cls.__name__, n)
