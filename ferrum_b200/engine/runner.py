@@ -53,10 +53,22 @@ class ModelRunner:
         self.ctx = StepContext(self.device, self.max_batch_tokens, self.max_batch_requests, widths, err=err)
         self.ctx.cache = cache
         # (guarded scratch buffers move whenever their size changes: no graphs then)
-        self.use_graphs = bool(use_graphs) and model.all_graph_safe() and not self.ctx.scratch.guard
+        self._graphs_possible = model.all_graph_safe() and not self.ctx.scratch.guard
+        self.use_graphs = bool(use_graphs)
         self._graphs = {}
         self._seen = {}
         self.graph_replays = 0
+
+    @property
+    def use_graphs(self):
+        """Whether decode-only steps are captured and replayed.  Never with a part that is not
+        graph-safe, nor with guarded scratch buffers (they move when a size changes, and a captured
+        graph would keep writing to where they were)."""
+        return self._use_graphs and self._graphs_possible
+
+    @use_graphs.setter
+    def use_graphs(self, on):
+        self._use_graphs = bool(on)
 
     def step(self, entries: List[StepEntry], commit=True, check=True, ahead_of_commit=False, tokens_on_device=False):
         """Returns float32 logits [n_wanted, V] on the device (a view that the next step
