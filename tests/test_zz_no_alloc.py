@@ -71,6 +71,10 @@ def test_noalloc_swiglu_and_refusals(cuda):
         got = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
         assert call_noalloc(lib, x, w, got, M, F, K, ops.TC_SWIGLU, F, err) == 0
         assert torch.equal(got, want)
+    # ... and against exact arithmetic on the same operands: silu(gate) * up, rounded to bfloat16 once
+    gate, up = x.double() @ w[:F].double().T, x.double() @ w[F:].double().T
+    ref = gate / (1 + torch.exp(-gate)) * up
+    assert ((got.double() - ref).abs() <= 8e-3 * torch.clamp(ref.abs(), min=1.0)).all()
     # shapes beyond the built-in scratch are refused before anything is launched
     big = torch.zeros(512, K, device="cuda", dtype=torch.bfloat16)
     out = torch.full((512, 2 * F), 7.0, device="cuda")
@@ -80,3 +84,24 @@ def test_noalloc_swiglu_and_refusals(cuda):
     assert (out == 7.0).all() and err.item() == 0
     bad = torch.zeros(4, 172, device="cuda", dtype=torch.bfloat16)          # rows that TMA cannot address
     assert call_noalloc(lib, bad, bad, out, 4, 4, 172, ops.TC_STORE_F32, 0, err) != 0
+
+
+def test_noalloc_call_leaves_the_free_memory_as_it_was(cuda):
+    """A warmed-up call takes no device memory: the driver's free figure is the same before and
+    after (the first call on a device may resolve the built-in scratch's address and is made here
+    before the measurement)."""
+    from ferrum_b200.ops import lib as ops
+    lib = ops.lib()
+    M, N, K = 8, 1024, 512
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert call_noalloc(lib, x, w, out, M, N, K, ops.TC_STORE_F32, 0, err) == 0
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert call_noalloc(lib, x, w, out, M, N, K, ops.TC_STORE_F32, 0, err) == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0 and err.item() == 0
